@@ -1,0 +1,234 @@
+/*
+ * nvj_b200.h — C ABI of the B200 (sm_100a) paged KV-cache hot path.
+ *
+ * Every entry point takes raw device pointers, sizes and a CUDA stream, launches
+ * asynchronously on that stream, never synchronises the host, and returns 0 or a
+ * negative nvj_status code.  No torch / JAX types appear in any signature.  The
+ * functions are the plain-C form of the reference project's kernel ABI for this
+ * path; the citation on each declaration names the reference interface it
+ * replaces (paths are relative to the reference project root).
+ *
+ * Layouts (identical to the reference, nanovllm_jax/kv_cache.py:22-32):
+ *   cache layer   [num_blocks, block_size, num_kv_heads, head_dim]   (one layer slice)
+ *   flat slot     slot = block_id * block_size + position % block_size
+ *   block tables  [rows, table_width] int32, unused entries 0
+ *
+ * Device-side problems (a block id outside the pool, a wait that ran out) never
+ * trap: the kernel skips the access, ORs a NVJ_DEV_* bit into a status word and
+ * returns.  The status word is `int32_t* status` where a function takes one, or
+ * word 0 of the decode workspace.
+ */
+#ifndef NVJ_B200_H_
+#define NVJ_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define NVJ_ABI_VERSION 1
+
+/* cudaStream_t, kept opaque so the header needs no CUDA include. */
+typedef void* nvj_stream_t;
+
+typedef enum nvj_status {
+  NVJ_OK = 0,
+  NVJ_ERR_INVALID_ARGUMENT = -1, /* null pointer, negative size, bad alignment   */
+  NVJ_ERR_UNSUPPORTED = -2,      /* shape / dtype outside what the kernels cover */
+  NVJ_ERR_LAUNCH = -3,           /* cudaGetLastError() after the launch          */
+  NVJ_ERR_WORKSPACE = -4         /* workspace missing or too small               */
+} nvj_status;
+
+typedef enum nvj_dtype { NVJ_BF16 = 0, NVJ_F16 = 1, NVJ_F32 = 2 } nvj_dtype;
+
+/* Bits a kernel may OR into a device status word. */
+#define NVJ_DEV_TIMEOUT 1      /* a bounded wait ran out; results are invalid   */
+#define NVJ_DEV_BAD_BLOCK_ID 2 /* block id / slot outside the pool; skipped     */
+#define NVJ_DEV_BAD_LENGTH 4   /* seq_len beyond table_width * block_size; clipped */
+
+int nvj_abi_version(void);
+const char* nvj_status_string(int status);
+
+/* ------------------------------------------------------------------ append */
+
+/*
+ * Slot-mapped append of new K/V rows into one layer of the paged cache.
+ * Replaces nanovllm_jax/kv_cache.py:476-564 (update_kv_cache) as called from
+ * nanovllm_jax/backends.py:980-1067 (PureJAXBackend.write_kv).
+ *
+ *   new_k/new_v    [n_rows, n_cols, num_kv_heads, head_dim], src_dtype
+ *   slot_mapping   [n_rows, n_cols] int32 flat slots
+ *   valid_mask     nullable [n_rows, n_cols] int32, non-zero = write
+ *   query_start_loc nullable [qsl_rows + 1] int32.  packed != 0: token i is
+ *                  written iff i < query_start_loc[qsl_rows] (backends.py:1050-1054);
+ *                  packed == 0: token (b, t) iff t < qsl[b+1] - qsl[b] (1055-1057).
+ * A token must pass every rule that is given.  Source rows are converted to
+ * cache_dtype (f32 -> bf16/f16 round-to-nearest-even; same dtype = byte copy).
+ * Slots outside [0, num_slots) are skipped and flagged NVJ_DEV_BAD_BLOCK_ID.
+ * Two valid tokens with the same slot: last writer unspecified (as in XLA).
+ */
+int nvj_kv_append(const void* new_k, const void* new_v, int src_dtype,
+                  const int32_t* slot_mapping, const int32_t* valid_mask,
+                  const int32_t* query_start_loc, int qsl_rows, int packed,
+                  int n_rows, int n_cols,
+                  void* k_cache_layer, void* v_cache_layer, int cache_dtype,
+                  int64_t num_slots, int num_kv_heads, int head_dim,
+                  int32_t* status, nvj_stream_t stream);
+
+/*
+ * Page-table (CSR) form of the append: page = kv_indices[kv_indptr[b] + pos / P],
+ * cache[page, pos % P] = append[i].  Replaces the FP32 custom call
+ * nanovllm_jax/kernels/cuda_fp32_ffi.py:323-382 (handler
+ * nanovllm_jax/kernels/csrc/fp32_kv_append.cu:801-841,1563-1627) and the
+ * reference nanovllm_jax/kernels/flashinfer_ffi.py:626-665.
+ */
+int nvj_kv_append_nhd(const void* append_key, const void* append_value, int src_dtype,
+                      const int32_t* batch_indices, const int32_t* positions, int nnz,
+                      void* k_cache, void* v_cache, int cache_dtype,
+                      int64_t num_pages, int page_size, int num_kv_heads, int head_dim,
+                      const int32_t* kv_indices, int64_t kv_indices_len,
+                      const int32_t* kv_indptr, int batch,
+                      const int32_t* valid_mask,
+                      int32_t* status, nvj_stream_t stream);
+
+/* ------------------------------------------------------------------ decode */
+
+/*
+ * Bytes of caller-owned scratch the decode entry points need for `max_batch`
+ * rows on the current device.  The first NVJ_DECODE_WS_HEADER_BYTES hold the
+ * status word and the per-row arrival counters and must be zero before the
+ * first use (nvj_paged_decode_workspace_init does that); the kernels leave
+ * them zero again on success.  One workspace serves one stream at a time.
+ */
+size_t nvj_paged_decode_workspace_bytes(int max_batch);
+int nvj_paged_decode_workspace_init(void* workspace, size_t workspace_bytes,
+                                    nvj_stream_t stream);
+
+/*
+ * Width-1 paged GQA decode attention over one cache layer, online softmax,
+ * fp32 accumulate, fp32 output.  Replaces nanovllm_jax/kv_cache.py:852-998
+ * (paged_attention_decode), nanovllm_jax/kernels/paged_attention.py:101-194
+ * and the FP32 custom call nanovllm_jax/kernels/cuda_fp32_ffi.py:527-572
+ * (handler nanovllm_jax/kernels/csrc/fp32_kv_append.cu:843-957,1629-1697).
+ *
+ *   q            [batch, num_q_heads, head_dim], q_dtype (bf16 or f32)
+ *   block_tables int32; row b starts at kv_indptr[b] when kv_indptr != NULL,
+ *                else at b * table_width
+ *   seq_lens     [batch] int32 keys attended per row; rows with len <= 0 get zeros
+ *   kv_last_page_len nullable [batch]; with kv_indptr it clips the length to
+ *                (pages - 1) * P + last_page_len as paged_attention.py:171-178 does
+ *   out          [batch, num_q_heads, head_dim] float32
+ *   variant      0 = auto, 1 = generic kernel, 2 = bulk-copy pipelined kernel
+ *                (bf16 cache, block_size 16, 2 kv heads x 4 q heads, head_dim 256)
+ */
+int nvj_paged_decode(const void* q, int q_dtype,
+                     const void* k_cache_layer, const void* v_cache_layer, int kv_dtype,
+                     int64_t num_blocks, int block_size, int num_kv_heads, int head_dim,
+                     int num_q_heads,
+                     const int32_t* block_tables, int table_width,
+                     const int32_t* kv_indptr, const int32_t* kv_last_page_len,
+                     const int32_t* seq_lens, int batch, float scale,
+                     float* out,
+                     void* workspace, size_t workspace_bytes,
+                     int variant, nvj_stream_t stream);
+
+/*
+ * Fused decode step: write row b's new K/V at positions[b], then attend
+ * seq_lens[b] keys (the new one included).  Replaces
+ * nanovllm_jax/kernels/full_attention_triton.py:488-581
+ * (paged_decode_attention_with_kv_append_triton) behind
+ * nanovllm_jax/backends.py:1411-1442.  new_k/new_v are [batch, num_kv_heads,
+ * head_dim] in the cache dtype.  Rows with seq_lens[b] <= 0 are inactive: no
+ * write, zero output.  Cache contents equal nvj_kv_append followed by
+ * nvj_paged_decode bit for bit.
+ */
+int nvj_paged_decode_fused_append(const void* q, int q_dtype,
+                                  const void* new_k, const void* new_v,
+                                  const int32_t* positions,
+                                  void* k_cache_layer, void* v_cache_layer, int kv_dtype,
+                                  int64_t num_blocks, int block_size, int num_kv_heads,
+                                  int head_dim, int num_q_heads,
+                                  const int32_t* block_tables, int table_width,
+                                  const int32_t* seq_lens, int batch, float scale,
+                                  float* out,
+                                  void* workspace, size_t workspace_bytes,
+                                  int variant, nvj_stream_t stream);
+
+/* ----------------------------------------------------------------- prefill */
+
+/*
+ * Ragged packed prefill attention over the paged cache (this chunk's rows are
+ * already appended).  Token i of row r at absolute position positions[i] attends
+ * keys p < kv_lens[r] and p <= positions[i]; tokens at or beyond
+ * query_start_loc[rows] produce zeros.  Replaces
+ * nanovllm_jax/kv_cache.py:721-849 (paged_attention_prefill_packed) and
+ * nanovllm_jax/kernels/full_attention_triton.py:148-221.
+ *
+ *   q          [token_bucket, num_q_heads, head_dim], q_dtype
+ *   out        [token_bucket, num_q_heads, head_dim] float32
+ */
+int nvj_paged_prefill_packed(const void* q, int q_dtype,
+                             const void* k_cache_layer, const void* v_cache_layer, int kv_dtype,
+                             int64_t num_blocks, int block_size, int num_kv_heads,
+                             int head_dim, int num_q_heads,
+                             const int32_t* block_tables, int table_width,
+                             const int32_t* kv_lens, const int32_t* positions,
+                             const int32_t* query_start_loc, int rows,
+                             int token_bucket, float scale,
+                             float* out, int32_t* status, nvj_stream_t stream);
+
+/* ------------------------------------------------------------------ copies */
+
+/*
+ * Copy whole cache blocks dst_ids[i] <- src_ids[i] in every layer of K and V
+ * (prefix reuse by copy; the oracle is cache[:, dst] = cache[:, src]).  The
+ * reference shares prefix blocks by reference count
+ * (nanovllm_jax/engine/block_manager.py:194-254) and has no copy; this entry
+ * point serves callers that need a private copy of a shared prefix.
+ * layer_stride_bytes = num_blocks * block_bytes for the contiguous 5-D cache.
+ */
+int nvj_copy_blocks(void* k_cache, void* v_cache, int num_layers,
+                    int64_t num_blocks, int64_t block_bytes, int64_t layer_stride_bytes,
+                    const int32_t* src_ids, const int32_t* dst_ids, int n_pairs,
+                    int32_t* status, nvj_stream_t stream);
+
+/*
+ * GDN hybrid-state snapshot: pool[pool_slots[i]] <- table[table_slots[i]] for
+ * the conv-state and recurrent-state arrays (either may be NULL).  Replaces
+ * nanovllm_jax/engine/model_runner.py:3843-3854 (_get_hybrid_state).
+ * row bytes: conv = layers*conv_dim*kernel*itemsize, recurrent = layers*H*Dv*Dk*4.
+ */
+int nvj_hybrid_snapshot(const void* conv_table, void* conv_pool, int64_t conv_row_bytes,
+                        const void* rec_table, void* rec_pool, int64_t rec_row_bytes,
+                        int64_t table_rows, int64_t pool_rows,
+                        const int32_t* table_slots, const int32_t* pool_slots, int n,
+                        int32_t* status, nvj_stream_t stream);
+
+/*
+ * GDN hybrid-state restore: table[table_slots[i]] <- pool[pool_slots[i]].
+ * Replaces nanovllm_jax/engine/model_runner.py:3856-3867 (_set_hybrid_state)
+ * as driven by install_cached_prefix_hybrid_states (3886-3905).
+ */
+int nvj_hybrid_restore(void* conv_table, const void* conv_pool, int64_t conv_row_bytes,
+                       void* rec_table, const void* rec_pool, int64_t rec_row_bytes,
+                       int64_t table_rows, int64_t pool_rows,
+                       const int32_t* table_slots, const int32_t* pool_slots, int n,
+                       int32_t* status, nvj_stream_t stream);
+
+/* ------------------------------------------------------------------ tokens */
+
+/*
+ * Per-row argmax over `row_len` floats -> int32 (first maximum wins).  Stand-in
+ * for the sampler when one attention layer is benchmarked alone: it turns the
+ * attention output of a row into the per-step token that the ranks all-gather.
+ * The reference has no counterpart (it is single-device and samples from logits).
+ */
+int nvj_row_argmax(const float* x, int rows, int row_len, int32_t* tokens,
+                   nvj_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NVJ_B200_H_ */

@@ -1,0 +1,214 @@
+// Index-list copies on the path: whole cache blocks (prefix reuse by copy) and
+// GDN hybrid-state rows (snapshot into / restore from a pool keyed by prefix
+// hash), plus the per-row argmax that stands in for the sampler.
+//
+// All three copies are HBM-bound: 16-byte vector accesses, four independent
+// loads in flight per thread, a 2-D grid of (chunk group, row pair).  The
+// algorithmic traffic is 2 x bytes moved (one read, one write).
+
+#include "nvj_common.cuh"
+
+namespace nvj {
+
+constexpr int kCopyThreads = 256;
+constexpr int kCopyUnroll = 4;
+constexpr long long kCopyTileBytes = (long long)kCopyThreads * kCopyUnroll * 16;  // 16 KiB
+
+__device__ __forceinline__ void st_cs_u4(void* p, uint4 v) {
+  asm volatile("st.global.cs.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
+// Copies `bytes` (multiple of 16, both pointers 16-byte aligned) with the CTAs
+// blockIdx.x, blockIdx.x + gridDim.x, ... each moving 16 KiB tiles.
+__device__ __forceinline__ void copy_span16(const char* src, char* dst, long long bytes) {
+  const long long chunks = bytes >> 4;
+  for (long long base = (long long)blockIdx.x * kCopyThreads * kCopyUnroll; base < chunks;
+       base += (long long)gridDim.x * kCopyThreads * kCopyUnroll) {
+    uint4 v[kCopyUnroll];
+#pragma unroll
+    for (int u = 0; u < kCopyUnroll; ++u) {
+      const long long c = base + u * kCopyThreads + threadIdx.x;
+      if (c < chunks) v[u] = ld_nc_u4(src + (c << 4));
+    }
+#pragma unroll
+    for (int u = 0; u < kCopyUnroll; ++u) {
+      const long long c = base + u * kCopyThreads + threadIdx.x;
+      if (c < chunks) st_cs_u4(dst + (c << 4), v[u]);
+    }
+  }
+}
+
+__device__ __forceinline__ void copy_span1(const char* src, char* dst, long long bytes) {
+  for (long long c = (long long)blockIdx.x * kCopyThreads + threadIdx.x; c < bytes;
+       c += (long long)gridDim.x * kCopyThreads)
+    dst[c] = src[c];
+}
+
+// dst_base[dst_idx[i]] <- src_base[src_idx[i]], rows of row_bytes; grid.y = pair.
+__global__ void __launch_bounds__(kCopyThreads)
+copy_rows_kernel(const char* src_base, long long src_rows, const int32_t* src_idx, char* dst_base,
+                 long long dst_rows, const int32_t* dst_idx, long long row_bytes, int vec16,
+                 int32_t* status) {
+  const int i = blockIdx.y;
+  const long long s = src_idx[i], d = dst_idx[i];
+  if (s < 0 || s >= src_rows || d < 0 || d >= dst_rows) {
+    if (threadIdx.x == 0 && blockIdx.x == 0 && status) atomicOr(status, NVJ_DEV_BAD_BLOCK_ID);
+    return;
+  }
+  const char* src = src_base + s * row_bytes;
+  char* dst = dst_base + d * row_bytes;
+  if (vec16) copy_span16(src, dst, row_bytes);
+  else copy_span1(src, dst, row_bytes);
+}
+
+// Block copy across layers and K/V: grid.y = pair, grid.z = layer * 2 + (0: K, 1: V).
+__global__ void __launch_bounds__(kCopyThreads)
+copy_blocks_kernel(char* k_cache, char* v_cache, long long num_blocks, long long block_bytes,
+                   long long layer_stride, const int32_t* src_ids, const int32_t* dst_ids, int vec16,
+                   int32_t* status) {
+  const int i = blockIdx.y;
+  const long long s = src_ids[i], d = dst_ids[i];
+  if (s < 0 || s >= num_blocks || d < 0 || d >= num_blocks) {
+    if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.z == 0 && status)
+      atomicOr(status, NVJ_DEV_BAD_BLOCK_ID);
+    return;
+  }
+  if (s == d) return;
+  char* base = (blockIdx.z & 1) ? v_cache : k_cache;
+  base += (long long)(blockIdx.z >> 1) * layer_stride;
+  if (vec16) copy_span16(base + s * block_bytes, base + d * block_bytes, block_bytes);
+  else copy_span1(base + s * block_bytes, base + d * block_bytes, block_bytes);
+}
+
+// One CTA per row; the first maximum wins, NaNs are never selected unless the
+// whole row is NaN (then index 0).
+__global__ void __launch_bounds__(128)
+row_argmax_kernel(const float* x, int row_len, int32_t* tokens) {
+  const float* row = x + (long long)blockIdx.x * row_len;
+  float best = -INFINITY;
+  int best_i = 0x7fffffff;
+  for (int i = threadIdx.x; i < row_len; i += blockDim.x) {
+    const float v = row[i];
+    if (v > best || (v == best && i < best_i)) { best = v; best_i = i; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(kFullMask, best, o);
+    const int oi = __shfl_xor_sync(kFullMask, best_i, o);
+    if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
+  }
+  __shared__ float sv[4];
+  __shared__ int si[4];
+  if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = best; si[threadIdx.x >> 5] = best_i; }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 4; ++w)
+      if (sv[w] > best || (sv[w] == best && si[w] < best_i)) { best = sv[w]; best_i = si[w]; }
+    tokens[blockIdx.x] = best_i == 0x7fffffff ? 0 : best_i;
+  }
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+static int grid_x_for(long long bytes, int pairs) {
+  // Enough CTAs to fill the machine a few times over, never more than one per tile.
+  long long tiles = (bytes + kCopyTileBytes - 1) / kCopyTileBytes;
+  long long want = (148LL * 16 + pairs - 1) / pairs;
+  long long gx = tiles < want ? tiles : want;
+  return gx < 1 ? 1 : (int)gx;
+}
+
+static int launch_copy_rows(const void* src, long long src_rows, const int32_t* src_idx, void* dst,
+                            long long dst_rows, const int32_t* dst_idx, int n, long long row_bytes,
+                            int32_t* status, cudaStream_t stream) {
+  if (!src || !dst || row_bytes == 0) return NVJ_OK;
+  const int vec16 = aligned16(src) && aligned16(dst) && row_bytes % 16 == 0;
+  dim3 grid(grid_x_for(row_bytes, n), n, 1);
+  copy_rows_kernel<<<grid, kCopyThreads, 0, stream>>>(static_cast<const char*>(src), src_rows, src_idx,
+                                                      static_cast<char*>(dst), dst_rows, dst_idx,
+                                                      row_bytes, vec16, status);
+  return cudaGetLastError() == cudaSuccess ? NVJ_OK : NVJ_ERR_LAUNCH;
+}
+
+}  // namespace nvj
+
+extern "C" int nvj_abi_version(void) { return NVJ_ABI_VERSION; }
+
+extern "C" const char* nvj_status_string(int status) {
+  switch (status) {
+    case NVJ_OK: return "ok";
+    case NVJ_ERR_INVALID_ARGUMENT: return "invalid argument";
+    case NVJ_ERR_UNSUPPORTED: return "unsupported shape or dtype";
+    case NVJ_ERR_LAUNCH: return "kernel launch failed";
+    case NVJ_ERR_WORKSPACE: return "workspace missing or too small";
+    default: return "unknown status";
+  }
+}
+
+extern "C" int nvj_copy_blocks(void* k_cache, void* v_cache, int num_layers, int64_t num_blocks,
+                               int64_t block_bytes, int64_t layer_stride_bytes,
+                               const int32_t* src_ids, const int32_t* dst_ids, int n_pairs,
+                               int32_t* status, nvj_stream_t stream) {
+  using namespace nvj;
+  if (num_layers < 0 || num_blocks < 0 || block_bytes < 0 || n_pairs < 0 || layer_stride_bytes < 0)
+    return NVJ_ERR_INVALID_ARGUMENT;
+  if (n_pairs == 0 || num_layers == 0 || block_bytes == 0) return NVJ_OK;
+  if (!k_cache || !v_cache || !src_ids || !dst_ids) return NVJ_ERR_INVALID_ARGUMENT;
+  if (n_pairs > 65535 || num_layers * 2 > 65535) return NVJ_ERR_UNSUPPORTED;
+  const int vec16 = aligned16(k_cache) && aligned16(v_cache) && block_bytes % 16 == 0 &&
+                    layer_stride_bytes % 16 == 0;
+  dim3 grid(grid_x_for(block_bytes, n_pairs * num_layers * 2), n_pairs, num_layers * 2);
+  copy_blocks_kernel<<<grid, kCopyThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<char*>(k_cache), static_cast<char*>(v_cache), num_blocks, block_bytes,
+      layer_stride_bytes, src_ids, dst_ids, vec16, status);
+  return cudaGetLastError() == cudaSuccess ? NVJ_OK : NVJ_ERR_LAUNCH;
+}
+
+static int hybrid_copy(const void* conv_src, void* conv_dst, int64_t conv_row_bytes,
+                       const void* rec_src, void* rec_dst, int64_t rec_row_bytes,
+                       int64_t src_rows, int64_t dst_rows, const int32_t* src_slots,
+                       const int32_t* dst_slots, int n, int32_t* status, nvj_stream_t stream) {
+  using namespace nvj;
+  if (n < 0 || conv_row_bytes < 0 || rec_row_bytes < 0 || src_rows < 0 || dst_rows < 0)
+    return NVJ_ERR_INVALID_ARGUMENT;
+  if (n == 0) return NVJ_OK;
+  if (!src_slots || !dst_slots) return NVJ_ERR_INVALID_ARGUMENT;
+  if (n > 65535) return NVJ_ERR_UNSUPPORTED;
+  if ((conv_src == nullptr) != (conv_dst == nullptr) || (rec_src == nullptr) != (rec_dst == nullptr))
+    return NVJ_ERR_INVALID_ARGUMENT;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int rc = launch_copy_rows(rec_src, src_rows, src_slots, rec_dst, dst_rows, dst_slots, n,
+                            rec_row_bytes, status, s);
+  if (rc != NVJ_OK) return rc;
+  return launch_copy_rows(conv_src, src_rows, src_slots, conv_dst, dst_rows, dst_slots, n,
+                          conv_row_bytes, status, s);
+}
+
+extern "C" int nvj_hybrid_snapshot(const void* conv_table, void* conv_pool, int64_t conv_row_bytes,
+                                   const void* rec_table, void* rec_pool, int64_t rec_row_bytes,
+                                   int64_t table_rows, int64_t pool_rows,
+                                   const int32_t* table_slots, const int32_t* pool_slots, int n,
+                                   int32_t* status, nvj_stream_t stream) {
+  return hybrid_copy(conv_table, conv_pool, conv_row_bytes, rec_table, rec_pool, rec_row_bytes,
+                     table_rows, pool_rows, table_slots, pool_slots, n, status, stream);
+}
+
+extern "C" int nvj_hybrid_restore(void* conv_table, const void* conv_pool, int64_t conv_row_bytes,
+                                  void* rec_table, const void* rec_pool, int64_t rec_row_bytes,
+                                  int64_t table_rows, int64_t pool_rows,
+                                  const int32_t* table_slots, const int32_t* pool_slots, int n,
+                                  int32_t* status, nvj_stream_t stream) {
+  return hybrid_copy(conv_pool, conv_table, conv_row_bytes, rec_pool, rec_table, rec_row_bytes,
+                     pool_rows, table_rows, pool_slots, table_slots, n, status, stream);
+}
+
+extern "C" int nvj_row_argmax(const float* x, int rows, int row_len, int32_t* tokens,
+                              nvj_stream_t stream) {
+  using namespace nvj;
+  if (rows < 0 || row_len <= 0) return NVJ_ERR_INVALID_ARGUMENT;
+  if (rows == 0) return NVJ_OK;
+  if (!x || !tokens) return NVJ_ERR_INVALID_ARGUMENT;
+  row_argmax_kernel<<<rows, 128, 0, static_cast<cudaStream_t>(stream)>>>(x, row_len, tokens);
+  return cudaGetLastError() == cudaSuccess ? NVJ_OK : NVJ_ERR_LAUNCH;
+}

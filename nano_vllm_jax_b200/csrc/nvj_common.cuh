@@ -1,0 +1,154 @@
+// Shared device helpers for the sm_100a paged KV-cache kernels: bf16 unpacking,
+// mbarrier / bulk-copy wrappers with bounded waits, and small warp utilities.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/nvj_b200.h"
+
+namespace nvj {
+
+constexpr unsigned kFullMask = 0xffffffffu;
+
+// Longest time any device-side wait may poll before the kernel gives up, flags
+// NVJ_DEV_TIMEOUT and runs to its end without waiting any more.
+constexpr unsigned long long kWaitLimitNs = 1000ull * 1000ull * 1000ull;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+// ---- bf16 pair unpack: a 32-bit word holds elements (2i, 2i+1) = (low, high).
+__device__ __forceinline__ float2 bf16x2_to_float2(uint32_t w) {
+  float2 r;
+  r.x = __uint_as_float(w << 16);
+  r.y = __uint_as_float(w & 0xffff0000u);
+  return r;
+}
+
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// d = a * b + c on packed fp32 pairs (one FFMA2 on sm_100).
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+  return __ffma2_rn(a, b, c);
+}
+
+// ---- mbarrier (shared::cta) ------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void mbar_fence_init() {
+  // Make the initialised barriers visible to the async proxy before first use.
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Bounded wait.  `abort_flag` lives in shared memory and is set by the first
+// waiter of the CTA that runs out of time; once set, every wait returns at once
+// so that all warps reach the end of the kernel (results are then invalid and
+// the status word says so).
+static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity,
+                                            volatile int* abort_flag, int32_t* status) {
+  const unsigned long long t0 = global_timer_ns();
+  for (uint32_t i = 0;; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 31u) == 31u) {
+      if (*abort_flag) return false;
+      if (global_timer_ns() - t0 > kWaitLimitNs) {
+        *abort_flag = 1;
+        if (status) atomicOr(status, NVJ_DEV_TIMEOUT);
+        return false;
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
+                                          volatile int* abort_flag, int32_t* status) {
+  if (*abort_flag) return false;
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, abort_flag, status);
+}
+
+// ---- 1-D bulk async copy global -> this CTA's shared memory -----------------
+// Source and destination 16-byte aligned, size a multiple of 16 bytes.  The
+// copy signals `bar` with complete_tx for `bytes`.
+__device__ __forceinline__ void bulk_g2s(uint32_t smem_dst, const void* gmem_src, uint32_t bytes,
+                                         uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(smem_dst), "l"(gmem_src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+
+// Order this thread's earlier generic-proxy writes before later async-proxy
+// (bulk copy) reads of the same memory.
+__device__ __forceinline__ void fence_proxy_async_all() {
+  asm volatile("fence.proxy.async;" ::: "memory");
+}
+
+__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+// ---- loads that must see other CTAs' recent global writes -------------------
+__device__ __forceinline__ float ld_cg_f32(const float* p) {
+  float v;
+  asm volatile("ld.global.cg.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ float2 ld_cg_f32x2(const float* p) {
+  float2 v;
+  asm volatile("ld.global.cg.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "l"(p) : "memory");
+  return v;
+}
+
+// Streaming 16-byte load that does not allocate in L1 (read-once data).
+__device__ __forceinline__ uint4 ld_nc_u4(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+__host__ __device__ __forceinline__ int dtype_size(int dt) {
+  return dt == NVJ_F32 ? 4 : 2;
+}
+
+}  // namespace nvj

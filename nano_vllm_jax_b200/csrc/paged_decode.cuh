@@ -1,0 +1,95 @@
+// Parameters and workspace layout shared by the paged decode kernels.
+#pragma once
+
+#include "nvj_common.cuh"
+
+namespace nvj {
+
+// Shape the bulk-copy pipelined kernel is specialised for (the model's
+// full-attention layer: 8 query heads over 2 KV heads, head_dim 256, 16-token
+// blocks, bf16 cache).
+constexpr int kBlk = 16;                                // tokens per cache block
+constexpr int kD = 256;                                 // head_dim
+constexpr int kHkv = 2;                                 // KV heads
+constexpr int kG = 4;                                   // query heads per KV head
+constexpr int kHq = kHkv * kG;                          // query heads
+constexpr int kRowBytes = kD * 2;                       // one (token, kv head) row, bf16
+constexpr int kTokenBytes = kHkv * kRowBytes;           // 1024
+constexpr int kTileBytes = kBlk * kTokenBytes;          // 16 KiB: one block of K (or of V)
+
+struct DecodeParams {
+  const void* q;
+  const char* k_cache;  // one layer
+  const char* v_cache;
+  const int32_t* block_tables;
+  const int32_t* kv_indptr;         // nullable
+  const int32_t* kv_last_page_len;  // nullable
+  const int32_t* seq_lens;
+  // fused append (nullable)
+  const void* new_k;
+  const void* new_v;
+  const int32_t* positions;
+  // packed prefill through the generic kernel (nullable): query i belongs to the
+  // table row r with query_start_loc[r] <= i < query_start_loc[r + 1] and attends
+  // keys p <= query_positions[i]
+  const int32_t* query_start_loc;
+  const int32_t* query_positions;
+  int qsl_rows;
+  float* out;
+  // workspace
+  int32_t* status;
+  int32_t* counters;  // [batch], zero between launches
+  float* part_ml;     // [2 * num_ctas][kHq][2]  (running max in log2 units, sum)
+  float* part_acc;    // [2 * num_ctas][kHq][kD] un-normalised accumulators
+  long long num_blocks;
+  int batch;
+  int table_width;
+  int block_size;
+  int num_kv_heads;
+  int num_q_heads;
+  int head_dim;
+  int q_dtype;
+  int kv_dtype;
+  float scale;
+};
+
+// Keys row b attends: seq_lens[b], clipped to what its page list can hold.
+__device__ __forceinline__ int decode_row_len(const DecodeParams& p, int b) {
+  int len = p.seq_lens[b];
+  int pages = p.table_width;
+  if (p.kv_indptr) {
+    pages = p.kv_indptr[b + 1] - p.kv_indptr[b];
+    if (p.kv_last_page_len) {
+      const int eff = pages > 0 ? (pages - 1) * p.block_size + p.kv_last_page_len[b] : 0;
+      len = len < eff ? len : eff;
+    }
+  }
+  const long long cap = (long long)pages * p.block_size;
+  if (len > cap) {
+    atomicOr(p.status, NVJ_DEV_BAD_LENGTH);
+    len = (int)cap;
+  }
+  return len < 0 ? 0 : len;
+}
+
+__device__ __forceinline__ long long decode_table_base(const DecodeParams& p, int b) {
+  return p.kv_indptr ? (long long)p.kv_indptr[b] : (long long)b * p.table_width;
+}
+
+constexpr size_t kWsAlign = 256;
+__host__ __device__ inline size_t ws_round(size_t x) { return (x + kWsAlign - 1) / kWsAlign * kWsAlign; }
+// Header = status word (64 B) + one int32 counter per row.
+inline size_t ws_header_bytes(int max_batch) { return ws_round(64 + sizeof(int32_t) * (size_t)max_batch); }
+inline size_t ws_ml_bytes(int num_ctas) { return ws_round(sizeof(float) * 2ull * num_ctas * kHq * 2); }
+inline size_t ws_acc_bytes(int num_ctas) { return ws_round(sizeof(float) * 2ull * num_ctas * kHq * kD); }
+
+int decode_num_ctas();  // 2 per SM of the current device
+int launch_decode_generic(const DecodeParams& p, cudaStream_t stream);
+int launch_decode_pipelined(const DecodeParams& p, int num_ctas, cudaStream_t stream);
+int append_decode_rows(const void* new_k, const void* new_v, const int32_t* positions,
+                       const int32_t* seq_lens, void* k_cache, void* v_cache, int kv_dtype,
+                       long long num_blocks, int block_size, int row_elems,
+                       const int32_t* block_tables, int table_width, int batch, int32_t* status,
+                       cudaStream_t stream);
+
+}  // namespace nvj

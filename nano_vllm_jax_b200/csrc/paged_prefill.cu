@@ -1,0 +1,51 @@
+// Ragged packed prefill attention over the paged cache: C ABI and dispatch.
+//
+// Token i of table row r (query_start_loc[r] <= i < query_start_loc[r + 1]) sits
+// at absolute position positions[i] and attends keys p < kv_lens[r], p <=
+// positions[i]; tokens at or beyond query_start_loc[rows] are padding and get
+// zeros (nanovllm_jax/kv_cache.py:831-849,
+// nanovllm_jax/kernels/full_attention_triton.py:51-145,218-221).
+
+#include "paged_decode.cuh"
+
+extern "C" int nvj_paged_prefill_packed(const void* q, int q_dtype, const void* k_cache_layer,
+                                        const void* v_cache_layer, int kv_dtype,
+                                        int64_t num_blocks, int block_size, int num_kv_heads,
+                                        int head_dim, int num_q_heads,
+                                        const int32_t* block_tables, int table_width,
+                                        const int32_t* kv_lens, const int32_t* positions,
+                                        const int32_t* query_start_loc, int rows,
+                                        int token_bucket, float scale, float* out,
+                                        int32_t* status, nvj_stream_t stream) {
+  using namespace nvj;
+  if (rows < 0 || token_bucket < 0 || table_width < 0 || num_blocks < 0 || block_size <= 0 ||
+      num_kv_heads <= 0 || num_q_heads <= 0 || head_dim <= 0)
+    return NVJ_ERR_INVALID_ARGUMENT;
+  if (num_q_heads % num_kv_heads != 0) return NVJ_ERR_INVALID_ARGUMENT;
+  if (token_bucket == 0) return NVJ_OK;
+  if (!q || !k_cache_layer || !v_cache_layer || !block_tables || !kv_lens || !positions ||
+      !query_start_loc || !out || !status)
+    return NVJ_ERR_INVALID_ARGUMENT;
+  DecodeParams p{};
+  p.q = q;
+  p.k_cache = static_cast<const char*>(k_cache_layer);
+  p.v_cache = static_cast<const char*>(v_cache_layer);
+  p.block_tables = block_tables;
+  p.seq_lens = kv_lens;
+  p.query_start_loc = query_start_loc;
+  p.query_positions = positions;
+  p.qsl_rows = rows;
+  p.out = out;
+  p.status = status;
+  p.num_blocks = num_blocks;
+  p.batch = token_bucket;
+  p.table_width = table_width;
+  p.block_size = block_size;
+  p.num_kv_heads = num_kv_heads;
+  p.num_q_heads = num_q_heads;
+  p.head_dim = head_dim;
+  p.q_dtype = q_dtype;
+  p.kv_dtype = kv_dtype;
+  p.scale = scale;
+  return launch_decode_generic(p, static_cast<cudaStream_t>(stream));
+}
