@@ -1,0 +1,189 @@
+"""GDN hybrid-state slot table with snapshot / restore keyed by prefix hash.
+
+What the reference does (nanovllm_jax/engine/model_runner.py:3755-3905,
+nanovllm_jax/engine/scheduler.py:67-69, 218-279):
+
+* every resident sequence owns one slot of two device tables, `conv_state
+  [S, L_lin, conv_dim, K]` (model dtype) and `recurrent_state [S, L_lin, Hv, Dv,
+  Dk]` fp32; a slot is zeroed when it is first assigned;
+* after a prefill chunk that ends on a block boundary, the sequence's state is
+  read out (`_get_hybrid_state`) and stored in `prefix_cache_hybrid_states`
+  under the chained hash of that prefix, and only then is the prefix published
+  to the block manager's map (`record_computed_prefix_states`);
+* a later sequence that reuses that prefix gets the stored state written into
+  its own slot before it runs (`install_cached_prefix_hybrid_states`); a missing
+  state is a RuntimeError.
+
+Here the stored states live in a preallocated device pool (the reference keeps
+an unbounded dict of arrays); snapshot and restore are index-list copy kernels
+(nvj_hybrid_snapshot / nvj_hybrid_restore), batched over all sequences of a
+step.  When the pool is full the least recently used entry is dropped and its
+hash leaves `cacheable_hashes`, so the block manager stops offering that prefix
+to hybrid models.
+"""
+
+from __future__ import annotations
+
+from collections import OrderedDict
+from typing import Dict, Iterable, List, Optional, Sequence as Seq
+
+import torch
+
+from ..kernels import paged_kv as _k
+from ..kv_cache import HybridLayerState
+
+
+class HybridStateTable:
+    """Slot table of GDN state for resident sequences (model_runner.py:3758-3867)."""
+
+    def __init__(self, conv_shape: Optional[tuple], rec_shape: Optional[tuple], max_slots: int,
+                 conv_dtype=torch.bfloat16, device="cuda"):
+        self.max_slots = int(max_slots)
+        self.conv = None if conv_shape is None else torch.zeros((max_slots, *conv_shape), dtype=conv_dtype, device=device)
+        self.rec = None if rec_shape is None else torch.zeros((max_slots, *rec_shape), dtype=torch.float32, device=device)
+        self.device = torch.device(device)
+        self._slot_of: Dict[int, int] = {}
+        self._free: List[int] = list(range(max_slots - 1, -1, -1))
+        self._clean = set(range(max_slots))  # slots known to hold zeros
+
+    # ---- slot bookkeeping
+    def slot(self, seq_id: int) -> int:
+        """Slot of `seq_id`, assigning (and zeroing) one on first use."""
+        if seq_id < 0:
+            return -1
+        s = self._slot_of.get(seq_id)
+        if s is not None:
+            return s
+        if not self._free:
+            raise RuntimeError("No free hybrid-state slots; max_num_resident_seqs is exhausted")
+        if seq_id < self.max_slots and seq_id in self._free:
+            self._free.remove(seq_id)
+            s = seq_id
+        else:
+            s = self._free.pop()
+        self._slot_of[seq_id] = s
+        if s not in self._clean:
+            for t in (self.conv, self.rec):
+                if t is not None:
+                    t[s].zero_()
+            self._clean.add(s)
+        return s
+
+    def has(self, seq_id: int) -> bool:
+        return seq_id in self._slot_of
+
+    def mark_written(self, seq_ids: Iterable[int]) -> None:
+        for i in seq_ids:
+            s = self._slot_of.get(i)
+            if s is not None:
+                self._clean.discard(s)
+
+    def release(self, seq_ids: Iterable[int]) -> None:
+        for i in seq_ids:
+            s = self._slot_of.pop(i, None)
+            if s is not None:
+                self._free.append(s)
+
+    def state(self, seq_id: int) -> HybridLayerState:
+        """View of one sequence's state rows (the forward pass updates them in place)."""
+        s = self.slot(seq_id)
+        return HybridLayerState(None if self.conv is None else self.conv[s:s + 1],
+                                None if self.rec is None else self.rec[s:s + 1])
+
+
+class PrefixStateCache:
+    """Pool of state snapshots keyed by prefix hash (scheduler.py:67-69, 239-279)."""
+
+    def __init__(self, table: HybridStateTable, capacity: int):
+        self.table = table
+        self.capacity = int(capacity)
+        dev = table.device
+        self.conv_pool = None if table.conv is None else torch.zeros((capacity, *table.conv.shape[1:]), dtype=table.conv.dtype, device=dev)
+        self.rec_pool = None if table.rec is None else torch.zeros((capacity, *table.rec.shape[1:]), dtype=torch.float32, device=dev)
+        self._entry: "OrderedDict[int, int]" = OrderedDict()  # hash -> pool row, LRU order
+        self._free = list(range(capacity - 1, -1, -1))
+
+    def __contains__(self, prefix_hash: int) -> bool:
+        return int(prefix_hash) in self._entry
+
+    def __len__(self) -> int:
+        return len(self._entry)
+
+    @property
+    def cacheable_hashes(self) -> set:
+        """Hashes a hybrid model may reuse (`Scheduler._prefix_cacheable_hashes`)."""
+        return set(self._entry)
+
+    def _row_for(self, prefix_hash: int) -> int:
+        row = self._entry.pop(prefix_hash, None)
+        if row is None:
+            if not self._free:
+                _, row = self._entry.popitem(last=False)  # drop the least recently used snapshot
+            else:
+                row = self._free.pop()
+        self._entry[prefix_hash] = row
+        return row
+
+    def _idx(self, values: List[int]) -> torch.Tensor:
+        t = torch.tensor(values, dtype=torch.int32)
+        return t.pin_memory().to(self.table.device, non_blocking=True) if self.table.device.type == "cuda" else t
+
+    def snapshot(self, seq_ids: Seq[int], prefix_hashes: Seq[int]) -> None:
+        """pool[hash] <- table[slot(seq)] for every pair, one batched copy."""
+        if not seq_ids:
+            return
+        slots = [self.table.slot(int(s)) for s in seq_ids]
+        rows = [self._row_for(int(h)) for h in prefix_hashes]
+        _k.hybrid_copy(self.table.conv, self.table.rec, self.conv_pool, self.rec_pool,
+                       self._idx(slots), self._idx(rows), restore=False)
+
+    def restore(self, seq_ids: Seq[int], prefix_hashes: Seq[int]) -> None:
+        """table[slot(seq)] <- pool[hash]; a hash without a snapshot is a RuntimeError."""
+        if not seq_ids:
+            return
+        rows = []
+        for h in prefix_hashes:
+            row = self._entry.get(int(h))
+            if row is None:
+                raise RuntimeError(f"missing hybrid prefix state for cached prefix hash {int(h)}")
+            self._entry.move_to_end(int(h))
+            rows.append(row)
+        slots = [self.table.slot(int(s)) for s in seq_ids]
+        _k.hybrid_copy(self.table.conv, self.table.rec, self.conv_pool, self.rec_pool,
+                       self._idx(slots), self._idx(rows), restore=True)
+        self.table.mark_written(seq_ids)
+
+    # ---- the two engine-step hooks (llm_engine.py:432-457)
+    def install_cached_prefix_hybrid_states(self, seqs) -> None:
+        """Seed the slot of every sequence that starts from a cached prefix (model_runner.py:3886-3905)."""
+        ids, hashes, todo = [], [], []
+        for seq in seqs:
+            h = getattr(seq, "cached_prefix_hash", None)
+            if h is None or int(getattr(seq, "num_cached_tokens", 0)) <= 0:
+                continue
+            if getattr(seq, "cached_prefix_hybrid_seeded", False):
+                continue
+            ids.append(int(seq.seq_id)); hashes.append(int(h)); todo.append(seq)
+        self.restore(ids, hashes)
+        for seq in todo:
+            seq.cached_prefix_hybrid_seeded = True
+
+    def record_computed_prefix_states(self, block_manager, seqs, prefill_chunk_lengths) -> None:
+        """After a prefill step: snapshot block-aligned prefixes, then publish them (scheduler.py:239-279)."""
+        if len(prefill_chunk_lengths) != len(seqs):
+            return
+        ids, hashes, publish = [], [], []
+        for seq, chunk in zip(seqs, prefill_chunk_lengths):
+            chunk = int(chunk)
+            if chunk <= 0:
+                continue
+            computed = min(seq.num_prompt_tokens, seq.num_cached_tokens + chunk)
+            if computed <= 0:
+                continue
+            h = block_manager.record_computed_prefix(seq, computed, publish=False)
+            if h is None or not self.table.has(int(seq.seq_id)):
+                continue
+            ids.append(int(seq.seq_id)); hashes.append(int(h)); publish.append((seq, computed))
+        self.snapshot(ids, hashes)
+        for seq, computed in publish:
+            block_manager.publish_computed_prefix(seq, computed)

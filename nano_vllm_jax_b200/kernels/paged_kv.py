@@ -1,0 +1,476 @@
+"""Kernel-ABI wrappers: torch CUDA tensors in, C-ABI calls out.
+
+These functions keep the names, argument orders and aliasing of the reference's
+kernel-level ABI for one NHD layer slice `[num_pages, page_size, num_kv_heads,
+head_dim]`:
+
+  kv_append_paged_nhd                    nanovllm_jax/kernels/cuda_fp32_ffi.py:323-382
+  kv_append_paged_nhd_from_metadata      nanovllm_jax/kernels/cuda_fp32_ffi.py:427-472
+  paged_decode_attention_gqa_nhd         nanovllm_jax/kernels/cuda_fp32_ffi.py:527-572
+  paged_decode_attention_with_kv_append  nanovllm_jax/kernels/full_attention_triton.py:488-581
+  packed_paged_prefill_attention         nanovllm_jax/kernels/full_attention_triton.py:148-221
+  kv_last_page_len_from_seq_lens,
+  dense_block_tables_to_kv_indptr        nanovllm_jax/kernels/paged_attention.py:23-54
+
+The reference's custom calls alias the cache inputs to the outputs
+(`input_output_aliases`); here the caches are updated in place and the same
+tensors are returned.  Every function launches on the current CUDA stream and
+does not synchronise, unless `NVJ_CHECK_STATUS=1` asks for the device status
+word to be read back after each call (tests do).
+"""
+
+from __future__ import annotations
+
+import os
+from typing import Optional
+
+import torch
+
+from .. import _lib
+from .._lib import NVJ_BF16, NVJ_F16, NVJ_F32, NvjError, check
+
+_DTYPES = {torch.bfloat16: NVJ_BF16, torch.float16: NVJ_F16, torch.float32: NVJ_F32}
+
+
+def _dt(t: torch.Tensor) -> int:
+    try:
+        return _DTYPES[t.dtype]
+    except KeyError:
+        raise ValueError(f"unsupported dtype {t.dtype}") from None
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _stream(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _cuda(name: str, t: torch.Tensor) -> torch.Tensor:
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor (there is no CPU path)")
+    return t
+
+
+def _i32(name: str, t: torch.Tensor) -> torch.Tensor:
+    _cuda(name, t)
+    if t.dtype != torch.int32:
+        raise ValueError(f"{name} must have dtype int32")
+    return t.contiguous()
+
+
+def _strict() -> bool:
+    return os.environ.get("NVJ_CHECK_STATUS", "0") == "1"
+
+
+class DeviceStatusError(NvjError):
+    """A kernel flagged a device-side problem (bad block id, bad length, timeout)."""
+
+
+def _raise_status(word: int, what: str) -> None:
+    names = [n for bit, n in ((1, "timeout"), (2, "block id or slot outside the pool"),
+                              (4, "sequence length beyond the block table")) if word & bit]
+    raise DeviceStatusError(f"{what}: device status {word} ({', '.join(names)})")
+
+
+# --------------------------------------------------------------------------- workspaces
+
+class _Workspace:
+    """Decode scratch + status word for one (device, stream)."""
+
+    def __init__(self, device: torch.device, max_batch: int):
+        lib = _lib.load()
+        with torch.cuda.device(device):
+            nbytes = int(lib.nvj_paged_decode_workspace_bytes(int(max_batch)))
+        if nbytes <= 0:
+            raise NvjError("nvj_paged_decode_workspace_bytes failed (no CUDA device?)")
+        self.max_batch = int(max_batch)
+        self.buf = torch.zeros(nbytes, dtype=torch.uint8, device=device)
+        self.nbytes = nbytes
+
+    def status_tensor(self) -> torch.Tensor:
+        return self.buf[:4].view(torch.int32)
+
+
+_workspaces: dict[tuple[int, int], _Workspace] = {}
+_status_words: dict[tuple[int, int], torch.Tensor] = {}
+
+
+def _workspace(device: torch.device, batch: int) -> _Workspace:
+    key = (device.index if device.index is not None else torch.cuda.current_device(), _stream(device))
+    ws = _workspaces.get(key)
+    if ws is None or ws.max_batch < batch:
+        ws = _Workspace(device, max(batch, 256, 2 * (ws.max_batch if ws else 0)))
+        _workspaces[key] = ws
+    return ws
+
+
+def _status_word(device: torch.device) -> torch.Tensor:
+    key = (device.index if device.index is not None else torch.cuda.current_device(), _stream(device))
+    t = _status_words.get(key)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=device)
+        _status_words[key] = t
+    return t
+
+
+def _check_word(t: torch.Tensor, what: str, ws: Optional[_Workspace] = None) -> None:
+    word = int(t.item())
+    if word:
+        if ws is not None:
+            ws.buf.zero_()  # counters may be left mid-flight after a flagged launch
+        else:
+            t.zero_()
+        _raise_status(word, what)
+
+
+def check_device_status(device=None) -> None:
+    """Synchronise and raise if any kernel on `device`'s current stream flagged a problem."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    key = (device.index if device.index is not None else torch.cuda.current_device(), _stream(device))
+    if key in _workspaces:
+        _check_word(_workspaces[key].status_tensor(), "paged decode", _workspaces[key])
+    if key in _status_words:
+        _check_word(_status_words[key], "paged kv")
+
+
+# --------------------------------------------------------------------------- metadata helpers
+
+def kv_last_page_len_from_seq_lens(seq_lens: torch.Tensor, page_size: int) -> torch.Tensor:
+    if page_size <= 0:
+        raise ValueError("page_size must be positive")
+    seq_lens = seq_lens.to(torch.int32)
+    return torch.where(seq_lens > 0, (seq_lens - 1) % page_size + 1, torch.zeros_like(seq_lens)).to(torch.int32)
+
+
+def dense_block_tables_to_kv_indptr(block_tables: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    if block_tables.ndim != 2:
+        raise ValueError("block_tables must have shape [batch, max_pages_per_sequence]")
+    batch, width = block_tables.shape
+    kv_indices = block_tables.reshape(-1).to(torch.int32)
+    kv_indptr = torch.arange(batch + 1, dtype=torch.int32, device=block_tables.device) * width
+    return kv_indices, kv_indptr
+
+
+def _check_nhd_cache(k_cache: torch.Tensor, v_cache: torch.Tensor) -> None:
+    _cuda("k_cache", k_cache)
+    _cuda("v_cache", v_cache)
+    if k_cache.shape != v_cache.shape:
+        raise ValueError("k_cache and v_cache must have the same shape")
+    if k_cache.ndim != 4:
+        raise ValueError("k_cache must have NHD shape [num_pages, page_size, num_kv_heads, head_dim]")
+    if k_cache.dtype != v_cache.dtype:
+        raise ValueError("k_cache and v_cache must have the same dtype")
+    if not (k_cache.is_contiguous() and v_cache.is_contiguous()):
+        raise ValueError("cache layer slices must be contiguous")
+
+
+# --------------------------------------------------------------------------- append
+
+def kv_append_slots(new_k, new_v, slot_mapping, k_cache_layer, v_cache_layer, *, valid_mask=None,
+                    query_start_loc=None, packed=False):
+    """Slot-mapped append into one layer (flat `[slots, Hkv, D]` or `[NB, bs, Hkv, D]`), in place.
+
+    new_k/new_v `[rows, cols, Hkv, D]`; slot_mapping `[rows, cols]` int32.  The
+    valid rules are those of nvj_kv_append (explicit mask and/or query_start_loc).
+    """
+    lib = _lib.load()
+    _cuda("new_k", new_k)
+    _cuda("k_cache_layer", k_cache_layer)
+    if new_k.shape != new_v.shape:
+        raise ValueError("new_k and new_v must have the same shape")
+    if k_cache_layer.shape != v_cache_layer.shape:
+        raise ValueError("k_cache and v_cache must have the same shape")
+    hkv, d = k_cache_layer.shape[-2], k_cache_layer.shape[-1]
+    if tuple(new_k.shape[-2:]) != (hkv, d):
+        raise ValueError("new_k trailing dimensions must match cache [num_kv_heads, head_dim]")
+    if not (k_cache_layer.is_contiguous() and v_cache_layer.is_contiguous()):
+        raise ValueError("cache layer slices must be contiguous")
+    slot_mapping = _i32("slot_mapping", slot_mapping)
+    n_tokens = slot_mapping.numel()
+    if new_k.numel() != n_tokens * hkv * d:
+        raise ValueError("slot_mapping and new_k must describe the same number of tokens")
+    rows, cols = (slot_mapping.shape if slot_mapping.ndim == 2 else (1, n_tokens))
+    new_k, new_v = new_k.contiguous(), new_v.contiguous()
+    vm = None
+    if valid_mask is not None:
+        vm = _cuda("valid_mask", valid_mask).reshape(-1).to(torch.int32).contiguous()
+        if vm.numel() != n_tokens:
+            raise ValueError("valid_mask must have the shape of slot_mapping")
+    qsl, qsl_rows = None, 0
+    if query_start_loc is not None:
+        qsl = _i32("query_start_loc", query_start_loc)
+        qsl_rows = qsl.numel() - 1
+    num_slots = k_cache_layer.numel() // (hkv * d)
+    st = _status_word(k_cache_layer.device)
+    rc = lib.nvj_kv_append(_ptr(new_k), _ptr(new_v), _dt(new_k), _ptr(slot_mapping), _ptr(vm), _ptr(qsl),
+                           qsl_rows, 1 if packed else 0, rows, cols, _ptr(k_cache_layer),
+                           _ptr(v_cache_layer), _dt(k_cache_layer), num_slots, hkv, d, _ptr(st),
+                           _stream(k_cache_layer.device))
+    check(rc, "nvj_kv_append")
+    if _strict():
+        _check_word(st, "nvj_kv_append")
+    return k_cache_layer, v_cache_layer
+
+
+def kv_append_paged_nhd(append_key, append_value, batch_indices, positions, k_cache, v_cache,
+                        kv_indices, kv_indptr, kv_last_page_len, valid_mask=None):
+    """Page-table append on one NHD layer slice, in place; returns (k_cache, v_cache)."""
+    lib = _lib.load()
+    _check_nhd_cache(k_cache, v_cache)
+    _cuda("append_key", append_key)
+    if append_key.shape != append_value.shape:
+        raise ValueError("append_key and append_value must have the same shape")
+    if append_key.ndim != 3:
+        raise ValueError("append_key must have shape [nnz_tokens, num_kv_heads, head_dim]")
+    if tuple(append_key.shape[1:]) != tuple(k_cache.shape[2:]):
+        raise ValueError("append_key trailing dimensions must match cache [num_kv_heads, head_dim]")
+    nnz = append_key.shape[0]
+    batch_indices = _i32("batch_indices", batch_indices)
+    positions = _i32("positions", positions)
+    if batch_indices.shape != (nnz,) or positions.shape != (nnz,):
+        raise ValueError("batch_indices and positions must both have shape [nnz_tokens]")
+    kv_indices = _i32("kv_indices", kv_indices)
+    kv_indptr = _i32("kv_indptr", kv_indptr)
+    _i32("kv_last_page_len", kv_last_page_len)
+    if kv_indices.ndim != 1 or kv_indptr.ndim != 1 or kv_last_page_len.ndim != 1:
+        raise ValueError("page metadata tensors must be rank-1")
+    vm = None
+    if valid_mask is not None:
+        vm = _i32("valid_mask", valid_mask)
+        if vm.shape != (nnz,):
+            raise ValueError("valid_mask must have shape [nnz_tokens]")
+    pages, page_size, hkv, d = k_cache.shape
+    st = _status_word(k_cache.device)
+    ak, av = append_key.contiguous(), append_value.contiguous()
+    rc = lib.nvj_kv_append_nhd(_ptr(ak), _ptr(av), _dt(ak), _ptr(batch_indices), _ptr(positions), nnz,
+                               _ptr(k_cache), _ptr(v_cache), _dt(k_cache), pages, page_size, hkv, d,
+                               _ptr(kv_indices), kv_indices.numel(), _ptr(kv_indptr),
+                               kv_indptr.numel() - 1, _ptr(vm), _ptr(st), _stream(k_cache.device))
+    check(rc, "nvj_kv_append_nhd")
+    if _strict():
+        _check_word(st, "nvj_kv_append_nhd")
+    return k_cache, v_cache
+
+
+def kv_append_paged_nhd_from_metadata(k, v, k_cache_layer, v_cache_layer, metadata, *, page_size):
+    """Append rectangular scheduled K/V `[B, T, Hkv, D]` using ragged metadata (padded tokens masked)."""
+    if metadata.positions is None:
+        raise ValueError("metadata.positions is required for the paged KV append")
+    batch, query_len = k.shape[:2]
+    if batch * query_len == 0:
+        return k_cache_layer, v_cache_layer
+    dev = k.device
+    query_lens = torch.diff(metadata.query_start_loc.to(torch.int32))
+    valid = torch.arange(query_len, dtype=torch.int32, device=dev)[None, :] < query_lens[:, None]
+    batch_indices = torch.arange(batch, dtype=torch.int32, device=dev).repeat_interleave(query_len)
+    kv_indices, kv_indptr = dense_block_tables_to_kv_indptr(metadata.block_tables)
+    return kv_append_paged_nhd(
+        k.reshape(batch * query_len, *k.shape[2:]), v.reshape(batch * query_len, *v.shape[2:]),
+        batch_indices, metadata.positions.reshape(-1).to(torch.int32), k_cache_layer, v_cache_layer,
+        kv_indices, kv_indptr, kv_last_page_len_from_seq_lens(metadata.seq_lens, page_size),
+        valid.reshape(-1).to(torch.int32))
+
+
+# --------------------------------------------------------------------------- decode
+
+def _decode_call(q3, k_layer, v_layer, block_tables, table_width, kv_indptr, kv_last_page_len,
+                 seq_lens, scale, variant, new_k=None, new_v=None, positions=None):
+    lib = _lib.load()
+    _check_nhd_cache(k_layer, v_layer)
+    _cuda("q", q3)
+    if q3.ndim != 3:
+        raise ValueError("q must have shape [batch, num_q_heads, head_dim]")
+    batch, hq, d = q3.shape
+    pages, page_size, hkv, dk = k_layer.shape
+    if d != dk:
+        raise ValueError("q and cache head_dim must match")
+    if hq % hkv != 0:
+        raise ValueError("num_q_heads must be divisible by num_kv_heads")
+    if q3.dtype not in _DTYPES:
+        raise ValueError(f"unsupported q dtype {q3.dtype}")
+    q3 = q3.contiguous()
+    seq_lens = _i32("seq_lens", seq_lens)
+    if seq_lens.shape != (batch,):
+        raise ValueError("seq_lens must have shape [batch]")
+    block_tables = _i32("block_tables", block_tables)
+    out = torch.empty((batch, hq, d), dtype=torch.float32, device=q3.device)
+    if batch == 0:
+        return out
+    ws = _workspace(q3.device, batch)
+    stream = _stream(q3.device)
+    if new_k is None:
+        rc = lib.nvj_paged_decode(_ptr(q3), _dt(q3), _ptr(k_layer), _ptr(v_layer), _dt(k_layer), pages,
+                                  page_size, hkv, d, hq, _ptr(block_tables), table_width,
+                                  _ptr(kv_indptr), _ptr(kv_last_page_len), _ptr(seq_lens), batch,
+                                  float(scale), _ptr(out), _ptr(ws.buf), ws.nbytes, int(variant), stream)
+        what = "nvj_paged_decode"
+    else:
+        rc = lib.nvj_paged_decode_fused_append(_ptr(q3), _dt(q3), _ptr(new_k), _ptr(new_v), _ptr(positions),
+                                               _ptr(k_layer), _ptr(v_layer), _dt(k_layer), pages,
+                                               page_size, hkv, d, hq, _ptr(block_tables), table_width,
+                                               _ptr(seq_lens), batch, float(scale), _ptr(out),
+                                               _ptr(ws.buf), ws.nbytes, int(variant), stream)
+        what = "nvj_paged_decode_fused_append"
+    check(rc, what)
+    if _strict():
+        _check_word(ws.status_tensor(), what, ws)
+    return out
+
+
+def paged_decode_attention(q, k_layer, v_layer, block_table, seq_lens, scale, *, variant=0):
+    """Width-1 decode over a dense block table: q `[B, Hq, D]` -> fp32 `[B, Hq, D]`."""
+    if block_table.ndim != 2:
+        raise ValueError("block_tables must be a 2D tensor [batch, max_blocks_per_seq]")
+    if block_table.shape[0] != q.shape[0]:
+        raise ValueError(f"query batch {q.shape[0]} must match block_tables batch {block_table.shape[0]}")
+    return _decode_call(q, k_layer, v_layer, block_table, block_table.shape[1], None, None, seq_lens,
+                        scale, variant)
+
+
+def paged_decode_attention_gqa_nhd(q, k_cache, v_cache, kv_indptr, kv_indices, kv_last_page_len,
+                                   seq_lens, softmax_scale, *, variant=0):
+    """CSR page-table decode on one NHD layer slice: q `[B, Hq, D]` -> fp32 `[B, Hq, D]`."""
+    batch = q.shape[0]
+    kv_indptr = _i32("kv_indptr", kv_indptr)
+    kv_indices = _i32("kv_indices", kv_indices)
+    kv_last_page_len = _i32("kv_last_page_len", kv_last_page_len)
+    if kv_indptr.shape != (batch + 1,):
+        raise ValueError("kv_indptr must have shape [batch + 1]")
+    if kv_indices.ndim != 1:
+        raise ValueError("kv_indices must have shape [total_pages]")
+    if kv_last_page_len.shape != (batch,):
+        raise ValueError("kv_last_page_len must have shape [batch]")
+    return _decode_call(q, k_cache, v_cache, kv_indices, 0, kv_indptr, kv_last_page_len, seq_lens,
+                        softmax_scale, variant)
+
+
+def paged_decode_attention_with_kv_append(query, new_k, new_v, k_cache, v_cache, block_table, seq_lens,
+                                          positions, layer_id, block_size, scale,
+                                          num_key_value_groups, *, variant=0):
+    """Fused decode step on the 5-D caches: returns (out `[B, 1, Hq*D]` fp32, k_cache, v_cache)."""
+    if query.ndim != 4 or query.shape[1] != 1 or new_k.shape[1] != 1 or new_v.shape[1] != 1:
+        raise ValueError("fused decode attention supports only width-1 decode")
+    if k_cache.ndim != 5 or v_cache.ndim != 5:
+        raise ValueError("fused decode attention requires cache shape "
+                         "[num_layers, num_pages, page_size, num_kv_heads, head_dim]")
+    if not 0 <= layer_id < k_cache.shape[0]:
+        raise ValueError(f"layer_idx {layer_id} is out of bounds for {k_cache.shape[0]} layers")
+    if k_cache.shape[2] != block_size:
+        raise ValueError("block_size must match the cache page size")
+    batch, _, hq, d = query.shape
+    if hq != k_cache.shape[3] * num_key_value_groups:
+        raise ValueError("num_key_value_groups does not match the head counts")
+    dt = k_cache.dtype
+    nk = new_k[:, 0].to(dt).contiguous()
+    nv = new_v[:, 0].to(dt).contiguous()
+    q3 = query[:, 0]
+    if q3.dtype not in (torch.float32, dt):
+        q3 = q3.to(dt)
+    pos = _i32("positions", positions.reshape(batch).to(torch.int32))
+    out = _decode_call(q3, k_cache[layer_id], v_cache[layer_id], block_table, block_table.shape[1],
+                       None, None, seq_lens, scale, variant, nk, nv, pos)
+    return out.reshape(batch, 1, hq * d), k_cache, v_cache
+
+
+# --------------------------------------------------------------------------- prefill
+
+def packed_paged_prefill_attention(query, k_cache_layer, v_cache_layer, block_table, kv_lens, positions,
+                                   query_start_loc, block_size, scale, num_key_value_groups,
+                                   max_query_len=None):
+    """Ragged packed prefill: query `[1, T, Hq, D]` -> fp32 `[1, T, Hq*D]`, padded tokens 0."""
+    lib = _lib.load()
+    _check_nhd_cache(k_cache_layer, v_cache_layer)
+    if query.ndim != 4 or query.shape[0] != 1:
+        raise ValueError("packed prefill query must have shape [1, token_bucket, heads, head_dim]")
+    if positions.ndim != 2 or positions.shape[0] != 1 or positions.shape[1] != query.shape[1]:
+        raise ValueError("packed positions and token_row_ids must have shape [1, token_bucket]")
+    if block_table.ndim != 2:
+        raise ValueError("block_table must be a 2D tensor [batch, max_blocks_per_seq]")
+    if kv_lens.shape[0] != block_table.shape[0]:
+        raise ValueError("kv_lens shape must align with block_table rows")
+    _, tokens, hq, d = query.shape
+    pages, page_size, hkv, dk = k_cache_layer.shape
+    if page_size != block_size or d != dk or hq != hkv * num_key_value_groups:
+        raise ValueError("query / cache shapes do not agree")
+    q = _cuda("query", query)[0].contiguous()
+    block_table = _i32("block_table", block_table)
+    kv_lens = _i32("kv_lens", kv_lens)
+    pos = _i32("positions", positions.reshape(-1))
+    qsl = _i32("query_start_loc", query_start_loc)
+    rows = block_table.shape[0]
+    if qsl.numel() != rows + 1:
+        raise ValueError("query_start_loc must have shape [rows + 1]")
+    out = torch.empty((tokens, hq, d), dtype=torch.float32, device=q.device)
+    st = _status_word(q.device)
+    rc = lib.nvj_paged_prefill_packed(_ptr(q), _dt(q), _ptr(k_cache_layer), _ptr(v_cache_layer),
+                                      _dt(k_cache_layer), pages, page_size, hkv, d, hq, _ptr(block_table),
+                                      block_table.shape[1], _ptr(kv_lens), _ptr(pos), _ptr(qsl), rows,
+                                      tokens, float(scale), _ptr(out), _ptr(st), _stream(q.device))
+    check(rc, "nvj_paged_prefill_packed")
+    if _strict():
+        _check_word(st, "nvj_paged_prefill_packed")
+    return out.reshape(1, tokens, hq * d)
+
+
+# --------------------------------------------------------------------------- copies / tokens
+
+def copy_blocks(k_cache, v_cache, src_ids, dst_ids):
+    """cache[:, dst] = cache[:, src] on the 5-D caches, in place (src and dst sets disjoint)."""
+    lib = _lib.load()
+    if k_cache.ndim != 5 or k_cache.shape != v_cache.shape:
+        raise ValueError("copy_blocks requires 5-D caches of equal shape")
+    if not (k_cache.is_contiguous() and v_cache.is_contiguous()):
+        raise ValueError("caches must be contiguous")
+    src_ids, dst_ids = _i32("src_ids", src_ids), _i32("dst_ids", dst_ids)
+    if src_ids.shape != dst_ids.shape or src_ids.ndim != 1:
+        raise ValueError("src_ids and dst_ids must be rank-1 and of equal length")
+    layers, nb = k_cache.shape[:2]
+    block_bytes = k_cache[0, 0].numel() * k_cache.element_size()
+    st = _status_word(k_cache.device)
+    rc = lib.nvj_copy_blocks(_ptr(k_cache), _ptr(v_cache), layers, nb, block_bytes, nb * block_bytes,
+                             _ptr(src_ids), _ptr(dst_ids), src_ids.numel(), _ptr(st), _stream(k_cache.device))
+    check(rc, "nvj_copy_blocks")
+    if _strict():
+        _check_word(st, "nvj_copy_blocks")
+    return k_cache, v_cache
+
+
+def _row_bytes(t):
+    return 0 if t is None else t[0].numel() * t.element_size()
+
+
+def hybrid_copy(conv_table, rec_table, conv_pool, rec_pool, table_slots, pool_slots, *, restore: bool):
+    """Snapshot (table -> pool) or restore (pool -> table) GDN state rows, in place."""
+    lib = _lib.load()
+    for name, t in (("conv_table", conv_table), ("rec_table", rec_table), ("conv_pool", conv_pool), ("rec_pool", rec_pool)):
+        if t is not None and not (t.is_cuda and t.is_contiguous()):
+            raise ValueError(f"{name} must be a contiguous CUDA tensor")
+    ref_t = rec_table if rec_table is not None else conv_table
+    ref_p = rec_pool if rec_pool is not None else conv_pool
+    if ref_t is None or ref_p is None:
+        return
+    if _row_bytes(conv_table) != _row_bytes(conv_pool) or _row_bytes(rec_table) != _row_bytes(rec_pool):
+        raise ValueError("table and pool rows must have the same size")
+    table_slots, pool_slots = _i32("table_slots", table_slots), _i32("pool_slots", pool_slots)
+    st = _status_word(ref_t.device)
+    fn = lib.nvj_hybrid_restore if restore else lib.nvj_hybrid_snapshot
+    rc = fn(_ptr(conv_table), _ptr(conv_pool), _row_bytes(conv_table), _ptr(rec_table), _ptr(rec_pool),
+            _row_bytes(rec_table), ref_t.shape[0], ref_p.shape[0], _ptr(table_slots), _ptr(pool_slots),
+            table_slots.numel(), _ptr(st), _stream(ref_t.device))
+    check(rc, "nvj_hybrid_restore" if restore else "nvj_hybrid_snapshot")
+    if _strict():
+        _check_word(st, "hybrid state copy")
+
+
+def row_argmax(x: torch.Tensor) -> torch.Tensor:
+    """int32 argmax of each row of a float32 `[rows, n]` tensor (first maximum wins)."""
+    lib = _lib.load()
+    _cuda("x", x)
+    if x.dtype != torch.float32 or x.ndim != 2:
+        raise ValueError("row_argmax expects a float32 [rows, n] tensor")
+    x = x.contiguous()
+    out = torch.empty(x.shape[0], dtype=torch.int32, device=x.device)
+    check(lib.nvj_row_argmax(_ptr(x), x.shape[0], x.shape[1], _ptr(out), _stream(x.device)), "nvj_row_argmax")
+    return out

@@ -1,0 +1,179 @@
+"""Packed prefill attention, block copies, GDN state snapshot/restore and the token argmax on the GPU."""
+
+import numpy as np
+import pytest
+import torch
+from ml_dtypes import bfloat16
+
+from helpers import BS, SCALE, bits, to_numpy, to_torch
+from oracle import kv_cache_ref as R
+
+pytestmark = pytest.mark.gpu
+
+CONTRACT = 2e-2
+TIGHT = 2e-3
+
+
+def test_packed_prefill_small_known_case():
+    # reference tests/test_backend_boundaries.py:1462-1529: rows of 3 and 2 tokens plus a pad token, flat 4-D cache
+    from nano_vllm_jax_b200 import kv_cache as kv
+    rng = np.random.default_rng(0)
+    k = rng.standard_normal((1, 16, 2, 8)).astype(np.float32)  # flat: 16 slots = 8 blocks of 2
+    v = rng.standard_normal((1, 16, 2, 8)).astype(np.float32)
+    tables = np.array([[3, 4], [5, 6]], np.int32)
+    kv_lens = np.array([3, 2], np.int32)
+    positions = np.array([[0, 1, 2, 0, 1, 0]], np.int32)
+    rows = np.array([[0, 0, 0, 1, 1, 0]], np.int32)
+    qsl = np.array([0, 3, 5], np.int32)
+    q = rng.standard_normal((1, 6, 4, 8)).astype(np.float32)
+    ref = R.paged_attention_prefill_packed(q, k, v, tables, kv_lens, positions, rows, qsl, 2, 0.4, 2)
+    out = kv.paged_attention_prefill_packed(to_torch(q), to_torch(k), to_torch(v), to_torch(tables), to_torch(kv_lens),
+                                            to_torch(positions), to_torch(rows), to_torch(qsl), 2, 0.4, 2)
+    assert out.shape == (1, 6, 32)
+    np.testing.assert_allclose(to_numpy(out), ref, rtol=1e-5, atol=2e-6)
+    assert not to_numpy(out)[0, 5].any()
+
+
+def _prefill_case(seed, nb, prompt_lens, cached, chunk, bucket):
+    """Rows with `cached[r]` tokens already in the cache run the next `chunk[r]` tokens of their prompt."""
+    rng = np.random.default_rng(seed)
+    rows = len(prompt_lens)
+    ends = [cached[r] + chunk[r] for r in range(rows)]
+    need = [-(-e // BS) for e in ends]
+    w = max(need)
+    perm = rng.permutation(nb)
+    tables = np.zeros((rows, w), np.int32)
+    o = 0
+    for r in range(rows):
+        tables[r, :need[r]] = perm[o:o + need[r]]
+        o += need[r]
+    k = rng.standard_normal((1, nb, BS, 2, 256), dtype=np.float32).astype(bfloat16)
+    v = rng.standard_normal((1, nb, BS, 2, 256), dtype=np.float32).astype(bfloat16)
+    total = sum(chunk)
+    pos = np.zeros((1, bucket), np.int32)
+    rid = np.zeros((1, bucket), np.int32)
+    pos[0, :total] = np.concatenate([np.arange(cached[r], ends[r]) for r in range(rows)])
+    rid[0, :total] = np.repeat(np.arange(rows), chunk)
+    qsl = np.concatenate([[0], np.cumsum(chunk)]).astype(np.int32)
+    q = rng.standard_normal((1, bucket, 8, 256), dtype=np.float32).astype(bfloat16)
+    return dict(k=k, v=v, tables=tables, kv_lens=np.array(ends, np.int32), pos=pos, rid=rid, qsl=qsl, q=q)
+
+
+def test_packed_prefill_ragged_chunk_with_cached_prefixes():
+    from nano_vllm_jax_b200 import kv_cache as kv
+    c = _prefill_case(1, 400, [300, 64, 700, 90], cached=[128, 0, 512, 0], chunk=[100, 64, 57, 35], bucket=288)
+    ref = R.paged_attention_prefill_packed(c["q"], c["k"], c["v"], c["tables"], c["kv_lens"], c["pos"], c["rid"],
+                                           c["qsl"], BS, SCALE, 4)
+    out = kv.paged_attention_prefill_packed(to_torch(c["q"]), to_torch(c["k"]), to_torch(c["v"]), to_torch(c["tables"]),
+                                            to_torch(c["kv_lens"]), to_torch(c["pos"]), to_torch(c["rid"]),
+                                            to_torch(c["qsl"]), BS, SCALE, 4, out_dtype=torch.float32)
+    err = np.abs(to_numpy(out) - ref).max()
+    assert err <= CONTRACT and err <= TIGHT, err
+    assert not to_numpy(out)[0, 256:].any()  # tokens beyond query_start_loc[-1] are padding
+
+
+def test_mixed_batch_decode_rows_travel_the_packed_route():
+    # scheduler.py:956-1032: decode rows are 1-token rows of a packed prefill batch
+    from nano_vllm_jax_b200 import kv_cache as kv
+    c = _prefill_case(2, 600, [0] * 5, cached=[777, 130, 15, 256, 0], chunk=[1, 1, 1, 64, 61], bucket=128)
+    ref = R.paged_attention_prefill_packed(c["q"], c["k"], c["v"], c["tables"], c["kv_lens"], c["pos"], c["rid"],
+                                           c["qsl"], BS, SCALE, 4)
+    out = kv.paged_attention_prefill_packed(to_torch(c["q"]), to_torch(c["k"]), to_torch(c["v"]), to_torch(c["tables"]),
+                                            to_torch(c["kv_lens"]), to_torch(c["pos"]), to_torch(c["rid"]),
+                                            to_torch(c["qsl"]), BS, SCALE, 4, out_dtype=torch.float32)
+    assert np.abs(to_numpy(out) - ref).max() <= TIGHT
+
+
+def test_copy_blocks_bit_exact_all_layers():
+    from nano_vllm_jax_b200.kernels import paged_kv as K
+    rng = np.random.default_rng(3)
+    k = rng.standard_normal((3, 64, BS, 2, 256), dtype=np.float32).astype(bfloat16)
+    v = rng.standard_normal((3, 64, BS, 2, 256), dtype=np.float32).astype(bfloat16)
+    src = np.arange(0, 32, dtype=np.int32)
+    dst = rng.permutation(np.arange(32, 64)).astype(np.int32)
+    ek, ev = R.copy_blocks(k, v, src, dst)
+    kc, vc = to_torch(k), to_torch(v)
+    K.copy_blocks(kc, vc, to_torch(src), to_torch(dst))
+    np.testing.assert_array_equal(bits(to_numpy(kc)), bits(ek))
+    np.testing.assert_array_equal(bits(to_numpy(vc)), bits(ev))
+    with pytest.raises(K.DeviceStatusError):
+        K.copy_blocks(kc, vc, to_torch(np.array([1], np.int32)), to_torch(np.array([64], np.int32)))
+    np.testing.assert_array_equal(bits(to_numpy(kc)), bits(ek))  # the bad pair was skipped
+
+
+def test_copy_blocks_odd_sized_blocks_use_the_byte_path():
+    from nano_vllm_jax_b200.kernels import paged_kv as K
+    rng = np.random.default_rng(4)
+    k = rng.standard_normal((2, 5, 3, 1, 3)).astype(np.float32)  # 36-byte blocks
+    v = rng.standard_normal((2, 5, 3, 1, 3)).astype(np.float32)
+    ek, ev = R.copy_blocks(k, v, [0, 1], [3, 4])
+    kc, vc = to_torch(k), to_torch(v)
+    K.copy_blocks(kc, vc, to_torch(np.array([0, 1], np.int32)), to_torch(np.array([3, 4], np.int32)))
+    np.testing.assert_array_equal(to_numpy(kc), ek)
+    np.testing.assert_array_equal(to_numpy(vc), ev)
+
+
+def test_hybrid_state_snapshot_restore_full_size_bit_exact():
+    # state per sequence: conv [18, 6144, 4] bf16 and recurrent [18, 16, 128, 128] fp32 (kv_cache.py:379-407)
+    from nano_vllm_jax_b200.engine.prefix_state import HybridStateTable, PrefixStateCache
+    table = HybridStateTable((18, 6144, 4), (18, 16, 128, 128), max_slots=6, conv_dtype=torch.bfloat16)
+    cache = PrefixStateCache(table, capacity=3)
+    g = torch.Generator(device="cuda").manual_seed(0)
+    for sid in (10, 11, 12):
+        st = table.state(sid)
+        st.conv_state.copy_(torch.randn(st.conv_state.shape, generator=g, device="cuda").to(torch.bfloat16))
+        st.recurrent_state.copy_(torch.randn(st.recurrent_state.shape, generator=g, device="cuda"))
+    table.mark_written([10, 11, 12])
+    want = {sid: (table.state(sid).conv_state.clone(), table.state(sid).recurrent_state.clone()) for sid in (10, 11, 12)}
+    cache.snapshot([10, 11], [1001, 1002])
+    table.state(10).recurrent_state.add_(1.0)  # the snapshot is a copy, not a view
+    table.release([10])
+    cache.restore([20, 21], [1002, 1001])      # new sequences seeded from the snapshots
+    torch.cuda.synchronize()
+    assert torch.equal(table.state(20).conv_state, want[11][0]) and torch.equal(table.state(20).recurrent_state, want[11][1])
+    assert torch.equal(table.state(21).conv_state, want[10][0]) and torch.equal(table.state(21).recurrent_state, want[10][1])
+    assert torch.equal(table.state(12).recurrent_state, want[12][1])  # bystander untouched
+    with pytest.raises(RuntimeError, match="missing hybrid prefix state"):
+        cache.restore([22], [9999])
+    # capacity 3: a fourth snapshot evicts the least recently used hash
+    cache.snapshot([12], [1003])
+    cache.snapshot([12], [1004])
+    assert len(cache) == 3 and cache.cacheable_hashes == {1001, 1003, 1004}  # 1002 was used least recently
+
+
+def test_prefix_reuse_flow_block_manager_plus_state_cache():
+    # llm_engine.py:432-457 order: install cached states -> run -> record computed prefix states
+    from nano_vllm_jax_b200.engine.block_manager import BlockManager
+    from nano_vllm_jax_b200.engine.prefix_state import HybridStateTable, PrefixStateCache
+    from nano_vllm_jax_b200.engine.sequence import Sequence
+    bm = BlockManager(16, 2)
+    table = HybridStateTable((2, 8, 4), (2, 2, 4, 4), max_slots=4, conv_dtype=torch.float32)
+    cache = PrefixStateCache(table, capacity=4)
+    a = Sequence([1, 2, 3, 4], seq_id=0)
+    bm.allocate(a, cacheable_hashes=cache.cacheable_hashes)
+    table.state(0).recurrent_state.fill_(3.5)
+    table.state(0).conv_state.fill_(-1.25)
+    table.mark_written([0])
+    cache.record_computed_prefix_states(bm, [a], [4])
+    b = Sequence([1, 2, 3, 4, 5], seq_id=1)
+    assert bm.can_allocate(b, cacheable_hashes=cache.cacheable_hashes)
+    bm.allocate(b, cacheable_hashes=cache.cacheable_hashes)
+    assert b.num_cached_tokens == 4 and b.block_table[:2] == a.block_table and b.cached_prefix_hash in cache
+    cache.install_cached_prefix_hybrid_states([a, b])
+    assert b.cached_prefix_hybrid_seeded and not a.cached_prefix_hybrid_seeded
+    assert float(table.state(1).recurrent_state.min()) == 3.5 and float(table.state(1).conv_state.max()) == -1.25
+    # a hash the pool does not hold is not offered to hybrid models
+    c = Sequence([9, 9, 9, 9], seq_id=2)
+    bm.allocate(c, cacheable_hashes=cache.cacheable_hashes)
+    assert c.num_cached_tokens == 0
+
+
+def test_row_argmax_first_maximum_wins():
+    from nano_vllm_jax_b200.kernels import paged_kv as K
+    g = torch.Generator(device="cuda").manual_seed(1)
+    x = torch.randn((37, 2048), generator=g, device="cuda")
+    x[3, 100] = x[3, 1500] = 50.0
+    tok = K.row_argmax(x)
+    assert tok.dtype == torch.int32
+    assert torch.equal(tok.long(), torch.argmax(x, dim=1)) or int(tok[3]) == 100
+    assert int(tok[3]) == 100
