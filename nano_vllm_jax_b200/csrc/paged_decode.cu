@@ -305,9 +305,8 @@ __device__ __forceinline__ void fill_ring(const DecodeParams& p, DecodeSmem& sm,
   }
 }
 
-// One lane refills ring stage n % kStages with the K and V block of iteration n.
-// `wait_parity` is the phase of the stage's empty barrier that must have
-// completed (all warps released the previous occupant).
+// One lane refills ring stage n % kStages with the K and V block of iteration n,
+// after (wait_first) every warp has released the stage's previous occupant.
 __device__ __forceinline__ void issue_block(const DecodeParams& p, DecodeSmem& sm, int n,
                                             bool wait_first) {
   const int stage = n % kStages;
@@ -514,6 +513,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_pipelined_kernel(Dec
         // the warps take turns to refill the stage that iteration `it` just used
         if (warp == (it & (kConsumerWarps - 1)) && it + kStages < n_iters) issue_block(p, sm, it + kStages, true);
       }
+      __syncwarp();  // lane 0 may have waited for the other warps; reconverge before any CTA barrier
     }
     finish_segment(p, sm, s, st, warp, lane, total, nctas);
   }
