@@ -258,7 +258,8 @@ __device__ __forceinline__ void append_new_row(const DecodeParams& p, const Seg&
   uint4* dv = reinterpret_cast<uint4*>(const_cast<char*>(p.v_cache) + dst);
   dk[0] = k0; dk[1] = k1;
   dv[0] = v0; dv[1] = v1;
-  fence_proxy_async_all();  // these generic-proxy writes are read back by a bulk copy
+  __threadfence();          // the row must be in L2 before the copy engine reads the block
+  fence_proxy_async_all();  // generic-proxy writes -> async-proxy (bulk copy) reads
 }
 
 // Look-ahead walker that fills the block-id ring.
@@ -428,7 +429,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_pipelined_kernel(Dec
   extern __shared__ __align__(128) unsigned char smem_raw[];
   DecodeSmem& sm = *reinterpret_cast<DecodeSmem*>(smem_raw);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int nctas = gridDim.x;
+  const int grid = gridDim.x;
 
   // ---- pass 1: total number of blocks; zero the output of inactive rows
   int mine = 0;
@@ -437,7 +438,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_pipelined_kernel(Dec
     int len = 0;
     if (b < p.batch) len = decode_row_len(p, b);
     mine += (len + kBlk - 1) / kBlk;
-    const unsigned idle = __ballot_sync(kFullMask, b < p.batch && len <= 0 && (b % nctas) == (int)blockIdx.x);
+    const unsigned idle = __ballot_sync(kFullMask, b < p.batch && len <= 0 && (b % grid) == (int)blockIdx.x);
     for (unsigned m = idle; m; m &= m - 1) {
       const int bb = base + (warp << 5) + (__ffs(m) - 1);
       float4* o = reinterpret_cast<float4*>(p.out + (long long)bb * kHq * kD);
@@ -447,6 +448,10 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_pipelined_kernel(Dec
   int total = 0;
   cta_inclusive_scan(mine, sm.scan, total);
   if (total == 0) return;
+  // With fewer blocks than CTAs only the first `total` CTAs take part (one block
+  // each), so that every CTA id inside a row's span really delivers a partial.
+  const int nctas = total < grid ? total : grid;
+  if ((int)blockIdx.x >= nctas) return;
   const long long g0 = cta_range_start(blockIdx.x, total, nctas);
   const long long g1 = cta_range_start(blockIdx.x + 1, total, nctas);
   if (g0 == g1) return;

@@ -64,6 +64,12 @@ def _strict() -> bool:
     return os.environ.get("NVJ_CHECK_STATUS", "0") == "1"
 
 
+def _poison() -> bool:
+    # Debug aid (tests set it): fill output buffers with NaN before a launch so that an
+    # element the kernel fails to write cannot pass for a result left by an earlier call.
+    return os.environ.get("NVJ_POISON_OUTPUT", "0") == "1"
+
+
 class DeviceStatusError(NvjError):
     """A kernel flagged a device-side problem (bad block id, bad length, timeout)."""
 
@@ -298,6 +304,8 @@ def _decode_call(q3, k_layer, v_layer, block_tables, table_width, kv_indptr, kv_
     out = torch.empty((batch, hq, d), dtype=torch.float32, device=q3.device)
     if batch == 0:
         return out
+    if _poison():
+        out.fill_(float("nan"))
     ws = _workspace(q3.device, batch)
     stream = _stream(q3.device)
     if new_k is None:
@@ -403,6 +411,8 @@ def packed_paged_prefill_attention(query, k_cache_layer, v_cache_layer, block_ta
     if qsl.numel() != rows + 1:
         raise ValueError("query_start_loc must have shape [rows + 1]")
     out = torch.empty((tokens, hq, d), dtype=torch.float32, device=q.device)
+    if _poison():
+        out.fill_(float("nan"))
     st = _status_word(q.device)
     rc = lib.nvj_paged_prefill_packed(_ptr(q), _dt(q), _ptr(k_cache_layer), _ptr(v_cache_layer),
                                       _dt(k_cache_layer), pages, page_size, hkv, d, hq, _ptr(block_table),

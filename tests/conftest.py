@@ -9,6 +9,8 @@ if ROOT not in sys.path:
 
 # GPU tests read the device status word after every call.
 os.environ.setdefault("NVJ_CHECK_STATUS", "1")
+# ... and start every output buffer as NaN, so an unwritten element cannot pass for an old result.
+os.environ.setdefault("NVJ_POISON_OUTPUT", "1")
 
 
 def pytest_configure(config):

@@ -132,7 +132,7 @@ def test_long_ranges_refill_the_block_id_ring():
 @pytest.mark.parametrize("variant", [GENERIC, PIPELINED])
 def test_fused_append_cache_bit_exact_and_attention(variant):
     K = _K()
-    c = decode_case(7, 700, 33, 1, 900, layers=2, empty_rows=(5,))
+    c = decode_case(7, 2048, 33, 1, 900, layers=2, empty_rows=(5,))
     layer = 1
     slots = R.compute_slot_mapping(c["positions"], c["tables"], BS)
     valid = (c["seq_lens"] > 0)[:, None]
