@@ -45,6 +45,9 @@ WORKLOADS = {
     # name: (total rows at N=1 or overall, ctx_lo, ctx_hi, pool blocks per rank or None = sized to fit, scaling)
     "c2": dict(rows=256, lo=1024, hi=4096, pool=400_000, scaling="weak", seed=2,
                desc="decode step, 256 rows/GPU, ctx U[1024,4096], 400k-block bf16 pool, 8q/2kv heads, head_dim 256, block 16"),
+    # reduced c2 for profiler captures: a few GB on the device, still far larger than L2 per step
+    "c2small": dict(rows=64, lo=1024, hi=4096, pool=40_000, scaling="weak", seed=2,
+                    desc="decode step, 64 rows/GPU, ctx U[1024,4096], 40k-block bf16 pool (reduced c2 for profiling)"),
     "c5": dict(rows=2048, lo=8192, hi=32768, pool=None, scaling="strong", seed=5,
                desc="decode step, 2048 rows round-robin over the GPUs, ctx U[8192,32768], bf16 pool sized to the rows"),
 }
