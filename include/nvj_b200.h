@@ -38,7 +38,8 @@ typedef enum nvj_status {
   NVJ_ERR_INVALID_ARGUMENT = -1, /* null pointer, negative size, bad alignment   */
   NVJ_ERR_UNSUPPORTED = -2,      /* shape / dtype outside what the kernels cover */
   NVJ_ERR_LAUNCH = -3,           /* cudaGetLastError() after the launch          */
-  NVJ_ERR_WORKSPACE = -4         /* workspace missing or too small               */
+  NVJ_ERR_WORKSPACE = -4,        /* workspace missing or too small               */
+  NVJ_ERR_TOO_LARGE = -5         /* size beyond a built-in limit of the entry point */
 } nvj_status;
 
 typedef enum nvj_dtype { NVJ_BF16 = 0, NVJ_F16 = 1, NVJ_F32 = 2 } nvj_dtype;
@@ -155,6 +156,35 @@ int nvj_paged_decode_fused_append(const void* q, int q_dtype,
                                   float* out,
                                   void* workspace, size_t workspace_bytes,
                                   int variant, nvj_stream_t stream);
+
+/*
+ * nvj_paged_decode for callers that cannot allocate device memory (no counterpart
+ * in the reference).  A custom-call handler that only receives its operands, or a
+ * plugin that runs inside another runtime's memory pool, has nowhere to keep the
+ * decode workspace; here it comes from a fixed array inside the library
+ * (NVJ_STATIC_SCRATCH_BYTES on every GPU that loads the library), so the call
+ * itself allocates nothing.  Same arguments and results as nvj_paged_decode over a
+ * dense block table, minus the workspace.
+ *
+ *   limit        batch <= NVJ_STATIC_SCRATCH_MAX_BATCH, else NVJ_ERR_TOO_LARGE
+ *   status_out   nullable device int32: receives the NVJ_DEV_* bits of this call
+ *   first call   the first call on each device resolves the array's device address
+ *                (cudaGetSymbolAddress); make that first call outside any stream
+ *                capture.  Later calls only enqueue a small memset, the kernel and
+ *                an optional 4-byte copy.
+ *   sharing      every call on a device uses the same array: calls that may overlap
+ *                on the GPU (different streams, no dependency) race and must be
+ *                serialised by the caller.
+ */
+#define NVJ_STATIC_SCRATCH_MAX_BATCH 4096
+#define NVJ_STATIC_SCRATCH_BYTES 5300480
+int nvj_paged_decode_static_scratch(const void* q, int q_dtype,
+                                    const void* k_cache_layer, const void* v_cache_layer,
+                                    int kv_dtype, int64_t num_blocks, int block_size,
+                                    int num_kv_heads, int head_dim, int num_q_heads,
+                                    const int32_t* block_tables, int table_width,
+                                    const int32_t* seq_lens, int batch, float scale,
+                                    float* out, int32_t* status_out, nvj_stream_t stream);
 
 /* ----------------------------------------------------------------- prefill */
 

@@ -37,6 +37,9 @@ SIGNATURES = {
                                               c_int, c_int, c_void_p, c_int, c_void_p, c_int,
                                               c_float, c_void_p, c_void_p, c_size_t, c_int,
                                               c_void_p]),
+    "nvj_paged_decode_static_scratch": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int64, c_int,
+                                                c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int,
+                                                c_float, c_void_p, c_void_p, c_void_p]),
     "nvj_paged_prefill_packed": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int64, c_int,
                                          c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p,
                                          c_void_p, c_int, c_int, c_float, c_void_p, c_void_p,

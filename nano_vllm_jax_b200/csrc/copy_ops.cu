@@ -142,6 +142,7 @@ extern "C" const char* nvj_status_string(int status) {
     case NVJ_ERR_UNSUPPORTED: return "unsupported shape or dtype";
     case NVJ_ERR_LAUNCH: return "kernel launch failed";
     case NVJ_ERR_WORKSPACE: return "workspace missing or too small";
+    case NVJ_ERR_TOO_LARGE: return "size exceeds a built-in limit of this entry point";
     default: return "unknown status";
   }
 }

@@ -337,6 +337,40 @@ def paged_decode_attention(q, k_layer, v_layer, block_table, seq_lens, scale, *,
                         scale, variant)
 
 
+STATIC_SCRATCH_MAX_BATCH = 4096
+
+
+def paged_decode_attention_no_alloc(q, k_layer, v_layer, block_table, seq_lens, scale, out, status_out=None):
+    """Width-1 decode that allocates nothing: every buffer, `out` included, comes from the caller.
+
+    For hosts that may not allocate device memory while a step runs (a handler that
+    only sees its operands, a plugin inside another runtime's memory pool): the
+    decode workspace is a fixed array inside the library instead of a tensor.  The
+    array is shared by all calls on a device, so calls must not overlap on the GPU;
+    at most `STATIC_SCRATCH_MAX_BATCH` rows.  `status_out` (optional int32[1] CUDA
+    tensor) receives the device status bits; nothing is read back here.
+    """
+    lib = _lib.load()
+    _check_nhd_cache(k_layer, v_layer)
+    _cuda("q", q)
+    if q.ndim != 3 or block_table.ndim != 2 or block_table.shape[0] != q.shape[0]:
+        raise ValueError("q must be [batch, heads, head_dim] and block_table [batch, width]")
+    batch, hq, d = q.shape
+    if tuple(out.shape) != (batch, hq, d) or out.dtype != torch.float32 or not out.is_cuda or not out.is_contiguous():
+        raise ValueError("out must be a contiguous float32 CUDA tensor [batch, heads, head_dim]")
+    if not q.is_contiguous():
+        raise ValueError("q must be contiguous (this call makes no copies)")
+    block_table = _i32("block_table", block_table)
+    seq_lens = _i32("seq_lens", seq_lens)
+    pages, page_size, hkv, _ = k_layer.shape
+    rc = lib.nvj_paged_decode_static_scratch(_ptr(q), _dt(q), _ptr(k_layer), _ptr(v_layer), _dt(k_layer), pages,
+                                             page_size, hkv, d, hq, _ptr(block_table), block_table.shape[1],
+                                             _ptr(seq_lens), batch, float(scale), _ptr(out), _ptr(status_out),
+                                             _stream(q.device))
+    check(rc, "nvj_paged_decode_static_scratch")
+    return out
+
+
 def paged_decode_attention_gqa_nhd(q, k_cache, v_cache, kv_indptr, kv_indices, kv_last_page_len,
                                    seq_lens, softmax_scale, *, variant=0):
     """CSR page-table decode on one NHD layer slice: q `[B, Hq, D]` -> fp32 `[B, Hq, D]`."""
