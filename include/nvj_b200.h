@@ -52,6 +52,20 @@ typedef enum nvj_dtype { NVJ_BF16 = 0, NVJ_F16 = 1, NVJ_F32 = 2 } nvj_dtype;
 int nvj_abi_version(void);
 const char* nvj_status_string(int status);
 
+/* ------------------------------------------------------------- slot mapping */
+
+/*
+ * slot[b, t] = block_tables[row, pos / bs] * bs + pos % bs for positions [n_rows, n_cols].
+ * row = b when token_row_ids == NULL (nanovllm_jax/kv_cache.py:410-446, compute_slot_mapping),
+ * else the token's token_row_ids entry clipped to [0, table_rows) (kv_cache.py:449-473,
+ * compute_packed_slot_mapping).  A block index beyond the table is clamped to its last
+ * column, as the reference's XLA gather does.
+ */
+int nvj_compute_slot_mapping(const int32_t* positions, const int32_t* block_tables,
+                             const int32_t* token_row_ids, int n_rows, int n_cols,
+                             int table_rows, int table_width, int block_size,
+                             int32_t* slot_mapping, nvj_stream_t stream);
+
 /* ------------------------------------------------------------------ append */
 
 /*
@@ -98,7 +112,7 @@ int nvj_kv_append_nhd(const void* append_key, const void* append_value, int src_
 
 /*
  * Bytes of caller-owned scratch the decode entry points need for `max_batch`
- * rows on the current device.  The first NVJ_DECODE_WS_HEADER_BYTES hold the
+ * rows on the current device.  Its leading header (64 bytes + 4 bytes per row) holds the
  * status word and the per-row arrival counters and must be zero before the
  * first use (nvj_paged_decode_workspace_init does that); the kernels leave
  * them zero again on success.  One workspace serves one stream at a time.

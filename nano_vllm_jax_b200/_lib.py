@@ -21,6 +21,8 @@ NVJ_DEV_TIMEOUT, NVJ_DEV_BAD_BLOCK_ID, NVJ_DEV_BAD_LENGTH = 1, 2, 4
 SIGNATURES = {
     "nvj_abi_version": (c_int, []),
     "nvj_status_string": (c_char_p, [c_int]),
+    "nvj_compute_slot_mapping": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                         c_void_p, c_void_p]),
     "nvj_kv_append": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
                               c_int, c_int, c_void_p, c_void_p, c_int, c_int64, c_int, c_int,
                               c_void_p, c_void_p]),

@@ -94,9 +94,11 @@ class B200Backend:
             slot_mapping = kvc.compute_slot_mapping(positions, block_tables, block_size, is_prefill)
         batch, query_len = positions.shape
         if query_start_loc is None:
-            qlens = seq_lens.to(torch.int32) if is_prefill else torch.ones_like(seq_lens, dtype=torch.int32)
-            query_start_loc = torch.cat([torch.zeros(1, dtype=torch.int32, device=qlens.device),
-                                         torch.cumsum(qlens, 0).to(torch.int32)])
+            if is_prefill:
+                query_start_loc = torch.cat([torch.zeros(1, dtype=torch.int32, device=seq_lens.device),
+                                             torch.cumsum(seq_lens.to(torch.int32), 0).to(torch.int32)])
+            else:  # one query token per row
+                query_start_loc = torch.arange(seq_lens.shape[0] + 1, dtype=torch.int32, device=seq_lens.device)
         return AttentionMetadata(
             slot_mapping=slot_mapping, block_tables=block_tables, seq_lens=seq_lens,
             query_start_loc=query_start_loc,

@@ -180,6 +180,22 @@ __global__ void __launch_bounds__(256) append_scalar_kernel(AppendParams p) {
   }
 }
 
+// slot[i] = block_table[row(i), pos / bs] * bs + pos % bs; row(i) is the token's own row
+// (rectangular batches) or its clipped token_row_ids entry (packed batches).
+__global__ void __launch_bounds__(256)
+slot_mapping_kernel(const int32_t* positions, const int32_t* block_tables, const int32_t* token_row_ids,
+                    int n_rows, int n_cols, int table_rows, int table_width, int block_size,
+                    int32_t* slots) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n_rows * n_cols) return;
+  int row = token_row_ids ? token_row_ids[i] : i / n_cols;
+  row = row < 0 ? 0 : (row >= table_rows ? table_rows - 1 : row);
+  const int pos = positions[i];
+  int col = pos / block_size;
+  col = col < 0 ? 0 : (col >= table_width ? table_width - 1 : col);  // clamped like an XLA gather
+  slots[i] = block_tables[(long long)row * table_width + col] * block_size + pos % block_size;
+}
+
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 static int launch_append(const AppendParams& p, cudaStream_t stream) {
@@ -306,4 +322,20 @@ extern "C" int nvj_kv_append_nhd(const void* append_key, const void* append_valu
   p.src_dtype = src_dtype;
   p.dst_dtype = cache_dtype;
   return launch_append(p, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int nvj_compute_slot_mapping(const int32_t* positions, const int32_t* block_tables,
+                                        const int32_t* token_row_ids, int n_rows, int n_cols,
+                                        int table_rows, int table_width, int block_size,
+                                        int32_t* slot_mapping, nvj_stream_t stream) {
+  if (n_rows < 0 || n_cols < 0 || table_rows <= 0 || table_width <= 0 || block_size <= 0)
+    return NVJ_ERR_INVALID_ARGUMENT;
+  const long long n = (long long)n_rows * n_cols;
+  if (n == 0) return NVJ_OK;
+  if (n > 0x7fffffffLL) return NVJ_ERR_UNSUPPORTED;
+  if (!positions || !block_tables || !slot_mapping) return NVJ_ERR_INVALID_ARGUMENT;
+  nvj::slot_mapping_kernel<<<(unsigned)((n + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      positions, block_tables, token_row_ids, n_rows, n_cols, table_rows, table_width, block_size,
+      slot_mapping);
+  return cudaGetLastError() == cudaSuccess ? NVJ_OK : NVJ_ERR_LAUNCH;
 }

@@ -100,8 +100,8 @@ static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity
 
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
                                           volatile int* abort_flag, int32_t* status) {
-  if (*abort_flag) return false;
   if (mbar_try_wait(bar, parity)) return true;
+  if (*abort_flag) return false;
   return mbar_wait_slow(bar, parity, abort_flag, status);
 }
 

@@ -133,7 +133,7 @@ __device__ __forceinline__ void process_unit(const char* kt, const char* vt, int
     unpack8(kr, k2);
 #pragma unroll
     for (int h = 0; h < kG; ++h) {
-      float2 a = make_float2(st.q2[h][0].x * k2[0].x, st.q2[h][0].y * k2[0].y);
+      float2 a = fma2(st.q2[h][0], k2[0], make_float2(0.f, 0.f));
       a = fma2(st.q2[h][1], k2[1], a);
       a = fma2(st.q2[h][2], k2[2], a);
       a = fma2(st.q2[h][3], k2[3], a);
@@ -187,13 +187,27 @@ __device__ __forceinline__ void process_unit(const char* kt, const char* vt, int
   }
 }
 
-__device__ __forceinline__ long long cta_range_start(long long c, long long total, long long nctas) {
-  return c * total / nctas;
+// How the global block sequence [0, total) is cut into one contiguous range per CTA: CTA c
+// of n gets [c * total / n, (c + 1) * total / n).  With fewer blocks than CTAs only `total`
+// CTAs take part (one block each), so every CTA id inside a row's span delivers a partial.
+// (Giving the CTA that arrives first on an SM a larger share was measured and does not
+// help: the two CTAs of an SM share its bandwidth, so the SM finishes at the same time.)
+struct Partition {
+  long long total;
+  int n;
+
+  __device__ __forceinline__ long long start(int c) const { return (long long)c * total / n; }
+  // The CTA whose range holds global block g (the last CTA whose start is <= g).
+  __device__ __forceinline__ int cta_of(long long g) const { return (int)(((g + 1) * n - 1) / total); }
+};
+
+__device__ __forceinline__ Partition make_partition(long long total, int grid) {
+  Partition pt;
+  pt.total = total;
+  pt.n = total < grid ? (int)total : grid;
+  return pt;
 }
-// The CTA whose range holds global block g.
-__device__ __forceinline__ int cta_of_block(long long g, long long total, long long nctas) {
-  return (int)(((g + 1) * nctas - 1) / total);
-}
+
 // Where a CTA parks its partial result for a row it shares with other CTAs: a
 // CTA holds at most one segment that continues a row begun elsewhere (slot 2c)
 // and at most one that begins a row finished elsewhere (slot 2c + 1).
@@ -235,33 +249,6 @@ __device__ __forceinline__ void reset_state(WarpState& st) {
   st.l_part = 0.f;
 }
 
-// Fused append: the CTA that owns block min(pos / 16, nb - 1) of row s.b writes the
-// row's new K/V at positions[s.b] (one warp, 64 bytes per lane) before any bulk
-// copy of that block is issued.
-__device__ __forceinline__ void append_new_row(const DecodeParams& p, const Seg& s, int lane) {
-  const int pos = p.positions[s.b];
-  if (pos < 0) return;
-  const int jt = pos >> 4;
-  const int jw = jt < s.nb - 1 ? jt : s.nb - 1;
-  if (jw < s.j0 || jw >= s.j1) return;
-  const long long tgt = jt < p.table_width ? (long long)p.block_tables[decode_table_base(p, s.b) + jt] : -1;
-  if (tgt < 0 || tgt >= p.num_blocks) {
-    if (lane == 0) atomicOr(p.status, NVJ_DEV_BAD_BLOCK_ID);
-    return;
-  }
-  const long long dst = (tgt * kBlk + (pos & 15)) * kTokenBytes + lane * 32;
-  const char* sk = static_cast<const char*>(p.new_k) + (long long)s.b * kTokenBytes + lane * 32;
-  const char* sv = static_cast<const char*>(p.new_v) + (long long)s.b * kTokenBytes + lane * 32;
-  const uint4 k0 = *reinterpret_cast<const uint4*>(sk), k1 = *reinterpret_cast<const uint4*>(sk + 16);
-  const uint4 v0 = *reinterpret_cast<const uint4*>(sv), v1 = *reinterpret_cast<const uint4*>(sv + 16);
-  uint4* dk = reinterpret_cast<uint4*>(const_cast<char*>(p.k_cache) + dst);
-  uint4* dv = reinterpret_cast<uint4*>(const_cast<char*>(p.v_cache) + dst);
-  dk[0] = k0; dk[1] = k1;
-  dv[0] = v0; dv[1] = v1;
-  __threadfence();          // the row must be in L2 before the copy engine reads the block
-  fence_proxy_async_all();  // generic-proxy writes -> async-proxy (bulk copy) reads
-}
-
 // Look-ahead walker that fills the block-id ring.
 struct FillState {
   Seg s;
@@ -278,13 +265,11 @@ struct FillState {
 // separates it from the readers of the ring with CTA barriers.
 __device__ __forceinline__ void fill_ring(const DecodeParams& p, DecodeSmem& sm, FillState& f,
                                           long long g1, int n0, int count) {
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   while (count > 0) {
     if (!f.has || f.j >= f.s.j1) {
       if (!next_seg(p, f.b, f.jn, f.g, g1, f.s)) break;
       f.j = f.s.j0;
       f.has = true;
-      if (p.new_k && warp == (f.nsegs & (kConsumerWarps - 1))) append_new_row(p, f.s, lane);
       ++f.nsegs;
     }
     const int take = count < f.s.j1 - f.j ? count : f.s.j1 - f.j;
@@ -333,8 +318,7 @@ __device__ __forceinline__ void issue_block(const DecodeParams& p, DecodeSmem& s
 // output row (the segment covered the whole row) or this CTA's partial; the CTA
 // that delivers a row's last partial combines all of them.
 __device__ __forceinline__ void finish_segment(const DecodeParams& p, DecodeSmem& sm, const Seg& s,
-                                               WarpState& st, int warp, int lane, long long total,
-                                               int nctas) {
+                                               WarpState& st, int warp, int lane, const Partition& pt) {
   const int kvh = warp & 1;
   const int tid = warp * 32 + lane;
   // per-head sum of weights: add the four token positions
@@ -394,8 +378,8 @@ __device__ __forceinline__ void finish_segment(const DecodeParams& p, DecodeSmem
   if (whole_row) return;
   // ---- cross-CTA: count this partial in; the last arrival combines them all
   const long long row_g0 = s.g0 - s.j0;
-  const int c_lo = cta_of_block(row_g0, total, nctas);
-  const int c_hi = cta_of_block(row_g0 + s.nb - 1, total, nctas);
+  const int c_lo = pt.cta_of(row_g0);
+  const int c_hi = pt.cta_of(row_g0 + s.nb - 1);
   __threadfence();
   named_bar_sync(1, kConsumerThreads);
   if (tid == 0) {
@@ -405,22 +389,51 @@ __device__ __forceinline__ void finish_segment(const DecodeParams& p, DecodeSmem
   named_bar_sync(1, kConsumerThreads);
   if (!sm.is_last) return;
   __threadfence();
+  // Thread tid owns head_dim element tid of every head.  Parts are folded four at
+  // a time with all their loads (L2, never L1) issued together, so a merge costs
+  // about one memory round trip per four parts rather than one per value.
+  const int nparts = c_hi - c_lo + 1;
 #pragma unroll 1
-  for (int head = 0; head < kHq; ++head) {
-    float M = kNegBig;
-    for (int c = c_lo; c <= c_hi; ++c) {
-      const int sl = partial_slot(c, c == c_lo);
-      M = fmaxf(M, ld_cg_f32(p.part_ml + ((long long)sl * kHq + head) * 2));
+  for (int h0 = 0; h0 < kHq; h0 += 4) {
+    float M[4], L[4], o[4];
+#pragma unroll
+    for (int h = 0; h < 4; ++h) { M[h] = kNegBig; L[h] = 0.f; o[h] = 0.f; }
+#pragma unroll 1
+    for (int c0 = 0; c0 < nparts; c0 += 4) {
+      float2 e[4][4];
+      float a[4][4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int c = c_lo + c0 + i;
+        const bool ok = c <= c_hi;
+        const long long sl = partial_slot(ok ? c : c_lo, ok ? c == c_lo : true);
+#pragma unroll
+        for (int h = 0; h < 4; ++h) {
+          const long long row = sl * kHq + h0 + h;
+          e[h][i] = ok ? __ldcg(reinterpret_cast<const float2*>(p.part_ml + row * 2)) : make_float2(kNegBig, 0.f);
+          a[h][i] = ok ? __ldcg(p.part_acc + row * kD + tid) : 0.f;
+        }
+      }
+#pragma unroll
+      for (int h = 0; h < 4; ++h) {
+        float mx = M[h];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) mx = fmaxf(mx, e[h][i].x);
+        const float keep = ex2_approx(M[h] - mx);
+        L[h] *= keep;
+        o[h] *= keep;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float w = ex2_approx(e[h][i].x - mx);
+          L[h] = fmaf(e[h][i].y, w, L[h]);
+          o[h] = fmaf(a[h][i], w, o[h]);
+        }
+        M[h] = mx;
+      }
     }
-    float L = 0.f, o = 0.f;
-    for (int c = c_lo; c <= c_hi; ++c) {
-      const int sl = partial_slot(c, c == c_lo);
-      const float2 e = ld_cg_f32x2(p.part_ml + ((long long)sl * kHq + head) * 2);
-      const float w = ex2_approx(e.x - M);
-      L += e.y * w;
-      o += ld_cg_f32(p.part_acc + ((long long)sl * kHq + head) * kD + tid) * w;
-    }
-    p.out[((long long)s.b * kHq + head) * kD + tid] = L > 0.f ? o / L : 0.f;
+#pragma unroll
+    for (int h = 0; h < 4; ++h)
+      p.out[((long long)s.b * kHq + h0 + h) * kD + tid] = L[h] > 0.f ? o[h] / L[h] : 0.f;
   }
   if (tid == 0) p.counters[s.b] = 0;
 }
@@ -448,12 +461,10 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_pipelined_kernel(Dec
   int total = 0;
   cta_inclusive_scan(mine, sm.scan, total);
   if (total == 0) return;
-  // With fewer blocks than CTAs only the first `total` CTAs take part (one block
-  // each), so that every CTA id inside a row's span really delivers a partial.
-  const int nctas = total < grid ? total : grid;
-  if ((int)blockIdx.x >= nctas) return;
-  const long long g0 = cta_range_start(blockIdx.x, total, nctas);
-  const long long g1 = cta_range_start(blockIdx.x + 1, total, nctas);
+  const Partition pt = make_partition(total, grid);
+  if ((int)blockIdx.x >= pt.n) return;
+  const long long g0 = pt.start(blockIdx.x);
+  const long long g1 = pt.start(blockIdx.x + 1);
   if (g0 == g1) return;
   const int n_iters = (int)(g1 - g0);
 
@@ -496,6 +507,31 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_pipelined_kernel(Dec
   while (next_seg(p, b, j, g, g1, s)) {
     load_query(p, s.b, kvh, lane, st);
     reset_state(st);
+    // Fused append.  The CTA that owns block min(pos / 16, nb - 1) of the row writes the new
+    // K/V row; inside it the two warps (one per KV head) that handle the row's token group
+    // each store their 512-byte half.  The bulk copy of that block may race with the store,
+    // so the same warps overwrite the row in the staged tile from registers once the copy
+    // has landed: no fence is needed and nothing waits for the store.
+    int patch_j = -1, patch_t = 0;
+    if (p.new_k) {
+      const int pos = p.positions[s.b];
+      const int jt = pos >> 4;
+      const int jw = jt < s.nb - 1 ? jt : s.nb - 1;
+      if (pos >= 0 && jw >= s.j0 && jw < s.j1 && (warp >> 1) == ((pos & 15) >> 2)) {
+        const long long tgt = jt < p.table_width ? (long long)p.block_tables[decode_table_base(p, s.b) + jt] : -1;
+        if (tgt >= 0 && tgt < p.num_blocks) {
+          const long long src = (long long)s.b * kTokenBytes + kvh * kRowBytes + lane * 16;
+          const uint4 new_k16 = *reinterpret_cast<const uint4*>(static_cast<const char*>(p.new_k) + src);
+          const uint4 new_v16 = *reinterpret_cast<const uint4*>(static_cast<const char*>(p.new_v) + src);
+          const long long dst = (tgt * kBlk + (pos & 15)) * kTokenBytes + kvh * kRowBytes + lane * 16;
+          *reinterpret_cast<uint4*>(const_cast<char*>(p.k_cache) + dst) = new_k16;
+          *reinterpret_cast<uint4*>(const_cast<char*>(p.v_cache) + dst) = new_v16;
+          if (jt == jw && pos < s.len) { patch_j = jw; patch_t = pos & 3; }
+        } else if (lane == 0) {
+          atomicOr(p.status, NVJ_DEV_BAD_BLOCK_ID);
+        }
+      }
+    }
     for (int jb = s.j0; jb < s.j1; ++jb, ++it) {
       if ((it & (kRing / 2 - 1)) == 0 && it > 0) {
         // every thread is done with ring entries below `it`: refill the half behind us
@@ -507,8 +543,16 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_pipelined_kernel(Dec
       const int stage = it % kStages;
       mbar_wait(smem_u32(&sm.full_bar[stage]), (uint32_t)(it / kStages) & 1u, &sm.abort_flag, p.status);
       const int rows = sm.ring_rows[it & (kRing - 1)];
-      const char* kt = sm.tiles[stage][0] + tok0 * kTokenBytes + kvh * kRowBytes;
-      const char* vt = sm.tiles[stage][1] + tok0 * kTokenBytes + kvh * kRowBytes;
+      char* kt = sm.tiles[stage][0] + tok0 * kTokenBytes + kvh * kRowBytes;
+      char* vt = sm.tiles[stage][1] + tok0 * kTokenBytes + kvh * kRowBytes;
+      if (jb == patch_j) {  // only this warp reads these two rows of the tile; the source is cache-hot
+        const long long src = (long long)s.b * kTokenBytes + kvh * kRowBytes + lane * 16;
+        *reinterpret_cast<uint4*>(kt + patch_t * kTokenBytes + lane * 16) =
+            *reinterpret_cast<const uint4*>(static_cast<const char*>(p.new_k) + src);
+        *reinterpret_cast<uint4*>(vt + patch_t * kTokenBytes + lane * 16) =
+            *reinterpret_cast<const uint4*>(static_cast<const char*>(p.new_v) + src);
+        __syncwarp();
+      }
       float* pb = sm.pbuf[warp][it & 1];
       if (rows >= tok0 + 4) process_unit<false>(kt, vt, lane, 4, st, pb);
       else if (rows > tok0) process_unit<true>(kt, vt, lane, rows - tok0, st, pb);
@@ -520,7 +564,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_pipelined_kernel(Dec
       }
       __syncwarp();  // lane 0 may have waited for the other warps; reconverge before any CTA barrier
     }
-    finish_segment(p, sm, s, st, warp, lane, total, nctas);
+    finish_segment(p, sm, s, st, warp, lane, pt);
   }
   // Only after a timeout can copies still be in flight with nobody waiting for
   // them: hold the CTA's shared memory until they have landed.
@@ -552,10 +596,15 @@ int decode_num_ctas() {
 
 int launch_decode_pipelined(const DecodeParams& p, int num_ctas, cudaStream_t stream) {
   static_assert(sizeof(DecodeSmem) <= 113 * 1024, "two CTAs must fit one SM");
-  cudaError_t e = cudaFuncSetAttribute(decode_pipelined_kernel,
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       (int)sizeof(DecodeSmem));
-  if (e != cudaSuccess) return NVJ_ERR_LAUNCH;
+  static bool smem_opted_in[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return NVJ_ERR_LAUNCH;
+  if (!smem_opted_in[dev]) {
+    if (cudaFuncSetAttribute(decode_pipelined_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)sizeof(DecodeSmem)) != cudaSuccess)
+      return NVJ_ERR_LAUNCH;
+    smem_opted_in[dev] = true;
+  }
   decode_pipelined_kernel<<<num_ctas, kDecodeThreads, sizeof(DecodeSmem), stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? NVJ_OK : NVJ_ERR_LAUNCH;
 }

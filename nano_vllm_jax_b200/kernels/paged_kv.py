@@ -172,6 +172,30 @@ def _check_nhd_cache(k_cache: torch.Tensor, v_cache: torch.Tensor) -> None:
         raise ValueError("cache layer slices must be contiguous")
 
 
+# --------------------------------------------------------------------------- slot mapping
+
+def compute_slot_mapping(positions, block_table, block_size, token_row_ids=None):
+    """int32 slots for positions `[rows, cols]`; packed batches pass `token_row_ids` of the same shape."""
+    lib = _lib.load()
+    positions = _i32("positions", positions)
+    block_table = _i32("block_table", block_table)
+    if positions.ndim != 2 or block_table.ndim != 2:
+        raise ValueError("positions and block_table must be 2D")
+    rid = None
+    if token_row_ids is not None:
+        rid = _i32("token_row_ids", token_row_ids)
+        if rid.shape != positions.shape:
+            raise ValueError("positions and token_row_ids must have matching shapes")
+    elif positions.shape[0] > block_table.shape[0]:
+        raise ValueError("positions and block_tables batch dimensions must match")
+    out = torch.empty(positions.shape, dtype=torch.int32, device=positions.device)
+    check(lib.nvj_compute_slot_mapping(_ptr(positions), _ptr(block_table), _ptr(rid), positions.shape[0],
+                                       positions.shape[1], block_table.shape[0], block_table.shape[1],
+                                       int(block_size), _ptr(out), _stream(positions.device)),
+          "nvj_compute_slot_mapping")
+    return out
+
+
 # --------------------------------------------------------------------------- append
 
 def kv_append_slots(new_k, new_v, slot_mapping, k_cache_layer, v_cache_layer, *, valid_mask=None,

@@ -188,9 +188,7 @@ def _paged_layer(cache: torch.Tensor, layer_idx: int, block_size: int) -> torch.
 
 def compute_slot_mapping(positions, block_table, block_size, is_prefill: bool = True):
     """slot = block_table[b, pos // bs] * bs + pos % bs for positions `[B, T]` (kv_cache.py:410-446)."""
-    positions = positions.to(torch.int64)
-    blocks = torch.gather(block_table.to(torch.int64)[: positions.shape[0]], 1, positions // block_size)
-    return (blocks * block_size + positions % block_size).to(torch.int32)
+    return _k.compute_slot_mapping(positions.to(torch.int32), block_table.to(torch.int32), block_size)
 
 
 def compute_packed_slot_mapping(positions, block_table, token_row_ids, block_size):
@@ -201,10 +199,8 @@ def compute_packed_slot_mapping(positions, block_table, token_row_ids, block_siz
         raise ValueError("block_table must be a 2D tensor [batch, max_blocks_per_seq]")
     if block_size <= 0:
         raise ValueError("block_size must be positive")
-    rows = token_row_ids.to(torch.int64).clamp(0, block_table.shape[0] - 1)
-    pos = positions.to(torch.int64)
-    blocks = block_table.to(torch.int64)[rows, pos // block_size]
-    return (blocks * block_size + pos % block_size).to(torch.int32)
+    return _k.compute_slot_mapping(positions.to(torch.int32), block_table.to(torch.int32), block_size,
+                                   token_row_ids.to(torch.int32))
 
 
 def update_kv_cache(k_cache, v_cache, slot_mapping, new_k, new_v, layer_idx: int = 0, valid_mask=None):
