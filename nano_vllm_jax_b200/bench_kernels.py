@@ -1,0 +1,206 @@
+"""Per-kernel timings of the path on one GPU (one JSON line per kernel).
+
+    python -m nano_vllm_jax_b200.bench_kernels [--iters N]
+
+Every case uses seeded synthetic inputs with the shapes of the baseline
+configurations (append and decode: 256 rows, contexts U[1024, 4096]; prefill and
+block copy: 8 prompts U[64, 2048] in 512-token chunks with a shared 512-token
+prefix; GDN state: 18 layers x [16, 128, 128] fp32 + conv [6144, 4] bf16).
+Timing: CUDA events around each launch, an L2 flush (a 256 MiB write) before
+every timed launch of the small kernels, median over the iterations.  Bytes are
+the algorithmic minimum each kernel must move (stated per case).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+
+import numpy as np
+import torch
+
+from .engine.prefix_state import HybridStateTable, PrefixStateCache
+from .kernels import paged_kv as K
+
+BS, HQ, HKV, D = 16, 8, 2, 256
+SCALE = 1.0 / 16.0
+TOKEN_BYTES = 2 * HKV * D * 2
+NOMINAL_GBS, MEASURED_GBS = 8000.0, 6555.5
+
+
+def _randn_bf16(shape, seed, dev):
+    g = torch.Generator(device=dev).manual_seed(seed)
+    out = torch.empty(shape, dtype=torch.bfloat16, device=dev)
+    flat = out.view(-1)
+    step = 1 << 26
+    for i in range(0, flat.numel(), step):
+        part = flat[i:i + step]
+        part.copy_(torch.randn(part.shape, generator=g, device=dev))
+    return out
+
+
+class Timer:
+    def __init__(self, dev, iters, flush=True):
+        self.iters = iters
+        self.flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if flush else None
+
+    def run(self, fn, setup=None):
+        times = []
+        for i in range(self.iters + 3):
+            if setup is not None:
+                setup()
+            if self.flush is not None:
+                self.flush.zero_()
+            torch.cuda._sleep(300_000)  # keep the GPU busy while the host enqueues: the events then bracket only the kernel
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            if i >= 3:
+                times.append(e0.elapsed_time(e1) * 1e3)
+        return statistics.median(times)
+
+
+def report(name, us, nbytes, extra=None):
+    gbs = nbytes / us / 1e3
+    line = {"kernel": name, "us": round(us, 2), "algorithmic_bytes": int(nbytes), "GB/s": round(gbs, 1),
+            "pct_of_8TBs": round(100 * gbs / NOMINAL_GBS, 1), "pct_of_measured_copy": round(100 * gbs / MEASURED_GBS, 1)}
+    if extra:
+        line.update(extra)
+    print(json.dumps(line), flush=True)
+
+
+def tables_for(lens, pool, rng):
+    need = -(-lens // BS)
+    perm = rng.permutation(pool)
+    t = np.zeros((len(lens), int(need.max())), np.int32)
+    o = 0
+    for b in range(len(lens)):
+        t[b, :need[b]] = perm[o:o + need[b]]
+        o += need[b]
+    return t
+
+
+def decode_cases(dev, iters):
+    rng = np.random.default_rng(2)
+    rows, pool = 256, 400_000
+    ctx = rng.integers(1024, 4097, size=rows)
+    lens = (ctx + 1).astype(np.int32)
+    tables = torch.from_numpy(tables_for(lens, pool, rng)).to(dev)
+    k = _randn_bf16((1, pool, BS, HKV, D), 1, dev)
+    v = _randn_bf16((1, pool, BS, HKV, D), 2, dev)
+    q = _randn_bf16((rows, 1, HQ, D), 3, dev)
+    nk = _randn_bf16((rows, 1, HKV, D), 4, dev)
+    nv = _randn_bf16((rows, 1, HKV, D), 5, dev)
+    t_lens = torch.from_numpy(lens).to(dev)
+    pos = (t_lens - 1).view(rows, 1).contiguous()
+    slots = K.compute_slot_mapping(pos, tables, BS)
+    kv_bytes = int(lens.sum()) * TOKEN_BYTES
+    table_bytes = int((-(-lens // BS)).sum()) * 4
+    io = rows * HQ * D * 2 + rows * HQ * D * 4 + table_bytes + rows * 12
+    small = Timer(dev, iters)
+    big = Timer(dev, iters, flush=False)  # 1.3 GB of K/V per launch: far beyond L2
+    report("kv_append (decode step, 256 tokens)", small.run(lambda: K.kv_append_slots(nk, nv, slots, k[0], v[0])),
+           2 * rows * TOKEN_BYTES + rows * 4, {"workload": "c2"})
+    report("compute_slot_mapping (256 tokens)", small.run(lambda: K.compute_slot_mapping(pos, tables, BS)),
+           rows * 12, {"workload": "c2"})
+    report("paged_decode (pipelined)", big.run(lambda: K.paged_decode_attention(q[:, 0], k[0], v[0], tables, t_lens, SCALE, variant=2)),
+           kv_bytes + io, {"workload": "c2", "tok/s": None})
+    report("paged_decode + fused append (pipelined)",
+           big.run(lambda: K.paged_decode_attention_with_kv_append(q, nk, nv, k, v, tables, t_lens, pos, 0, BS, SCALE, 4, variant=2)),
+           kv_bytes + io + 2 * rows * TOKEN_BYTES, {"workload": "c2"})
+    sub = 16  # the generic kernel re-reads K/V once per query head: time a 16-row slice
+    report("paged_decode (generic kernel, 16 rows)",
+           Timer(dev, max(3, iters // 4), flush=False).run(
+               lambda: K.paged_decode_attention(q[:sub, 0], k[0], v[0], tables[:sub], t_lens[:sub], SCALE, variant=1)),
+           int(lens[:sub].sum()) * TOKEN_BYTES, {"workload": "c2, first 16 rows"})
+    K.check_device_status(dev)
+    del k, v
+
+
+def prefill_and_copy_cases(dev, iters):
+    rng = np.random.default_rng(3)
+    pool, chunk = 65_536, 512
+    prompts = rng.integers(64, 2049, size=8)
+    prompts[:4] = np.maximum(prompts[:4], 513)  # rows 0-3 share a 512-token prefix
+    k = _randn_bf16((6, pool, BS, HKV, D), 11, dev)
+    v = _randn_bf16((6, pool, BS, HKV, D), 12, dev)
+    tables_np = tables_for(prompts.astype(np.int32), pool, rng)
+    tables = torch.from_numpy(tables_np).to(dev)
+    # one representative packed chunk: 512 tokens over the rows that still have work after 512 tokens each
+    done = np.minimum(prompts, 512)
+    take, left = [], chunk
+    for r in range(8):
+        t = int(min(prompts[r] - done[r], left))
+        take.append(t)
+        left -= t
+    rows = [r for r in range(8) if take[r] > 0]
+    qsl = np.concatenate([[0], np.cumsum([take[r] for r in rows])]).astype(np.int32)
+    total = int(qsl[-1])
+    pos = np.zeros((1, chunk), np.int32)
+    rid = np.zeros((1, chunk), np.int32)
+    pos[0, :total] = np.concatenate([np.arange(done[r], done[r] + take[r]) for r in rows])
+    rid[0, :total] = np.repeat(np.arange(len(rows)), [take[r] for r in rows])
+    kv_lens = np.array([done[r] + take[r] for r in rows], np.int32)
+    t_tab = tables[torch.tensor(rows, device=dev)].contiguous()
+    t_pos, t_rid = torch.from_numpy(pos).to(dev), torch.from_numpy(rid).to(dev)
+    t_qsl, t_len = torch.from_numpy(qsl).to(dev), torch.from_numpy(kv_lens).to(dev)
+    q = _randn_bf16((1, chunk, HQ, D), 13, dev)
+    nk = _randn_bf16((1, chunk, HKV, D), 14, dev)
+    nv = _randn_bf16((1, chunk, HKV, D), 15, dev)
+    slots = K.compute_slot_mapping(t_pos, t_tab, BS, t_rid)
+    tm = Timer(dev, iters)
+    report("kv_append (packed prefill chunk, %d valid of 512 tokens)" % total,
+           tm.run(lambda: K.kv_append_slots(nk, nv, slots, k[0], v[0], query_start_loc=t_qsl, packed=True)),
+           2 * total * TOKEN_BYTES + chunk * 4, {"workload": "c3 chunk"})
+    visible = int(sum(int(pos[0, i]) + 1 for i in range(total)))
+    flops = 4 * HQ * D * visible
+    nbytes = total * TOKEN_BYTES * 2 + int(kv_lens.sum()) * TOKEN_BYTES + total * (HQ * D * 2 + HQ * D * 4)
+    us = tm.run(lambda: K.packed_paged_prefill_attention(q, k[0], v[0], t_tab, t_len, t_pos, t_qsl, BS, SCALE, 4))
+    report("packed prefill attention (%d tokens, %d rows)" % (total, len(rows)), us, nbytes,
+           {"workload": "c3 chunk", "TFLOP/s": round(flops / us / 1e6, 2), "flops": flops})
+    src = torch.from_numpy(tables_np[0, :32].copy()).to(dev)
+    used = set(tables_np.reshape(-1).tolist())
+    dst = torch.tensor([b for b in range(pool) if b not in used][:32], dtype=torch.int32, device=dev)
+    report("copy_blocks (32-block prefix, 6 layers, K and V)", tm.run(lambda: K.copy_blocks(k, v, src, dst)),
+           2 * 32 * 2 * BS * HKV * D * 2 * 6, {"workload": "c3 prefix"})
+    K.check_device_status(dev)
+    del k, v
+
+
+def hybrid_cases(dev, iters):
+    for n in (1, 8):
+        table = HybridStateTable((18, 6144, 4), (18, 16, 128, 128), max_slots=16, conv_dtype=torch.bfloat16, device=dev)
+        cache = PrefixStateCache(table, capacity=16)
+        ids = list(range(n))
+        for i in ids:
+            table.state(i).recurrent_state.normal_()
+        row = 18 * 16 * 128 * 128 * 4 + 18 * 6144 * 4 * 2
+        tm = Timer(dev, iters)
+        report("hybrid snapshot (%d sequences)" % n, tm.run(lambda: cache.snapshot(ids, [100 + i for i in ids])),
+               2 * n * row, {"workload": "c4 state", "note": "includes the host-side index upload"})
+        report("hybrid restore (%d sequences)" % n, tm.run(lambda: cache.restore(ids, [100 + i for i in ids])),
+               2 * n * row, {"workload": "c4 state", "note": "includes the host-side index upload"})
+        del table, cache
+    K.check_device_status(dev)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "hybrid"])
+    args = ap.parse_args()
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    if args.only in ("all", "decode"):
+        decode_cases(dev, args.iters)
+    if args.only in ("all", "prefill"):
+        prefill_and_copy_cases(dev, args.iters)
+    if args.only in ("all", "hybrid"):
+        hybrid_cases(dev, args.iters)
+
+
+if __name__ == "__main__":
+    main()

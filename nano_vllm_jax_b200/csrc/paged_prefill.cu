@@ -1,4 +1,5 @@
-// Ragged packed prefill attention over the paged cache: C ABI and dispatch.
+// Ragged packed prefill attention over the paged cache: C ABI and dispatch (tensor-core tile
+// kernel for the model's shape, the generic CUDA-core kernel for every other shape).
 //
 // Token i of table row r (query_start_loc[r] <= i < query_start_loc[r + 1]) sits
 // at absolute position positions[i] and attends keys p < kv_lens[r], p <=
@@ -7,6 +8,14 @@
 // nanovllm_jax/kernels/full_attention_triton.py:51-145,218-221).
 
 #include "paged_decode.cuh"
+
+namespace nvj {
+int launch_prefill_mma(const void* q, int q_dtype, const char* k_cache, const char* v_cache,
+                       long long num_blocks, const int32_t* block_tables, int table_width,
+                       const int32_t* kv_lens, const int32_t* positions, const int32_t* query_start_loc,
+                       int rows, int token_bucket, float scale, float* out, int32_t* status,
+                       cudaStream_t stream);
+}
 
 extern "C" int nvj_paged_prefill_packed(const void* q, int q_dtype, const void* k_cache_layer,
                                         const void* v_cache_layer, int kv_dtype,
@@ -26,6 +35,14 @@ extern "C" int nvj_paged_prefill_packed(const void* q, int q_dtype, const void* 
   if (!q || !k_cache_layer || !v_cache_layer || !block_tables || !kv_lens || !positions ||
       !query_start_loc || !out || !status)
     return NVJ_ERR_INVALID_ARGUMENT;
+  const bool a16 = ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_cache_layer) |
+                     reinterpret_cast<uintptr_t>(v_cache_layer) | reinterpret_cast<uintptr_t>(out)) & 15u) == 0;
+  if (kv_dtype == NVJ_BF16 && block_size == kBlk && num_kv_heads == kHkv && num_q_heads == kHq &&
+      head_dim == kD && (q_dtype == NVJ_BF16 || q_dtype == NVJ_F32) && a16)
+    return launch_prefill_mma(q, q_dtype, static_cast<const char*>(k_cache_layer),
+                              static_cast<const char*>(v_cache_layer), num_blocks, block_tables, table_width,
+                              kv_lens, positions, query_start_loc, rows, token_bucket, scale, out, status,
+                              static_cast<cudaStream_t>(stream));
   DecodeParams p{};
   p.q = q;
   p.k_cache = static_cast<const char*>(k_cache_layer);

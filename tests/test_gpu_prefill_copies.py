@@ -12,6 +12,9 @@ pytestmark = pytest.mark.gpu
 
 CONTRACT = 2e-2
 TIGHT = 2e-3
+# The tensor-core prefill kernel rounds the softmax weights to bf16 for the P x V product (as every
+# tensor-core flash kernel does); its regression bound is looser than the fp32 CUDA-core kernels' TIGHT.
+PREFILL_TC = 6e-3
 
 
 def test_packed_prefill_small_known_case():
@@ -68,7 +71,7 @@ def test_packed_prefill_ragged_chunk_with_cached_prefixes():
                                             to_torch(c["kv_lens"]), to_torch(c["pos"]), to_torch(c["rid"]),
                                             to_torch(c["qsl"]), BS, SCALE, 4, out_dtype=torch.float32)
     err = np.abs(to_numpy(out) - ref).max()
-    assert err <= CONTRACT and err <= TIGHT, err
+    assert err <= CONTRACT and err <= PREFILL_TC, err
     assert not to_numpy(out)[0, 256:].any()  # tokens beyond query_start_loc[-1] are padding
 
 
@@ -81,7 +84,7 @@ def test_mixed_batch_decode_rows_travel_the_packed_route():
     out = kv.paged_attention_prefill_packed(to_torch(c["q"]), to_torch(c["k"]), to_torch(c["v"]), to_torch(c["tables"]),
                                             to_torch(c["kv_lens"]), to_torch(c["pos"]), to_torch(c["rid"]),
                                             to_torch(c["qsl"]), BS, SCALE, 4, out_dtype=torch.float32)
-    assert np.abs(to_numpy(out) - ref).max() <= TIGHT
+    assert np.abs(to_numpy(out) - ref).max() <= PREFILL_TC
 
 
 def test_copy_blocks_bit_exact_all_layers():
