@@ -8,7 +8,7 @@
 // staged with 16-byte cp.async into a 2-stage ring, rows ordered [head][token] /
 // [kv head][key] and padded to 528 bytes so that ldmatrix is bank-conflict free.  Per tile: S = Q K^T (16 x 32 per warp),
 // mask p < kv_len and p <= position(token), online softmax in log2 units,
-// O += P V with P rounded to bf16.  Output fp32; tokens at or beyond
+// O += P V with P carried as two bf16 terms (hi + lo).  Output fp32; tokens at or beyond
 // query_start_loc[rows] are left at the zero the launcher wrote.
 // Semantics: nanovllm_jax/kv_cache.py:831-849 and
 // nanovllm_jax/kernels/full_attention_triton.py:51-145.
@@ -218,15 +218,21 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_mma_kernel(PrefillParam
     l_a *= al_a; l_b *= al_b;
 #pragma unroll
     for (int i = 0; i < 32; ++i) { o[i][0] *= al_a; o[i][1] *= al_a; o[i][2] *= al_b; o[i][3] *= al_b; }
-    uint32_t pa[2][4];
+    // The weights enter the P x V product as two bf16 terms, P = hi + lo with lo = bf16(P - hi):
+    // their sum carries 16 mantissa bits, so the product matches fp32 weights far inside the
+    // tolerance instead of losing bf16's 2^-9 per weight.
+    uint32_t pa[2][4], pl[2][4];
 #pragma unroll
     for (int nt = 0; nt < 4; ++nt) {
       const float p0 = ex2_approx(s[nt][0] - ms_a), p1 = ex2_approx(s[nt][1] - ms_a);
       const float p2 = ex2_approx(s[nt][2] - ms_b), p3 = ex2_approx(s[nt][3] - ms_b);
       l_a += p0 + p1;
       l_b += p2 + p3;
-      pa[nt >> 1][(nt & 1) * 2] = pack2_bf16(p0, p1);      // row g,   keys of this n-tile
-      pa[nt >> 1][(nt & 1) * 2 + 1] = pack2_bf16(p2, p3);  // row g+8
+      const __nv_bfloat162 h01 = __floats2bfloat162_rn(p0, p1), h23 = __floats2bfloat162_rn(p2, p3);
+      pa[nt >> 1][(nt & 1) * 2] = *reinterpret_cast<const uint32_t*>(&h01);      // row g,   keys of this n-tile
+      pa[nt >> 1][(nt & 1) * 2 + 1] = *reinterpret_cast<const uint32_t*>(&h23);  // row g+8
+      pl[nt >> 1][(nt & 1) * 2] = pack2_bf16(p0 - __low2float(h01), p1 - __high2float(h01));
+      pl[nt >> 1][(nt & 1) * 2 + 1] = pack2_bf16(p2 - __low2float(h23), p3 - __high2float(h23));
     }
     // ---- O += P V
 #pragma unroll
@@ -237,6 +243,8 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_mma_kernel(PrefillParam
         ldsm_x4_trans(b, smem_u32(&sm.v[stage][v_row + s2 * 16][v_col + dn * 32]));
         mma_bf16(o[2 * dn], pa[s2], b[0], b[1]);
         mma_bf16(o[2 * dn + 1], pa[s2], b[2], b[3]);
+        mma_bf16(o[2 * dn], pl[s2], b[0], b[1]);
+        mma_bf16(o[2 * dn + 1], pl[s2], b[2], b[3]);
       }
     }
     __syncthreads();  // the next iteration's prefetch overwrites this stage's neighbour only after everyone left it
