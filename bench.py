@@ -16,8 +16,8 @@ to the ranks (strong scaling).
 Prints ONE JSON line (rank 0).  `value` = rows per second over all ranks with the
 inputs resident in HBM; `e2e` = the same through the backend API from pinned host
 buffers, copies inside the timed region; `roofline` = algorithmic bytes of the
-fused append+decode kernel over its CUDA-event duration against the measured HBM
-copy peak; `cpu_baseline` = the CPU restatement of the reference path on a
+fused append+decode kernel over its CUDA-event duration (events around every
+launch of the timed region) against the measured HBM copy peak; `cpu_baseline` = the CPU restatement of the reference path on a
 bounded sample of the same rows.
 """
 
@@ -40,6 +40,10 @@ BS, HQ, HKV, D = 16, 8, 2, 256
 SCALE = 1.0 / 16.0
 TOKEN_BYTES = 2 * HKV * D * 2  # K + V row of one token, bf16
 FALLBACK_HBM_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum of decode_pipelined_kernel over its algorithmic bytes, from the
+# ncu capture of `--workload c2small` (profiles/decode_pipelined_c2small_ncu_full.md): 316-320 MB moved for
+# 311.2 MB algorithmic.  K/V traffic grows in proportion to the tokens read, so the ratio carries over to c2.
+DRAM_TRAFFIC_RATIO = 1.02
 
 WORKLOADS = {
     # name: (total rows at N=1 or overall, ctx_lo, ctx_hi, pool blocks per rank or None = sized to fit, scaling)
@@ -250,7 +254,7 @@ def run_b200(args, w):
     from nano_vllm_jax_b200.kv_cache import KVCacheStorage
 
     K_steps, W_steps = args.steps, max(args.warmup, 3)
-    n_passes = 3  # device-resident pass, kernel-only pass, end-to-end pass
+    n_passes = 2  # device-resident pass (also times every kernel launch), end-to-end pass
     total_steps = n_passes * (K_steps + W_steps) + 4
     ctx, tables_np, pool = make_rows(w, rank, world, total_steps)
     rows = len(ctx)
@@ -275,21 +279,21 @@ def run_b200(args, w):
     gathered = torch.empty(rows * world, dtype=torch.int32, device=dev) if world > 1 else None
     step_no = [0]
 
+    kernel_events = []  # (start, end) CUDA events around every fused append+decode launch of the timed passes
+
     def device_step():
         s = step_no[0]
         step_no[0] += 1
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
         out, _, _ = K.paged_decode_attention_with_kv_append(q, nk, nv, k_cache, v_cache, tables, all_len[s],
                                                             all_pos[s], 0, BS, SCALE, HQ // HKV)
+        e1.record()
+        kernel_events.append((s, e0, e1))
         tok = K.row_argmax(out.view(rows, HQ * D))
         if world > 1:
             dist.all_gather_into_tensor(gathered, tok)
         return tok
-
-    def kernel_only_step():
-        s = step_no[0]
-        step_no[0] += 1
-        K.paged_decode_attention_with_kv_append(q, nk, nv, k_cache, v_cache, tables, all_len[s], all_pos[s], 0, BS,
-                                                SCALE, HQ // HKV)
 
     # end-to-end: host (pinned) -> device inputs every step, result back to the host every step
     h_q, h_k, h_v = (t.cpu().pin_memory() for t in (q, nk, nv))
@@ -337,10 +341,8 @@ def run_b200(args, w):
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    first_step_of_kernel_pass = None
     ms_dev = timed(device_step)
-    first_step_of_kernel_pass = step_no[0] + W_steps
-    ms_kernel = timed(kernel_only_step)
+    timed_events = kernel_events[-K_steps:]  # the launches of the timed region (warm-up launches come first)
     ms_e2e = timed(e2e_step)
     clocks = sampler.stop() if rank == 0 else None
     K.check_device_status(dev)
@@ -352,10 +354,12 @@ def run_b200(args, w):
         total_rows = int(cnt.item())
 
     # roofline of the fused append+decode kernel: bytes of the timed launches over their duration
-    mid = first_step_of_kernel_pass + K_steps // 2
-    bytes_per_launch = algorithmic_bytes(ctx + mid + 1, rows)
+    kernel_ms = [e0.elapsed_time(e1) for _, e0, e1 in timed_events]
+    ms_kernel = sum(kernel_ms)
+    bytes_total = sum(algorithmic_bytes(ctx + s + 1, rows) for s, _, _ in timed_events)
+    bytes_per_launch = bytes_total // K_steps
     peak, peak_kind = measured_hbm_peak()
-    achieved = bytes_per_launch / (ms_kernel / K_steps * 1e-3) / 1e9
+    achieved = bytes_total / (ms_kernel * 1e-3) / 1e9
 
     cpu = None
     if rank == 0 and world == 1:
@@ -377,7 +381,8 @@ def run_b200(args, w):
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": peak_kind + " HBM copy bandwidth", "frac_of_8TBs_nominal": achieved / 8000.0,
                          "bytes_per_launch": bytes_per_launch, "us_per_launch": ms_kernel / K_steps * 1e3,
-                         "traffic": None},
+                         "traffic": DRAM_TRAFFIC_RATIO * bytes_per_launch,
+                         "traffic_source": "ncu dram bytes of the c2small capture scaled by algorithmic bytes (ratio 1.02)"},
             "cpu_baseline": cpu,
             "clocks": clocks,
         }

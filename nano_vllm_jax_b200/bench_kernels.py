@@ -170,6 +170,44 @@ def prefill_and_copy_cases(dev, iters):
     del k, v
 
 
+def mixed_step_case(dev, iters):
+    """The KV path of one mixed continuous-batching step over 6 layers: 32 decode rows (contexts in
+    [128, 2048]) plus 2 prefill chunks of 256 tokens, packed; per layer one append and one attention."""
+    from .backends import B200Backend
+    from .kv_cache import KVCacheStorage
+    rng = np.random.default_rng(4)
+    layers, pool = 6, 8192
+    ctx = rng.integers(128, 2049, size=32)
+    starts = np.concatenate([ctx - 1, [256, 0]])          # first position each row runs this step
+    qlens = np.array([1] * 32 + [256, 256])
+    kv_lens = (starts + qlens).astype(np.int32)
+    tables = torch.from_numpy(tables_for(kv_lens, pool, rng)).to(dev)
+    total = int(qlens.sum())
+    pos = torch.from_numpy(np.concatenate([np.arange(s, s + n) for s, n in zip(starts, qlens)]).astype(np.int32)[None]).to(dev)
+    rid = torch.from_numpy(np.repeat(np.arange(34), qlens).astype(np.int32)[None]).to(dev)
+    qsl = torch.from_numpy(np.concatenate([[0], np.cumsum(qlens)]).astype(np.int32)).to(dev)
+    t_len = torch.from_numpy(kv_lens).to(dev)
+    k = _randn_bf16((layers, pool, BS, HKV, D), 21, dev)
+    v = _randn_bf16((layers, pool, BS, HKV, D), 22, dev)
+    q = _randn_bf16((1, total, HQ, D), 23, dev)
+    nk = _randn_bf16((1, total, HKV, D), 24, dev)
+    nv = _randn_bf16((1, total, HKV, D), 25, dev)
+    be = B200Backend(device=dev)
+    cache = KVCacheStorage(k, v)
+    md = be.build_attention_metadata(pos, tables, t_len, BS, True, query_start_loc=qsl, token_row_ids=rid)
+
+    def step():
+        for layer in range(layers):
+            be.write_kv_and_attention(layer, q, nk, nv, cache, md, BS, SCALE, 4, True)
+
+    visible = int(sum(int(x) + 1 for x in pos[0].tolist()))
+    nbytes = layers * (2 * total * TOKEN_BYTES + int(kv_lens.sum()) * TOKEN_BYTES + total * (HQ * D * 2 + HQ * D * 4))
+    us = Timer(dev, iters).run(step)
+    report("mixed step KV path, 6 layers (32 decode rows + 2 x 256 prefill tokens, packed)", us, nbytes,
+           {"workload": "c4", "TFLOP/s": round(layers * 4 * HQ * D * visible / us / 1e6, 2), "launches": 3 * layers})
+    K.check_device_status(dev)
+
+
 def hybrid_cases(dev, iters):
     for n in (1, 8):
         table = HybridStateTable((18, 6144, 4), (18, 16, 128, 128), max_slots=16, conv_dtype=torch.bfloat16, device=dev)
@@ -190,7 +228,7 @@ def hybrid_cases(dev, iters):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--iters", type=int, default=20)
-    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "hybrid"])
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "hybrid", "mixed"])
     args = ap.parse_args()
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
@@ -200,6 +238,8 @@ def main():
         prefill_and_copy_cases(dev, args.iters)
     if args.only in ("all", "hybrid"):
         hybrid_cases(dev, args.iters)
+    if args.only in ("all", "mixed"):
+        mixed_step_case(dev, args.iters)
 
 
 if __name__ == "__main__":
