@@ -212,6 +212,10 @@ int nvj_paged_decode_static_scratch(const void* q, int q_dtype,
  *
  *   q          [token_bucket, num_q_heads, head_dim], q_dtype
  *   out        [token_bucket, num_q_heads, head_dim] float32
+ *   workspace  nullable decode workspace (nvj_paged_decode_workspace_bytes(rows)); when given,
+ *              rows that hold exactly one query token (the decode rows of a mixed batch,
+ *              nanovllm_jax/engine/scheduler.py:956-1032) are served by the pipelined decode
+ *              kernel instead of a 16-token tile
  */
 int nvj_paged_prefill_packed(const void* q, int q_dtype,
                              const void* k_cache_layer, const void* v_cache_layer, int kv_dtype,
@@ -221,7 +225,8 @@ int nvj_paged_prefill_packed(const void* q, int q_dtype,
                              const int32_t* kv_lens, const int32_t* positions,
                              const int32_t* query_start_loc, int rows,
                              int token_bucket, float scale,
-                             float* out, int32_t* status, nvj_stream_t stream);
+                             float* out, int32_t* status,
+                             void* workspace, size_t workspace_bytes, nvj_stream_t stream);
 
 /* ------------------------------------------------------------------ copies */
 

@@ -219,9 +219,10 @@ __device__ __forceinline__ void load_query(const DecodeParams& p, int b, int kvh
                                            WarpState& st) {
   const int hperm = (lane >> 1) & 3;
   const float c = p.scale * kLog2e;
+  const long long qi = decode_query_index(p, b);
 #pragma unroll
   for (int h = 0; h < kG; ++h) {
-    const long long off = ((long long)b * kHq + kvh * kG + (h ^ hperm)) * kD + lane * 8;
+    const long long off = (qi * kHq + kvh * kG + (h ^ hperm)) * kD + lane * 8;
     if (p.q_dtype == NVJ_BF16) {
       const uint4 w = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.q) + off);
       unpack8(w, st.q2[h]);
@@ -349,6 +350,7 @@ __device__ __forceinline__ void finish_segment(const DecodeParams& p, DecodeSmem
     if (warp < 2 && lane == 0) sm.ML[kvh][j] = make_float2(M, L);
   }
   const bool whole_row = (s.j0 == 0 && s.j1 == s.nb);
+  const long long out_row = decode_query_index(p, s.b);
   const int slot = partial_slot(blockIdx.x, s.j0 == 0);
   const int o_kvh = tid >> 7, o_d = (tid & 127) * 2;
 #pragma unroll
@@ -368,7 +370,7 @@ __device__ __forceinline__ void finish_segment(const DecodeParams& p, DecodeSmem
     const float2 MLv = sm.ML[o_kvh][j];
     if (whole_row) {
       const float inv = MLv.y > 0.f ? 1.f / MLv.y : 0.f;
-      *reinterpret_cast<float2*>(p.out + ((long long)s.b * kHq + head) * kD + o_d) = make_float2(o.x * inv, o.y * inv);
+      *reinterpret_cast<float2*>(p.out + (out_row * kHq + head) * kD + o_d) = make_float2(o.x * inv, o.y * inv);
     } else {
       *reinterpret_cast<float2*>(p.part_acc + ((long long)slot * kHq + head) * kD + o_d) = o;
       if (o_d == 0) *reinterpret_cast<float2*>(p.part_ml + ((long long)slot * kHq + head) * 2) = MLv;
@@ -433,7 +435,7 @@ __device__ __forceinline__ void finish_segment(const DecodeParams& p, DecodeSmem
     }
 #pragma unroll
     for (int h = 0; h < 4; ++h)
-      p.out[((long long)s.b * kHq + h0 + h) * kD + tid] = L[h] > 0.f ? o[h] / L[h] : 0.f;
+      p.out[(out_row * kHq + h0 + h) * kD + tid] = L[h] > 0.f ? o[h] / L[h] : 0.f;
   }
   if (tid == 0) p.counters[s.b] = 0;
 }
@@ -451,7 +453,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_pipelined_kernel(Dec
     int len = 0;
     if (b < p.batch) len = decode_row_len(p, b);
     mine += (len + kBlk - 1) / kBlk;
-    const unsigned idle = __ballot_sync(kFullMask, b < p.batch && len <= 0 && (b % grid) == (int)blockIdx.x);
+    const unsigned idle = __ballot_sync(kFullMask, !p.packed_rows && b < p.batch && len <= 0 && (b % grid) == (int)blockIdx.x);
     for (unsigned m = idle; m; m &= m - 1) {
       const int bb = base + (warp << 5) + (__ffs(m) - 1);
       float4* o = reinterpret_cast<float4*>(p.out + (long long)bb * kHq * kD);

@@ -35,6 +35,11 @@ struct DecodeParams {
   const int32_t* query_start_loc;
   const int32_t* query_positions;
   int qsl_rows;
+  // packed_rows != 0 (pipelined kernel inside a packed batch): `batch` counts table rows; a row
+  // takes part only if it holds exactly one query token, i = query_start_loc[b]; it reads q[i],
+  // writes out[i] and attends min(seq_lens[b], query_positions[i] + 1) keys.  Other rows are left
+  // alone (no zero fill): the prefill kernel owns them.
+  int packed_rows;
   float* out;
   // workspace
   int32_t* status;
@@ -56,6 +61,12 @@ struct DecodeParams {
 // Keys row b attends: seq_lens[b], clipped to what its page list can hold.
 __device__ __forceinline__ int decode_row_len(const DecodeParams& p, int b) {
   int len = p.seq_lens[b];
+  if (p.packed_rows) {
+    const int i = p.query_start_loc[b];
+    if (p.query_start_loc[b + 1] - i != 1) return 0;
+    const int cap = p.query_positions[i] + 1;
+    len = len < cap ? len : cap;
+  }
   int pages = p.table_width;
   if (p.kv_indptr) {
     pages = p.kv_indptr[b + 1] - p.kv_indptr[b];
@@ -70,6 +81,11 @@ __device__ __forceinline__ int decode_row_len(const DecodeParams& p, int b) {
     len = (int)cap;
   }
   return len < 0 ? 0 : len;
+}
+
+// Index of row b's query / output vector.
+__device__ __forceinline__ long long decode_query_index(const DecodeParams& p, int b) {
+  return p.packed_rows ? (long long)p.query_start_loc[b] : (long long)b;
 }
 
 __device__ __forceinline__ long long decode_table_base(const DecodeParams& p, int b) {

@@ -14,7 +14,7 @@ int launch_prefill_mma(const void* q, int q_dtype, const char* k_cache, const ch
                        long long num_blocks, const int32_t* block_tables, int table_width,
                        const int32_t* kv_lens, const int32_t* positions, const int32_t* query_start_loc,
                        int rows, int token_bucket, float scale, float* out, int32_t* status,
-                       cudaStream_t stream);
+                       int skip_single, cudaStream_t stream);
 }
 
 extern "C" int nvj_paged_prefill_packed(const void* q, int q_dtype, const void* k_cache_layer,
@@ -25,7 +25,8 @@ extern "C" int nvj_paged_prefill_packed(const void* q, int q_dtype, const void* 
                                         const int32_t* kv_lens, const int32_t* positions,
                                         const int32_t* query_start_loc, int rows,
                                         int token_bucket, float scale, float* out,
-                                        int32_t* status, nvj_stream_t stream) {
+                                        int32_t* status, void* workspace, size_t workspace_bytes,
+                                        nvj_stream_t stream) {
   using namespace nvj;
   if (rows < 0 || token_bucket < 0 || table_width < 0 || num_blocks < 0 || block_size <= 0 ||
       num_kv_heads <= 0 || num_q_heads <= 0 || head_dim <= 0)
@@ -38,11 +39,52 @@ extern "C" int nvj_paged_prefill_packed(const void* q, int q_dtype, const void* 
   const bool a16 = ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_cache_layer) |
                      reinterpret_cast<uintptr_t>(v_cache_layer) | reinterpret_cast<uintptr_t>(out)) & 15u) == 0;
   if (kv_dtype == NVJ_BF16 && block_size == kBlk && num_kv_heads == kHkv && num_q_heads == kHq &&
-      head_dim == kD && (q_dtype == NVJ_BF16 || q_dtype == NVJ_F32) && a16)
+      head_dim == kD && (q_dtype == NVJ_BF16 || q_dtype == NVJ_F32) && a16) {
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // Rows that carry a single query token (the decode rows of a mixed batch) go to the pipelined
+    // decode kernel when the caller lends it a decode workspace; everything else goes to the tile kernel.
+    int skip_single = 0;
+    const int num_ctas = decode_num_ctas();
+    const size_t need = ws_header_bytes(rows) + ws_ml_bytes(num_ctas) + ws_acc_bytes(num_ctas);
+    if (workspace && num_ctas > 0 && workspace_bytes >= need && rows > 0 &&
+        (reinterpret_cast<uintptr_t>(workspace) & 15u) == 0) {
+      if (cudaMemsetAsync(out, 0, sizeof(float) * (size_t)token_bucket * kHq * kD, s) != cudaSuccess)
+        return NVJ_ERR_LAUNCH;
+      char* w = static_cast<char*>(workspace);
+      DecodeParams d{};
+      d.q = q;
+      d.k_cache = static_cast<const char*>(k_cache_layer);
+      d.v_cache = static_cast<const char*>(v_cache_layer);
+      d.block_tables = block_tables;
+      d.seq_lens = kv_lens;
+      d.query_start_loc = query_start_loc;
+      d.query_positions = positions;
+      d.qsl_rows = rows;
+      d.packed_rows = 1;
+      d.out = out;
+      d.status = reinterpret_cast<int32_t*>(w);
+      d.counters = reinterpret_cast<int32_t*>(w + 64);
+      d.part_ml = reinterpret_cast<float*>(w + ws_header_bytes(rows));
+      d.part_acc = reinterpret_cast<float*>(w + ws_header_bytes(rows) + ws_ml_bytes(num_ctas));
+      d.num_blocks = num_blocks;
+      d.batch = rows;
+      d.table_width = table_width;
+      d.block_size = block_size;
+      d.num_kv_heads = num_kv_heads;
+      d.num_q_heads = num_q_heads;
+      d.head_dim = head_dim;
+      d.q_dtype = q_dtype;
+      d.kv_dtype = kv_dtype;
+      d.scale = scale;
+      const int rc = launch_decode_pipelined(d, num_ctas, s);
+      if (rc != NVJ_OK) return rc;
+      skip_single = 1;
+    }
     return launch_prefill_mma(q, q_dtype, static_cast<const char*>(k_cache_layer),
                               static_cast<const char*>(v_cache_layer), num_blocks, block_tables, table_width,
                               kv_lens, positions, query_start_loc, rows, token_bucket, scale, out, status,
-                              static_cast<cudaStream_t>(stream));
+                              skip_single, s);
+  }
   DecodeParams p{};
   p.q = q;
   p.k_cache = static_cast<const char*>(k_cache_layer);

@@ -35,6 +35,7 @@ struct PrefillParams {
   int32_t* status;
   long long num_blocks;
   int rows, token_bucket, table_width, q_dtype;
+  int skip_single;  // rows with exactly one query token are served by the decode kernel
   float scale;
 };
 
@@ -108,7 +109,8 @@ __global__ void __launch_bounds__(kPfThreads, 1) prefill_mma_kernel(PrefillParam
       const int lo = p.query_start_loc[r];
       int hi = p.query_start_loc[r + 1];
       hi = hi < p.token_bucket ? hi : p.token_bucket;
-      const int tiles = hi > lo ? (hi - lo + kPfTokens - 1) / kPfTokens : 0;
+      int tiles = hi > lo ? (hi - lo + kPfTokens - 1) / kPfTokens : 0;
+      if (p.skip_single && p.query_start_loc[r + 1] - lo == 1) tiles = 0;
       if (idx < tiles) {
         row = r;
         tok0 = lo + idx * kPfTokens;
@@ -272,7 +274,7 @@ int launch_prefill_mma(const void* q, int q_dtype, const char* k_cache, const ch
                        long long num_blocks, const int32_t* block_tables, int table_width,
                        const int32_t* kv_lens, const int32_t* positions, const int32_t* query_start_loc,
                        int rows, int token_bucket, float scale, float* out, int32_t* status,
-                       cudaStream_t stream) {
+                       int skip_single, cudaStream_t stream) {
   static bool opted_in[64];
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return NVJ_ERR_LAUNCH;
@@ -282,14 +284,16 @@ int launch_prefill_mma(const void* q, int q_dtype, const char* k_cache, const ch
       return NVJ_ERR_LAUNCH;
     opted_in[dev] = true;
   }
-  // padded tokens (and rows that see no key) are defined to be zero
-  if (cudaMemsetAsync(out, 0, sizeof(float) * (size_t)token_bucket * kHq * kD, stream) != cudaSuccess)
+  // padded tokens (and rows that see no key) are defined to be zero; with skip_single the caller
+  // has already cleared the output and the decode kernel has written the single-token rows
+  if (!skip_single &&
+      cudaMemsetAsync(out, 0, sizeof(float) * (size_t)token_bucket * kHq * kD, stream) != cudaSuccess)
     return NVJ_ERR_LAUNCH;
   PrefillParams p{};
   p.q = q; p.k_cache = k_cache; p.v_cache = v_cache; p.block_tables = block_tables; p.kv_lens = kv_lens;
   p.positions = positions; p.query_start_loc = query_start_loc; p.out = out; p.status = status;
   p.num_blocks = num_blocks; p.rows = rows; p.token_bucket = token_bucket; p.table_width = table_width;
-  p.q_dtype = q_dtype; p.scale = scale;
+  p.q_dtype = q_dtype; p.scale = scale; p.skip_single = skip_single;
   const int grid = (token_bucket + kPfTokens - 1) / kPfTokens + rows;
   prefill_mma_kernel<<<grid, kPfThreads, sizeof(PrefillSmem), stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? NVJ_OK : NVJ_ERR_LAUNCH;

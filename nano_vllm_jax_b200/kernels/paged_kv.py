@@ -472,13 +472,16 @@ def packed_paged_prefill_attention(query, k_cache_layer, v_cache_layer, block_ta
     if _poison():
         out.fill_(float("nan"))
     st = _status_word(q.device)
+    ws = _workspace(q.device, rows)
     rc = lib.nvj_paged_prefill_packed(_ptr(q), _dt(q), _ptr(k_cache_layer), _ptr(v_cache_layer),
                                       _dt(k_cache_layer), pages, page_size, hkv, d, hq, _ptr(block_table),
                                       block_table.shape[1], _ptr(kv_lens), _ptr(pos), _ptr(qsl), rows,
-                                      tokens, float(scale), _ptr(out), _ptr(st), _stream(q.device))
+                                      tokens, float(scale), _ptr(out), _ptr(st), _ptr(ws.buf), ws.nbytes,
+                                      _stream(q.device))
     check(rc, "nvj_paged_prefill_packed")
     if _strict():
         _check_word(st, "nvj_paged_prefill_packed")
+        _check_word(ws.status_tensor(), "nvj_paged_prefill_packed (decode rows)", ws)
     return out.reshape(1, tokens, hq * d)
 
 
