@@ -215,7 +215,11 @@ int nvj_paged_decode_static_scratch(const void* q, int q_dtype,
  *   workspace  nullable decode workspace (nvj_paged_decode_workspace_bytes(rows)); when given,
  *              rows that hold exactly one query token (the decode rows of a mixed batch,
  *              nanovllm_jax/engine/scheduler.py:956-1032) are served by the pipelined decode
- *              kernel instead of a 16-token tile
+ *              kernel instead of a query tile
+ *   variant    0 = automatic; 1 = generic CUDA-core kernel (any shape or dtype); for the model's
+ *              shape (bf16 cache, block 16, 2 KV x 4 query heads, head_dim 256): 2 = mma.sync
+ *              tiles of 16 tokens, 3 = tcgen05 tiles of 32 tokens with accumulators in tensor
+ *              memory.  NVJ_ERR_UNSUPPORTED when 2 or 3 is asked for another shape.
  */
 int nvj_paged_prefill_packed(const void* q, int q_dtype,
                              const void* k_cache_layer, const void* v_cache_layer, int kv_dtype,
@@ -226,7 +230,8 @@ int nvj_paged_prefill_packed(const void* q, int q_dtype,
                              const int32_t* query_start_loc, int rows,
                              int token_bucket, float scale,
                              float* out, int32_t* status,
-                             void* workspace, size_t workspace_bytes, nvj_stream_t stream);
+                             void* workspace, size_t workspace_bytes, int variant,
+                             nvj_stream_t stream);
 
 /* ------------------------------------------------------------------ copies */
 

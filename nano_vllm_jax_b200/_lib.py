@@ -45,7 +45,7 @@ SIGNATURES = {
     "nvj_paged_prefill_packed": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int64, c_int,
                                          c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p,
                                          c_void_p, c_int, c_int, c_float, c_void_p, c_void_p,
-                                         c_void_p, c_size_t, c_void_p]),
+                                         c_void_p, c_size_t, c_int, c_void_p]),
     "nvj_copy_blocks": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p,
                                 c_void_p, c_int, c_void_p, c_void_p]),
     "nvj_hybrid_snapshot": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int64,

@@ -1,5 +1,5 @@
 // Ragged packed prefill attention over the paged cache: C ABI and dispatch (tensor-core tile
-// kernel for the model's shape, the generic CUDA-core kernel for every other shape).
+// kernels, tcgen05 first and mma.sync second, for the model's shape, the generic CUDA-core kernel for every other shape).
 //
 // Token i of table row r (query_start_loc[r] <= i < query_start_loc[r + 1]) sits
 // at absolute position positions[i] and attends keys p < kv_lens[r], p <=
@@ -15,6 +15,11 @@ int launch_prefill_mma(const void* q, int q_dtype, const char* k_cache, const ch
                        const int32_t* kv_lens, const int32_t* positions, const int32_t* query_start_loc,
                        int rows, int token_bucket, float scale, float* out, int32_t* status,
                        int skip_single, cudaStream_t stream);
+int launch_prefill_umma(const void* q, int q_dtype, const char* k_cache, const char* v_cache,
+                        long long num_blocks, const int32_t* block_tables, int table_width,
+                        const int32_t* kv_lens, const int32_t* positions, const int32_t* query_start_loc,
+                        int rows, int token_bucket, float scale, float* out, int32_t* status,
+                        int skip_single, cudaStream_t stream);
 }
 
 extern "C" int nvj_paged_prefill_packed(const void* q, int q_dtype, const void* k_cache_layer,
@@ -26,20 +31,22 @@ extern "C" int nvj_paged_prefill_packed(const void* q, int q_dtype, const void* 
                                         const int32_t* query_start_loc, int rows,
                                         int token_bucket, float scale, float* out,
                                         int32_t* status, void* workspace, size_t workspace_bytes,
-                                        nvj_stream_t stream) {
+                                        int variant, nvj_stream_t stream) {
   using namespace nvj;
   if (rows < 0 || token_bucket < 0 || table_width < 0 || num_blocks < 0 || block_size <= 0 ||
       num_kv_heads <= 0 || num_q_heads <= 0 || head_dim <= 0)
     return NVJ_ERR_INVALID_ARGUMENT;
-  if (num_q_heads % num_kv_heads != 0) return NVJ_ERR_INVALID_ARGUMENT;
+  if (num_q_heads % num_kv_heads != 0 || variant < 0 || variant > 3) return NVJ_ERR_INVALID_ARGUMENT;
   if (token_bucket == 0) return NVJ_OK;
   if (!q || !k_cache_layer || !v_cache_layer || !block_tables || !kv_lens || !positions ||
       !query_start_loc || !out || !status)
     return NVJ_ERR_INVALID_ARGUMENT;
   const bool a16 = ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_cache_layer) |
                      reinterpret_cast<uintptr_t>(v_cache_layer) | reinterpret_cast<uintptr_t>(out)) & 15u) == 0;
-  if (kv_dtype == NVJ_BF16 && block_size == kBlk && num_kv_heads == kHkv && num_q_heads == kHq &&
-      head_dim == kD && (q_dtype == NVJ_BF16 || q_dtype == NVJ_F32) && a16) {
+  const bool tile_ok = kv_dtype == NVJ_BF16 && block_size == kBlk && num_kv_heads == kHkv && num_q_heads == kHq &&
+                       head_dim == kD && (q_dtype == NVJ_BF16 || q_dtype == NVJ_F32) && a16;
+  if (variant >= 2 && !tile_ok) return NVJ_ERR_UNSUPPORTED;
+  if (tile_ok && variant != 1) {
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     // Rows that carry a single query token (the decode rows of a mixed batch) go to the pipelined
     // decode kernel when the caller lends it a decode workspace; everything else goes to the tile kernel.
@@ -80,10 +87,15 @@ extern "C" int nvj_paged_prefill_packed(const void* q, int q_dtype, const void* 
       if (rc != NVJ_OK) return rc;
       skip_single = 1;
     }
-    return launch_prefill_mma(q, q_dtype, static_cast<const char*>(k_cache_layer),
-                              static_cast<const char*>(v_cache_layer), num_blocks, block_tables, table_width,
-                              kv_lens, positions, query_start_loc, rows, token_bucket, scale, out, status,
-                              skip_single, s);
+    const char* kc = static_cast<const char*>(k_cache_layer);
+    const char* vc = static_cast<const char*>(v_cache_layer);
+    if (variant != 2) {  // tcgen05 tiles first; they decline fp32 queries and batches under 32 tokens
+      const int rc = launch_prefill_umma(q, q_dtype, kc, vc, num_blocks, block_tables, table_width, kv_lens, positions,
+                                         query_start_loc, rows, token_bucket, scale, out, status, skip_single, s);
+      if (rc != NVJ_ERR_UNSUPPORTED || variant == 3) return rc;
+    }
+    return launch_prefill_mma(q, q_dtype, kc, vc, num_blocks, block_tables, table_width, kv_lens, positions,
+                              query_start_loc, rows, token_bucket, scale, out, status, skip_single, s);
   }
   DecodeParams p{};
   p.q = q;

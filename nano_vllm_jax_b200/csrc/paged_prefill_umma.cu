@@ -1,0 +1,478 @@
+// Ragged packed prefill attention on the 5th-generation tensor cores: tcgen05.mma with the
+// accumulators in tensor memory (TMEM) and operands staged by TMA, for the model's
+// full-attention shape (bf16 cache, 16-token blocks, 2 KV heads x 4 query heads, head_dim 256).
+//
+// One CTA = 32 consecutive query tokens of one table row x the 4 query heads of one KV head
+// = 128 query rows (UMMA M = 128, TMEM lane = row = head * 32 + token).  Keys are walked once,
+// in tiles of 64, through the row's block table.  Six warps, three roles:
+//   warp 0     producer: TMA tile loads (cp.async.bulk.tensor, 128-byte swizzle) of Q once and
+//              of K and V per key tile (one box of 16 keys x 64 dims per cache block and 64-dim
+//              chunk) into a 2-stage ring, completion on mbarriers;
+//   warp 1     one lane issues the MMAs: S(t+1) = Q K^T (M128 N64 K16 x 16) into one of two S
+//              buffers in TMEM while the softmax of tile t runs, then O += P(t) V(t)
+//              (M128 N256 K16 x 4, V read as an MN-major operand, P as two bf16 terms hi + lo);
+//              tcgen05.commit signals the barriers that free S, P and the K/V stage;
+//   warps 2-5  softmax: each thread owns one query row (tcgen05.ld of its TMEM lane), masks,
+//              keeps a running maximum that is only raised when a tile exceeds it by more than
+//              2^8 (then the warp rescales its 32 lanes of O in TMEM with tcgen05.ld/st, which is
+//              rare), writes P to swizzled shared memory; at the end O / l goes to global.
+// TMEM columns: S buffers at [0, 64) and [64, 128), O at [128, 384).
+// Shared-memory operands use the canonical 128-byte-swizzle layouts of the UMMA descriptors:
+// rows of 128 bytes (64 bf16), 16-byte chunk j of row r stored at chunk j ^ (r & 7), 8-row
+// groups 1024 bytes apart.  K and V tiles share one physical layout ([64-d chunk][key][128 B]);
+// only the descriptor says which dimension is contracted.
+// Rows of the cache that were never written must hold finite values (the allocator zero-fills):
+// a masked key has weight 0, and 0 x NaN would still poison the row.
+// Every wait is bounded; on a timeout the kernel flags NVJ_DEV_TIMEOUT, stops issuing, lets
+// copies in flight land, and still frees its TMEM.
+// Semantics: nanovllm_jax/kv_cache.py:831-849, nanovllm_jax/kernels/full_attention_triton.py:51-145.
+
+#include <cuda.h>
+
+#include "paged_decode.cuh"
+
+namespace nvj {
+
+constexpr int kUmTokens = 32;    // query tokens per CTA
+constexpr int kUmRows = 128;     // query rows = tokens x 4 heads
+constexpr int kUmKeys = 64;      // keys per tile
+constexpr int kUmThreads = 192;  // producer warp, MMA warp, 4 softmax warps
+constexpr int kUmSoftmaxThreads = 128;
+constexpr int kUmTmemCols = 512;
+constexpr int kUmColS = 0;       // two S accumulators: columns [0, 64) and [64, 128)
+constexpr int kUmColO = 128;     // O accumulator: columns [128, 384)
+constexpr uint32_t kUmTileBytes = kUmKeys * kRowBytes;  // one K (or V) tile of one KV head: 32 KiB
+constexpr float kUmLog2e = 1.4426950408889634f;
+constexpr float kUmRescaleGap = 8.f;  // log2 units a tile may exceed the running maximum before O is rescaled
+
+struct UmmaPrefillParams {
+  const int32_t* block_tables;
+  const int32_t* kv_lens;
+  const int32_t* positions;
+  const int32_t* query_start_loc;
+  float* out;
+  int32_t* status;
+  long long num_blocks;
+  int rows, token_bucket, table_width, skip_single;
+  float scale;
+};
+
+struct UmmaSmem {
+  alignas(1024) char q[4][kUmRows * 128];     // [64-d chunk][row][128 B], swizzled
+  alignas(1024) char k[2][4][kUmKeys * 128];  // [stage][64-d chunk][key][128 B]
+  alignas(1024) char v[2][4][kUmKeys * 128];
+  alignas(1024) char p_hi[kUmRows * 128];     // [row][64 keys]
+  alignas(1024) char p_lo[kUmRows * 128];
+  alignas(8) unsigned long long q_full, k_full[2], v_full[2], kv_empty[2], s_full[2], s_empty[2], p_full, p_empty;
+  uint32_t tmem_base;
+  int row, tok0, ntok, abort_flag;
+};
+
+// ---- tcgen05 / TMA wrappers ----------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// 32 consecutive 32-bit columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
+        "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])),
+        "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])),
+        "r"(__float_as_uint(v[11])), "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])),
+        "r"(__float_as_uint(v[15])), "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])),
+        "r"(__float_as_uint(v[19])), "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])),
+        "r"(__float_as_uint(v[23])), "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])),
+        "r"(__float_as_uint(v[27])), "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])),
+        "r"(__float_as_uint(v[31]))
+      : "memory");
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+// One box of a 3-D tensor map into shared memory; x is in elements and must be a multiple of 8 (16 bytes).
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(bar)
+      : "memory");
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle (layout type 2), descriptor version 1.
+// Offsets are in bytes; the 4 low bits are dropped by the encoding.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, uint32_t leading_bytes, uint32_t stride_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3ffffu) >> 4);
+  d |= (uint64_t)((leading_bytes >> 4) & 0x3fffu) << 16;
+  d |= (uint64_t)((stride_bytes >> 4) & 0x3fffu) << 32;
+  d |= (uint64_t)1 << 46;  // version
+  d |= (uint64_t)2 << 61;  // SWIZZLE_128B
+  return d;
+}
+// Instruction descriptor, kind::f16: fp32 accumulate, bf16 A and B, M = 128.
+__device__ __forceinline__ constexpr uint32_t umma_idesc(int n, bool b_mn_major) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) | ((128u >> 4) << 24);
+}
+
+// A bounded wait whose outcome is the same in every lane of the (converged) warp.
+__device__ __forceinline__ bool um_wait(unsigned long long* bar, uint32_t parity, int* abort_flag, int32_t* status) {
+  return __all_sync(0xffffffffu, mbar_wait(smem_u32(bar), parity, abort_flag, status));
+}
+
+__device__ __forceinline__ uint32_t swz(int row, int chunk) { return (uint32_t)(row * 128 + ((chunk ^ (row & 7)) << 4)); }
+
+// ---- warp 0: TMA loads ------------------------------------------------------------------------
+__device__ __forceinline__ void um_producer(const CUtensorMap* q_map, const CUtensorMap* k_map, const CUtensorMap* v_map,
+                                            const UmmaPrefillParams& p, UmmaSmem& sm, int row, int tok0, int kvh,
+                                            int kv_len, int n_tiles, int lane) {
+  if (lane == 0) {
+    const uint32_t bar = smem_u32(&sm.q_full);
+    mbar_arrive_expect_tx(bar, 4 * kUmRows * 128);
+    for (int c = 0; c < 4; ++c)
+      for (int h = 0; h < kG; ++h)
+        tma_load_3d(smem_u32(&sm.q[c][0]) + h * (kUmTokens * 128), q_map, c * 64, kvh * kG + h, tok0, bar);
+  }
+  const int need_blocks = (kv_len + kBlk - 1) / kBlk;
+  const int oob = (int)(p.num_blocks * kBlk);  // a box that starts here is filled with zeros
+  int ids = -1;
+  for (int t = 0; t < n_tiles; ++t) {
+    const int s = t & 1;
+    if ((t & 7) == 0) {  // block ids of the next 8 tiles, one per lane
+      const int bi = t * 4 + lane;
+      ids = -1;
+      if (bi < need_blocks && bi < p.table_width) {
+        ids = p.block_tables[(long long)row * p.table_width + bi];
+        if (ids < 0 || ids >= p.num_blocks) {
+          atomicOr(p.status, NVJ_DEV_BAD_BLOCK_ID);
+          ids = -1;
+        }
+      }
+    }
+    if (t >= 2 && !um_wait(&sm.kv_empty[s], ((t >> 1) & 1) ^ 1, &sm.abort_flag, p.status)) break;
+    int z[4];
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+      const int id = __shfl_sync(0xffffffffu, ids, (t & 7) * 4 + b);
+      z[b] = id >= 0 ? id * kBlk : oob;
+    }
+    if (lane == 0) {
+      const uint32_t kb = smem_u32(&sm.k_full[s]), vb = smem_u32(&sm.v_full[s]);
+      mbar_arrive_expect_tx(kb, kUmTileBytes);
+#pragma unroll
+      for (int b = 0; b < 4; ++b)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tma_load_3d(smem_u32(&sm.k[s][c][0]) + b * (kBlk * 128), k_map, c * 64, kvh, z[b], kb);
+      mbar_arrive_expect_tx(vb, kUmTileBytes);
+#pragma unroll
+      for (int b = 0; b < 4; ++b)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tma_load_3d(smem_u32(&sm.v[s][c][0]) + b * (kBlk * 128), v_map, c * 64, kvh, z[b], vb);
+    }
+    __syncwarp();
+  }
+}
+
+// ---- warp 1: MMA issue ----------------------------------------------------------------------
+__device__ __forceinline__ bool um_issue_s(UmmaSmem& sm, const UmmaPrefillParams& p, uint32_t tmem, int t, int lane) {
+  const int s = t & 1;
+  if (!um_wait(&sm.k_full[s], (t >> 1) & 1, &sm.abort_flag, p.status)) return false;
+  if (t >= 2 && !um_wait(&sm.s_empty[s], ((t >> 1) & 1) ^ 1, &sm.abort_flag, p.status)) return false;
+  tc_fence_after_sync();
+  if (lane == 0) {
+    const uint32_t q_base = smem_u32(&sm.q[0][0]), k_base = smem_u32(&sm.k[s][0][0]);
+    constexpr uint32_t idesc = umma_idesc(kUmKeys, false);
+#pragma unroll
+    for (int ks = 0; ks < 16; ++ks) {  // 16 dims per MMA: chunk ks / 4, 32 bytes into the swizzled row per step
+      const uint32_t off = (uint32_t)(ks & 3) * 32;
+      umma_bf16(tmem + kUmColS + s * kUmKeys, umma_desc(q_base + (ks >> 2) * (kUmRows * 128) + off, 16, 1024),
+                umma_desc(k_base + (ks >> 2) * (kUmKeys * 128) + off, 16, 1024), idesc, ks > 0 ? 1u : 0u);
+    }
+    umma_commit(smem_u32(&sm.s_full[s]));
+  }
+  __syncwarp();
+  return true;
+}
+
+__device__ __forceinline__ void um_mma_warp(UmmaSmem& sm, const UmmaPrefillParams& p, uint32_t tmem, int n_tiles, int lane) {
+  if (!um_wait(&sm.q_full, 0, &sm.abort_flag, p.status)) return;
+  if (!um_issue_s(sm, p, tmem, 0, lane)) return;
+  for (int t = 0; t < n_tiles; ++t) {
+    const int s = t & 1;
+    if (t + 1 < n_tiles && !um_issue_s(sm, p, tmem, t + 1, lane)) return;
+    if (!um_wait(&sm.v_full[s], (t >> 1) & 1, &sm.abort_flag, p.status)) return;
+    if (!um_wait(&sm.p_full, t & 1, &sm.abort_flag, p.status)) return;
+    tc_fence_after_sync();
+    if (lane == 0) {
+      const uint32_t v_base = smem_u32(&sm.v[s][0][0]), ph = smem_u32(sm.p_hi), pl = smem_u32(sm.p_lo);
+      constexpr uint32_t idesc = umma_idesc(kD, true);
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) {  // 16 keys per MMA: 32 bytes along P's rows, two 8-key groups of V
+        const uint64_t dv = umma_desc(v_base + kk * 2048, kUmKeys * 128, 1024);
+        umma_bf16(tmem + kUmColO, umma_desc(ph + kk * 32, 16, 1024), dv, idesc, (t > 0 || kk > 0) ? 1u : 0u);
+        umma_bf16(tmem + kUmColO, umma_desc(pl + kk * 32, 16, 1024), dv, idesc, 1u);
+      }
+      umma_commit(smem_u32(&sm.kv_empty[s]));
+      umma_commit(smem_u32(&sm.p_empty));
+    }
+    __syncwarp();
+  }
+}
+
+// ---- warps 2-5: softmax and epilogue -------------------------------------------------------
+__device__ __forceinline__ void um_softmax_warps(UmmaSmem& sm, const UmmaPrefillParams& p, uint32_t tmem, int tok0,
+                                                 int ntok, int kvh, int kv_len, int n_tiles, int warp, int lane) {
+  const int quarter = warp & 3;  // a warp may only touch TMEM lanes [32 * (warp % 4), +32)
+  const int r = quarter * 32 + lane, token = lane, hl = quarter;
+  const uint32_t my_tmem = tmem + ((uint32_t)(quarter * 32) << 16);
+  const int my_pos = token < ntok ? p.positions[tok0 + token] : -1;
+  const int last_key = my_pos < kv_len - 1 ? my_pos : kv_len - 1;  // last key this row may see
+  const float scale_log2 = p.scale * kUmLog2e;
+  float m_row = -INFINITY, l_row = 0.f;
+  bool ok = true;
+
+  for (int t = 0; t < n_tiles && ok; ++t) {
+    const int b = t & 1;
+    if (!um_wait(&sm.s_full[b], (t >> 1) & 1, &sm.abort_flag, p.status)) { ok = false; break; }
+    tc_fence_after_sync();
+    float s[64];
+    {
+      float t0[32], t1[32];
+      tmem_ld32(my_tmem + kUmColS + b * kUmKeys, t0);
+      tmem_ld32(my_tmem + kUmColS + b * kUmKeys + 32, t1);
+#pragma unroll
+      for (int i = 0; i < 32; ++i) { s[i] = t0[i]; s[32 + i] = t1[i]; }
+    }
+    tc_fence_before_sync();
+    mbar_arrive(smem_u32(&sm.s_empty[b]));
+    const int lim = last_key - t * kUmKeys;  // columns [0, lim] are visible
+    float tmax = -INFINITY;
+    if (lim >= kUmKeys - 1) {
+#pragma unroll
+      for (int i = 0; i < 64; ++i) { s[i] *= scale_log2; tmax = fmaxf(tmax, s[i]); }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 64; ++i) { s[i] = i <= lim ? s[i] * scale_log2 : -INFINITY; tmax = fmaxf(tmax, s[i]); }
+    }
+    if (t == 0) {
+      m_row = tmax;
+    } else if (__any_sync(0xffffffffu, tmax > m_row + kUmRescaleGap)) {
+      // rare: raise the maxima of this warp's rows and rescale their O, once the last P V has landed
+      if (!um_wait(&sm.p_empty, (t - 1) & 1, &sm.abort_flag, p.status)) { ok = false; break; }
+      tc_fence_after_sync();
+      const float m_new = fmaxf(m_row, tmax);
+      const float f = m_new == -INFINITY ? 1.f : ex2_approx(m_row - m_new);
+      m_row = m_new;
+      l_row *= f;
+#pragma unroll 1
+      for (int cc = 0; cc < kD / 32; ++cc) {
+        float o[32];
+        tmem_ld32(my_tmem + kUmColO + cc * 32, o);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[i] *= f;
+        tmem_st32(my_tmem + kUmColO + cc * 32, o);
+      }
+      tc_fence_before_sync();
+    }
+    const float m_safe = m_row == -INFINITY ? 0.f : m_row;
+    uint32_t hi[32], lo[32];
+#pragma unroll
+    for (int e = 0; e < 32; ++e) {
+      const float p0 = ex2_approx(s[2 * e] - m_safe), p1 = ex2_approx(s[2 * e + 1] - m_safe);
+      l_row += p0 + p1;
+      const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+      const __nv_bfloat162 g = __floats2bfloat162_rn(p0 - __low2float(h), p1 - __high2float(h));
+      hi[e] = *reinterpret_cast<const uint32_t*>(&h);
+      lo[e] = *reinterpret_cast<const uint32_t*>(&g);
+    }
+    // the P V product of the previous tile must have consumed P before it is overwritten
+    if (t >= 1 && !um_wait(&sm.p_empty, (t - 1) & 1, &sm.abort_flag, p.status)) { ok = false; break; }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      *reinterpret_cast<uint4*>(sm.p_hi + swz(r, j)) = make_uint4(hi[4 * j], hi[4 * j + 1], hi[4 * j + 2], hi[4 * j + 3]);
+      *reinterpret_cast<uint4*>(sm.p_lo + swz(r, j)) = make_uint4(lo[4 * j], lo[4 * j + 1], lo[4 * j + 2], lo[4 * j + 3]);
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    mbar_arrive(smem_u32(&sm.p_full));
+  }
+  if (!ok) return;
+  // ---- epilogue: O / l -> global
+  if (!um_wait(&sm.p_empty, (n_tiles - 1) & 1, &sm.abort_flag, p.status)) return;
+  tc_fence_after_sync();
+  const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
+  float* dst = p.out + ((long long)(tok0 + token) * kHq + kvh * kG + hl) * kD;
+#pragma unroll 1
+  for (int cc = 0; cc < kD / 32; ++cc) {
+    float o[32];
+    tmem_ld32(my_tmem + kUmColO + cc * 32, o);
+    if (token < ntok) {
+#pragma unroll
+      for (int i = 0; i < 32; i += 4)
+        *reinterpret_cast<float4*>(dst + cc * 32 + i) = make_float4(o[i] * inv, o[i + 1] * inv, o[i + 2] * inv, o[i + 3] * inv);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kUmThreads, 1)
+prefill_umma_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
+                    const __grid_constant__ CUtensorMap v_map, const UmmaPrefillParams p) {
+  extern __shared__ unsigned char um_smem_raw[];
+  UmmaSmem& sm = *reinterpret_cast<UmmaSmem*>((reinterpret_cast<uintptr_t>(um_smem_raw) + 1023) & ~(uintptr_t)1023);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kvh = blockIdx.y;
+
+  // ---- set-up: TMEM, barriers, which (table row, 32-token tile) this CTA serves
+  if (warp == 1) tmem_alloc(smem_u32(&sm.tmem_base), kUmTmemCols);
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&sm.q_full), 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(&sm.k_full[i]), 1);
+      mbar_init(smem_u32(&sm.v_full[i]), 1);
+      mbar_init(smem_u32(&sm.kv_empty[i]), 1);
+      mbar_init(smem_u32(&sm.s_full[i]), 1);
+      mbar_init(smem_u32(&sm.s_empty[i]), kUmSoftmaxThreads);
+    }
+    mbar_init(smem_u32(&sm.p_full), kUmSoftmaxThreads);
+    mbar_init(smem_u32(&sm.p_empty), 1);
+    mbar_fence_init();
+    sm.abort_flag = 0;
+    // heaviest tiles (the last tokens of a row see the most keys) get the lowest block indices
+    int idx = gridDim.x - 1 - blockIdx.x, row = -1, tok0 = 0, ntok = 0;
+    for (int r = 0; r < p.rows; ++r) {
+      const int lo = p.query_start_loc[r];
+      int hi = p.query_start_loc[r + 1];
+      hi = hi < p.token_bucket ? hi : p.token_bucket;
+      int tiles = hi > lo ? (hi - lo + kUmTokens - 1) / kUmTokens : 0;
+      if (p.skip_single && p.query_start_loc[r + 1] - lo == 1) tiles = 0;
+      if (idx < tiles) {
+        row = r;
+        tok0 = lo + idx * kUmTokens;
+        ntok = hi - tok0 < kUmTokens ? hi - tok0 : kUmTokens;
+        break;
+      }
+      idx -= tiles;
+    }
+    sm.row = row; sm.tok0 = tok0; sm.ntok = ntok;
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = sm.tmem_base;
+  const int row = sm.row, tok0 = sm.tok0, ntok = sm.ntok;
+
+  int kv_len = row >= 0 ? p.kv_lens[row] : 0;
+  if (kv_len > p.table_width * kBlk) {
+    if (threadIdx.x == 0) atomicOr(p.status, NVJ_DEV_BAD_LENGTH);
+    kv_len = p.table_width * kBlk;
+  }
+  // positions grow along a row's chunk: the tile's last token sees the most keys
+  const int max_pos = (row >= 0 && ntok > 0) ? p.positions[tok0 + ntok - 1] : -1;
+  const int key_end = kv_len < max_pos + 1 ? kv_len : max_pos + 1;
+  const int n_tiles = key_end > 0 ? (key_end + kUmKeys - 1) / kUmKeys : 0;
+
+  if (n_tiles > 0) {
+    if (warp == 0) um_producer(&q_map, &k_map, &v_map, p, sm, row, tok0, kvh, kv_len, n_tiles, lane);
+    else if (warp == 1) um_mma_warp(sm, p, tmem, n_tiles, lane);
+    else um_softmax_warps(sm, p, tmem, tok0, ntok, kvh, kv_len, n_tiles, warp, lane);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (sm.abort_flag) {  // give copies and MMAs in flight time to land before the CTA's memory is released
+    const unsigned long long t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) tmem_dealloc(tmem, kUmTmemCols);
+}
+
+typedef CUresult (*UmEncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static UmEncodeTiledFn um_encode_fn() {
+  static UmEncodeTiledFn fn = [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult res;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &res) != cudaSuccess ||
+        res != cudaDriverEntryPointSuccess)
+      ptr = nullptr;
+    return reinterpret_cast<UmEncodeTiledFn>(ptr);
+  }();
+  return fn;
+}
+
+// bf16 tensor [outer, mid, 256] (row pitch 512 B), boxes of [box_outer, 1, 64], 128-byte swizzle
+static bool um_make_map(CUtensorMap* map, const void* base, uint64_t mid, uint64_t outer, uint32_t box_outer) {
+  const cuuint64_t dims[3] = {(cuuint64_t)kD, mid, outer};
+  const cuuint64_t strides[2] = {(cuuint64_t)kRowBytes, (cuuint64_t)kRowBytes * mid};
+  const cuuint32_t box[3] = {64, 1, box_outer};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  return um_encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Returns NVJ_ERR_UNSUPPORTED when the driver offers no tensor-map encoder or the batch is too
+// small for a 32-token box; the caller then takes the mma.sync kernel.
+int launch_prefill_umma(const void* q, int q_dtype, const char* k_cache, const char* v_cache,
+                        long long num_blocks, const int32_t* block_tables, int table_width,
+                        const int32_t* kv_lens, const int32_t* positions, const int32_t* query_start_loc,
+                        int rows, int token_bucket, float scale, float* out, int32_t* status,
+                        int skip_single, cudaStream_t stream) {
+  static bool opted_in[64];
+  constexpr int kSmemBytes = (int)sizeof(UmmaSmem) + 1024;
+  if (q_dtype != NVJ_BF16 || token_bucket < kUmTokens || num_blocks < 1 || !um_encode_fn()) return NVJ_ERR_UNSUPPORTED;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return NVJ_ERR_LAUNCH;
+  if (!opted_in[dev]) {
+    if (cudaFuncSetAttribute(prefill_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
+      return NVJ_ERR_LAUNCH;
+    opted_in[dev] = true;
+  }
+  CUtensorMap q_map, k_map, v_map;
+  if (!um_make_map(&q_map, q, kHq, (uint64_t)token_bucket, kUmTokens) ||
+      !um_make_map(&k_map, k_cache, kHkv, (uint64_t)num_blocks * kBlk, kBlk) ||
+      !um_make_map(&v_map, v_cache, kHkv, (uint64_t)num_blocks * kBlk, kBlk))
+    return NVJ_ERR_UNSUPPORTED;
+  if (!skip_single &&
+      cudaMemsetAsync(out, 0, sizeof(float) * (size_t)token_bucket * kHq * kD, stream) != cudaSuccess)
+    return NVJ_ERR_LAUNCH;
+  UmmaPrefillParams p{};
+  p.block_tables = block_tables; p.kv_lens = kv_lens; p.positions = positions; p.query_start_loc = query_start_loc;
+  p.out = out; p.status = status; p.num_blocks = num_blocks; p.rows = rows; p.token_bucket = token_bucket;
+  p.table_width = table_width; p.skip_single = skip_single; p.scale = scale;
+  dim3 grid((token_bucket + kUmTokens - 1) / kUmTokens + rows, kHkv, 1);
+  prefill_umma_kernel<<<grid, kUmThreads, kSmemBytes, stream>>>(q_map, k_map, v_map, p);
+  return cudaGetLastError() == cudaSuccess ? NVJ_OK : NVJ_ERR_LAUNCH;
+}
+
+}  // namespace nvj

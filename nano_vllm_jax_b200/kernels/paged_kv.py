@@ -444,8 +444,12 @@ def paged_decode_attention_with_kv_append(query, new_k, new_v, k_cache, v_cache,
 
 def packed_paged_prefill_attention(query, k_cache_layer, v_cache_layer, block_table, kv_lens, positions,
                                    query_start_loc, block_size, scale, num_key_value_groups,
-                                   max_query_len=None):
-    """Ragged packed prefill: query `[1, T, Hq, D]` -> fp32 `[1, T, Hq*D]`, padded tokens 0."""
+                                   max_query_len=None, variant=None):
+    """Ragged packed prefill: query `[1, T, Hq, D]` -> fp32 `[1, T, Hq*D]`, padded tokens 0.
+
+    `variant`: 0 automatic, 1 generic, 2 mma.sync tiles, 3 tcgen05 tiles (default: the
+    `NVJ_PREFILL_VARIANT` environment variable, else 0).
+    """
     lib = _lib.load()
     _check_nhd_cache(k_cache_layer, v_cache_layer)
     if query.ndim != 4 or query.shape[0] != 1:
@@ -477,6 +481,7 @@ def packed_paged_prefill_attention(query, k_cache_layer, v_cache_layer, block_ta
                                       _dt(k_cache_layer), pages, page_size, hkv, d, hq, _ptr(block_table),
                                       block_table.shape[1], _ptr(kv_lens), _ptr(pos), _ptr(qsl), rows,
                                       tokens, float(scale), _ptr(out), _ptr(st), _ptr(ws.buf), ws.nbytes,
+                                      int(os.environ.get("NVJ_PREFILL_VARIANT", "0")) if variant is None else int(variant),
                                       _stream(q.device))
     check(rc, "nvj_paged_prefill_packed")
     if _strict():

@@ -75,6 +75,65 @@ def test_packed_prefill_ragged_chunk_with_cached_prefixes():
     assert not to_numpy(out)[0, 256:].any()  # tokens beyond query_start_loc[-1] are padding
 
 
+@pytest.mark.parametrize("variant", [1, 2, 3])
+@pytest.mark.parametrize("q_f32", [False, True])
+def test_packed_prefill_every_kernel_variant(variant, q_f32):
+    # 1 = CUDA-core kernel, 2 = mma.sync tiles, 3 = tcgen05 tiles; a 1-token row, a row that ends
+    # in the middle of a block, a row over several 64-key tiles with a cached prefix, and padding
+    from nano_vllm_jax_b200.kernels import paged_kv as K
+    c = _prefill_case(7 + variant, 500, [1, 330, 900, 45, 64], cached=[40, 0, 768, 0, 0], chunk=[1, 330, 132, 45, 64], bucket=608)
+    q = c["q"].astype(np.float32) if q_f32 else c["q"]
+    ref = R.paged_attention_prefill_packed(q, c["k"], c["v"], c["tables"], c["kv_lens"], c["pos"], c["rid"],
+                                           c["qsl"], BS, SCALE, 4)
+    args = (to_torch(q), to_torch(c["k"])[0], to_torch(c["v"])[0], to_torch(c["tables"]), to_torch(c["kv_lens"]),
+            to_torch(c["pos"]), to_torch(c["qsl"]), BS, SCALE, 4)
+    if variant == 3 and q_f32:  # the TMA path stages bf16 queries only; fp32 queries take variant 0 / 2
+        from nano_vllm_jax_b200._lib import NvjError
+        with pytest.raises(NvjError):
+            K.packed_paged_prefill_attention(*args, variant=3)
+        out = K.packed_paged_prefill_attention(*args, variant=0)
+    else:
+        out = K.packed_paged_prefill_attention(*args, variant=variant)
+    torch.cuda.synchronize()
+    err = np.abs(to_numpy(out) - ref).max()
+    assert err <= PREFILL_TC, err
+    assert not to_numpy(out)[0, 572:].any()
+
+
+@pytest.mark.parametrize("variant", [2, 3])
+def test_packed_prefill_scores_that_grow_along_the_sequence(variant):
+    # Keys get longer with their position, so later key tiles raise the row maxima by far more
+    # than 2^8: the tcgen05 kernel's deferred rescaling of O in tensor memory has to run.
+    from nano_vllm_jax_b200.kernels import paged_kv as K
+    c = _prefill_case(21, 300, [700, 200], cached=[256, 0], chunk=[444, 200], bucket=672)
+    k32 = c["k"].astype(np.float32)
+    for r in range(2):
+        for pos in range(int(c["kv_lens"][r])):
+            k32[0, c["tables"][r, pos // BS], pos % BS] *= 1.0 + pos / 40.0
+    c["k"] = k32.astype(bfloat16)
+    ref = R.paged_attention_prefill_packed(c["q"], c["k"], c["v"], c["tables"], c["kv_lens"], c["pos"], c["rid"],
+                                           c["qsl"], BS, SCALE, 4)
+    out = K.packed_paged_prefill_attention(to_torch(c["q"]), to_torch(c["k"])[0], to_torch(c["v"])[0], to_torch(c["tables"]),
+                                           to_torch(c["kv_lens"]), to_torch(c["pos"]), to_torch(c["qsl"]), BS, SCALE, 4,
+                                           variant=variant)
+    torch.cuda.synchronize()
+    err = np.abs(to_numpy(out) - ref).max()
+    assert err <= 5e-3, err  # near one-hot weights: the bound is that of a single bf16 V row
+
+
+def test_packed_prefill_tile_variants_refuse_other_shapes():
+    from nano_vllm_jax_b200.kernels import paged_kv as K
+    from nano_vllm_jax_b200._lib import NvjError
+    k = torch.zeros((8, 16, 2, 64), dtype=torch.bfloat16, device="cuda")
+    q = torch.zeros((1, 16, 8, 64), dtype=torch.bfloat16, device="cuda")
+    i32 = dict(dtype=torch.int32, device="cuda")
+    for variant in (2, 3):
+        with pytest.raises(NvjError):
+            K.packed_paged_prefill_attention(q, k, k, torch.zeros((1, 1), **i32), torch.tensor([16], **i32),
+                                             torch.arange(16, **i32)[None], torch.tensor([0, 16], **i32), BS, 0.125, 4,
+                                             variant=variant)
+
+
 def test_mixed_batch_decode_rows_travel_the_packed_route():
     # scheduler.py:956-1032: decode rows are 1-token rows of a packed prefill batch
     from nano_vllm_jax_b200 import kv_cache as kv
