@@ -120,13 +120,13 @@ def decode_cases(dev, iters):
     del k, v
 
 
-def prefill_and_copy_cases(dev, iters):
+def prefill_and_copy_cases(dev, iters, small=False):
     rng = np.random.default_rng(3)
-    pool, chunk = 65_536, 512
+    pool, chunk, layers = (4096, 512, 1) if small else (65_536, 512, 6)
     prompts = rng.integers(64, 2049, size=8)
     prompts[:4] = np.maximum(prompts[:4], 513)  # rows 0-3 share a 512-token prefix
-    k = _randn_bf16((6, pool, BS, HKV, D), 11, dev)
-    v = _randn_bf16((6, pool, BS, HKV, D), 12, dev)
+    k = _randn_bf16((layers, pool, BS, HKV, D), 11, dev)
+    v = _randn_bf16((layers, pool, BS, HKV, D), 12, dev)
     tables_np = tables_for(prompts.astype(np.int32), pool, rng)
     tables = torch.from_numpy(tables_np).to(dev)
     # one representative packed chunk: 512 tokens over the rows that still have work after 512 tokens each
@@ -165,7 +165,7 @@ def prefill_and_copy_cases(dev, iters):
                {"workload": "c3 chunk", "TFLOP/s": round(flops / us / 1e6, 2), "flops": flops})
     # one long prompt in a single chunk: 4096 tokens, nothing cached
     n_long = 4096
-    l_tab = torch.from_numpy(tables_np.reshape(-1)[:n_long // BS].reshape(1, -1).copy()).to(dev)
+    l_tab = torch.from_numpy(rng.permutation(pool)[:n_long // BS].astype(np.int32).reshape(1, -1)).to(dev)
     l_pos = torch.arange(n_long, dtype=torch.int32, device=dev)[None]
     l_qsl = torch.tensor([0, n_long], dtype=torch.int32, device=dev)
     l_len = torch.tensor([n_long], dtype=torch.int32, device=dev)
@@ -180,8 +180,8 @@ def prefill_and_copy_cases(dev, iters):
     src = torch.from_numpy(tables_np[0, :32].copy()).to(dev)
     used = set(tables_np.reshape(-1).tolist())
     dst = torch.tensor([b for b in range(pool) if b not in used][:32], dtype=torch.int32, device=dev)
-    report("copy_blocks (32-block prefix, 6 layers, K and V)", tm.run(lambda: K.copy_blocks(k, v, src, dst)),
-           2 * 32 * 2 * BS * HKV * D * 2 * 6, {"workload": "c3 prefix"})
+    report("copy_blocks (32-block prefix, %d layers, K and V)" % layers, tm.run(lambda: K.copy_blocks(k, v, src, dst)),
+           2 * 32 * 2 * BS * HKV * D * 2 * layers, {"workload": "c3 prefix"})
     K.check_device_status(dev)
     del k, v
 
@@ -245,13 +245,15 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "hybrid", "mixed"])
+    ap.add_argument("--small", action="store_true",
+                    help="prefill cases on a 1-layer, 4096-block cache (128 MiB): the size to run under a profiler")
     args = ap.parse_args()
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
     if args.only in ("all", "decode"):
         decode_cases(dev, args.iters)
     if args.only in ("all", "prefill"):
-        prefill_and_copy_cases(dev, args.iters)
+        prefill_and_copy_cases(dev, args.iters, small=args.small)
     if args.only in ("all", "hybrid"):
         hybrid_cases(dev, args.iters)
     if args.only in ("all", "mixed"):

@@ -89,7 +89,7 @@ extern "C" int nvj_paged_prefill_packed(const void* q, int q_dtype, const void* 
     }
     const char* kc = static_cast<const char*>(k_cache_layer);
     const char* vc = static_cast<const char*>(v_cache_layer);
-    if (variant != 2) {  // tcgen05 tiles first; they decline fp32 queries and batches under 32 tokens
+    if (variant != 2) {  // tcgen05 tiles first; they decline when the driver has no tensor-map encoder
       const int rc = launch_prefill_umma(q, q_dtype, kc, vc, num_blocks, block_tables, table_width, kv_lens, positions,
                                          query_start_loc, rows, token_bucket, scale, out, status, skip_single, s);
       if (rc != NVJ_ERR_UNSUPPORTED || variant == 3) return rc;

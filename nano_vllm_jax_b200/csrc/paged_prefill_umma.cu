@@ -1,26 +1,37 @@
-// Ragged packed prefill attention on the 5th-generation tensor cores: tcgen05.mma with the
-// accumulators in tensor memory (TMEM) and operands staged by TMA, for the model's
-// full-attention shape (bf16 cache, 16-token blocks, 2 KV heads x 4 query heads, head_dim 256).
+// Ragged packed prefill attention on the 5th-generation tensor cores: tcgen05.mma with both
+// accumulators and the left-hand operands (Q, P) in tensor memory (TMEM), K and V staged by TMA,
+// for the model's full-attention shape (bf16 cache, 16-token blocks, 2 KV heads x 4 query heads,
+// head_dim 256).
 //
 // One CTA = 32 consecutive query tokens of one table row x the 4 query heads of one KV head
 // = 128 query rows (UMMA M = 128, TMEM lane = row = head * 32 + token).  Keys are walked once,
-// in tiles of 64, through the row's block table.  Six warps, three roles:
-//   warp 0     producer: TMA tile loads (cp.async.bulk.tensor, 128-byte swizzle) of Q once and
-//              of K and V per key tile (one box of 16 keys x 64 dims per cache block and 64-dim
-//              chunk) into a 2-stage ring, completion on mbarriers;
-//   warp 1     one lane issues the MMAs: S(t+1) = Q K^T (M128 N64 K16 x 16) into one of two S
-//              buffers in TMEM while the softmax of tile t runs, then O += P(t) V(t)
-//              (M128 N256 K16 x 4, V read as an MN-major operand, P as two bf16 terms hi + lo);
-//              tcgen05.commit signals the barriers that free S, P and the K/V stage;
-//   warps 2-5  softmax: each thread owns one query row (tcgen05.ld of its TMEM lane), masks,
-//              keeps a running maximum that is only raised when a tile exceeds it by more than
-//              2^8 (then the warp rescales its 32 lanes of O in TMEM with tcgen05.ld/st, which is
-//              rare), writes P to swizzled shared memory; at the end O / l goes to global.
-// TMEM columns: S buffers at [0, 64) and [64, 128), O at [128, 384).
+// in tiles of 64, through the row's block table.  Ten warps, three roles:
+//   warp 0     producer: TMA tile loads (cp.async.bulk.tensor, 128-byte swizzle) of K and V per
+//              key tile (one box of 16 keys x 64 dims per cache block and 64-dim chunk) into
+//              3-stage rings; a K stage is released when its S product retires, a V stage when
+//              its P V product does;
+//   warp 1     one elected lane issues the MMAs: S(t) = Q K(t)^T (M128 N64 K16 x 16, A = Q from
+//              TMEM) into one of two S buffers, and O += P(t) V(t) (M128 N256 K16 x 4, A = P
+//              from TMEM as two bf16 terms hi + lo, V read as an MN-major operand); S(t + 2) is
+//              issued as soon as P V (t) has retired, so it overlaps the softmax of tile t + 1;
+//   warps 2-9  two threads per query row (a warp may only touch TMEM lanes 32 * (warp % 4) ..
+//              + 31, so the two halves of a row's columns sit in warps w and w + 4).  They stage
+//              Q into TMEM once (global -> registers -> tcgen05.st), then per tile read S
+//              (tcgen05.ld), mask, exchange half maxima through shared memory, and write
+//              P = exp2(S - m) over the S columns they came from.  The running maximum m is
+//              only raised when a tile exceeds it by more than 2^8; then the warp rescales its
+//              lanes of O in TMEM (tcgen05.ld/st), which is rare.  At the end O / l -> global.
+// TMEM columns: Q [0, 128) (two bf16 per column), S/P buffers [128, 192) and [192, 256),
+// O [256, 512).
 // Shared-memory operands use the canonical 128-byte-swizzle layouts of the UMMA descriptors:
 // rows of 128 bytes (64 bf16), 16-byte chunk j of row r stored at chunk j ^ (r & 7), 8-row
 // groups 1024 bytes apart.  K and V tiles share one physical layout ([64-d chunk][key][128 B]);
 // only the descriptor says which dimension is contracted.
+// What bounds it: every 64-key tile costs 64 KiB of L2 -> shared memory traffic per CTA for
+// 12.6 MFLOP of tensor work; an SM takes in about 20-30 bytes per clock through TMA, so a tile
+// takes ~2850 cycles while its MMAs need ~1540.
+// mbarrier parity waits can only tell two consecutive phases apart: every waiter here observes
+// every phase of the barriers it uses, in order.
 // Rows of the cache that were never written must hold finite values (the allocator zero-fills):
 // a masked key has weight 0, and 0 x NaN would still poison the row.
 // Every wait is bounded; on a timeout the kernel flags NVJ_DEV_TIMEOUT, stops issuing, lets
@@ -36,16 +47,19 @@ namespace nvj {
 constexpr int kUmTokens = 32;    // query tokens per CTA
 constexpr int kUmRows = 128;     // query rows = tokens x 4 heads
 constexpr int kUmKeys = 64;      // keys per tile
-constexpr int kUmThreads = 192;  // producer warp, MMA warp, 4 softmax warps
-constexpr int kUmSoftmaxThreads = 128;
+constexpr int kUmStages = 3;     // K and V tiles in flight
+constexpr int kUmThreads = 320;  // producer warp, MMA warp, 8 softmax warps
+constexpr int kUmSoftmaxThreads = 256;
 constexpr int kUmTmemCols = 512;
-constexpr int kUmColS = 0;       // two S accumulators: columns [0, 64) and [64, 128)
-constexpr int kUmColO = 128;     // O accumulator: columns [128, 384)
+constexpr int kUmColQ = 0;       // Q as the A operand: 256 bf16 per row = 128 columns
+constexpr int kUmColS = 128;     // two S accumulators of 64 columns; P (hi: 32 columns, lo: 32) overwrites its S
+constexpr int kUmColO = 256;     // O accumulator: columns [256, 512)
 constexpr uint32_t kUmTileBytes = kUmKeys * kRowBytes;  // one K (or V) tile of one KV head: 32 KiB
 constexpr float kUmLog2e = 1.4426950408889634f;
 constexpr float kUmRescaleGap = 8.f;  // log2 units a tile may exceed the running maximum before O is rescaled
 
 struct UmmaPrefillParams {
+  const void* q;
   const int32_t* block_tables;
   const int32_t* kv_lens;
   const int32_t* positions;
@@ -53,17 +67,16 @@ struct UmmaPrefillParams {
   float* out;
   int32_t* status;
   long long num_blocks;
-  int rows, token_bucket, table_width, skip_single;
+  int rows, token_bucket, table_width, skip_single, q_dtype;
   float scale;
 };
 
 struct UmmaSmem {
-  alignas(1024) char q[4][kUmRows * 128];     // [64-d chunk][row][128 B], swizzled
-  alignas(1024) char k[2][4][kUmKeys * 128];  // [stage][64-d chunk][key][128 B]
-  alignas(1024) char v[2][4][kUmKeys * 128];
-  alignas(1024) char p_hi[kUmRows * 128];     // [row][64 keys]
-  alignas(1024) char p_lo[kUmRows * 128];
-  alignas(8) unsigned long long q_full, k_full[2], v_full[2], kv_empty[2], s_full[2], s_empty[2], p_full, p_empty;
+  alignas(1024) char k[kUmStages][4][kUmKeys * 128];  // [stage][64-d chunk][key][128 B], swizzled
+  alignas(1024) char v[kUmStages][4][kUmKeys * 128];
+  alignas(8) unsigned long long q_full, k_full[kUmStages], v_full[kUmStages], k_empty[kUmStages], v_empty[kUmStages],
+      s_full[2], p_full, pv_done, x_full;
+  float xchg[2][2][kUmRows];  // [tile parity][column half][row]: half maxima, at the end half sums
   uint32_t tmem_base;
   int row, tok0, ntok, abort_flag;
 };
@@ -78,11 +91,13 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
 }
 __device__ __forceinline__ void tc_fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+// D[128 x N] (+)= A[128 x 16] B[16 x N]: A in tensor memory (row = lane, two bf16 of K per 32-bit
+// column), B through a shared-memory descriptor
+__device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
       "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
       : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
@@ -120,6 +135,15 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) 
       : "memory");
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
+// 16 consecutive 32-bit columns; the caller issues tmem_st_wait() before it signals anyone
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+        "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 // One box of a 3-D tensor map into shared memory; x is in elements and must be a multiple of 8 (16 bytes).
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
   asm volatile(
@@ -144,29 +168,57 @@ __device__ __forceinline__ constexpr uint32_t umma_idesc(int n, bool b_mn_major)
   return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) | ((128u >> 4) << 24);
 }
 
+// try_wait that lets the hardware park the warp for up to `hint_ns` until the phase completes:
+// a warp that polls in a tight loop would take issue slots from the MMA warp on its scheduler.
+__device__ __forceinline__ bool um_try_wait_parked(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+static __device__ __noinline__ bool um_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag, int32_t* status) {
+  const unsigned long long t0 = global_timer_ns();
+  for (;;) {
+    if (um_try_wait_parked(bar, parity, 4000u)) return true;
+    if (*abort_flag) return false;
+    if (global_timer_ns() - t0 > kWaitLimitNs) {
+      *abort_flag = 1;
+      if (status) atomicOr(status, NVJ_DEV_TIMEOUT);
+      return false;
+    }
+  }
+}
 // A bounded wait whose outcome is the same in every lane of the (converged) warp.
 __device__ __forceinline__ bool um_wait(unsigned long long* bar, uint32_t parity, int* abort_flag, int32_t* status) {
-  return __all_sync(0xffffffffu, mbar_wait(smem_u32(bar), parity, abort_flag, status));
+  const uint32_t b = smem_u32(bar);
+  bool ok = mbar_try_wait(b, parity);
+  if (!ok) ok = um_wait_slow(b, parity, abort_flag, status);
+  return __all_sync(0xffffffffu, ok);
 }
 
-__device__ __forceinline__ uint32_t swz(int row, int chunk) { return (uint32_t)(row * 128 + ((chunk ^ (row & 7)) << 4)); }
+// One lane of a converged warp (the lowest); unlike a comparison with the lane index this keeps
+// the code that follows eligible for the uniform datapath the MMA instructions are issued from.
+__device__ __forceinline__ bool um_elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.u32 %0, 1, 0, P;\n\t}" : "=r"(pred));
+  return pred != 0;
+}
+
 
 // ---- warp 0: TMA loads ------------------------------------------------------------------------
-__device__ __forceinline__ void um_producer(const CUtensorMap* q_map, const CUtensorMap* k_map, const CUtensorMap* v_map,
-                                            const UmmaPrefillParams& p, UmmaSmem& sm, int row, int tok0, int kvh,
-                                            int kv_len, int n_tiles, int lane) {
-  if (lane == 0) {
-    const uint32_t bar = smem_u32(&sm.q_full);
-    mbar_arrive_expect_tx(bar, 4 * kUmRows * 128);
-    for (int c = 0; c < 4; ++c)
-      for (int h = 0; h < kG; ++h)
-        tma_load_3d(smem_u32(&sm.q[c][0]) + h * (kUmTokens * 128), q_map, c * 64, kvh * kG + h, tok0, bar);
-  }
+__device__ __forceinline__ void um_producer(const CUtensorMap* k_map, const CUtensorMap* v_map, const UmmaPrefillParams& p,
+                                            UmmaSmem& sm, int row, int kvh, int kv_len, int n_tiles, int lane) {
   const int need_blocks = (kv_len + kBlk - 1) / kBlk;
   const int oob = (int)(p.num_blocks * kBlk);  // a box that starts here is filled with zeros
   int ids = -1;
   for (int t = 0; t < n_tiles; ++t) {
-    const int s = t & 1;
+    const int s = t % kUmStages;
+    const uint32_t reuse_parity = ((t / kUmStages) - 1) & 1;  // phase in which the stage's previous tile (t - 3) released it
     if ((t & 7) == 0) {  // block ids of the next 8 tiles, one per lane
       const int bi = t * 4 + lane;
       ids = -1;
@@ -178,20 +230,25 @@ __device__ __forceinline__ void um_producer(const CUtensorMap* q_map, const CUte
         }
       }
     }
-    if (t >= 2 && !um_wait(&sm.kv_empty[s], ((t >> 1) & 1) ^ 1, &sm.abort_flag, p.status)) break;
     int z[4];
 #pragma unroll
     for (int b = 0; b < 4; ++b) {
       const int id = __shfl_sync(0xffffffffu, ids, (t & 7) * 4 + b);
       z[b] = id >= 0 ? id * kBlk : oob;
     }
+    // K is released as soon as S(t - 3) has been computed, V only after P V (t - 3)
+    if (t >= kUmStages && !um_wait(&sm.k_empty[s], reuse_parity, &sm.abort_flag, p.status)) break;
     if (lane == 0) {
-      const uint32_t kb = smem_u32(&sm.k_full[s]), vb = smem_u32(&sm.v_full[s]);
+      const uint32_t kb = smem_u32(&sm.k_full[s]);
       mbar_arrive_expect_tx(kb, kUmTileBytes);
 #pragma unroll
       for (int b = 0; b < 4; ++b)
 #pragma unroll
         for (int c = 0; c < 4; ++c) tma_load_3d(smem_u32(&sm.k[s][c][0]) + b * (kBlk * 128), k_map, c * 64, kvh, z[b], kb);
+    }
+    if (t >= kUmStages && !um_wait(&sm.v_empty[s], reuse_parity, &sm.abort_flag, p.status)) break;
+    if (lane == 0) {
+      const uint32_t vb = smem_u32(&sm.v_full[s]);
       mbar_arrive_expect_tx(vb, kUmTileBytes);
 #pragma unroll
       for (int b = 0; b < 4; ++b)
@@ -203,137 +260,186 @@ __device__ __forceinline__ void um_producer(const CUtensorMap* q_map, const CUte
 }
 
 // ---- warp 1: MMA issue ----------------------------------------------------------------------
-__device__ __forceinline__ bool um_issue_s(UmmaSmem& sm, const UmmaPrefillParams& p, uint32_t tmem, int t, int lane) {
-  const int s = t & 1;
-  if (!um_wait(&sm.k_full[s], (t >> 1) & 1, &sm.abort_flag, p.status)) return false;
-  if (t >= 2 && !um_wait(&sm.s_empty[s], ((t >> 1) & 1) ^ 1, &sm.abort_flag, p.status)) return false;
+// One lane issues everything.
+// Descriptors are built once; stepping through a tile only adds to the 14-bit start-address field
+// (shared-memory addresses are below 256 KiB, so the sum never carries out of the field).
+__device__ __forceinline__ bool um_issue_s(UmmaSmem& sm, const UmmaPrefillParams& p, uint32_t tmem, uint64_t k_desc0, int t,
+                                           int stage, uint32_t full_parity, int lane) {
+  if (!um_wait(&sm.k_full[stage], full_parity, &sm.abort_flag, p.status)) return false;
   tc_fence_after_sync();
-  if (lane == 0) {
-    const uint32_t q_base = smem_u32(&sm.q[0][0]), k_base = smem_u32(&sm.k[s][0][0]);
+  if (um_elect_one()) {
     constexpr uint32_t idesc = umma_idesc(kUmKeys, false);
+    const uint64_t k_desc = k_desc0 + (uint64_t)((stage * 4 * kUmKeys * 128) >> 4);
+    const uint32_t d = tmem + kUmColS + (t & 1) * kUmKeys;
 #pragma unroll
-    for (int ks = 0; ks < 16; ++ks) {  // 16 dims per MMA: chunk ks / 4, 32 bytes into the swizzled row per step
-      const uint32_t off = (uint32_t)(ks & 3) * 32;
-      umma_bf16(tmem + kUmColS + s * kUmKeys, umma_desc(q_base + (ks >> 2) * (kUmRows * 128) + off, 16, 1024),
-                umma_desc(k_base + (ks >> 2) * (kUmKeys * 128) + off, 16, 1024), idesc, ks > 0 ? 1u : 0u);
-    }
-    umma_commit(smem_u32(&sm.s_full[s]));
+    for (int ks = 0; ks < 16; ++ks)  // 16 dims per MMA: 8 columns of Q; K chunk ks / 4, 32 bytes into its swizzled rows
+      umma_bf16_ts(d, tmem + kUmColQ + ks * 8, k_desc + (uint64_t)(((ks >> 2) * (kUmKeys * 128) + (ks & 3) * 32) >> 4), idesc,
+                   ks > 0 ? 1u : 0u);
+    umma_commit(smem_u32(&sm.s_full[t & 1]));
+    umma_commit(smem_u32(&sm.k_empty[stage]));
   }
   __syncwarp();
   return true;
 }
 
 __device__ __forceinline__ void um_mma_warp(UmmaSmem& sm, const UmmaPrefillParams& p, uint32_t tmem, int n_tiles, int lane) {
+  const uint64_t k_desc0 = umma_desc(smem_u32(&sm.k[0][0][0]), 16, 1024);
+  const uint64_t v_desc0 = umma_desc(smem_u32(&sm.v[0][0][0]), kUmKeys * 128, 1024);
   if (!um_wait(&sm.q_full, 0, &sm.abort_flag, p.status)) return;
-  if (!um_issue_s(sm, p, tmem, 0, lane)) return;
+  if (!um_issue_s(sm, p, tmem, k_desc0, 0, 0, 0, lane)) return;
+  if (n_tiles > 1 && !um_issue_s(sm, p, tmem, k_desc0, 1, 1, 0, lane)) return;
+  int sv = 0, sk = 2 % kUmStages;      // stage of V(t) and of K(t + 2)
+  uint32_t pv = 0, pk = 2 / kUmStages;  // parities of their full barriers
   for (int t = 0; t < n_tiles; ++t) {
-    const int s = t & 1;
-    if (t + 1 < n_tiles && !um_issue_s(sm, p, tmem, t + 1, lane)) return;
-    if (!um_wait(&sm.v_full[s], (t >> 1) & 1, &sm.abort_flag, p.status)) return;
+    if (!um_wait(&sm.v_full[sv], pv, &sm.abort_flag, p.status)) return;
     if (!um_wait(&sm.p_full, t & 1, &sm.abort_flag, p.status)) return;
     tc_fence_after_sync();
-    if (lane == 0) {
-      const uint32_t v_base = smem_u32(&sm.v[s][0][0]), ph = smem_u32(sm.p_hi), pl = smem_u32(sm.p_lo);
+    if (um_elect_one()) {
       constexpr uint32_t idesc = umma_idesc(kD, true);
+      const uint64_t v_desc = v_desc0 + (uint64_t)((sv * 4 * kUmKeys * 128) >> 4);
+      const uint32_t pa = tmem + kUmColS + (t & 1) * kUmKeys;
 #pragma unroll
-      for (int kk = 0; kk < 4; ++kk) {  // 16 keys per MMA: 32 bytes along P's rows, two 8-key groups of V
-        const uint64_t dv = umma_desc(v_base + kk * 2048, kUmKeys * 128, 1024);
-        umma_bf16(tmem + kUmColO, umma_desc(ph + kk * 32, 16, 1024), dv, idesc, (t > 0 || kk > 0) ? 1u : 0u);
-        umma_bf16(tmem + kUmColO, umma_desc(pl + kk * 32, 16, 1024), dv, idesc, 1u);
+      for (int kk = 0; kk < 4; ++kk) {  // 16 keys per MMA: 8 columns of P, two 8-key groups of V
+        const uint64_t dv = v_desc + (uint64_t)((kk * 2048) >> 4);
+        umma_bf16_ts(tmem + kUmColO, pa + kk * 8, dv, idesc, (t > 0 || kk > 0) ? 1u : 0u);
+        umma_bf16_ts(tmem + kUmColO, pa + 32 + kk * 8, dv, idesc, 1u);
       }
-      umma_commit(smem_u32(&sm.kv_empty[s]));
-      umma_commit(smem_u32(&sm.p_empty));
+      umma_commit(smem_u32(&sm.v_empty[sv]));
+      umma_commit(smem_u32(&sm.pv_done));
     }
     __syncwarp();
+    // S(t + 2) overwrites the columns P V (t) reads P(t) from; MMAs of different shapes are not
+    // ordered against each other, so wait for P V (t) to retire first
+    if (t + 2 < n_tiles) {
+      if (!um_wait(&sm.pv_done, t & 1, &sm.abort_flag, p.status)) return;
+      if (!um_issue_s(sm, p, tmem, k_desc0, t + 2, sk, pk, lane)) return;
+    }
+    if (++sv == kUmStages) { sv = 0; pv ^= 1u; }
+    if (++sk == kUmStages) { sk = 0; pk ^= 1u; }
   }
 }
 
-// ---- warps 2-5: softmax and epilogue -------------------------------------------------------
+// ---- warps 2-9: Q staging, softmax, epilogue ------------------------------------------------
+// Two threads per query row: warp w works on TMEM lanes [32 * (w % 4), +32) (the only ones it may
+// touch) and on half (w - 2) / 4 of the columns.  The halves exchange their tile maxima through
+// shared memory so that both keep the same running maximum.
 __device__ __forceinline__ void um_softmax_warps(UmmaSmem& sm, const UmmaPrefillParams& p, uint32_t tmem, int tok0,
                                                  int ntok, int kvh, int kv_len, int n_tiles, int warp, int lane) {
-  const int quarter = warp & 3;  // a warp may only touch TMEM lanes [32 * (warp % 4), +32)
+  const int quarter = warp & 3, half = (warp - 2) >> 2;
   const int r = quarter * 32 + lane, token = lane, hl = quarter;
   const uint32_t my_tmem = tmem + ((uint32_t)(quarter * 32) << 16);
+  // ---- this row's half of Q (128 dims) -> 64 TMEM columns, two bf16 per column
+  {
+    const long long qrow = ((long long)(tok0 + token) * kHq + kvh * kG + hl) * kD + half * (kD / 2);
+#pragma unroll 1
+    for (int part = 0; part < 4; ++part) {  // 32 dims = 16 columns at a time
+      uint32_t w[16];
+      if (token >= ntok) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) w[i] = 0u;
+      } else if (p.q_dtype == NVJ_BF16) {
+        const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.q) + qrow + part * 32);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const uint4 u = ld_nc_u4(src + i);
+          w[4 * i] = u.x; w[4 * i + 1] = u.y; w[4 * i + 2] = u.z; w[4 * i + 3] = u.w;
+        }
+      } else {
+        const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(p.q) + qrow + part * 32);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float4 f = src[i];
+          const __nv_bfloat162 a = __floats2bfloat162_rn(f.x, f.y), b2 = __floats2bfloat162_rn(f.z, f.w);
+          w[2 * i] = *reinterpret_cast<const uint32_t*>(&a);
+          w[2 * i + 1] = *reinterpret_cast<const uint32_t*>(&b2);
+        }
+      }
+      tmem_st16(my_tmem + kUmColQ + half * 64 + part * 16, w);
+    }
+    tmem_st_wait();
+    tc_fence_before_sync();
+    mbar_arrive(smem_u32(&sm.q_full));
+  }
   const int my_pos = token < ntok ? p.positions[tok0 + token] : -1;
   const int last_key = my_pos < kv_len - 1 ? my_pos : kv_len - 1;  // last key this row may see
   const float scale_log2 = p.scale * kUmLog2e;
-  float m_row = -INFINITY, l_row = 0.f;
-  bool ok = true;
+  float m_row = -INFINITY, l_row = 0.f;  // m_row in units of log2(e) * scale, the same in both halves
 
-  for (int t = 0; t < n_tiles && ok; ++t) {
+  for (int t = 0; t < n_tiles; ++t) {
     const int b = t & 1;
-    if (!um_wait(&sm.s_full[b], (t >> 1) & 1, &sm.abort_flag, p.status)) { ok = false; break; }
+    const uint32_t s_tmem = my_tmem + kUmColS + b * kUmKeys;
+    if (!um_wait(&sm.s_full[b], (t >> 1) & 1, &sm.abort_flag, p.status)) return;
     tc_fence_after_sync();
-    float s[64];
-    {
-      float t0[32], t1[32];
-      tmem_ld32(my_tmem + kUmColS + b * kUmKeys, t0);
-      tmem_ld32(my_tmem + kUmColS + b * kUmKeys + 32, t1);
+    float s[32];
+    tmem_ld32(s_tmem + half * 32, s);
+    const int lim = last_key - t * kUmKeys - half * 32;  // columns [0, lim] of this half are visible
+    float hmax = -INFINITY;
+    if (lim >= 31) {
 #pragma unroll
-      for (int i = 0; i < 32; ++i) { s[i] = t0[i]; s[32 + i] = t1[i]; }
-    }
-    tc_fence_before_sync();
-    mbar_arrive(smem_u32(&sm.s_empty[b]));
-    const int lim = last_key - t * kUmKeys;  // columns [0, lim] are visible
-    float tmax = -INFINITY;
-    if (lim >= kUmKeys - 1) {
-#pragma unroll
-      for (int i = 0; i < 64; ++i) { s[i] *= scale_log2; tmax = fmaxf(tmax, s[i]); }
+      for (int i = 0; i < 32; i += 2) hmax = fmaxf(hmax, fmaxf(s[i], s[i + 1]));
     } else {
 #pragma unroll
-      for (int i = 0; i < 64; ++i) { s[i] = i <= lim ? s[i] * scale_log2 : -INFINITY; tmax = fmaxf(tmax, s[i]); }
+      for (int i = 0; i < 32; ++i) { s[i] = i <= lim ? s[i] : -INFINITY; hmax = fmaxf(hmax, s[i]); }
     }
+    sm.xchg[b][half][r] = hmax;
+    mbar_arrive(smem_u32(&sm.x_full));  // release; the bounded wait below acquires the partner's value
+    if (!um_wait(&sm.x_full, t & 1, &sm.abort_flag, p.status)) return;
+    // from here on both halves have read their S columns: P may overwrite them
+    const float tmax = fmaxf(hmax, sm.xchg[b][half ^ 1][r]) * scale_log2;  // scale > 0
     if (t == 0) {
       m_row = tmax;
     } else if (__any_sync(0xffffffffu, tmax > m_row + kUmRescaleGap)) {
       // rare: raise the maxima of this warp's rows and rescale their O, once the last P V has landed
-      if (!um_wait(&sm.p_empty, (t - 1) & 1, &sm.abort_flag, p.status)) { ok = false; break; }
+      if (!um_wait(&sm.pv_done, (t - 1) & 1, &sm.abort_flag, p.status)) return;
       tc_fence_after_sync();
       const float m_new = fmaxf(m_row, tmax);
       const float f = m_new == -INFINITY ? 1.f : ex2_approx(m_row - m_new);
       m_row = m_new;
       l_row *= f;
 #pragma unroll 1
-      for (int cc = 0; cc < kD / 32; ++cc) {
+      for (int cc = 0; cc < kD / 64; ++cc) {
         float o[32];
-        tmem_ld32(my_tmem + kUmColO + cc * 32, o);
+        tmem_ld32(my_tmem + kUmColO + half * (kD / 2) + cc * 32, o);
 #pragma unroll
         for (int i = 0; i < 32; ++i) o[i] *= f;
-        tmem_st32(my_tmem + kUmColO + cc * 32, o);
+        tmem_st32(my_tmem + kUmColO + half * (kD / 2) + cc * 32, o);
       }
-      tc_fence_before_sync();
     }
-    const float m_safe = m_row == -INFINITY ? 0.f : m_row;
-    uint32_t hi[32], lo[32];
+    const float neg_m = m_row == -INFINITY ? 0.f : -m_row;
+    uint32_t hi[16], lo[16];
 #pragma unroll
-    for (int e = 0; e < 32; ++e) {
-      const float p0 = ex2_approx(s[2 * e] - m_safe), p1 = ex2_approx(s[2 * e + 1] - m_safe);
+    for (int e = 0; e < 16; ++e) {
+      const float p0 = ex2_approx(fmaf(s[2 * e], scale_log2, neg_m)), p1 = ex2_approx(fmaf(s[2 * e + 1], scale_log2, neg_m));
       l_row += p0 + p1;
       const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
       const __nv_bfloat162 g = __floats2bfloat162_rn(p0 - __low2float(h), p1 - __high2float(h));
       hi[e] = *reinterpret_cast<const uint32_t*>(&h);
       lo[e] = *reinterpret_cast<const uint32_t*>(&g);
     }
-    // the P V product of the previous tile must have consumed P before it is overwritten
-    if (t >= 1 && !um_wait(&sm.p_empty, (t - 1) & 1, &sm.abort_flag, p.status)) { ok = false; break; }
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      *reinterpret_cast<uint4*>(sm.p_hi + swz(r, j)) = make_uint4(hi[4 * j], hi[4 * j + 1], hi[4 * j + 2], hi[4 * j + 3]);
-      *reinterpret_cast<uint4*>(sm.p_lo + swz(r, j)) = make_uint4(lo[4 * j], lo[4 * j + 1], lo[4 * j + 2], lo[4 * j + 3]);
-    }
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    // A parity wait only tells two consecutive phases apart, so every phase of pv_done has to be
+    // observed in turn (the rescaling above and the epilogue rely on it); P V (t - 1) has
+    // normally retired by now.
+    if (t >= 1 && !um_wait(&sm.pv_done, (t - 1) & 1, &sm.abort_flag, p.status)) return;
+    // P(t) as the A operand of P V: keys 2j, 2j + 1 of this half in column half * 16 + j; hi then lo
+    tmem_st16(s_tmem + half * 16, hi);
+    tmem_st16(s_tmem + 32 + half * 16, lo);
+    tmem_st_wait();
+    tc_fence_before_sync();
     mbar_arrive(smem_u32(&sm.p_full));
   }
-  if (!ok) return;
-  // ---- epilogue: O / l -> global
-  if (!um_wait(&sm.p_empty, (n_tiles - 1) & 1, &sm.abort_flag, p.status)) return;
+  // ---- epilogue: O / l -> global, each half its 128 columns
+  sm.xchg[n_tiles & 1][half][r] = l_row;
+  mbar_arrive(smem_u32(&sm.x_full));
+  if (!um_wait(&sm.x_full, n_tiles & 1, &sm.abort_flag, p.status)) return;
+  l_row += sm.xchg[n_tiles & 1][half ^ 1][r];
+  if (!um_wait(&sm.pv_done, (n_tiles - 1) & 1, &sm.abort_flag, p.status)) return;
   tc_fence_after_sync();
   const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
-  float* dst = p.out + ((long long)(tok0 + token) * kHq + kvh * kG + hl) * kD;
+  float* dst = p.out + ((long long)(tok0 + token) * kHq + kvh * kG + hl) * kD + half * (kD / 2);
 #pragma unroll 1
-  for (int cc = 0; cc < kD / 32; ++cc) {
+  for (int cc = 0; cc < kD / 64; ++cc) {
     float o[32];
-    tmem_ld32(my_tmem + kUmColO + cc * 32, o);
+    tmem_ld32(my_tmem + kUmColO + half * (kD / 2) + cc * 32, o);
     if (token < ntok) {
 #pragma unroll
       for (int i = 0; i < 32; i += 4)
@@ -343,8 +449,8 @@ __device__ __forceinline__ void um_softmax_warps(UmmaSmem& sm, const UmmaPrefill
 }
 
 __global__ void __launch_bounds__(kUmThreads, 1)
-prefill_umma_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
-                    const __grid_constant__ CUtensorMap v_map, const UmmaPrefillParams p) {
+prefill_umma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
+                    const UmmaPrefillParams p) {
   extern __shared__ unsigned char um_smem_raw[];
   UmmaSmem& sm = *reinterpret_cast<UmmaSmem*>((reinterpret_cast<uintptr_t>(um_smem_raw) + 1023) & ~(uintptr_t)1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -353,16 +459,18 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
   // ---- set-up: TMEM, barriers, which (table row, 32-token tile) this CTA serves
   if (warp == 1) tmem_alloc(smem_u32(&sm.tmem_base), kUmTmemCols);
   if (threadIdx.x == 0) {
-    mbar_init(smem_u32(&sm.q_full), 1);
-    for (int i = 0; i < 2; ++i) {
+    mbar_init(smem_u32(&sm.q_full), kUmSoftmaxThreads);
+    for (int i = 0; i < kUmStages; ++i) {
       mbar_init(smem_u32(&sm.k_full[i]), 1);
       mbar_init(smem_u32(&sm.v_full[i]), 1);
-      mbar_init(smem_u32(&sm.kv_empty[i]), 1);
-      mbar_init(smem_u32(&sm.s_full[i]), 1);
-      mbar_init(smem_u32(&sm.s_empty[i]), kUmSoftmaxThreads);
+      mbar_init(smem_u32(&sm.k_empty[i]), 1);
+      mbar_init(smem_u32(&sm.v_empty[i]), 1);
     }
+    mbar_init(smem_u32(&sm.s_full[0]), 1);
+    mbar_init(smem_u32(&sm.s_full[1]), 1);
     mbar_init(smem_u32(&sm.p_full), kUmSoftmaxThreads);
-    mbar_init(smem_u32(&sm.p_empty), 1);
+    mbar_init(smem_u32(&sm.pv_done), 1);
+    mbar_init(smem_u32(&sm.x_full), kUmSoftmaxThreads);
     mbar_fence_init();
     sm.abort_flag = 0;
     // heaviest tiles (the last tokens of a row see the most keys) get the lowest block indices
@@ -400,7 +508,7 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_cons
   const int n_tiles = key_end > 0 ? (key_end + kUmKeys - 1) / kUmKeys : 0;
 
   if (n_tiles > 0) {
-    if (warp == 0) um_producer(&q_map, &k_map, &v_map, p, sm, row, tok0, kvh, kv_len, n_tiles, lane);
+    if (warp == 0) um_producer(&k_map, &v_map, p, sm, row, kvh, kv_len, n_tiles, lane);
     else if (warp == 1) um_mma_warp(sm, p, tmem, n_tiles, lane);
     else um_softmax_warps(sm, p, tmem, tok0, ntok, kvh, kv_len, n_tiles, warp, lane);
   }
@@ -441,8 +549,8 @@ static bool um_make_map(CUtensorMap* map, const void* base, uint64_t mid, uint64
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-// Returns NVJ_ERR_UNSUPPORTED when the driver offers no tensor-map encoder or the batch is too
-// small for a 32-token box; the caller then takes the mma.sync kernel.
+// Returns NVJ_ERR_UNSUPPORTED when the driver offers no tensor-map encoder or the scale is not
+// positive (row maxima are taken before scaling); the caller then takes the mma.sync kernel.
 int launch_prefill_umma(const void* q, int q_dtype, const char* k_cache, const char* v_cache,
                         long long num_blocks, const int32_t* block_tables, int table_width,
                         const int32_t* kv_lens, const int32_t* positions, const int32_t* query_start_loc,
@@ -450,7 +558,8 @@ int launch_prefill_umma(const void* q, int q_dtype, const char* k_cache, const c
                         int skip_single, cudaStream_t stream) {
   static bool opted_in[64];
   constexpr int kSmemBytes = (int)sizeof(UmmaSmem) + 1024;
-  if (q_dtype != NVJ_BF16 || token_bucket < kUmTokens || num_blocks < 1 || !um_encode_fn()) return NVJ_ERR_UNSUPPORTED;
+  static_assert(kSmemBytes <= 232448, "tiles exceed the shared memory of one CTA");
+  if (!(scale > 0.f) || num_blocks < 1 || !um_encode_fn()) return NVJ_ERR_UNSUPPORTED;
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return NVJ_ERR_LAUNCH;
   if (!opted_in[dev]) {
@@ -458,20 +567,20 @@ int launch_prefill_umma(const void* q, int q_dtype, const char* k_cache, const c
       return NVJ_ERR_LAUNCH;
     opted_in[dev] = true;
   }
-  CUtensorMap q_map, k_map, v_map;
-  if (!um_make_map(&q_map, q, kHq, (uint64_t)token_bucket, kUmTokens) ||
-      !um_make_map(&k_map, k_cache, kHkv, (uint64_t)num_blocks * kBlk, kBlk) ||
+  CUtensorMap k_map, v_map;
+  if (!um_make_map(&k_map, k_cache, kHkv, (uint64_t)num_blocks * kBlk, kBlk) ||
       !um_make_map(&v_map, v_cache, kHkv, (uint64_t)num_blocks * kBlk, kBlk))
     return NVJ_ERR_UNSUPPORTED;
   if (!skip_single &&
       cudaMemsetAsync(out, 0, sizeof(float) * (size_t)token_bucket * kHq * kD, stream) != cudaSuccess)
     return NVJ_ERR_LAUNCH;
   UmmaPrefillParams p{};
+  p.q = q; p.q_dtype = q_dtype;
   p.block_tables = block_tables; p.kv_lens = kv_lens; p.positions = positions; p.query_start_loc = query_start_loc;
   p.out = out; p.status = status; p.num_blocks = num_blocks; p.rows = rows; p.token_bucket = token_bucket;
   p.table_width = table_width; p.skip_single = skip_single; p.scale = scale;
   dim3 grid((token_bucket + kUmTokens - 1) / kUmTokens + rows, kHkv, 1);
-  prefill_umma_kernel<<<grid, kUmThreads, kSmemBytes, stream>>>(q_map, k_map, v_map, p);
+  prefill_umma_kernel<<<grid, kUmThreads, kSmemBytes, stream>>>(k_map, v_map, p);
   return cudaGetLastError() == cudaSuccess ? NVJ_OK : NVJ_ERR_LAUNCH;
 }
 
