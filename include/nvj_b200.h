@@ -219,7 +219,8 @@ int nvj_paged_decode_static_scratch(const void* q, int q_dtype,
  *   variant    0 = automatic; 1 = generic CUDA-core kernel (any shape or dtype); for the model's
  *              shape (bf16 cache, block 16, 2 KV x 4 query heads, head_dim 256): 2 = mma.sync
  *              tiles of 16 tokens, 3 = tcgen05 tiles of 32 tokens with accumulators in tensor
- *              memory.  NVJ_ERR_UNSUPPORTED when 2 or 3 is asked for another shape.
+ *              memory, 4 = the same on CTA pairs (cta_group::2, 64 tokens per pair; what
+ *              automatic picks first).  NVJ_ERR_UNSUPPORTED when 2-4 is asked for another shape.
  */
 int nvj_paged_prefill_packed(const void* q, int q_dtype,
                              const void* k_cache_layer, const void* v_cache_layer, int kv_dtype,

@@ -158,25 +158,30 @@ def prefill_and_copy_cases(dev, iters, small=False):
     visible = int(sum(int(pos[0, i]) + 1 for i in range(total)))
     flops = 4 * HQ * D * visible
     nbytes = total * TOKEN_BYTES * 2 + int(kv_lens.sum()) * TOKEN_BYTES + total * (HQ * D * 2 + HQ * D * 4)
-    for variant, name in ((2, "mma.sync tiles"), (3, "tcgen05 tiles")):
+    for variant, name in ((2, "mma.sync tiles"), (3, "tcgen05 tiles"), (4, "tcgen05 CTA pairs")):
         us = tm.run(lambda: K.packed_paged_prefill_attention(q, k[0], v[0], t_tab, t_len, t_pos, t_qsl, BS, SCALE, 4,
                                                              variant=variant))
         report("packed prefill attention, %s (%d tokens, %d rows)" % (name, total, len(rows)), us, nbytes,
                {"workload": "c3 chunk", "TFLOP/s": round(flops / us / 1e6, 2), "flops": flops})
-    # one long prompt in a single chunk: 4096 tokens, nothing cached
-    n_long = 4096
-    l_tab = torch.from_numpy(rng.permutation(pool)[:n_long // BS].astype(np.int32).reshape(1, -1)).to(dev)
-    l_pos = torch.arange(n_long, dtype=torch.int32, device=dev)[None]
-    l_qsl = torch.tensor([0, n_long], dtype=torch.int32, device=dev)
-    l_len = torch.tensor([n_long], dtype=torch.int32, device=dev)
-    lq = _randn_bf16((1, n_long, HQ, D), 16, dev)
-    l_flops = 4 * HQ * D * (n_long * (n_long + 1) // 2)
-    l_bytes = n_long * TOKEN_BYTES + n_long * (HQ * D * 2 + HQ * D * 4)
-    for variant, name in ((2, "mma.sync tiles"), (3, "tcgen05 tiles")):
-        us = tm.run(lambda: K.packed_paged_prefill_attention(lq, k[0], v[0], l_tab, l_len, l_pos, l_qsl, BS, SCALE, 4,
-                                                             variant=variant))
-        report("packed prefill attention, %s (one row of %d tokens)" % (name, n_long), us, l_bytes,
-               {"workload": "long prompt", "TFLOP/s": round(l_flops / us / 1e6, 2), "flops": l_flops})
+    # long prompts in a single chunk, nothing cached
+    for n_long in (4096, 16384):
+        if n_long // BS > pool:
+            continue
+        l_tab = torch.from_numpy(rng.permutation(pool)[:n_long // BS].astype(np.int32).reshape(1, -1)).to(dev)
+        l_pos = torch.arange(n_long, dtype=torch.int32, device=dev)[None]
+        l_qsl = torch.tensor([0, n_long], dtype=torch.int32, device=dev)
+        l_len = torch.tensor([n_long], dtype=torch.int32, device=dev)
+        lq = _randn_bf16((1, n_long, HQ, D), 16, dev)
+        l_flops = 4 * HQ * D * (n_long * (n_long + 1) // 2)
+        l_bytes = n_long * TOKEN_BYTES + n_long * (HQ * D * 2 + HQ * D * 4)
+        for variant, name in ((2, "mma.sync tiles"), (3, "tcgen05 tiles"), (4, "tcgen05 CTA pairs")):
+            if variant == 2 and n_long > 4096:
+                continue
+            us = tm.run(lambda: K.packed_paged_prefill_attention(lq, k[0], v[0], l_tab, l_len, l_pos, l_qsl, BS, SCALE, 4,
+                                                                 variant=variant))
+            report("packed prefill attention, %s (one row of %d tokens)" % (name, n_long), us, l_bytes,
+                   {"workload": "long prompt", "TFLOP/s": round(l_flops / us / 1e6, 2), "flops": l_flops})
+        del lq
     src = torch.from_numpy(tables_np[0, :32].copy()).to(dev)
     used = set(tables_np.reshape(-1).tolist())
     dst = torch.tensor([b for b in range(pool) if b not in used][:32], dtype=torch.int32, device=dev)

@@ -1,0 +1,484 @@
+// Ragged packed prefill attention on CTA pairs: the tcgen05 tile kernel with `cta_group::2`.
+//
+// The single-CTA kernel (paged_prefill_umma.cu) is bound by what one SM can take in from L2:
+// every 64-key tile costs it 64 KiB for 128 query rows.  Here two CTAs of a cluster (the two
+// SMs of a TPC) work on two neighbouring 32-token tiles of the same table row and KV head =
+// 256 query rows, and every K/V tile is loaded once for the pair: CTA r keeps keys
+// [32 r, 32 r + 32) of the K tile and head dims [128 r, 128 r + 128) of the V tile, 32 KiB per
+// tile and SM instead of 64.  `tcgen05.mma.cta_group::2` (issued by CTA 0 alone) multiplies the
+// 128 rows each CTA holds in its own tensor memory (Q, later P) with the B operand assembled
+// from both halves, and leaves each CTA's 128 x N result in that CTA's tensor memory.
+//   S:   M 256 (2 x 128), N 64 keys (2 x 32),  K 16 dims  x 16 per tile
+//   P V: M 256,           N 256 dims (2 x 128), K 16 keys x 4 per tile, P as hi + lo
+// Roles per CTA as in the single-CTA kernel (warp 0 TMA producer, warp 1 MMA issue in CTA 0,
+// warps 2-9 softmax); what crosses the pair:
+//   * both producers' TMA loads complete on CTA 0's full barriers (cp.async.bulk.tensor with
+//     .cta_group::2 and the barrier address of rank 0); no load is a multicast;
+//   * `tcgen05.commit` with a two-CTA mask releases K/V stages and S buffers in both CTAs;
+//   * the softmax threads of both CTAs arrive on CTA 0's "Q staged" and "P written" barriers.
+// A cluster barrier after set-up and one before the tensor memory is freed fence the pair.
+// Every mbarrier wait is bounded; a timeout flags NVJ_DEV_TIMEOUT and both CTAs still reach
+// the final cluster barrier and free their tensor memory.
+// Semantics: nanovllm_jax/kv_cache.py:831-849, nanovllm_jax/kernels/full_attention_triton.py:51-145.
+
+#include "paged_decode.cuh"
+#include "umma.cuh"
+
+namespace nvj {
+
+constexpr int kU2Tokens = 32;    // query tokens per CTA (64 per pair)
+constexpr int kU2Rows = 128;     // query rows per CTA
+constexpr int kU2Keys = 64;      // keys per tile
+constexpr int kU2Stages = 4;
+constexpr int kU2Threads = 320;
+constexpr int kU2SoftmaxThreads = 256;
+constexpr int kU2TmemCols = 512;
+constexpr int kU2ColQ = 0, kU2ColS = 128, kU2ColO = 256;
+constexpr uint32_t kU2TileBytes = kU2Keys * kRowBytes;  // a whole K (or V) tile: both CTAs' halves, 32 KiB
+constexpr uint32_t kU2LeaderMask = 0xFEFFFFFFu;         // clears the CTA-rank bit of a shared::cluster address
+constexpr float kU2Log2e = 1.4426950408889634f;
+constexpr float kU2RescaleGap = 8.f;
+
+struct Umma2Params {
+  const void* q;
+  const int32_t* block_tables;
+  const int32_t* kv_lens;
+  const int32_t* positions;
+  const int32_t* query_start_loc;
+  float* out;
+  int32_t* status;
+  long long num_blocks;
+  int rows, token_bucket, table_width, skip_single, q_dtype;
+  float scale;
+};
+
+struct Umma2Smem {
+  alignas(1024) char k[kU2Stages][4][32 * 128];  // [stage][64-d chunk][this CTA's 32 keys][128 B]
+  alignas(1024) char v[kU2Stages][2][64 * 128];  // [stage][this CTA's two 64-d chunks][64 keys][128 B]
+  // used in CTA 0 only: q_full, k_full, v_full, p_full; used in both: the rest
+  alignas(8) unsigned long long q_full, k_full[kU2Stages], v_full[kU2Stages], k_empty[kU2Stages], v_empty[kU2Stages],
+      s_full[2], p_full, pv_done, x_full;
+  float xchg[2][2][kU2Rows];
+  uint32_t tmem_base;
+  int row, tok0, ntok, pair_last_tok, abort_flag;
+};
+
+// ---- cta_group::2 wrappers ---------------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem2_alloc(uint32_t smem_dst, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem2_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+// D[256 x N] (+)= A[256 x 16] B[16 x N] over the CTA pair: each CTA's 128 rows of A and D in its own tensor
+// memory at the same addresses, each CTA's N / 2 columns of B in its own shared memory at the same offsets
+__device__ __forceinline__ void umma2_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
+      : "memory");
+}
+// arrives, once the MMAs issued so far have retired, on the barrier at this offset in both CTAs of the pair
+__device__ __forceinline__ void umma2_commit_pair(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(bar), "h"((uint16_t)3) : "memory");
+}
+// One box into this CTA's shared memory; the bytes are counted on CTA 0's barrier at `bar`'s offset.
+__device__ __forceinline__ void tma2_load_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(bar & kU2LeaderMask)
+      : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_leader(uint32_t bar) {
+  // default semantics (release at CTA scope): what the arrival publishes lives in tensor memory and is ordered by
+  // tcgen05.wait::st + tcgen05.fence; a cluster-scope release here cost ~1700 cycles per arrival
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar & kU2LeaderMask) : "memory");
+}
+// Instruction descriptor, kind::f16, fp32 accumulate, bf16 A and B, M = 256 over the pair.
+__device__ __forceinline__ constexpr uint32_t umma2_idesc(int n, bool b_mn_major) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) | ((256u >> 4) << 24);
+}
+
+// ---- warp 0 of both CTAs: TMA loads of this CTA's halves ------------------------------------
+__device__ __forceinline__ void u2_producer(const CUtensorMap* k_map, const CUtensorMap* v_map, const Umma2Params& p,
+                                            Umma2Smem& sm, int row, int kvh, int kv_len, int n_tiles, int rank, int lane) {
+  const int need_blocks = (kv_len + kBlk - 1) / kBlk;
+  const int oob = (int)(p.num_blocks * kBlk);  // a box that starts here is filled with zeros
+  int ids = -1;
+  for (int t = 0; t < n_tiles; ++t) {
+    const int s = t % kU2Stages;
+    const uint32_t reuse_parity = ((t / kU2Stages) - 1) & 1;
+    if ((t & 7) == 0) {  // block ids of the next 8 tiles, one per lane
+      const int bi = t * 4 + lane;
+      ids = -1;
+      if (bi < need_blocks && bi < p.table_width) {
+        ids = p.block_tables[(long long)row * p.table_width + bi];
+        if (ids < 0 || ids >= p.num_blocks) {
+          if (rank == 0) atomicOr(p.status, NVJ_DEV_BAD_BLOCK_ID);
+          ids = -1;
+        }
+      }
+    }
+    int z[4];
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+      const int id = __shfl_sync(0xffffffffu, ids, (t & 7) * 4 + b);
+      z[b] = id >= 0 ? id * kBlk : oob;
+    }
+    if (t >= kU2Stages && !um_wait(&sm.k_empty[s], reuse_parity, &sm.abort_flag, p.status)) break;
+    if (lane == 0) {
+      const uint32_t kb = smem_u32(&sm.k_full[s]);
+      if (rank == 0) mbar_arrive_expect_tx(kb, kU2TileBytes);  // both CTAs' halves are counted here
+#pragma unroll
+      for (int b2 = 0; b2 < 2; ++b2)  // this CTA's keys: cache blocks 2 rank, 2 rank + 1 of the tile
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+          tma2_load_3d(smem_u32(&sm.k[s][c][0]) + b2 * (kBlk * 128), k_map, c * 64, kvh, rank ? z[2 + b2] : z[b2], kb);
+    }
+    if (t >= kU2Stages && !um_wait(&sm.v_empty[s], reuse_parity, &sm.abort_flag, p.status)) break;
+    if (lane == 0) {
+      const uint32_t vb = smem_u32(&sm.v_full[s]);
+      if (rank == 0) mbar_arrive_expect_tx(vb, kU2TileBytes);
+#pragma unroll
+      for (int b = 0; b < 4; ++b)  // all keys, this CTA's head dims: 64-d chunks 2 rank, 2 rank + 1
+#pragma unroll
+        for (int c2 = 0; c2 < 2; ++c2)
+          tma2_load_3d(smem_u32(&sm.v[s][c2][0]) + b * (kBlk * 128), v_map, (2 * rank + c2) * 64, kvh, z[b], vb);
+    }
+    __syncwarp();
+  }
+}
+
+// ---- warp 1 of CTA 0: MMA issue for the pair -------------------------------------------------
+__device__ __forceinline__ bool u2_issue_s(Umma2Smem& sm, const Umma2Params& p, uint32_t tmem, uint64_t k_desc0, int t,
+                                           int stage, uint32_t full_parity) {
+  if (!um_wait(&sm.k_full[stage], full_parity, &sm.abort_flag, p.status)) return false;
+  tc_fence_after_sync();
+  if (um_elect_one()) {
+    constexpr uint32_t idesc = umma2_idesc(kU2Keys, false);
+    const uint64_t k_desc = k_desc0 + (uint64_t)((stage * 4 * 32 * 128) >> 4);
+    const uint32_t d = tmem + kU2ColS + (t & 1) * kU2Keys;
+#pragma unroll
+    for (int ks = 0; ks < 16; ++ks)  // 16 dims per MMA: 8 columns of Q; K chunk ks / 4, 32 bytes into its swizzled rows
+      umma2_bf16_ts(d, tmem + kU2ColQ + ks * 8, k_desc + (uint64_t)(((ks >> 2) * (32 * 128) + (ks & 3) * 32) >> 4), idesc,
+                    ks > 0 ? 1u : 0u);
+    umma2_commit_pair(smem_u32(&sm.s_full[t & 1]));
+    umma2_commit_pair(smem_u32(&sm.k_empty[stage]));
+  }
+  __syncwarp();
+  return true;
+}
+
+__device__ __forceinline__ void u2_mma_warp(Umma2Smem& sm, const Umma2Params& p, uint32_t tmem, int n_tiles) {
+  const uint64_t k_desc0 = umma_desc(smem_u32(&sm.k[0][0][0]), 16, 1024);
+  const uint64_t v_desc0 = umma_desc(smem_u32(&sm.v[0][0][0]), kU2Keys * 128, 1024);
+  if (!um_wait(&sm.q_full, 0, &sm.abort_flag, p.status)) return;
+  if (!u2_issue_s(sm, p, tmem, k_desc0, 0, 0, 0)) return;
+  if (n_tiles > 1 && !u2_issue_s(sm, p, tmem, k_desc0, 1, 1, 0)) return;
+  int sv = 0, sk = 2 % kU2Stages;
+  uint32_t pv = 0, pk = 2 / kU2Stages;
+  for (int t = 0; t < n_tiles; ++t) {
+    if (!um_wait(&sm.v_full[sv], pv, &sm.abort_flag, p.status)) return;
+    if (!um_wait(&sm.p_full, t & 1, &sm.abort_flag, p.status)) return;
+    tc_fence_after_sync();
+    if (um_elect_one()) {
+      constexpr uint32_t idesc = umma2_idesc(kD, true);
+      const uint64_t v_desc = v_desc0 + (uint64_t)((sv * 2 * kU2Keys * 128) >> 4);
+      const uint32_t pa = tmem + kU2ColS + (t & 1) * kU2Keys;
+#pragma unroll
+      for (int kk = 0; kk < 4; ++kk) {  // 16 keys per MMA: 8 columns of P, two 8-key groups of V
+        const uint64_t dv = v_desc + (uint64_t)((kk * 2048) >> 4);
+        umma2_bf16_ts(tmem + kU2ColO, pa + kk * 8, dv, idesc, (t > 0 || kk > 0) ? 1u : 0u);
+        umma2_bf16_ts(tmem + kU2ColO, pa + 32 + kk * 8, dv, idesc, 1u);
+      }
+      umma2_commit_pair(smem_u32(&sm.v_empty[sv]));
+      umma2_commit_pair(smem_u32(&sm.pv_done));
+    }
+    __syncwarp();
+    // S(t + 2) overwrites the columns P V (t) reads P(t) from; MMAs of different shapes are not
+    // ordered against each other, so wait for P V (t) to retire first
+    if (t + 2 < n_tiles) {
+      if (!um_wait(&sm.pv_done, t & 1, &sm.abort_flag, p.status)) return;
+      if (!u2_issue_s(sm, p, tmem, k_desc0, t + 2, sk, pk)) return;
+    }
+    if (++sv == kU2Stages) { sv = 0; pv ^= 1u; }
+    if (++sk == kU2Stages) { sk = 0; pk ^= 1u; }
+  }
+}
+
+// ---- warps 2-9 of both CTAs: Q staging, softmax, epilogue for this CTA's 128 rows -------------
+__device__ __forceinline__ void u2_softmax_warps(Umma2Smem& sm, const Umma2Params& p, uint32_t tmem, int tok0, int ntok,
+                                                 int kvh, int kv_len, int n_tiles, int warp, int lane) {
+  const int quarter = warp & 3, half = (warp - 2) >> 2;
+  const int r = quarter * 32 + lane, token = lane, hl = quarter;
+  const uint32_t my_tmem = tmem + ((uint32_t)(quarter * 32) << 16);
+  {  // this row's half of Q (128 dims) -> 64 TMEM columns, two bf16 per column
+    const long long qrow = ((long long)(tok0 + token) * kHq + kvh * kG + hl) * kD + half * (kD / 2);
+#pragma unroll 1
+    for (int part = 0; part < 4; ++part) {
+      uint32_t w[16];
+      if (token >= ntok) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) w[i] = 0u;
+      } else if (p.q_dtype == NVJ_BF16) {
+        const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.q) + qrow + part * 32);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const uint4 u = ld_nc_u4(src + i);
+          w[4 * i] = u.x; w[4 * i + 1] = u.y; w[4 * i + 2] = u.z; w[4 * i + 3] = u.w;
+        }
+      } else {
+        const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(p.q) + qrow + part * 32);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float4 f = src[i];
+          const __nv_bfloat162 a = __floats2bfloat162_rn(f.x, f.y), b2 = __floats2bfloat162_rn(f.z, f.w);
+          w[2 * i] = *reinterpret_cast<const uint32_t*>(&a);
+          w[2 * i + 1] = *reinterpret_cast<const uint32_t*>(&b2);
+        }
+      }
+      tmem_st16(my_tmem + kU2ColQ + half * 64 + part * 16, w);
+    }
+    tmem_st_wait();
+    tc_fence_before_sync();
+    mbar_arrive_leader(smem_u32(&sm.q_full));
+  }
+  const int my_pos = token < ntok ? p.positions[tok0 + token] : -1;
+  const int last_key = my_pos < kv_len - 1 ? my_pos : kv_len - 1;
+  const float scale_log2 = p.scale * kU2Log2e;
+  float m_row = -INFINITY, l_row = 0.f;
+
+  for (int t = 0; t < n_tiles; ++t) {
+    const int b = t & 1;
+    const uint32_t s_tmem = my_tmem + kU2ColS + b * kU2Keys;
+    if (!um_wait(&sm.s_full[b], (t >> 1) & 1, &sm.abort_flag, p.status)) return;
+    tc_fence_after_sync();
+    float s[32];
+    tmem_ld32(s_tmem + half * 32, s);
+    const int lim = last_key - t * kU2Keys - half * 32;
+    float hmax = -INFINITY;
+    if (lim >= 31) {
+#pragma unroll
+      for (int i = 0; i < 32; i += 2) hmax = fmaxf(hmax, fmaxf(s[i], s[i + 1]));
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) { s[i] = i <= lim ? s[i] : -INFINITY; hmax = fmaxf(hmax, s[i]); }
+    }
+    sm.xchg[b][half][r] = hmax;
+    mbar_arrive(smem_u32(&sm.x_full));
+    if (!um_wait(&sm.x_full, t & 1, &sm.abort_flag, p.status)) return;
+    const float tmax = fmaxf(hmax, sm.xchg[b][half ^ 1][r]) * scale_log2;  // scale > 0
+    if (t == 0) {
+      m_row = tmax;
+    } else if (__any_sync(0xffffffffu, tmax > m_row + kU2RescaleGap)) {
+      if (!um_wait(&sm.pv_done, (t - 1) & 1, &sm.abort_flag, p.status)) return;
+      tc_fence_after_sync();
+      const float m_new = fmaxf(m_row, tmax);
+      const float f = m_new == -INFINITY ? 1.f : ex2_approx(m_row - m_new);
+      m_row = m_new;
+      l_row *= f;
+#pragma unroll 1
+      for (int cc = 0; cc < kD / 64; ++cc) {
+        float o[32];
+        tmem_ld32(my_tmem + kU2ColO + half * (kD / 2) + cc * 32, o);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[i] *= f;
+        tmem_st32(my_tmem + kU2ColO + half * (kD / 2) + cc * 32, o);
+      }
+    }
+    const float neg_m = m_row == -INFINITY ? 0.f : -m_row;
+    uint32_t hi[16], lo[16];
+#pragma unroll
+    for (int e = 0; e < 16; ++e) {
+      const float p0 = ex2_approx(fmaf(s[2 * e], scale_log2, neg_m)), p1 = ex2_approx(fmaf(s[2 * e + 1], scale_log2, neg_m));
+      l_row += p0 + p1;
+      const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+      const __nv_bfloat162 g = __floats2bfloat162_rn(p0 - __low2float(h), p1 - __high2float(h));
+      hi[e] = *reinterpret_cast<const uint32_t*>(&h);
+      lo[e] = *reinterpret_cast<const uint32_t*>(&g);
+    }
+    // every phase of pv_done is observed in turn (parity waits tell only two phases apart)
+    if (t >= 1 && !um_wait(&sm.pv_done, (t - 1) & 1, &sm.abort_flag, p.status)) return;
+    tmem_st16(s_tmem + half * 16, hi);
+    tmem_st16(s_tmem + 32 + half * 16, lo);
+    tmem_st_wait();
+    tc_fence_before_sync();
+    mbar_arrive_leader(smem_u32(&sm.p_full));
+  }
+  // ---- epilogue
+  sm.xchg[n_tiles & 1][half][r] = l_row;
+  mbar_arrive(smem_u32(&sm.x_full));
+  if (!um_wait(&sm.x_full, n_tiles & 1, &sm.abort_flag, p.status)) return;
+  l_row += sm.xchg[n_tiles & 1][half ^ 1][r];
+  if (!um_wait(&sm.pv_done, (n_tiles - 1) & 1, &sm.abort_flag, p.status)) return;
+  tc_fence_after_sync();
+  const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
+  float* dst = p.out + ((long long)(tok0 + token) * kHq + kvh * kG + hl) * kD + half * (kD / 2);
+#pragma unroll 1
+  for (int cc = 0; cc < kD / 64; ++cc) {
+    float o[32];
+    tmem_ld32(my_tmem + kU2ColO + half * (kD / 2) + cc * 32, o);
+    if (token < ntok) {
+#pragma unroll
+      for (int i = 0; i < 32; i += 4)
+        *reinterpret_cast<float4*>(dst + cc * 32 + i) = make_float4(o[i] * inv, o[i + 1] * inv, o[i + 2] * inv, o[i + 3] * inv);
+    }
+  }
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kU2Threads, 1)
+prefill_umma2_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
+                     const Umma2Params p) {
+  extern __shared__ unsigned char u2_smem_raw[];
+  Umma2Smem& sm = *reinterpret_cast<Umma2Smem*>((reinterpret_cast<uintptr_t>(u2_smem_raw) + 1023) & ~(uintptr_t)1023);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kvh = blockIdx.y;
+  const int rank = (int)cluster_ctarank();  // == blockIdx.x & 1
+
+  // ---- which (table row, pair of 32-token tiles) this cluster serves; both CTAs compute the same
+  if (threadIdx.x == 0) {
+    // heaviest pairs (the last tokens of a row see the most keys) get the lowest cluster indices
+    int idx = (gridDim.x >> 1) - 1 - (blockIdx.x >> 1), row = -1, tok0 = 0, ntok = 0, last = 0;
+    for (int r = 0; r < p.rows; ++r) {
+      const int lo = p.query_start_loc[r];
+      int hi = p.query_start_loc[r + 1];
+      hi = hi < p.token_bucket ? hi : p.token_bucket;
+      int pairs = hi > lo ? (hi - lo + 2 * kU2Tokens - 1) / (2 * kU2Tokens) : 0;
+      if (p.skip_single && p.query_start_loc[r + 1] - lo == 1) pairs = 0;
+      if (idx < pairs) {
+        row = r;
+        tok0 = lo + (2 * idx + rank) * kU2Tokens;
+        ntok = hi - tok0 < kU2Tokens ? hi - tok0 : kU2Tokens;
+        if (ntok < 0) ntok = 0;
+        const int pair_end = lo + (2 * idx + 2) * kU2Tokens;
+        last = (pair_end < hi ? pair_end : hi) - 1;
+        break;
+      }
+      idx -= pairs;
+    }
+    sm.row = row; sm.tok0 = tok0; sm.ntok = ntok; sm.pair_last_tok = last; sm.abort_flag = 0;
+  }
+  __syncthreads();
+  const int row = sm.row, tok0 = sm.tok0, ntok = sm.ntok;
+  if (row < 0) return;  // the whole cluster leaves: nothing has been allocated or shared yet
+
+  int kv_len = p.kv_lens[row];
+  if (kv_len > p.table_width * kBlk) {
+    if (threadIdx.x == 0 && rank == 0) atomicOr(p.status, NVJ_DEV_BAD_LENGTH);
+    kv_len = p.table_width * kBlk;
+  }
+  // positions grow along a row's chunk: the pair's last token sees the most keys
+  const int max_pos = p.positions[sm.pair_last_tok];
+  const int key_end = kv_len < max_pos + 1 ? kv_len : max_pos + 1;
+  const int n_tiles = key_end > 0 ? (key_end + kU2Keys - 1) / kU2Keys : 0;
+  if (n_tiles == 0) return;  // same decision in both CTAs
+
+  if (warp == 1) tmem2_alloc(smem_u32(&sm.tmem_base), kU2TmemCols);
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&sm.q_full), 2 * kU2SoftmaxThreads);
+    for (int i = 0; i < kU2Stages; ++i) {
+      mbar_init(smem_u32(&sm.k_full[i]), 1);
+      mbar_init(smem_u32(&sm.v_full[i]), 1);
+      mbar_init(smem_u32(&sm.k_empty[i]), 1);
+      mbar_init(smem_u32(&sm.v_empty[i]), 1);
+    }
+    mbar_init(smem_u32(&sm.s_full[0]), 1);
+    mbar_init(smem_u32(&sm.s_full[1]), 1);
+    mbar_init(smem_u32(&sm.p_full), 2 * kU2SoftmaxThreads);
+    mbar_init(smem_u32(&sm.pv_done), 1);
+    mbar_init(smem_u32(&sm.x_full), kU2SoftmaxThreads);
+    mbar_fence_init();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers exist before anything is sent to them
+  tc_fence_after_sync();
+  const uint32_t tmem = sm.tmem_base;
+
+  if (warp == 0) u2_producer(&k_map, &v_map, p, sm, row, kvh, kv_len, n_tiles, rank, lane);
+  else if (warp == 1) { if (rank == 0) u2_mma_warp(sm, p, tmem, n_tiles); }
+  else u2_softmax_warps(sm, p, tmem, tok0, ntok, kvh, kv_len, n_tiles, warp, lane);
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (sm.abort_flag) {  // give copies and MMAs in flight time to land before memory is released
+    const unsigned long long t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  cluster_sync_all();  // CTA 0's MMAs read this CTA's shared and tensor memory until its last commit
+  if (warp == 1) tmem2_dealloc(tmem, kU2TmemCols);
+}
+
+typedef CUresult (*U2EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static U2EncodeTiledFn u2_encode_fn() {
+  static U2EncodeTiledFn fn = [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult res;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &res) != cudaSuccess ||
+        res != cudaDriverEntryPointSuccess)
+      ptr = nullptr;
+    return reinterpret_cast<U2EncodeTiledFn>(ptr);
+  }();
+  return fn;
+}
+
+static bool u2_make_map(CUtensorMap* map, const void* base, uint64_t outer) {
+  const cuuint64_t dims[3] = {(cuuint64_t)kD, (cuuint64_t)kHkv, outer};
+  const cuuint64_t strides[2] = {(cuuint64_t)kRowBytes, (cuuint64_t)kRowBytes * kHkv};
+  const cuuint32_t box[3] = {64, 1, (cuuint32_t)kBlk};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  return u2_encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// Returns NVJ_ERR_UNSUPPORTED when the driver offers no tensor-map encoder or the scale is not positive.
+int launch_prefill_umma2(const void* q, int q_dtype, const char* k_cache, const char* v_cache,
+                         long long num_blocks, const int32_t* block_tables, int table_width,
+                         const int32_t* kv_lens, const int32_t* positions, const int32_t* query_start_loc,
+                         int rows, int token_bucket, float scale, float* out, int32_t* status,
+                         int skip_single, cudaStream_t stream) {
+  static bool opted_in[64];
+  constexpr int kSmemBytes = (int)sizeof(Umma2Smem) + 1024;
+  static_assert(kSmemBytes <= 232448, "tiles exceed the shared memory of one CTA");
+  if (!(scale > 0.f) || num_blocks < 1 || !u2_encode_fn()) return NVJ_ERR_UNSUPPORTED;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return NVJ_ERR_LAUNCH;
+  if (!opted_in[dev]) {
+    if (cudaFuncSetAttribute(prefill_umma2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
+      return NVJ_ERR_LAUNCH;
+    opted_in[dev] = true;
+  }
+  CUtensorMap k_map, v_map;
+  if (!u2_make_map(&k_map, k_cache, (uint64_t)num_blocks * kBlk) || !u2_make_map(&v_map, v_cache, (uint64_t)num_blocks * kBlk))
+    return NVJ_ERR_UNSUPPORTED;
+  if (!skip_single &&
+      cudaMemsetAsync(out, 0, sizeof(float) * (size_t)token_bucket * kHq * kD, stream) != cudaSuccess)
+    return NVJ_ERR_LAUNCH;
+  Umma2Params p{};
+  p.q = q; p.q_dtype = q_dtype;
+  p.block_tables = block_tables; p.kv_lens = kv_lens; p.positions = positions; p.query_start_loc = query_start_loc;
+  p.out = out; p.status = status; p.num_blocks = num_blocks; p.rows = rows; p.token_bucket = token_bucket;
+  p.table_width = table_width; p.skip_single = skip_single; p.scale = scale;
+  const int pairs = (token_bucket + 2 * kU2Tokens - 1) / (2 * kU2Tokens) + rows;
+  dim3 grid(2 * pairs, kHkv, 1);
+  prefill_umma2_kernel<<<grid, kU2Threads, kSmemBytes, stream>>>(k_map, v_map, p);
+  return cudaGetLastError() == cudaSuccess ? NVJ_OK : NVJ_ERR_LAUNCH;
+}
+
+}  // namespace nvj

@@ -447,7 +447,7 @@ def packed_paged_prefill_attention(query, k_cache_layer, v_cache_layer, block_ta
                                    max_query_len=None, variant=None):
     """Ragged packed prefill: query `[1, T, Hq, D]` -> fp32 `[1, T, Hq*D]`, padded tokens 0.
 
-    `variant`: 0 automatic, 1 generic, 2 mma.sync tiles, 3 tcgen05 tiles (default: the
+    `variant`: 0 automatic, 1 generic, 2 mma.sync tiles, 3 tcgen05 tiles, 4 tcgen05 tiles on CTA pairs (default: the
     `NVJ_PREFILL_VARIANT` environment variable, else 0).
     """
     lib = _lib.load()

@@ -75,10 +75,10 @@ def test_packed_prefill_ragged_chunk_with_cached_prefixes():
     assert not to_numpy(out)[0, 256:].any()  # tokens beyond query_start_loc[-1] are padding
 
 
-@pytest.mark.parametrize("variant", [1, 2, 3])
+@pytest.mark.parametrize("variant", [1, 2, 3, 4])
 @pytest.mark.parametrize("q_f32", [False, True])
 def test_packed_prefill_every_kernel_variant(variant, q_f32):
-    # 1 = CUDA-core kernel, 2 = mma.sync tiles, 3 = tcgen05 tiles; a 1-token row, a row that ends
+    # 1 = CUDA-core kernel, 2 = mma.sync tiles, 3 = tcgen05 tiles, 4 = tcgen05 tiles on CTA pairs; a 1-token row, a row that ends
     # in the middle of a block, a row over several 64-key tiles with a cached prefix, and padding
     from nano_vllm_jax_b200.kernels import paged_kv as K
     c = _prefill_case(7 + variant, 500, [1, 330, 900, 45, 64], cached=[40, 0, 768, 0, 0], chunk=[1, 330, 132, 45, 64], bucket=608)
@@ -94,7 +94,7 @@ def test_packed_prefill_every_kernel_variant(variant, q_f32):
     assert not to_numpy(out)[0, 572:].any()
 
 
-@pytest.mark.parametrize("variant", [2, 3])
+@pytest.mark.parametrize("variant", [2, 3, 4])
 def test_packed_prefill_scores_that_grow_along_the_sequence(variant):
     # Keys get longer with their position, so later key tiles raise the row maxima by far more
     # than 2^8: the tcgen05 kernel's deferred rescaling of O in tensor memory has to run.
@@ -121,7 +121,7 @@ def test_packed_prefill_tile_variants_refuse_other_shapes():
     k = torch.zeros((8, 16, 2, 64), dtype=torch.bfloat16, device="cuda")
     q = torch.zeros((1, 16, 8, 64), dtype=torch.bfloat16, device="cuda")
     i32 = dict(dtype=torch.int32, device="cuda")
-    for variant in (2, 3):
+    for variant in (2, 3, 4):
         with pytest.raises(NvjError):
             K.packed_paged_prefill_attention(q, k, k, torch.zeros((1, 1), **i32), torch.tensor([16], **i32),
                                              torch.arange(16, **i32)[None], torch.tensor([0, 16], **i32), BS, 0.125, 4,
