@@ -108,6 +108,36 @@ int nvj_kv_append_nhd(const void* append_key, const void* append_value, int src_
                       const int32_t* valid_mask,
                       int32_t* status, nvj_stream_t stream);
 
+/*
+ * The step in front of the path fused with the append: per-head RMSNorm ((1 + w) form) of the
+ * query and key rows, half-split rotary embedding of their first `rotary_dim` elements, then
+ * key and value rows are stored at their slots and the query is returned ready for attention.
+ * Replaces the sequence rms_norm(q), rms_norm(k), apply_rope(q), apply_rope(k), write_kv of
+ * nanovllm_jax/model.py:3371-3396 + 3539-3550 (nanovllm_jax/layers.py:11-29, 49-199); the
+ * reference lists this fusion as its roadmap item P2.2 (docs/kernel_roadmap.md:26, 416-419).
+ *
+ *   q        token i, head h at q + i * q_token_stride + h * q_head_stride (elements), so a
+ *            query that lives inside a [tokens, heads, 2 * head_dim] query|gate projection
+ *            needs no copy; k, v rows [num_kv_heads, head_dim] at token strides
+ *   weights  q_norm, k_norm [head_dim], bf16 or f32
+ *   inv_freq [rotary_dim / 2] f32, the framework's own 1 / theta^(2 i / rotary_dim) table
+ *   rope_positions [tokens] (text positions; multimodal 3-row positions are not handled)
+ *   slots and masks as in nvj_kv_append; q_out [tokens, num_q_heads, head_dim] bf16
+ * bf16 activations and cache, head_dim 64 / 128 / 256; otherwise NVJ_ERR_UNSUPPORTED.
+ */
+int nvj_qk_norm_rope_kv_append(const void* q, int64_t q_token_stride, int64_t q_head_stride,
+                               const void* k, int64_t k_token_stride,
+                               const void* v, int64_t v_token_stride, int act_dtype,
+                               const void* q_norm_weight, const void* k_norm_weight, int weight_dtype,
+                               float eps, const float* inv_freq, int rotary_dim,
+                               const int32_t* rope_positions,
+                               const int32_t* slot_mapping, const int32_t* valid_mask,
+                               const int32_t* query_start_loc, int qsl_rows, int packed,
+                               int n_rows, int n_cols,
+                               void* k_cache_layer, void* v_cache_layer, int cache_dtype,
+                               int64_t num_slots, int num_q_heads, int num_kv_heads, int head_dim,
+                               void* q_out, int32_t* status, nvj_stream_t stream);
+
 /* ------------------------------------------------------------------ decode */
 
 /*

@@ -26,6 +26,11 @@ SIGNATURES = {
     "nvj_kv_append": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
                               c_int, c_int, c_void_p, c_void_p, c_int, c_int64, c_int, c_int,
                               c_void_p, c_void_p]),
+    "nvj_qk_norm_rope_kv_append": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int,
+                                           c_void_p, c_void_p, c_int, c_float, c_void_p, c_int, c_void_p,
+                                           c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                           c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_int,
+                                           c_void_p, c_void_p, c_void_p]),
     "nvj_kv_append_nhd": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int,
                                   c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_int,
                                   c_void_p, c_int64, c_void_p, c_int, c_void_p, c_void_p, c_void_p]),

@@ -191,6 +191,27 @@ def prefill_and_copy_cases(dev, iters, small=False):
     del k, v
 
 
+def norm_rope_append_cases(dev, iters):
+    """RMSNorm(q, k) + partial RoPE + append in one launch: a 256-row decode step and a 512-token prefill chunk."""
+    rng = np.random.default_rng(6)
+    pool = 65_536
+    k = _randn_bf16((1, pool, BS, HKV, D), 31, dev)
+    v = _randn_bf16((1, pool, BS, HKV, D), 32, dev)
+    qw, kw = _randn_bf16((D,), 33, dev) * 0.1, _randn_bf16((D,), 34, dev) * 0.1
+    tm = Timer(dev, iters)
+    for rows, cols, name in ((256, 1, "256 decode rows"), (1, 512, "512-token packed chunk")):
+        n = rows * cols
+        qg = _randn_bf16((rows, cols, HQ, 2 * D), 35, dev)  # query|gate projection: q is its strided first half
+        nk, nv = _randn_bf16((rows, cols, HKV, D), 36, dev), _randn_bf16((rows, cols, HKV, D), 37, dev)
+        pos = torch.from_numpy(rng.integers(0, 4096, size=(rows, cols)).astype(np.int32)).to(dev)
+        slots = torch.from_numpy(rng.permutation(pool * BS)[:n].reshape(rows, cols).astype(np.int32)).to(dev)
+        nbytes = n * (2 * HQ * D * 2 + 2 * 2 * HKV * D * 2 + 8)
+        us = tm.run(lambda: K.qk_norm_rope_kv_append(qg[..., :D], nk, nv, qw, kw, pos, slots, k[0], v[0]))
+        report("qk_norm + rope + kv_append fused (%s)" % name, us, nbytes, {"workload": "front of the path"})
+    K.check_device_status(dev)
+    del k, v
+
+
 def mixed_step_case(dev, iters):
     """The KV path of one mixed continuous-batching step over 6 layers: 32 decode rows (contexts in
     [128, 2048]) plus 2 prefill chunks of 256 tokens, packed; per layer one append and one attention."""
@@ -249,7 +270,7 @@ def hybrid_cases(dev, iters):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--iters", type=int, default=20)
-    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "hybrid", "mixed"])
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "hybrid", "mixed", "front"])
     ap.add_argument("--small", action="store_true",
                     help="prefill cases on a 1-layer, 4096-block cache (128 MiB): the size to run under a profiler")
     args = ap.parse_args()
@@ -263,6 +284,8 @@ def main():
         hybrid_cases(dev, args.iters)
     if args.only in ("all", "mixed"):
         mixed_step_case(dev, args.iters)
+    if args.only in ("all", "front"):
+        norm_rope_append_cases(dev, args.iters)
 
 
 if __name__ == "__main__":

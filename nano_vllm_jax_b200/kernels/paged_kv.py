@@ -490,6 +490,92 @@ def packed_paged_prefill_attention(query, k_cache_layer, v_cache_layer, block_ta
     return out.reshape(1, tokens, hq * d)
 
 
+# --------------------------------------------------------------------------- norm + rope + append
+
+_inv_freq_tables: dict[tuple, torch.Tensor] = {}
+
+
+def rope_inv_freq(rope_theta: float, rotary_dim: int, device) -> torch.Tensor:
+    """`1 / theta^(arange(0, rot, 2) / rot)` in fp32, formed as the reference forms it (layers.py:97, 143-145)."""
+    device = torch.device(device)
+    key = (float(rope_theta), int(rotary_dim), device.index)
+    t = _inv_freq_tables.get(key)
+    if t is None:
+        import numpy as np
+        inv = np.float32(1.0) / (np.float32(rope_theta) ** (np.arange(0, rotary_dim, 2, dtype=np.float32) / np.float32(rotary_dim)))
+        t = torch.from_numpy(inv.astype(np.float32)).to(device)
+        _inv_freq_tables[key] = t
+    return t
+
+
+def qk_norm_rope_kv_append(query, k, v, q_norm_weight, k_norm_weight, positions, slot_mapping, k_cache_layer,
+                           v_cache_layer, *, eps=1e-6, rope_theta=1e7, rotary_dim=64, valid_mask=None,
+                           query_start_loc=None, packed=False):
+    """RMSNorm(q), RMSNorm(k), partial RoPE on both, K/V rows into their slots; returns the query for attention.
+
+    query `[rows, cols, Hq, D]` (may be a strided view, e.g. the first half of a `[.., Hq, 2 D]` query|gate
+    projection), k, v `[rows, cols, Hkv, D]`, positions and slot_mapping `[rows, cols]` int32; the cache layer
+    is updated in place.  Fuses nanovllm_jax/model.py:3371-3396 with the append of 3539-3550.
+    """
+    lib = _lib.load()
+    for name, t in (("query", query), ("k", k), ("v", v), ("k_cache_layer", k_cache_layer), ("v_cache_layer", v_cache_layer)):
+        _cuda(name, t)
+    if query.ndim != 4 or k.ndim != 4 or k.shape != v.shape or query.shape[:2] != k.shape[:2]:
+        raise ValueError("query [rows, cols, Hq, D] and k, v [rows, cols, Hkv, D] must agree in rows and cols")
+    rows, cols, hq, d = query.shape
+    hkv = k.shape[2]
+    if tuple(k_cache_layer.shape[-2:]) != (hkv, d) or k_cache_layer.shape != v_cache_layer.shape:
+        raise ValueError("cache layer trailing dimensions must be [num_kv_heads, head_dim]")
+    if not (k_cache_layer.is_contiguous() and v_cache_layer.is_contiguous()):
+        raise ValueError("cache layer slices must be contiguous")
+    if query.stride(3) != 1 or k.stride(3) != 1 or v.stride(3) != 1:
+        raise ValueError("the head dimension must be contiguous")
+
+    def token_strides(t, heads):
+        # tokens must be evenly spaced: [rows, cols] collapses to one token axis
+        if rows * cols > 1 and cols > 1 and rows > 1 and t.stride(0) != t.stride(1) * cols:
+            return None
+        tok = t.stride(1) if cols > 1 else (t.stride(0) if rows > 1 else heads * d)
+        return tok, t.stride(2)
+
+    qs = token_strides(query, hq)
+    if qs is None:
+        query = query.contiguous()
+        qs = (hq * d, d)
+    ks, vs = token_strides(k, hkv), token_strides(v, hkv)
+    if ks is None or ks[1] != d:
+        k = k.contiguous(); ks = (hkv * d, d)
+    if vs is None or vs[1] != d:
+        v = v.contiguous(); vs = (hkv * d, d)
+    slot_mapping = _i32("slot_mapping", slot_mapping)
+    pos = _i32("positions", positions).reshape(-1)
+    if slot_mapping.numel() != rows * cols or pos.numel() != rows * cols:
+        raise ValueError("positions and slot_mapping must have shape [rows, cols]")
+    vm = None
+    if valid_mask is not None:
+        vm = _cuda("valid_mask", valid_mask).reshape(-1).to(torch.int32).contiguous()
+    qsl, qsl_rows = None, 0
+    if query_start_loc is not None:
+        qsl = _i32("query_start_loc", query_start_loc)
+        qsl_rows = qsl.numel() - 1
+    qw, kw = q_norm_weight.contiguous(), k_norm_weight.contiguous()
+    if qw.dtype != kw.dtype or qw.numel() != d or kw.numel() != d:
+        raise ValueError("q_norm and k_norm weights must be [head_dim] of one dtype")
+    inv = rope_inv_freq(rope_theta, rotary_dim, query.device) if rotary_dim > 0 else None
+    q_out = torch.empty((rows, cols, hq, d), dtype=query.dtype, device=query.device)
+    num_slots = k_cache_layer.numel() // (hkv * d)
+    st = _status_word(query.device)
+    rc = lib.nvj_qk_norm_rope_kv_append(_ptr(query), qs[0], qs[1], _ptr(k), ks[0], _ptr(v), vs[0], _dt(query),
+                                        _ptr(qw), _ptr(kw), _dt(qw), float(eps), _ptr(inv), int(rotary_dim), _ptr(pos),
+                                        _ptr(slot_mapping), _ptr(vm), _ptr(qsl), qsl_rows, 1 if packed else 0,
+                                        rows, cols, _ptr(k_cache_layer), _ptr(v_cache_layer), _dt(k_cache_layer),
+                                        num_slots, hq, hkv, d, _ptr(q_out), _ptr(st), _stream(query.device))
+    check(rc, "nvj_qk_norm_rope_kv_append")
+    if _strict():
+        _check_word(st, "nvj_qk_norm_rope_kv_append")
+    return q_out, k_cache_layer, v_cache_layer
+
+
 # --------------------------------------------------------------------------- copies / tokens
 
 def copy_blocks(k_cache, v_cache, src_ids, dst_ids):
