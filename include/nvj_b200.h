@@ -302,6 +302,22 @@ int nvj_hybrid_restore(void* conv_table, const void* conv_pool, int64_t conv_row
                        const int32_t* table_slots, const int32_t* pool_slots, int n,
                        int32_t* status, nvj_stream_t stream);
 
+/* ---------------------------------------------------- resident decode metadata */
+
+/*
+ * Advances device-resident decode metadata by one step without the host: for every row
+ * with seq_lens[b] > 0, positions[b] = seq_lens[b] and seq_lens[b] += 1 (the scheduler's
+ * decode batch has positions = num_tokens - 1, seq_lens = num_tokens,
+ * nanovllm_jax/engine/scheduler.py:790-803).  Serves the reference's resident / static decode
+ * metadata (nanovllm_jax/engine/scheduler.py:1100-1219, where the compiled executor recomputes
+ * width-1 positions from seq_lens, nanovllm_jax/engine/model_executor.py:560-562), so that a
+ * whole decode step can be replayed from a CUDA graph.  A row that would outgrow
+ * table_width * block_size is flagged NVJ_DEV_BAD_LENGTH and not advanced.
+ */
+int nvj_advance_decode_metadata(int32_t* seq_lens, int32_t* positions, int batch,
+                                int table_width, int block_size, int32_t* status,
+                                nvj_stream_t stream);
+
 /* ------------------------------------------------------------------ tokens */
 
 /*

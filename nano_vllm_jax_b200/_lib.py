@@ -57,6 +57,7 @@ SIGNATURES = {
                                     c_int64, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
     "nvj_hybrid_restore": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int64,
                                    c_int64, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
+    "nvj_advance_decode_metadata": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
     "nvj_row_argmax": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p]),
 }
 

@@ -131,6 +131,23 @@ static int launch_copy_rows(const void* src, long long src_rows, const int32_t* 
   return cudaGetLastError() == cudaSuccess ? NVJ_OK : NVJ_ERR_LAUNCH;
 }
 
+// One decode step of the batch metadata, on the device: every active row (seq_len > 0) grows by
+// the token it is about to append; its position is the old length.  Rows that would outgrow
+// their block table are flagged and left alone.
+__global__ void advance_decode_metadata_kernel(int32_t* seq_lens, int32_t* positions, int batch, long long capacity,
+                                               int32_t* status) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= batch) return;
+  const int len = seq_lens[b];
+  if (len <= 0) return;
+  if ((long long)len + 1 > capacity) {
+    if (status) atomicOr(status, NVJ_DEV_BAD_LENGTH);
+    return;
+  }
+  positions[b] = len;
+  seq_lens[b] = len + 1;
+}
+
 }  // namespace nvj
 
 extern "C" int nvj_abi_version(void) { return NVJ_ABI_VERSION; }
@@ -202,6 +219,18 @@ extern "C" int nvj_hybrid_restore(void* conv_table, const void* conv_pool, int64
                                   int32_t* status, nvj_stream_t stream) {
   return hybrid_copy(conv_pool, conv_table, conv_row_bytes, rec_pool, rec_table, rec_row_bytes,
                      pool_rows, table_rows, pool_slots, table_slots, n, status, stream);
+}
+
+extern "C" int nvj_advance_decode_metadata(int32_t* seq_lens, int32_t* positions, int batch,
+                                           int table_width, int block_size, int32_t* status,
+                                           nvj_stream_t stream) {
+  using namespace nvj;
+  if (batch < 0 || table_width < 0 || block_size <= 0) return NVJ_ERR_INVALID_ARGUMENT;
+  if (batch == 0) return NVJ_OK;
+  if (!seq_lens || !positions) return NVJ_ERR_INVALID_ARGUMENT;
+  advance_decode_metadata_kernel<<<(batch + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      seq_lens, positions, batch, (long long)table_width * block_size, status);
+  return cudaGetLastError() == cudaSuccess ? NVJ_OK : NVJ_ERR_LAUNCH;
 }
 
 extern "C" int nvj_row_argmax(const float* x, int rows, int row_len, int32_t* tokens,
