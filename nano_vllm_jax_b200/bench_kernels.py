@@ -116,6 +116,20 @@ def decode_cases(dev, iters):
            Timer(dev, max(3, iters // 4), flush=False).run(
                lambda: K.paged_decode_attention(q[:sub, 0], k[0], v[0], tables[:sub], t_lens[:sub], SCALE, variant=1)),
            int(lens[:sub].sum()) * TOKEN_BYTES, {"workload": "c2, first 16 rows"})
+    # speculative-verify decode: 4 query tokens per row at the last 4 positions (rows already appended)
+    from . import kv_cache as kvc
+    width = 4
+    qw = _randn_bf16((rows, width, HQ, D), 6, dev)
+    wpos = (t_lens[:, None] - width + torch.arange(width, device=dev, dtype=torch.int32)[None, :]).contiguous()
+    wbytes = kv_bytes + table_bytes + rows * width * (HQ * D * 2 + HQ * D * 4)
+    report("wide decode, 4 query tokens per row (packed tensor-core route)",
+           big.run(lambda: kvc.paged_attention_decode(qw, k, v, tables, t_lens, BS, SCALE, 4, positions=wpos, out_dtype=torch.float32)),
+           wbytes, {"workload": "c2, width 4"})
+    rep_tables = tables.repeat_interleave(width, dim=0)
+    rep_lens = torch.minimum(t_lens[:, None], wpos + 1).reshape(-1).contiguous()
+    report("wide decode as 4 width-1 rows per sequence (decode kernel)",
+           big.run(lambda: K.paged_decode_attention(qw.reshape(rows * width, HQ, D), k[0], v[0], rep_tables, rep_lens, SCALE)),
+           wbytes, {"workload": "c2, width 4", "note": "K/V read once per query token"})
     K.check_device_status(dev)
     del k, v
 

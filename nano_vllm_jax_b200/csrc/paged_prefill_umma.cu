@@ -372,8 +372,9 @@ prefill_umma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_cons
     if (threadIdx.x == 0) atomicOr(p.status, NVJ_DEV_BAD_LENGTH);
     kv_len = p.table_width * kBlk;
   }
-  // positions grow along a row's chunk: the tile's last token sees the most keys
-  const int max_pos = (row >= 0 && ntok > 0) ? p.positions[tok0 + ntok - 1] : -1;
+  // the token of the tile that sees the most keys bounds the key range (positions need not grow along the tile:
+  // a rectangular batch pads rows with position 0)
+  const int max_pos = __reduce_max_sync(0xffffffffu, (row >= 0 && lane < ntok) ? p.positions[tok0 + lane] : -1);
   const int key_end = kv_len < max_pos + 1 ? kv_len : max_pos + 1;
   const int n_tiles = key_end > 0 ? (key_end + kUmKeys - 1) / kUmKeys : 0;
 

@@ -379,8 +379,11 @@ prefill_umma2_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_con
     if (threadIdx.x == 0 && rank == 0) atomicOr(p.status, NVJ_DEV_BAD_LENGTH);
     kv_len = p.table_width * kBlk;
   }
-  // positions grow along a row's chunk: the pair's last token sees the most keys
-  const int max_pos = p.positions[sm.pair_last_tok];
+  // the token of the pair that sees the most keys bounds the key range (positions need not grow along the tiles)
+  const int pair_tok0 = tok0 - rank * kU2Tokens, pair_n = sm.pair_last_tok - pair_tok0 + 1;
+  int seen = lane < pair_n ? p.positions[pair_tok0 + lane] : -1;
+  if (lane + 32 < pair_n) seen = max(seen, p.positions[pair_tok0 + lane + 32]);
+  const int max_pos = __reduce_max_sync(0xffffffffu, seen);
   const int key_end = kv_len < max_pos + 1 ? kv_len : max_pos + 1;
   const int n_tiles = key_end > 0 ? (key_end + kU2Keys - 1) / kU2Keys : 0;
   if (n_tiles == 0) return;  // same decision in both CTAs

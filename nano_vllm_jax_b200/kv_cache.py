@@ -229,9 +229,8 @@ def paged_attention_decode(query, k_cache, v_cache, block_table, kv_lens, block_
                            out_dtype=None):
     """Decode attention over a bounded paged window (kv_cache.py:852-998) -> `[B, T, Hq*D]`.
 
-    Query width > 1 (speculative verification) applies the causal mask
-    p <= positions[b, t] by running each (row, t) as a width-1 row with length
-    min(kv_lens[b], positions[b, t] + 1).
+    Query width > 1 (speculative verification, rectangular prefill) applies the causal mask
+    p <= positions[b, t]; such a batch travels the packed prefill route with rows of equal width.
     """
     batch, query_len, num_heads, head_dim = query.shape
     if query_len < 1:
@@ -264,9 +263,15 @@ def paged_attention_decode(query, k_cache, v_cache, block_table, kv_lens, block_
     lens = kv_lens.to(torch.int32).clamp(max=int(max_kv_len))
     tables = block_table.to(torch.int32)
     if positions is not None and query_len > 1:
-        lens = torch.minimum(lens[:, None], positions.to(torch.int32) + 1).reshape(-1)
-        tables = tables.repeat_interleave(query_len, dim=0)
-    elif positions is not None:
+        # a rectangular batch is a packed batch with rows of equal width: K/V of a row are then read once for all
+        # of its query tokens (tensor-core tiles for the model's shape) instead of once per token
+        qsl = torch.arange(batch + 1, dtype=torch.int32, device=query.device) * query_len
+        out = _k.packed_paged_prefill_attention(query.reshape(1, batch * query_len, num_heads, head_dim), k_layer, v_layer,
+                                                tables.contiguous(), lens.contiguous(),
+                                                positions.to(torch.int32).reshape(1, -1), qsl, block_size, scale,
+                                                num_key_value_groups)
+        return out.reshape(batch, query_len, num_heads * head_dim).to(_promoted(query, k_cache, out_dtype))
+    if positions is not None:
         lens = torch.minimum(lens, positions.to(torch.int32).reshape(-1) + 1)
     out = _k.paged_decode_attention(query.reshape(batch * query_len, num_heads, head_dim), k_layer, v_layer,
                                     tables, lens, scale)

@@ -231,6 +231,25 @@ def test_wide_decode_with_positions_and_reference_dtype():
                                   to_torch(c["seq_lens"]), BS, SCALE, 4)
 
 
+def test_rectangular_prefill_with_rows_padded_at_position_zero():
+    # rows of a rectangular [B, T] prefill are padded with (token 0, position 0): positions do not grow along a row,
+    # and the key range of a query tile is set by the token that sees the most keys, wherever it sits
+    from nano_vllm_jax_b200 import kv_cache as kv
+    c = decode_case(12, 256, 3, 150, 400)
+    rng = np.random.default_rng(12)
+    width = 70
+    q = rng.standard_normal((3, width, 8, 256)).astype(bfloat16)
+    real = np.array([70, 41, 9])
+    pos = np.zeros((3, width), np.int32)
+    for r in range(3):
+        pos[r, :real[r]] = c["seq_lens"][r] - real[r] + np.arange(real[r])
+    ref = R.paged_attention_prefill(q, c["k_cache"], c["v_cache"], c["tables"], c["seq_lens"], pos, BS, SCALE, 4)
+    out = kv.paged_attention_prefill(to_torch(q), to_torch(c["k_cache"]), to_torch(c["v_cache"]), to_torch(c["tables"]),
+                                     to_torch(c["seq_lens"]), to_torch(pos), BS, SCALE, 4, out_dtype=torch.float32)
+    assert out.shape == (3, width, 2048)
+    assert np.abs(to_numpy(out) - ref).max() <= TIGHT
+
+
 @pytest.mark.parametrize("variant", [GENERIC, PIPELINED])
 def test_block_id_outside_the_pool_is_flagged_not_read(variant):
     K = _K()
