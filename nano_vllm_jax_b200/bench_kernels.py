@@ -226,6 +226,52 @@ def norm_rope_append_cases(dev, iters):
     del k, v
 
 
+def comparator_case(dev, iters):
+    """External yard-stick, not a dependency of the product: FlashInfer's batch decode over the same paged cache
+    (the reference's promoted decode route is this library, nanovllm_jax/kernels/flashinfer_ffi.py:991-1086),
+    timed on the C2 rows beside this library's decode kernel.  Skipped with a line saying so when FlashInfer
+    cannot be imported or cannot build its kernel offline."""
+    try:
+        import flashinfer
+    except Exception as exc:  # pragma: no cover
+        print(json.dumps({"kernel": "flashinfer BatchDecodeWithPagedKVCacheWrapper", "unavailable": repr(exc)}), flush=True)
+        return
+    rng = np.random.default_rng(2)
+    rows, pool = 256, 400_000
+    ctx = rng.integers(1024, 4097, size=rows)
+    lens = (ctx + 1).astype(np.int32)
+    tables_np = tables_for(lens, pool, rng)
+    need = -(-lens // BS)
+    indptr = np.concatenate([[0], np.cumsum(need)]).astype(np.int32)
+    indices = np.concatenate([tables_np[r, :need[r]] for r in range(rows)]).astype(np.int32)
+    last = ((lens - 1) % BS + 1).astype(np.int32)
+    k = _randn_bf16((pool, BS, HKV, D), 1, dev)
+    v = _randn_bf16((pool, BS, HKV, D), 2, dev)
+    q = _randn_bf16((rows, HQ, D), 3, dev)
+    tables, t_lens = torch.from_numpy(tables_np).to(dev), torch.from_numpy(lens).to(dev)
+    nbytes = int(lens.sum()) * TOKEN_BYTES + int(need.sum()) * 4 + rows * HQ * D * (2 + 4) + rows * 12
+    big = Timer(dev, iters, flush=False)
+    mine = K.paged_decode_attention(q, k, v, tables, t_lens, SCALE)
+    report("paged_decode (this library)", big.run(lambda: K.paged_decode_attention(q, k, v, tables, t_lens, SCALE)), nbytes,
+           {"workload": "c2"})
+    ws = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    for tc in (False, True):
+        name = "flashinfer %s BatchDecodeWithPagedKVCacheWrapper (use_tensor_cores=%s)" % (flashinfer.__version__, tc)
+        try:
+            w = flashinfer.BatchDecodeWithPagedKVCacheWrapper(ws, "NHD", use_tensor_cores=tc)
+            w.plan(torch.from_numpy(indptr).to(dev), torch.from_numpy(indices).to(dev), torch.from_numpy(last).to(dev),
+                   HQ, HKV, D, BS, pos_encoding_mode="NONE", q_data_type=torch.bfloat16, kv_data_type=torch.bfloat16,
+                   sm_scale=SCALE)
+            theirs = w.run(q, (k, v))
+            us = big.run(lambda: w.run(q, (k, v)))
+        except Exception as exc:
+            print(json.dumps({"kernel": name, "unavailable": repr(exc)[:200]}), flush=True)
+            continue
+        report(name, us, nbytes, {"workload": "c2", "max_abs_diff_vs_this_library": float((mine - theirs.float()).abs().max()),
+                                  "note": "bf16 output; plan() outside the timed region"})
+    del k, v
+
+
 def mixed_step_case(dev, iters):
     """The KV path of one mixed continuous-batching step over 6 layers: 32 decode rows (contexts in
     [128, 2048]) plus 2 prefill chunks of 256 tokens, packed; per layer one append and one attention."""
@@ -284,7 +330,7 @@ def hybrid_cases(dev, iters):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--iters", type=int, default=20)
-    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "hybrid", "mixed", "front"])
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "hybrid", "mixed", "front", "comparator"])
     ap.add_argument("--small", action="store_true",
                     help="prefill cases on a 1-layer, 4096-block cache (128 MiB): the size to run under a profiler")
     args = ap.parse_args()
@@ -300,6 +346,8 @@ def main():
         mixed_step_case(dev, args.iters)
     if args.only in ("all", "front"):
         norm_rope_append_cases(dev, args.iters)
+    if args.only == "comparator":
+        comparator_case(dev, args.iters)
 
 
 if __name__ == "__main__":
