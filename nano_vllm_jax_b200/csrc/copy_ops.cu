@@ -88,9 +88,31 @@ row_argmax_kernel(const float* x, int row_len, int32_t* tokens) {
   const float* row = x + (long long)blockIdx.x * row_len;
   float best = -INFINITY;
   int best_i = 0x7fffffff;
-  for (int i = threadIdx.x; i < row_len; i += blockDim.x) {
-    const float v = row[i];
-    if (v > best || (v == best && i < best_i)) { best = v; best_i = i; }
+  if ((row_len & 3) == 0 && (reinterpret_cast<uintptr_t>(row) & 15u) == 0) {
+    // 16-byte loads, four in flight per thread: the row is read in one or two round trips instead of row_len / 128
+    const float4* row4 = reinterpret_cast<const float4*>(row);
+    const int n4 = row_len >> 2;
+    for (int base = threadIdx.x; base < n4; base += 4 * blockDim.x) {
+      float4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int j = base + u * blockDim.x;
+        v[u] = j < n4 ? row4[j] : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i0 = (base + u * blockDim.x) * 4;
+        const float e[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+          if (e[c] > best || (e[c] == best && i0 + c < best_i)) { best = e[c]; best_i = i0 + c; }
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < row_len; i += blockDim.x) {
+      const float v = row[i];
+      if (v > best || (v == best && i < best_i)) { best = v; best_i = i; }
+    }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {

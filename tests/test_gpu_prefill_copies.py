@@ -233,3 +233,12 @@ def test_row_argmax_first_maximum_wins():
     assert tok.dtype == torch.int32
     assert torch.equal(tok.long(), torch.argmax(x, dim=1)) or int(tok[3]) == 100
     assert int(tok[3]) == 100
+    # every row length class: vector path with a ragged tail of float4s, the scalar path (odd length, misaligned rows)
+    for n in (4, 500, 516, 2048, 4100, 7, 1001):
+        y = torch.randn((5, n), generator=g, device="cuda")
+        y[2, n - 1] = 60.0            # the maximum in the very last element
+        y[4, 0] = y[4, n // 2] = 70.0  # a tie: the first index wins
+        t = K.row_argmax(y)
+        want = torch.argmax(y, dim=1)
+        assert int(t[2]) == n - 1 and int(t[4]) == 0
+        assert torch.equal(t[[0, 1, 3]].long(), want[[0, 1, 3]])
