@@ -73,7 +73,9 @@ class B200Backend:
     # ---- metadata (backends.py:910-978)
     def build_attention_metadata(self, positions, block_tables, seq_lens, block_size, is_prefill,
                                  query_start_loc=None, num_prefill_tokens=None, num_decode_tokens=None,
-                                 token_row_ids=None, max_query_len=None) -> AttentionMetadata:
+                                 token_row_ids=None, max_query_len=None, query_lens_host=None) -> AttentionMetadata:
+        # `query_lens_host` (the scheduler's host-side query lengths, engine/scheduler.py `query_lens_host`) is an
+        # optional extension: it tells a packed batch how many rows hold a single token without a device read
         if positions.ndim != 2:
             raise ValueError("positions must be a 2D tensor [batch, query_len]")
         if block_tables.ndim != 2:
@@ -107,7 +109,9 @@ class B200Backend:
             positions=positions,
             max_kv_len=block_tables.shape[1] * block_size if not is_prefill else None,
             token_row_ids=token_row_ids,
-            max_query_len=max_query_len if max_query_len is not None else query_len)
+            max_query_len=max_query_len if max_query_len is not None else query_len,
+            single_token_rows=(sum(1 for n in query_lens_host if int(n) == 1)
+                               if (query_lens_host is not None and token_row_ids is not None) else None))
 
     # ---- append (backends.py:980-1067)
     def write_kv(self, layer_id, k, v, cache: KVCacheStorage, metadata: AttentionMetadata) -> KVCacheStorage:
@@ -130,7 +134,8 @@ class B200Backend:
                 return kvc.paged_attention_prefill_packed(
                     query, cache.k_cache, cache.v_cache, metadata.block_tables, metadata.seq_lens,
                     metadata.positions, metadata.token_row_ids, metadata.query_start_loc, block_size, scale,
-                    num_key_value_groups, layer_idx=layer_id, max_query_len=metadata.max_query_len, out_dtype=f32)
+                    num_key_value_groups, layer_idx=layer_id, max_query_len=metadata.max_query_len, out_dtype=f32,
+                    num_decode_rows=metadata.single_token_rows)
             if metadata.positions is None:
                 return kvc.paged_attention(query, cache.k_cache, cache.v_cache, metadata.slot_mapping,
                                            metadata.seq_lens, scale, num_key_value_groups, layer_idx=layer_id,

@@ -174,7 +174,7 @@ def prefill_and_copy_cases(dev, iters, small=False):
     nbytes = total * TOKEN_BYTES * 2 + int(kv_lens.sum()) * TOKEN_BYTES + total * (HQ * D * 2 + HQ * D * 4)
     for variant, name in ((2, "mma.sync tiles"), (3, "tcgen05 tiles"), (4, "tcgen05 CTA pairs")):
         us = tm.run(lambda: K.packed_paged_prefill_attention(q, k[0], v[0], t_tab, t_len, t_pos, t_qsl, BS, SCALE, 4,
-                                                             variant=variant))
+                                                             variant=variant, num_decode_rows=0))
         report("packed prefill attention, %s (%d tokens, %d rows)" % (name, total, len(rows)), us, nbytes,
                {"workload": "c3 chunk", "TFLOP/s": round(flops / us / 1e6, 2), "flops": flops})
     # long prompts in a single chunk, nothing cached
@@ -192,7 +192,7 @@ def prefill_and_copy_cases(dev, iters, small=False):
             if variant == 2 and n_long > 4096:
                 continue
             us = tm.run(lambda: K.packed_paged_prefill_attention(lq, k[0], v[0], l_tab, l_len, l_pos, l_qsl, BS, SCALE, 4,
-                                                                 variant=variant))
+                                                                 variant=variant, num_decode_rows=0))
             report("packed prefill attention, %s (one row of %d tokens)" % (name, n_long), us, l_bytes,
                    {"workload": "long prompt", "TFLOP/s": round(l_flops / us / 1e6, 2), "flops": l_flops})
         del lq
@@ -296,7 +296,8 @@ def mixed_step_case(dev, iters):
     nv = _randn_bf16((1, total, HKV, D), 25, dev)
     be = B200Backend(device=dev)
     cache = KVCacheStorage(k, v)
-    md = be.build_attention_metadata(pos, tables, t_len, BS, True, query_start_loc=qsl, token_row_ids=rid)
+    md = be.build_attention_metadata(pos, tables, t_len, BS, True, query_start_loc=qsl, token_row_ids=rid,
+                                     query_lens_host=tuple(int(n) for n in qlens))
 
     def step():
         for layer in range(layers):

@@ -444,11 +444,13 @@ def paged_decode_attention_with_kv_append(query, new_k, new_v, k_cache, v_cache,
 
 def packed_paged_prefill_attention(query, k_cache_layer, v_cache_layer, block_table, kv_lens, positions,
                                    query_start_loc, block_size, scale, num_key_value_groups,
-                                   max_query_len=None, variant=None):
+                                   max_query_len=None, variant=None, num_decode_rows=None):
     """Ragged packed prefill: query `[1, T, Hq, D]` -> fp32 `[1, T, Hq*D]`, padded tokens 0.
 
     `variant`: 0 automatic, 1 generic, 2 mma.sync tiles, 3 tcgen05 tiles, 4 tcgen05 tiles on CTA pairs (default: the
-    `NVJ_PREFILL_VARIANT` environment variable, else 0).
+    `NVJ_PREFILL_VARIANT` environment variable, else 0).  `num_decode_rows`: how many rows hold a single query
+    token (the scheduler's `num_decode_tokens` of a mixed batch); 0 spares the launch that serves such rows,
+    None (unknown) keeps it.
     """
     lib = _lib.load()
     _check_nhd_cache(k_cache_layer, v_cache_layer)
@@ -476,17 +478,18 @@ def packed_paged_prefill_attention(query, k_cache_layer, v_cache_layer, block_ta
     if _poison():
         out.fill_(float("nan"))
     st = _status_word(q.device)
-    ws = _workspace(q.device, rows)
+    ws = _workspace(q.device, rows) if (num_decode_rows is None or num_decode_rows > 0) else None
     rc = lib.nvj_paged_prefill_packed(_ptr(q), _dt(q), _ptr(k_cache_layer), _ptr(v_cache_layer),
                                       _dt(k_cache_layer), pages, page_size, hkv, d, hq, _ptr(block_table),
                                       block_table.shape[1], _ptr(kv_lens), _ptr(pos), _ptr(qsl), rows,
-                                      tokens, float(scale), _ptr(out), _ptr(st), _ptr(ws.buf), ws.nbytes,
+                                      tokens, float(scale), _ptr(out), _ptr(st), _ptr(ws.buf) if ws else None, ws.nbytes if ws else 0,
                                       int(os.environ.get("NVJ_PREFILL_VARIANT", "0")) if variant is None else int(variant),
                                       _stream(q.device))
     check(rc, "nvj_paged_prefill_packed")
     if _strict():
         _check_word(st, "nvj_paged_prefill_packed")
-        _check_word(ws.status_tensor(), "nvj_paged_prefill_packed (decode rows)", ws)
+        if ws is not None:
+            _check_word(ws.status_tensor(), "nvj_paged_prefill_packed (decode rows)", ws)
     return out.reshape(1, tokens, hq * d)
 
 

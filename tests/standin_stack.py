@@ -90,7 +90,8 @@ def forward(weights, attn, backend, cache: KVCacheStorage, batch, block_size=16,
     """
     tokens, positions = batch.tokens, batch.positions
     md = backend.build_attention_metadata(positions, batch.block_tables, batch.seq_lens, block_size, batch.is_prefill,
-                                          query_start_loc=batch.query_start_loc, token_row_ids=batch.token_row_ids)
+                                          query_start_loc=batch.query_start_loc, token_row_ids=batch.token_row_ids,
+                                          query_lens_host=batch.query_lens_host if batch.token_row_ids is not None else None)
     shape = tokens.shape  # [1, T] packed or [B, 1] decode
     flat_tok, flat_pos = tokens.reshape(-1).long(), positions.reshape(-1)
     # Dense math in fp32 on the bf16-valued weights; only q/k/v are rounded to bf16, at the boundary
