@@ -172,7 +172,7 @@ def prefill_and_copy_cases(dev, iters, small=False):
     visible = int(sum(int(pos[0, i]) + 1 for i in range(total)))
     flops = 4 * HQ * D * visible
     nbytes = total * TOKEN_BYTES * 2 + int(kv_lens.sum()) * TOKEN_BYTES + total * (HQ * D * 2 + HQ * D * 4)
-    for variant, name in ((2, "mma.sync tiles"), (3, "tcgen05 tiles"), (4, "tcgen05 CTA pairs")):
+    for variant, name in ((2, "mma.sync tiles"), (3, "tcgen05 tiles"), (4, "tcgen05 CTA pairs"), (5, "tcgen05 CTA pairs, bf16 P")):
         us = tm.run(lambda: K.packed_paged_prefill_attention(q, k[0], v[0], t_tab, t_len, t_pos, t_qsl, BS, SCALE, 4,
                                                              variant=variant, num_decode_rows=0))
         report("packed prefill attention, %s (%d tokens, %d rows)" % (name, total, len(rows)), us, nbytes,
@@ -188,7 +188,7 @@ def prefill_and_copy_cases(dev, iters, small=False):
         lq = _randn_bf16((1, n_long, HQ, D), 16, dev)
         l_flops = 4 * HQ * D * (n_long * (n_long + 1) // 2)
         l_bytes = n_long * TOKEN_BYTES + n_long * (HQ * D * 2 + HQ * D * 4)
-        for variant, name in ((2, "mma.sync tiles"), (3, "tcgen05 tiles"), (4, "tcgen05 CTA pairs")):
+        for variant, name in ((2, "mma.sync tiles"), (3, "tcgen05 tiles"), (4, "tcgen05 CTA pairs"), (5, "tcgen05 CTA pairs, bf16 P")):
             if variant == 2 and n_long > 4096:
                 continue
             us = tm.run(lambda: K.packed_paged_prefill_attention(lq, k[0], v[0], l_tab, l_len, l_pos, l_qsl, BS, SCALE, 4,

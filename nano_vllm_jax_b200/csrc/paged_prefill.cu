@@ -19,7 +19,7 @@ int launch_prefill_umma2(const void* q, int q_dtype, const char* k_cache, const 
                          long long num_blocks, const int32_t* block_tables, int table_width,
                          const int32_t* kv_lens, const int32_t* positions, const int32_t* query_start_loc,
                          int rows, int token_bucket, float scale, float* out, int32_t* status,
-                         int skip_single, cudaStream_t stream);
+                         int skip_single, int split_p, cudaStream_t stream);
 int launch_prefill_umma(const void* q, int q_dtype, const char* k_cache, const char* v_cache,
                         long long num_blocks, const int32_t* block_tables, int table_width,
                         const int32_t* kv_lens, const int32_t* positions, const int32_t* query_start_loc,
@@ -41,7 +41,7 @@ extern "C" int nvj_paged_prefill_packed(const void* q, int q_dtype, const void* 
   if (rows < 0 || token_bucket < 0 || table_width < 0 || num_blocks < 0 || block_size <= 0 ||
       num_kv_heads <= 0 || num_q_heads <= 0 || head_dim <= 0)
     return NVJ_ERR_INVALID_ARGUMENT;
-  if (num_q_heads % num_kv_heads != 0 || variant < 0 || variant > 4) return NVJ_ERR_INVALID_ARGUMENT;
+  if (num_q_heads % num_kv_heads != 0 || variant < 0 || variant > 5) return NVJ_ERR_INVALID_ARGUMENT;
   if (token_bucket == 0) return NVJ_OK;
   if (!q || !k_cache_layer || !v_cache_layer || !block_tables || !kv_lens || !positions ||
       !query_start_loc || !out || !status)
@@ -96,10 +96,11 @@ extern "C" int nvj_paged_prefill_packed(const void* q, int q_dtype, const void* 
     const char* vc = static_cast<const char*>(v_cache_layer);
     // tcgen05 tiles first (CTA pairs, then single CTAs); they decline when the driver has no tensor-map
     // encoder or the scale is not positive, and the mma.sync tiles take over
-    if (variant == 0 || variant == 4) {
+    if (variant == 0 || variant == 4 || variant == 5) {
       const int rc = launch_prefill_umma2(q, q_dtype, kc, vc, num_blocks, block_tables, table_width, kv_lens, positions,
-                                          query_start_loc, rows, token_bucket, scale, out, status, skip_single, s);
-      if (rc != NVJ_ERR_UNSUPPORTED || variant == 4) return rc;
+                                          query_start_loc, rows, token_bucket, scale, out, status, skip_single,
+                                          variant == 5 ? 0 : 1, s);
+      if (rc != NVJ_ERR_UNSUPPORTED || variant != 0) return rc;
     }
     if (variant == 0 || variant == 3) {
       const int rc = launch_prefill_umma(q, q_dtype, kc, vc, num_blocks, block_tables, table_width, kv_lens, positions,

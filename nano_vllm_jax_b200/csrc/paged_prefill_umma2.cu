@@ -49,6 +49,7 @@ struct Umma2Params {
   int32_t* status;
   long long num_blocks;
   int rows, token_bucket, table_width, skip_single, q_dtype;
+  int split_p;  // 1: P enters P V as two bf16 terms (hi + lo), 0: as one (the weights are then bf16-rounded)
   float scale;
 };
 
@@ -201,7 +202,7 @@ __device__ __forceinline__ void u2_mma_warp(Umma2Smem& sm, const Umma2Params& p,
       for (int kk = 0; kk < 4; ++kk) {  // 16 keys per MMA: 8 columns of P, two 8-key groups of V
         const uint64_t dv = v_desc + (uint64_t)((kk * 2048) >> 4);
         umma2_bf16_ts(tmem + kU2ColO, pa + kk * 8, dv, idesc, (t > 0 || kk > 0) ? 1u : 0u);
-        umma2_bf16_ts(tmem + kU2ColO, pa + 32 + kk * 8, dv, idesc, 1u);
+        if (p.split_p) umma2_bf16_ts(tmem + kU2ColO, pa + 32 + kk * 8, dv, idesc, 1u);
       }
       umma2_commit_pair(smem_u32(&sm.v_empty[sv]));
       umma2_commit_pair(smem_u32(&sm.pv_done));
@@ -312,7 +313,7 @@ __device__ __forceinline__ void u2_softmax_warps(Umma2Smem& sm, const Umma2Param
     // every phase of pv_done is observed in turn (parity waits tell only two phases apart)
     if (t >= 1 && !um_wait(&sm.pv_done, (t - 1) & 1, &sm.abort_flag, p.status)) return;
     tmem_st16(s_tmem + half * 16, hi);
-    tmem_st16(s_tmem + 32 + half * 16, lo);
+    if (p.split_p) tmem_st16(s_tmem + 32 + half * 16, lo);
     tmem_st_wait();
     tc_fence_before_sync();
     mbar_arrive_leader(smem_u32(&sm.p_full));
@@ -455,7 +456,7 @@ int launch_prefill_umma2(const void* q, int q_dtype, const char* k_cache, const 
                          long long num_blocks, const int32_t* block_tables, int table_width,
                          const int32_t* kv_lens, const int32_t* positions, const int32_t* query_start_loc,
                          int rows, int token_bucket, float scale, float* out, int32_t* status,
-                         int skip_single, cudaStream_t stream) {
+                         int skip_single, int split_p, cudaStream_t stream) {
   static bool opted_in[64];
   constexpr int kSmemBytes = (int)sizeof(Umma2Smem) + 1024;
   static_assert(kSmemBytes <= 232448, "tiles exceed the shared memory of one CTA");
@@ -477,7 +478,7 @@ int launch_prefill_umma2(const void* q, int q_dtype, const char* k_cache, const 
   p.q = q; p.q_dtype = q_dtype;
   p.block_tables = block_tables; p.kv_lens = kv_lens; p.positions = positions; p.query_start_loc = query_start_loc;
   p.out = out; p.status = status; p.num_blocks = num_blocks; p.rows = rows; p.token_bucket = token_bucket;
-  p.table_width = table_width; p.skip_single = skip_single; p.scale = scale;
+  p.table_width = table_width; p.skip_single = skip_single; p.scale = scale; p.split_p = split_p;
   const int pairs = (token_bucket + 2 * kU2Tokens - 1) / (2 * kU2Tokens) + rows;
   dim3 grid(2 * pairs, kHkv, 1);
   prefill_umma2_kernel<<<grid, kU2Threads, kSmemBytes, stream>>>(k_map, v_map, p);

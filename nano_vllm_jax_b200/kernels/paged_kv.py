@@ -447,7 +447,8 @@ def packed_paged_prefill_attention(query, k_cache_layer, v_cache_layer, block_ta
                                    max_query_len=None, variant=None, num_decode_rows=None):
     """Ragged packed prefill: query `[1, T, Hq, D]` -> fp32 `[1, T, Hq*D]`, padded tokens 0.
 
-    `variant`: 0 automatic, 1 generic, 2 mma.sync tiles, 3 tcgen05 tiles, 4 tcgen05 tiles on CTA pairs (default: the
+    `variant`: 0 automatic, 1 generic, 2 mma.sync tiles, 3 tcgen05 tiles, 4 tcgen05 tiles on CTA pairs, 5 = 4 with
+    bf16-rounded softmax weights in P V (default: the
     `NVJ_PREFILL_VARIANT` environment variable, else 0).  `num_decode_rows`: how many rows hold a single query
     token (the scheduler's `num_decode_tokens` of a mixed batch); 0 spares the launch that serves such rows,
     None (unknown) keeps it.
