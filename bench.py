@@ -358,7 +358,15 @@ def run_b200(args, w):
     # append + decode -> token argmax, one graph launch per step; the token all-gather (N > 1) follows each replay.
     from nano_vllm_jax_b200.engine.resident_decode import DecodeStepGraph, ResidentDecodeMetadata
     meta = ResidentDecodeMetadata(rows, tables.shape[1], BS, device=dev)
-    graph = DecodeStepGraph(meta, k_cache, v_cache, 0, SCALE, HQ // HKV)
+    token_gather = None
+    if world > 1 and os.environ.get("NVJ_BENCH_NCCL_GATHER", "0") != "1":
+        from nano_vllm_jax_b200.parallel import P2PTokenGather
+        try:  # peer stores over NVLink inside the graph; all ranks succeed or all fall back to the NCCL gather
+            token_gather = P2PTokenGather(rows)
+        except Exception as exc:
+            if rank == 0:
+                print(f"[bench] NVLink token gather unavailable ({exc!r}); using the NCCL all-gather", file=sys.stderr, flush=True)
+    graph = DecodeStepGraph(meta, k_cache, v_cache, 0, SCALE, HQ // HKV, token_gather=token_gather)
     graph.query.copy_(q); graph.new_k.copy_(nk); graph.new_v.copy_(nv)
     graph_ready = [False]
 
@@ -370,7 +378,7 @@ def run_b200(args, w):
         else:
             _, tok = graph.replay()
         step_no[0] += 1
-        if world > 1:
+        if world > 1 and token_gather is None:
             dist.all_gather_into_tensor(gathered, tok)
 
     sampler = ClockSampler(local)
@@ -382,6 +390,12 @@ def run_b200(args, w):
     try:
         ms_dev = timed(graph_step)
         meta.check()
+        if token_gather is not None:
+            token_gather.check()
+            step_mode += " -> token all-gather by NVLink peer stores, all in the graph"
+            ok = torch.equal(graph.gathered.view(world, rows)[rank], graph.tokens)
+            if not ok:
+                raise SystemExit("token all-gather returned something else than this rank's own tokens")
     except Exception as exc:  # a capture problem must not cost the measurement: the eager pass is the same step
         if world > 1:
             raise
@@ -419,7 +433,8 @@ def run_b200(args, w):
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": args.workload + ": " + w["desc"], "rows_total": total_rows, "rows_per_gpu": rows,
                        "layers": 1, "pool_blocks_per_gpu": pool, "cache_timing": "inputs exceed L2 (>= 1.3 GB of K/V read per step)",
-                       "parallelism": f"request-partitioned x{world}, NCCL all-gather of tokens" if world > 1 else "single GPU"},
+                       "parallelism": (f"request-partitioned x{world}, all-gather of tokens (" +
+                                       ("NVLink peer stores" if token_gather is not None else "NCCL") + ")") if world > 1 else "single GPU"},
             "e2e": {"value": total_rows / (ms_e2e / K_steps * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e / K_steps,
                     "mode": "HostDecodePipeline: 2 steps in flight on copy/compute/copy streams; every step copies all operands "

@@ -322,6 +322,32 @@ int nvj_advance_decode_metadata(int32_t* seq_lens, int32_t* positions, int batch
                                 int table_width, int block_size, int32_t* status,
                                 nvj_stream_t stream);
 
+/* ------------------------------------------------- token all-gather over NVLink */
+
+/*
+ * All-gather of n int32 per rank (the per-step output tokens) for one process per GPU on one
+ * node, by peer stores into exchange buffers that the ranks map through CUDA IPC.  The reference
+ * is single-device and has no counterpart; the host side that exchanges the handles is
+ * nano_vllm_jax_b200/parallel.py (P2PTokenGather).
+ *
+ *   nvj_p2p_gather_buffer_bytes   size of one rank's exchange buffer for (world <= 16, n)
+ *   nvj_p2p_buffer_create         cudaMalloc + zero + IPC handle (64 bytes) of this rank's buffer
+ *   nvj_p2p_buffer_open / close   map / unmap a peer's buffer from its handle
+ *   nvj_p2p_buffer_destroy        free this rank's buffer (after every peer has closed it)
+ *   nvj_p2p_allgather_i32         one step: out[r * n + i] = rank r's local[i].  `peer_buffers` is a HOST array of
+ *                                 `world` device pointers ([rank] = this rank's own buffer); `epoch` starts at 1 and
+ *                                 grows by 1 per call on every rank, or is 0 on every call: the kernel then keeps
+ *                                 the count in the rank's buffer (a launch that can be replayed from a CUDA graph).  The kernel waits at most 1 s for its peers and
+ *                                 then flags NVJ_DEV_TIMEOUT in *status.
+ */
+size_t nvj_p2p_gather_buffer_bytes(int world, int n);
+int nvj_p2p_buffer_create(size_t bytes, void** dev_ptr, unsigned char* handle64);
+int nvj_p2p_buffer_open(const unsigned char* handle64, void** dev_ptr);
+int nvj_p2p_buffer_close(void* dev_ptr);
+int nvj_p2p_buffer_destroy(void* dev_ptr);
+int nvj_p2p_allgather_i32(const int32_t* local, int n, int rank, int world, void* const* peer_buffers,
+                          uint32_t epoch, int32_t* out, int32_t* status, nvj_stream_t stream);
+
 /* ------------------------------------------------------------------ tokens */
 
 /*

@@ -10,7 +10,7 @@ from __future__ import annotations
 import ctypes
 import os
 import threading
-from ctypes import c_char_p, c_float, c_int, c_int64, c_size_t, c_void_p
+from ctypes import c_char_p, c_float, c_int, c_int64, c_size_t, c_uint32, c_void_p
 
 from . import build as _build
 
@@ -58,6 +58,12 @@ SIGNATURES = {
     "nvj_hybrid_restore": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int64,
                                    c_int64, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
     "nvj_advance_decode_metadata": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "nvj_p2p_gather_buffer_bytes": (c_size_t, [c_int, c_int]),
+    "nvj_p2p_buffer_create": (c_int, [c_size_t, c_void_p, c_void_p]),
+    "nvj_p2p_buffer_open": (c_int, [c_void_p, c_void_p]),
+    "nvj_p2p_buffer_close": (c_int, [c_void_p]),
+    "nvj_p2p_buffer_destroy": (c_int, [c_void_p]),
+    "nvj_p2p_allgather_i32": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_uint32, c_void_p, c_void_p, c_void_p]),
     "nvj_row_argmax": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p]),
 }
 

@@ -12,6 +12,7 @@ costs no host-to-device traffic for metadata.  Here the same arrays are torch CU
                            (the only per-step host work, and only when a row crosses a block
                            boundary), `load()` (re)installs a batch.
   DecodeStepGraph          captures  advance -> fused append + paged decode -> token pick
+                           (-> all-gather of the tokens over NVLink, on several GPUs)
                            once and replays it: one graph launch per step, the kernels run
                            back to back, and nothing is allocated or copied per step.
 
@@ -79,7 +80,9 @@ class DecodeStepGraph:
     """advance -> append + decode -> argmax of one layer, captured once, replayed per step."""
 
     def __init__(self, meta: ResidentDecodeMetadata, k_cache: torch.Tensor, v_cache: torch.Tensor, layer_id: int,
-                 scale: float, num_key_value_groups: int, query_dtype=torch.bfloat16):
+                 scale: float, num_key_value_groups: int, query_dtype=torch.bfloat16, token_gather=None):
+        """`token_gather` (a `parallel.P2PTokenGather` over `meta.rows` tokens) appends the all-gather of the step's
+        tokens over NVLink to the captured step; `gathered` then holds every rank's tokens after each replay."""
         if k_cache.ndim != 5:
             raise ValueError("k_cache must be the 5-D cache [L, NB, bs, Hkv, D]")
         self.meta, self.k_cache, self.v_cache = meta, k_cache, v_cache
@@ -93,6 +96,9 @@ class DecodeStepGraph:
         self.new_v = torch.zeros((meta.rows, 1, hkv, d), dtype=v_cache.dtype, device=dev)
         self.out: Optional[torch.Tensor] = None
         self.tokens: Optional[torch.Tensor] = None
+        self.token_gather = token_gather
+        self.gathered = (torch.empty(token_gather.world * meta.rows, dtype=torch.int32, device=dev)
+                         if token_gather is not None else None)
         self._graph: Optional[torch.cuda.CUDAGraph] = None
         self._stream = torch.cuda.Stream(dev)
 
@@ -102,6 +108,8 @@ class DecodeStepGraph:
                                                              self.meta.block_tables, self.meta.seq_lens, self.meta.positions,
                                                              self.layer_id, self.meta.block_size, self.scale, self.groups)
         tokens = _k.row_argmax(out.view(self.meta.rows, -1))
+        if self.token_gather is not None:
+            self.token_gather.gather(tokens, out=self.gathered)
         return out, tokens
 
     def capture(self):

@@ -1,0 +1,52 @@
+"""Worker of tests/test_gpu_p2p_gather.py: one process per GPU under torch.distributed.run."""
+
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from nano_vllm_jax_b200.parallel import P2PTokenGather  # noqa: E402
+
+
+def main():
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    n, steps = 256, 60
+    g = P2PTokenGather(n)
+    ref = torch.empty(world * n, dtype=torch.int32, device=dev)
+    base = torch.arange(n, dtype=torch.int32, device=dev)
+    for s in range(steps):
+        tok = base + (rank * 100_000 + s * 1000)
+        if s % 7 == rank % 7:
+            torch.cuda._sleep(2_000_000)  # ranks drift apart: a late peer must be waited for, an early one must not overwrite
+        out = g.gather(tok)
+        dist.all_gather_into_tensor(ref, tok)
+        assert torch.equal(out, ref), f"rank {rank} step {s}: peer-store gather differs from the NCCL gather"
+    g.check()
+    # timing, both ways, 200 steps each
+    tok = base.clone()
+    for fn, name in ((lambda: g.gather(tok, out=ref), "p2p"), (lambda: dist.all_gather_into_tensor(ref, tok), "nccl")):
+        for _ in range(20):
+            fn()
+        dist.barrier(); torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(200):
+            fn()
+        e1.record(); torch.cuda.synchronize()
+        if rank == 0:
+            print(f"TIMING {name} {e0.elapsed_time(e1) / 200 * 1e3:.1f} us per gather of {n} int32 x {world} ranks", flush=True)
+    g.check()
+    g.close()
+    if rank == 0:
+        print("P2P_GATHER_OK", flush=True)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
