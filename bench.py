@@ -440,7 +440,8 @@ def run_b200(args, w):
                     "mode": "HostDecodePipeline: 2 steps in flight on copy/compute/copy streams; every step copies all operands "
                             "from pinned host memory and its whole result back",
                     "serial_value": total_rows / (ms_e2e_serial / K_steps * 1e-3), "serial_ms_per_step": ms_e2e_serial / K_steps},
-            "gpu_launches": 3 * K_steps,  # per step of the timed pass: metadata advance, fused append+decode, token argmax
+            # per step of the timed pass: metadata advance, fused append+decode, token argmax (+ the NVLink token gather)
+            "gpu_launches": (4 if token_gather is not None else 3) * K_steps,
             "step_mode": step_mode,
             "eager_value": total_rows / (ms_eager / K_steps * 1e-3), "eager_ms_per_step": ms_eager / K_steps,
             "roofline": {"bound": "hbm", "kernel": "decode_pipelined_kernel (fused append + paged GQA decode)",
