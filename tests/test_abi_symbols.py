@@ -28,6 +28,33 @@ def test_ctypes_signatures_cover_the_header():
     assert sorted(_lib.SIGNATURES) == _declared()
 
 
+def test_header_is_plain_c_and_a_c_program_links_against_the_library(tmp_path):
+    """The boundary is a C ABI: the header compiles as C99 with nothing but the standard headers, and a C program
+    that names an entry point of every group links against the shared library (no CUDA or torch types involved)."""
+    import shutil
+    import subprocess
+    gcc = shutil.which("gcc")
+    if gcc is None:  # pragma: no cover
+        import pytest
+        pytest.skip("gcc not available")
+    so = build.build()
+    src = tmp_path / "use_abi.c"
+    src.write_text(
+        '#include "nvj_b200.h"\n'
+        "int main(void) {\n"
+        "  int (*fns[])() = {(int (*)())nvj_kv_append, (int (*)())nvj_paged_decode_fused_append,\n"
+        "                    (int (*)())nvj_paged_prefill_packed, (int (*)())nvj_hybrid_snapshot,\n"
+        "                    (int (*)())nvj_qk_norm_rope_kv_append, (int (*)())nvj_p2p_allgather_i32};\n"
+        "  return nvj_abi_version() == 1 && sizeof(fns) > 0 && nvj_kv_append(0, 0, 0, 0, 0, 0, 0, 0, -1, 1, 0, 0, 0, 16, 2, 256, 0, 0) == NVJ_ERR_INVALID_ARGUMENT ? 0 : 1;\n"
+        "}\n")
+    exe = tmp_path / "use_abi"
+    r = subprocess.run([gcc, "-std=c99", "-Wall", "-Werror", "-pedantic", "-Wno-strict-prototypes", "-I", str(ROOT / "include"),
+                        str(src), "-o", str(exe), str(so), f"-Wl,-rpath,{so.parent}"], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    r = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+
+
 def test_status_strings_and_version():
     lib = _lib.load()
     assert lib.nvj_abi_version() == 1
