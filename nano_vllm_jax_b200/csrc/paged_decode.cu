@@ -31,6 +31,7 @@ constexpr int kConsumerWarps = 8;
 constexpr int kConsumerThreads = kConsumerWarps * 32;
 constexpr int kDecodeThreads = kConsumerThreads;
 constexpr int kStages = 3;
+constexpr int kMinBlocksPerCta = 6;
 constexpr int kRing = 1024;  // block-id look-ahead window (two halves of 512 iterations)
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kNegBig = -1.0e30f;
@@ -204,7 +205,10 @@ struct Partition {
 __device__ __forceinline__ Partition make_partition(long long total, int grid) {
   Partition pt;
   pt.total = total;
-  pt.n = total < grid ? (int)total : grid;
+  // at least kMinBlocksPerCta blocks per CTA: with fewer, a short batch is cut into so many partials that the
+  // CTA that merges a row becomes the long pole (8 rows of ~65 blocks: 51 us with one block per CTA, 31 us so)
+  const long long cap = (total + kMinBlocksPerCta - 1) / kMinBlocksPerCta;
+  pt.n = cap < grid ? (int)cap : grid;
   return pt;
 }
 
