@@ -270,6 +270,41 @@ def comparator_case(dev, iters):
         report(name, us, nbytes, {"workload": "c2", "max_abs_diff_vs_this_library": float((mine - theirs.float()).abs().max()),
                                   "note": "bf16 output; plan() outside the timed region"})
     del k, v
+    # ---- paged prefill: one prompt in one chunk, and a 512-token chunk behind a 512-token cached prefix
+    pool2 = 4096
+    k = _randn_bf16((pool2, BS, HKV, D), 11, dev)
+    v = _randn_bf16((pool2, BS, HKV, D), 12, dev)
+    tm = Timer(dev, iters)
+    ws2 = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
+    for n_ctx, chunk in ((1024, 512), (4096, 4096), (16384, 16384)):
+        nblk = n_ctx // BS
+        idx = rng.permutation(pool2)[:nblk].astype(np.int32)
+        q = _randn_bf16((chunk, HQ, D), 13, dev)
+        tab = torch.from_numpy(idx.reshape(1, -1)).to(dev)
+        pos = torch.arange(n_ctx - chunk, n_ctx, dtype=torch.int32, device=dev)[None]
+        qsl = torch.tensor([0, chunk], dtype=torch.int32, device=dev)
+        lens1 = torch.tensor([n_ctx], dtype=torch.int32, device=dev)
+        flops = 4 * HQ * D * (n_ctx * (n_ctx + 1) // 2 - (n_ctx - chunk) * (n_ctx - chunk + 1) // 2)
+        nb2 = chunk * (HQ * D * 2 + HQ * D * 4) + n_ctx * TOKEN_BYTES
+        mine = K.packed_paged_prefill_attention(q[None], k, v, tab, lens1, pos, qsl, BS, SCALE, 4, num_decode_rows=0)
+        us = tm.run(lambda: K.packed_paged_prefill_attention(q[None], k, v, tab, lens1, pos, qsl, BS, SCALE, 4, num_decode_rows=0))
+        report("packed prefill (this library), %d tokens at context %d" % (chunk, n_ctx), us, nb2,
+               {"workload": "prefill", "TFLOP/s": round(flops / us / 1e6, 1)})
+        name = "flashinfer %s BatchPrefillWithPagedKVCacheWrapper, %d tokens at context %d" % (flashinfer.__version__, chunk, n_ctx)
+        try:
+            w = flashinfer.BatchPrefillWithPagedKVCacheWrapper(ws2, "NHD")
+            w.plan(torch.tensor([0, chunk], dtype=torch.int32, device=dev), torch.tensor([0, nblk], dtype=torch.int32, device=dev),
+                   torch.from_numpy(idx).to(dev), torch.tensor([BS], dtype=torch.int32, device=dev), HQ, HKV, D, BS, causal=True,
+                   sm_scale=SCALE, q_data_type=torch.bfloat16, kv_data_type=torch.bfloat16)
+            theirs = w.run(q, (k, v))
+            us = tm.run(lambda: w.run(q, (k, v)))
+        except Exception as exc:
+            print(json.dumps({"kernel": name, "unavailable": repr(exc)[:200]}), flush=True)
+            continue
+        report(name, us, nb2, {"workload": "prefill", "TFLOP/s": round(flops / us / 1e6, 1),
+                               "max_abs_diff_vs_this_library": float((mine.reshape(chunk, HQ, D) - theirs.float()).abs().max()),
+                               "note": "bf16 output; plan() outside the timed region"})
+    del k, v
 
 
 def mixed_step_case(dev, iters):

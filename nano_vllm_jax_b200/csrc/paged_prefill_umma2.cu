@@ -49,6 +49,7 @@ struct Umma2Params {
   int32_t* status;
   long long num_blocks;
   int rows, token_bucket, table_width, skip_single, q_dtype;
+  int zero_fill;  // 1: the kernel itself zeroes what no tile writes (padding tokens, rows without keys)
   int split_p;  // 1: P enters P V as two bf16 terms (hi + lo), 0: as one (the weights are then bf16-rounded)
   float scale;
 };
@@ -61,7 +62,7 @@ struct Umma2Smem {
       s_full[2], p_full, pv_done, x_full;
   float xchg[2][2][kU2Rows];
   uint32_t tmem_base;
-  int row, tok0, ntok, pair_last_tok, abort_flag;
+  int row, tok0, ntok, pair_last_tok, idle_index, abort_flag;
 };
 
 // ---- cta_group::2 wrappers ---------------------------------------------------------------------
@@ -370,10 +371,23 @@ prefill_umma2_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_con
       idx -= pairs;
     }
     sm.row = row; sm.tok0 = tok0; sm.ntok = ntok; sm.pair_last_tok = last; sm.abort_flag = 0;
+    sm.idle_index = row < 0 ? idx : -1;  // clusters beyond the last pair: 0, 1, ...
   }
   __syncthreads();
   const int row = sm.row, tok0 = sm.tok0, ntok = sm.ntok;
-  if (row < 0) return;  // the whole cluster leaves: nothing has been allocated or shared yet
+  if (row < 0) {  // the whole cluster leaves: nothing has been allocated or shared yet
+    if (p.zero_fill && sm.idle_index == 0) {
+      // the first idle cluster (there is always one) zeroes the padding tokens, a quarter per CTA of the cluster pair x KV head
+      int real = p.query_start_loc[p.rows];
+      real = real < p.token_bucket ? real : p.token_bucket;
+      const long long n4 = (long long)(p.token_bucket - real) * kHq * kD / 4;
+      float4* pad = reinterpret_cast<float4*>(p.out + (long long)real * kHq * kD);
+      const int part = rank * kHkv + kvh;
+      for (long long i = (long long)part * kU2Threads + threadIdx.x; i < n4; i += 2LL * kHkv * kU2Threads)
+        pad[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    return;
+  }
 
   int kv_len = p.kv_lens[row];
   if (kv_len > p.table_width * kBlk) {
@@ -387,7 +401,15 @@ prefill_umma2_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_con
   const int max_pos = __reduce_max_sync(0xffffffffu, seen);
   const int key_end = kv_len < max_pos + 1 ? kv_len : max_pos + 1;
   const int n_tiles = key_end > 0 ? (key_end + kU2Keys - 1) / kU2Keys : 0;
-  if (n_tiles == 0) return;  // same decision in both CTAs
+  if (n_tiles == 0) {  // same decision in both CTAs; a row without keys produces zeros
+    if (p.zero_fill) {
+      for (int i = threadIdx.x; i < ntok * kG * (kD / 4); i += kU2Threads) {
+        const int t = i / (kG * (kD / 4)), rest = i - t * (kG * (kD / 4));
+        reinterpret_cast<float4*>(p.out + ((long long)(tok0 + t) * kHq + kvh * kG) * kD)[rest] = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    }
+    return;
+  }
 
   if (warp == 1) tmem2_alloc(smem_u32(&sm.tmem_base), kU2TmemCols);
   if (threadIdx.x == 0) {
@@ -471,10 +493,10 @@ int launch_prefill_umma2(const void* q, int q_dtype, const char* k_cache, const 
   CUtensorMap k_map, v_map;
   if (!u2_make_map(&k_map, k_cache, (uint64_t)num_blocks * kBlk) || !u2_make_map(&v_map, v_cache, (uint64_t)num_blocks * kBlk))
     return NVJ_ERR_UNSUPPORTED;
-  if (!skip_single &&
-      cudaMemsetAsync(out, 0, sizeof(float) * (size_t)token_bucket * kHq * kD, stream) != cudaSuccess)
-    return NVJ_ERR_LAUNCH;
+  // With skip_single the caller has zeroed `out` before its decode-row pass; otherwise the kernel zeroes what no
+  // tile writes itself, which spares a memset launch in front of every pure prefill batch.
   Umma2Params p{};
+  p.zero_fill = skip_single ? 0 : 1;
   p.q = q; p.q_dtype = q_dtype;
   p.block_tables = block_tables; p.kv_lens = kv_lens; p.positions = positions; p.query_start_loc = query_start_loc;
   p.out = out; p.status = status; p.num_blocks = num_blocks; p.rows = rows; p.token_bucket = token_bucket;
