@@ -231,6 +231,21 @@ def test_wide_decode_with_positions_and_reference_dtype():
                                   to_torch(c["seq_lens"]), BS, SCALE, 4)
 
 
+def test_legacy_prefill_gathers_keys_by_slot_mapping():
+    # kv_cache.py:567-647: token t of row b attends the slots slot_mapping[b, 0..t], wherever they sit in the cache
+    from nano_vllm_jax_b200 import kv_cache as kv
+    rng = np.random.default_rng(13)
+    k = rng.standard_normal((2, 64, 4, 2, 64)).astype(np.float32)
+    v = rng.standard_normal((2, 64, 4, 2, 64)).astype(np.float32)
+    slots = rng.permutation(64 * 4)[: 3 * 21].reshape(3, 21).astype(np.int32)
+    q = rng.standard_normal((3, 21, 8, 64)).astype(np.float32)
+    lens = np.full(3, 21, np.int32)
+    ref = R.paged_attention(q, k, v, slots, lens, 0.125, 4, layer_idx=1)
+    out = kv.paged_attention(to_torch(q), to_torch(k), to_torch(v), to_torch(slots), to_torch(lens), 0.125, 4, layer_idx=1)
+    assert out.shape == (3, 21, 8 * 64)
+    np.testing.assert_allclose(to_numpy(out), ref, rtol=1e-5, atol=3e-6)
+
+
 def test_rectangular_prefill_with_rows_padded_at_position_zero():
     # rows of a rectangular [B, T] prefill are padded with (token 0, position 0): positions do not grow along a row,
     # and the key range of a query tile is set by the token that sees the most keys, wherever it sits
