@@ -23,13 +23,14 @@ namespace nvj {
 
 constexpr int kStaticMaxBatch = NVJ_STATIC_SCRATCH_MAX_BATCH;
 constexpr int kStaticMaxCtas = 320;  // two CTAs per SM up to 160 SMs; a larger device runs 320 CTAs
-constexpr size_t kStaticHeaderBytes = (64 + sizeof(int32_t) * (size_t)kStaticMaxBatch + 255) / 256 * 256;
-constexpr size_t kStaticMlBytes = (sizeof(float) * 2ull * kStaticMaxCtas * kHq * 2 + 255) / 256 * 256;
-constexpr size_t kStaticAccBytes = (sizeof(float) * 2ull * kStaticMaxCtas * kHq * kD + 255) / 256 * 256;
+constexpr size_t kStaticSlots = 2ull * kStaticMaxCtas + 2ull * ((kStaticMaxCtas + kMergeGroup - 1) / kMergeGroup);
+constexpr size_t kStaticHeaderBytes = (64 + sizeof(int32_t) * ((size_t)kStaticMaxBatch + kGroupCounters) + 255) / 256 * 256;
+constexpr size_t kStaticMlBytes = (sizeof(float) * kStaticSlots * kHq * 2 + 255) / 256 * 256;
+constexpr size_t kStaticAccBytes = (sizeof(float) * kStaticSlots * kHq * kD + 255) / 256 * 256;
 constexpr size_t kStaticScratchBytes = kStaticHeaderBytes + kStaticMlBytes + kStaticAccBytes;
 static_assert(kStaticScratchBytes == NVJ_STATIC_SCRATCH_BYTES, "header and library disagree on the scratch size");
 
-// The scratch itself: status word, per-row arrival counters, per-CTA partial
+// The scratch itself: status word, arrival counters, per-CTA and per-group partial
 // results.  Every GPU that loads the library holds these ~5 MiB until exit.
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
@@ -101,7 +102,7 @@ extern "C" int nvj_paged_decode_static_scratch(const void* q, int q_dtype, const
   // always written before they are read, but the status word and the arrival
   // counters must start at zero, and a call that was flagged may have left them
   // dirty: clear the header every time (a memset node on the stream, no allocation).
-  if (cudaMemsetAsync(scratch, 0, 64 + sizeof(int32_t) * (size_t)batch, s) != cudaSuccess)
+  if (cudaMemsetAsync(scratch, 0, 64 + sizeof(int32_t) * ((size_t)batch + kGroupCounters), s) != cudaSuccess)
     return NVJ_ERR_LAUNCH;
 
   int num_ctas = decode_num_ctas();

@@ -319,6 +319,66 @@ __device__ __forceinline__ void issue_block(const DecodeParams& p, DecodeSmem& s
   }
 }
 
+// Folds n partial results into one.  Part i sits in slot base + 2 * (first + i), plus one if
+// first + i == row_first (the slot pairing of partial_slot).  kFinal: the normalised result goes to
+// output row dst; otherwise the un-normalised sum and its (max, sum) go to partial slot dst.
+// Thread tid owns head_dim element tid of every head.  Parts are folded four at a time with all
+// their loads (L2, never L1) issued together, so a fold costs about one memory round trip per
+// four parts rather than one per value.
+template <bool kFinal>
+__device__ __forceinline__ void fold_parts(const DecodeParams& p, int tid, long long base, int first, int row_first,
+                                           int n, long long dst) {
+#pragma unroll 1
+  for (int h0 = 0; h0 < kHq; h0 += 4) {
+    float M[4], L[4], o[4];
+#pragma unroll
+    for (int h = 0; h < 4; ++h) { M[h] = kNegBig; L[h] = 0.f; o[h] = 0.f; }
+#pragma unroll 1
+    for (int c0 = 0; c0 < n; c0 += 4) {
+      float2 e[4][4];
+      float a[4][4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const bool ok = c0 + i < n;
+        const int c = first + (ok ? c0 + i : 0);
+        const long long sl = base + 2 * c + (c == row_first ? 1 : 0);
+#pragma unroll
+        for (int h = 0; h < 4; ++h) {
+          const long long row = sl * kHq + h0 + h;
+          e[h][i] = ok ? __ldcg(reinterpret_cast<const float2*>(p.part_ml + row * 2)) : make_float2(kNegBig, 0.f);
+          a[h][i] = ok ? __ldcg(p.part_acc + row * kD + tid) : 0.f;
+        }
+      }
+#pragma unroll
+      for (int h = 0; h < 4; ++h) {
+        float mx = M[h];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) mx = fmaxf(mx, e[h][i].x);
+        const float keep = ex2_approx(M[h] - mx);
+        L[h] *= keep;
+        o[h] *= keep;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float w = ex2_approx(e[h][i].x - mx);
+          L[h] = fmaf(e[h][i].y, w, L[h]);
+          o[h] = fmaf(a[h][i], w, o[h]);
+        }
+        M[h] = mx;
+      }
+    }
+#pragma unroll
+    for (int h = 0; h < 4; ++h) {
+      const long long row = dst * kHq + h0 + h;
+      if (kFinal) {
+        p.out[row * kD + tid] = L[h] > 0.f ? o[h] / L[h] : 0.f;
+      } else {
+        p.part_acc[row * kD + tid] = o[h];
+        if (tid == 0) *reinterpret_cast<float2*>(p.part_ml + row * 2) = make_float2(M[h], L[h]);
+      }
+    }
+  }
+}
+
 // Merge the eight warp states of a finished segment and write either the final
 // output row (the segment covered the whole row) or this CTA's partial; the CTA
 // that delivers a row's last partial combines all of them.
@@ -382,65 +442,41 @@ __device__ __forceinline__ void finish_segment(const DecodeParams& p, DecodeSmem
     named_bar_sync(1, kConsumerThreads);
   }
   if (whole_row) return;
-  // ---- cross-CTA: count this partial in; the last arrival combines them all
+  // ---- cross-CTA: count this partial in; the last arrival combines them.  One CTA folding n partials takes
+  // ~0.13 us per partial (296 partials of one 32k-token row: 80 us for what took 10 us to stream), so a row cut
+  // into more than kTreeMergeMin partials is folded in two levels: per group of kMergeGroup consecutive CTA ids by
+  // the group's last arrival, then the group partials by the row's last group.  A group's CTAs lie inside at most
+  // two such rows (one ending, one beginning in it: a row lying wholly inside has at most kMergeGroup partials),
+  // which is why two counters and two partial slots per group are enough.
   const long long row_g0 = s.g0 - s.j0;
   const int c_lo = pt.cta_of(row_g0);
   const int c_hi = pt.cta_of(row_g0 + s.nb - 1);
+  const int grid = gridDim.x;
+  const bool tree = c_hi - c_lo + 1 > kTreeMergeMin && 2 * ws_groups(grid) <= kGroupCounters;
+  const int grp = blockIdx.x / kMergeGroup, g_lo = c_lo / kMergeGroup, g_hi = c_hi / kMergeGroup;
+  const int first = tree ? max(c_lo, grp * kMergeGroup) : c_lo;
+  const int last = tree ? min(c_hi, grp * kMergeGroup + kMergeGroup - 1) : c_hi;
+  int32_t* counter = tree ? p.counters + p.batch + 2 * grp + (grp == g_lo ? 1 : 0) : p.counters + s.b;
   __threadfence();
   named_bar_sync(1, kConsumerThreads);
-  if (tid == 0) {
-    const int prev = atomicAdd(p.counters + s.b, 1);
-    sm.is_last = (prev == c_hi - c_lo) ? 1 : 0;
-  }
+  if (tid == 0) sm.is_last = (atomicAdd(counter, 1) == last - first) ? 1 : 0;
   named_bar_sync(1, kConsumerThreads);
   if (!sm.is_last) return;
   __threadfence();
-  // Thread tid owns head_dim element tid of every head.  Parts are folded four at
-  // a time with all their loads (L2, never L1) issued together, so a merge costs
-  // about one memory round trip per four parts rather than one per value.
-  const int nparts = c_hi - c_lo + 1;
-#pragma unroll 1
-  for (int h0 = 0; h0 < kHq; h0 += 4) {
-    float M[4], L[4], o[4];
-#pragma unroll
-    for (int h = 0; h < 4; ++h) { M[h] = kNegBig; L[h] = 0.f; o[h] = 0.f; }
-#pragma unroll 1
-    for (int c0 = 0; c0 < nparts; c0 += 4) {
-      float2 e[4][4];
-      float a[4][4];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int c = c_lo + c0 + i;
-        const bool ok = c <= c_hi;
-        const long long sl = partial_slot(ok ? c : c_lo, ok ? c == c_lo : true);
-#pragma unroll
-        for (int h = 0; h < 4; ++h) {
-          const long long row = sl * kHq + h0 + h;
-          e[h][i] = ok ? __ldcg(reinterpret_cast<const float2*>(p.part_ml + row * 2)) : make_float2(kNegBig, 0.f);
-          a[h][i] = ok ? __ldcg(p.part_acc + row * kD + tid) : 0.f;
-        }
-      }
-#pragma unroll
-      for (int h = 0; h < 4; ++h) {
-        float mx = M[h];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) mx = fmaxf(mx, e[h][i].x);
-        const float keep = ex2_approx(M[h] - mx);
-        L[h] *= keep;
-        o[h] *= keep;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float w = ex2_approx(e[h][i].x - mx);
-          L[h] = fmaf(e[h][i].y, w, L[h]);
-          o[h] = fmaf(a[h][i], w, o[h]);
-        }
-        M[h] = mx;
-      }
-    }
-#pragma unroll
-    for (int h = 0; h < 4; ++h)
-      p.out[(out_row * kHq + h0 + h) * kD + tid] = L[h] > 0.f ? o[h] / L[h] : 0.f;
+  if (!tree) {
+    fold_parts<true>(p, tid, 0, c_lo, c_lo, c_hi - c_lo + 1, out_row);
+    if (tid == 0) *counter = 0;
+    return;
   }
+  fold_parts<false>(p, tid, 0, first, c_lo, last - first + 1, 2LL * grid + 2 * grp + (grp == g_lo ? 1 : 0));
+  if (tid == 0) *counter = 0;
+  __threadfence();
+  named_bar_sync(1, kConsumerThreads);
+  if (tid == 0) sm.is_last = (atomicAdd(p.counters + s.b, 1) == g_hi - g_lo) ? 1 : 0;
+  named_bar_sync(1, kConsumerThreads);
+  if (!sm.is_last) return;
+  __threadfence();
+  fold_parts<true>(p, tid, 2LL * grid, g_lo, g_lo, g_hi - g_lo + 1, out_row);
   if (tid == 0) p.counters[s.b] = 0;
 }
 

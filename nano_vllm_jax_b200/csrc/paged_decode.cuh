@@ -43,9 +43,9 @@ struct DecodeParams {
   float* out;
   // workspace
   int32_t* status;
-  int32_t* counters;  // [batch], zero between launches
-  float* part_ml;     // [2 * num_ctas][kHq][2]  (running max in log2 units, sum)
-  float* part_acc;    // [2 * num_ctas][kHq][kD] un-normalised accumulators
+  int32_t* counters;  // [batch + kGroupCounters], zero between launches
+  float* part_ml;     // [ws_slots(num_ctas)][kHq][2]  (running max in log2 units, sum)
+  float* part_acc;    // [ws_slots(num_ctas)][kHq][kD] un-normalised accumulators
   long long num_blocks;
   int batch;
   int table_width;
@@ -94,10 +94,20 @@ __device__ __forceinline__ long long decode_table_base(const DecodeParams& p, in
 
 constexpr size_t kWsAlign = 256;
 __host__ __device__ inline size_t ws_round(size_t x) { return (x + kWsAlign - 1) / kWsAlign * kWsAlign; }
-// Header = status word (64 B) + one int32 counter per row.
-inline size_t ws_header_bytes(int max_batch) { return ws_round(64 + sizeof(int32_t) * (size_t)max_batch); }
-inline size_t ws_ml_bytes(int num_ctas) { return ws_round(sizeof(float) * 2ull * num_ctas * kHq * 2); }
-inline size_t ws_acc_bytes(int num_ctas) { return ws_round(sizeof(float) * 2ull * num_ctas * kHq * kD); }
+// A row that is cut into more than kTreeMergeMin partials is merged in two levels: the CTAs of
+// one group of kMergeGroup consecutive CTA ids fold their partials into one group partial, and
+// the group that finishes last folds the group partials.  kGroupCounters arrival counters
+// (two per group) follow the per-row counters; a launch with more groups merges flat.
+constexpr int kMergeGroup = 16;
+constexpr int kTreeMergeMin = 32;
+constexpr int kGroupCounters = 64;
+__host__ __device__ inline int ws_groups(int num_ctas) { return (num_ctas + kMergeGroup - 1) / kMergeGroup; }
+// Partial slots: two per CTA, then two per group.
+__host__ __device__ inline size_t ws_slots(int num_ctas) { return 2ull * num_ctas + 2ull * ws_groups(num_ctas); }
+// Header = status word (64 B) + one int32 counter per row + the group counters.
+inline size_t ws_header_bytes(int max_batch) { return ws_round(64 + sizeof(int32_t) * ((size_t)max_batch + kGroupCounters)); }
+inline size_t ws_ml_bytes(int num_ctas) { return ws_round(sizeof(float) * ws_slots(num_ctas) * kHq * 2); }
+inline size_t ws_acc_bytes(int num_ctas) { return ws_round(sizeof(float) * ws_slots(num_ctas) * kHq * kD); }
 
 int decode_num_ctas();  // 2 per SM of the current device
 int launch_decode_generic(const DecodeParams& p, cudaStream_t stream);

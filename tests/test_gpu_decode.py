@@ -84,6 +84,25 @@ def test_rows_split_across_many_ctas():
     np.testing.assert_array_equal(bits(out), bits(again))
 
 
+@pytest.mark.parametrize("lens", [(20000,), (9000, 30, 9000, 700, 5), (3000, 12000, 1, 6000)])
+def test_few_long_rows_are_merged_in_two_levels(lens):
+    # rows cut into more than 32 partials: groups of 16 CTAs fold first, the last group folds the groups;
+    # short rows between them share CTAs and groups with the long ones
+    c = decode_case(9, 2600, len(lens), 1, 1)
+    rng = np.random.default_rng(9)
+    c["seq_lens"] = np.asarray(lens, np.int32)
+    need = -(-c["seq_lens"] // BS)
+    c["tables"] = np.zeros((len(lens), int(need.max())), np.int32)
+    perm, o = rng.permutation(2600), 0
+    for b in range(len(lens)):
+        c["tables"][b, :need[b]] = perm[o:o + need[b]]
+        o += need[b]
+    out = _run(c, PIPELINED)
+    _check(out, _oracle(c), np.ones(len(lens), bool))
+    again = _run(c, PIPELINED)  # row and group counters were left at zero
+    np.testing.assert_array_equal(bits(out), bits(again))
+
+
 def test_mixed_short_and_long_rows():
     c = decode_case(5, 4096, 40, 1, 1500)
     out = _run(c, PIPELINED)
