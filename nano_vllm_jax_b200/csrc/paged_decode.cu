@@ -319,63 +319,84 @@ __device__ __forceinline__ void issue_block(const DecodeParams& p, DecodeSmem& s
   }
 }
 
-// Folds n partial results into one.  Part i sits in slot base + 2 * (first + i), plus one if
+// Folds n <= 32 partial results into one.  Part i sits in slot base + 2 * (first + i), plus one if
 // first + i == row_first (the slot pairing of partial_slot).  kFinal: the normalised result goes to
 // output row dst; otherwise the un-normalised sum and its (max, sum) go to partial slot dst.
-// Thread tid owns head_dim element tid of every head.  Parts are folded four at a time with all
-// their loads (L2, never L1) issued together, so a fold costs about one memory round trip per
-// four parts rather than one per value.
+// Two phases, so that no load depends on another: (a) thread (part, head) reads the part's (max, sum),
+// the CTA reduces them to the head's max and sum and leaves one weight per (part, head) in shared
+// memory; (b) thread (head, 8 dims) sums weight * accumulator over the parts, eight parts (sixteen
+// 16-byte loads from L2, never L1) in flight at a time.  A fold of 16 parts costs about three memory
+// round trips.  All 256 threads call it; it uses sm.merge as scratch.
 template <bool kFinal>
-__device__ __forceinline__ void fold_parts(const DecodeParams& p, int tid, long long base, int first, int row_first,
-                                           int n, long long dst) {
+__device__ __forceinline__ void fold_parts(const DecodeParams& p, DecodeSmem& sm, int tid, long long base, int first,
+                                           int row_first, int n, long long dst) {
+  float* red = &sm.merge[0][0];   // [8 warps][8 heads]
+  float* m_sh = red + 64;         // [8 heads]
+  float* w_sh = red + 128;        // [32 parts][8 heads]
+  const int warp = tid >> 5, lane = tid & 31;
+  {
+    const int i = tid >> 3, h = tid & 7;
+    const bool ok = i < n;
+    const int c = first + (ok ? i : 0);
+    const long long sl = base + 2 * c + (c == row_first ? 1 : 0);
+    const float2 e = ok ? __ldcg(reinterpret_cast<const float2*>(p.part_ml + (sl * kHq + h) * 2)) : make_float2(kNegBig, 0.f);
+    float m = e.x;
+    m = fmaxf(m, __shfl_xor_sync(kFullMask, m, 8));
+    m = fmaxf(m, __shfl_xor_sync(kFullMask, m, 16));
+    if (lane < 8) red[warp * 8 + lane] = m;
+    named_bar_sync(1, kConsumerThreads);
+    float M = red[h];
+#pragma unroll
+    for (int w = 1; w < kConsumerWarps; ++w) M = fmaxf(M, red[w * 8 + h]);
+    const float wgt = ok ? ex2_approx(e.x - M) : 0.f;
+    w_sh[i * 8 + h] = wgt;
+    if (i == 0) m_sh[h] = M;
+    float l = e.y * wgt;
+    l += __shfl_xor_sync(kFullMask, l, 8);
+    l += __shfl_xor_sync(kFullMask, l, 16);
+    named_bar_sync(1, kConsumerThreads);  // every thread has read the maxima
+    if (lane < 8) red[warp * 8 + lane] = l;
+    named_bar_sync(1, kConsumerThreads);
+  }
+  const int h = warp, d0 = lane * 8;
+  float L = 0.f;
+#pragma unroll
+  for (int w = 0; w < kConsumerWarps; ++w) L += red[w * 8 + h];
+  float acc[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) acc[k] = 0.f;
 #pragma unroll 1
-  for (int h0 = 0; h0 < kHq; h0 += 4) {
-    float M[4], L[4], o[4];
+  for (int i0 = 0; i0 < n; i0 += 8) {
+    float4 x[8][2];
 #pragma unroll
-    for (int h = 0; h < 4; ++h) { M[h] = kNegBig; L[h] = 0.f; o[h] = 0.f; }
-#pragma unroll 1
-    for (int c0 = 0; c0 < n; c0 += 4) {
-      float2 e[4][4];
-      float a[4][4];
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const bool ok = c0 + i < n;
-        const int c = first + (ok ? c0 + i : 0);
-        const long long sl = base + 2 * c + (c == row_first ? 1 : 0);
-#pragma unroll
-        for (int h = 0; h < 4; ++h) {
-          const long long row = sl * kHq + h0 + h;
-          e[h][i] = ok ? __ldcg(reinterpret_cast<const float2*>(p.part_ml + row * 2)) : make_float2(kNegBig, 0.f);
-          a[h][i] = ok ? __ldcg(p.part_acc + row * kD + tid) : 0.f;
-        }
-      }
-#pragma unroll
-      for (int h = 0; h < 4; ++h) {
-        float mx = M[h];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) mx = fmaxf(mx, e[h][i].x);
-        const float keep = ex2_approx(M[h] - mx);
-        L[h] *= keep;
-        o[h] *= keep;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float w = ex2_approx(e[h][i].x - mx);
-          L[h] = fmaf(e[h][i].y, w, L[h]);
-          o[h] = fmaf(a[h][i], w, o[h]);
-        }
-        M[h] = mx;
-      }
+    for (int k = 0; k < 8; ++k) {
+      const bool ok = i0 + k < n;
+      const int c = first + (ok ? i0 + k : 0);
+      const long long sl = base + 2 * c + (c == row_first ? 1 : 0);
+      const float4* src = reinterpret_cast<const float4*>(p.part_acc + (sl * kHq + h) * kD + d0);
+      x[k][0] = ok ? __ldcg(src) : make_float4(0.f, 0.f, 0.f, 0.f);
+      x[k][1] = ok ? __ldcg(src + 1) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
 #pragma unroll
-    for (int h = 0; h < 4; ++h) {
-      const long long row = dst * kHq + h0 + h;
-      if (kFinal) {
-        p.out[row * kD + tid] = L[h] > 0.f ? o[h] / L[h] : 0.f;
-      } else {
-        p.part_acc[row * kD + tid] = o[h];
-        if (tid == 0) *reinterpret_cast<float2*>(p.part_ml + row * 2) = make_float2(M[h], L[h]);
-      }
+    for (int k = 0; k < 8; ++k) {
+      const float wgt = i0 + k < n ? w_sh[(i0 + k) * 8 + h] : 0.f;
+      acc[0] = fmaf(x[k][0].x, wgt, acc[0]); acc[1] = fmaf(x[k][0].y, wgt, acc[1]);
+      acc[2] = fmaf(x[k][0].z, wgt, acc[2]); acc[3] = fmaf(x[k][0].w, wgt, acc[3]);
+      acc[4] = fmaf(x[k][1].x, wgt, acc[4]); acc[5] = fmaf(x[k][1].y, wgt, acc[5]);
+      acc[6] = fmaf(x[k][1].z, wgt, acc[6]); acc[7] = fmaf(x[k][1].w, wgt, acc[7]);
     }
+  }
+  const long long row = dst * kHq + h;
+  if (kFinal) {
+    const float inv = L > 0.f ? 1.f / L : 0.f;
+    float4* o = reinterpret_cast<float4*>(p.out + row * kD + d0);
+    o[0] = make_float4(acc[0] * inv, acc[1] * inv, acc[2] * inv, acc[3] * inv);
+    o[1] = make_float4(acc[4] * inv, acc[5] * inv, acc[6] * inv, acc[7] * inv);
+  } else {
+    float4* o = reinterpret_cast<float4*>(p.part_acc + row * kD + d0);
+    o[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    o[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    if (lane == 0) *reinterpret_cast<float2*>(p.part_ml + row * 2) = make_float2(m_sh[h], L);
   }
 }
 
@@ -442,8 +463,8 @@ __device__ __forceinline__ void finish_segment(const DecodeParams& p, DecodeSmem
     named_bar_sync(1, kConsumerThreads);
   }
   if (whole_row) return;
-  // ---- cross-CTA: count this partial in; the last arrival combines them.  One CTA folding n partials takes
-  // ~0.13 us per partial (296 partials of one 32k-token row: 80 us for what took 10 us to stream), so a row cut
+  // ---- cross-CTA: count this partial in; the last arrival combines them.  One CTA can take in ~60 GB/s, and a
+  // partial is 8 KiB (296 partials of one 32k-token row: 40 us for what took 10 us to stream), so a row cut
   // into more than kTreeMergeMin partials is folded in two levels: per group of kMergeGroup consecutive CTA ids by
   // the group's last arrival, then the group partials by the row's last group.  A group's CTAs lie inside at most
   // two such rows (one ending, one beginning in it: a row lying wholly inside has at most kMergeGroup partials),
@@ -452,7 +473,7 @@ __device__ __forceinline__ void finish_segment(const DecodeParams& p, DecodeSmem
   const int c_lo = pt.cta_of(row_g0);
   const int c_hi = pt.cta_of(row_g0 + s.nb - 1);
   const int grid = gridDim.x;
-  const bool tree = c_hi - c_lo + 1 > kTreeMergeMin && 2 * ws_groups(grid) <= kGroupCounters;
+  const bool tree = c_hi - c_lo + 1 > kTreeMergeMin;
   const int grp = blockIdx.x / kMergeGroup, g_lo = c_lo / kMergeGroup, g_hi = c_hi / kMergeGroup;
   const int first = tree ? max(c_lo, grp * kMergeGroup) : c_lo;
   const int last = tree ? min(c_hi, grp * kMergeGroup + kMergeGroup - 1) : c_hi;
@@ -464,11 +485,11 @@ __device__ __forceinline__ void finish_segment(const DecodeParams& p, DecodeSmem
   if (!sm.is_last) return;
   __threadfence();
   if (!tree) {
-    fold_parts<true>(p, tid, 0, c_lo, c_lo, c_hi - c_lo + 1, out_row);
+    fold_parts<true>(p, sm, tid, 0, c_lo, c_lo, c_hi - c_lo + 1, out_row);
     if (tid == 0) *counter = 0;
     return;
   }
-  fold_parts<false>(p, tid, 0, first, c_lo, last - first + 1, 2LL * grid + 2 * grp + (grp == g_lo ? 1 : 0));
+  fold_parts<false>(p, sm, tid, 0, first, c_lo, last - first + 1, 2LL * grid + 2 * grp + (grp == g_lo ? 1 : 0));
   if (tid == 0) *counter = 0;
   __threadfence();
   named_bar_sync(1, kConsumerThreads);
@@ -476,7 +497,7 @@ __device__ __forceinline__ void finish_segment(const DecodeParams& p, DecodeSmem
   named_bar_sync(1, kConsumerThreads);
   if (!sm.is_last) return;
   __threadfence();
-  fold_parts<true>(p, tid, 2LL * grid, g_lo, g_lo, g_hi - g_lo + 1, out_row);
+  fold_parts<true>(p, sm, tid, 2LL * grid, g_lo, g_lo, g_hi - g_lo + 1, out_row);
   if (tid == 0) p.counters[s.b] = 0;
 }
 
@@ -631,7 +652,8 @@ int decode_num_ctas() {
   if (g_num_ctas[dev] == 0) {
     int sms = 0;
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
-    g_num_ctas[dev] = 2 * sms;
+    // no more CTAs than the group counters of the workspace header cover
+    g_num_ctas[dev] = 2 * sms < kMergeGroup * kGroupCounters / 2 ? 2 * sms : kMergeGroup * kGroupCounters / 2;
   }
   return g_num_ctas[dev];
 }

@@ -97,7 +97,7 @@ __host__ __device__ inline size_t ws_round(size_t x) { return (x + kWsAlign - 1)
 // A row that is cut into more than kTreeMergeMin partials is merged in two levels: the CTAs of
 // one group of kMergeGroup consecutive CTA ids fold their partials into one group partial, and
 // the group that finishes last folds the group partials.  kGroupCounters arrival counters
-// (two per group) follow the per-row counters; a launch with more groups merges flat.
+// (two per group) follow the per-row counters; a launch never has more CTAs than they cover.
 constexpr int kMergeGroup = 16;
 constexpr int kTreeMergeMin = 32;
 constexpr int kGroupCounters = 64;
