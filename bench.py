@@ -319,12 +319,28 @@ def run_b200(args, w):
         if world > 1:
             dist.all_gather_into_tensor(gathered, K.row_argmax(out.view(rows, HQ * D)))
 
+    token_gather = None
+    if world > 1 and os.environ.get("NVJ_BENCH_NCCL_GATHER", "0") != "1":
+        from nano_vllm_jax_b200.parallel import P2PTokenGather
+        try:  # peer stores over NVLink inside the graph; all ranks succeed or all fall back to the NCCL gather
+            token_gather = P2PTokenGather(rows)
+        except Exception as exc:
+            if rank == 0:
+                print(f"[bench] NVLink token gather unavailable ({exc!r}); using the NCCL all-gather", file=sys.stderr, flush=True)
     from nano_vllm_jax_b200.host_pipeline import HostDecodePipeline
-    pipe = HostDecodePipeline(backend, cache, rows, tables.shape[1], BS, SCALE, HQ // HKV, depth=2)
+    # The compute stage of each pipeline slot (append + decode, token pick, NVLink token gather) is replayed from a CUDA
+    # graph; with the NCCL gather in it (no peer access) it is launched eagerly.
+    pipe_capture = (world == 1 or token_gather is not None) and os.environ.get("NVJ_BENCH_EAGER_PIPELINE", "0") != "1"
+    pipe = HostDecodePipeline(backend, cache, rows, tables.shape[1], BS, SCALE, HQ // HKV, depth=2, capture=pipe_capture)
+    gathered_p2p = torch.empty(world * rows, dtype=torch.int32, device=dev) if token_gather is not None else None
 
     def gather_tokens(out):
         if world > 1:
-            dist.all_gather_into_tensor(gathered, K.row_argmax(out.view(rows, HQ * D)))
+            tok = K.row_argmax(out.view(rows, HQ * D))
+            if token_gather is not None:
+                token_gather.gather(tok, out=gathered_p2p)
+            else:
+                dist.all_gather_into_tensor(gathered, tok)
 
     def e2e_pipelined_step():
         s = step_no[0]
@@ -358,14 +374,6 @@ def run_b200(args, w):
     # append + decode -> token argmax, one graph launch per step; the token all-gather (N > 1) follows each replay.
     from nano_vllm_jax_b200.engine.resident_decode import DecodeStepGraph, ResidentDecodeMetadata
     meta = ResidentDecodeMetadata(rows, tables.shape[1], BS, device=dev)
-    token_gather = None
-    if world > 1 and os.environ.get("NVJ_BENCH_NCCL_GATHER", "0") != "1":
-        from nano_vllm_jax_b200.parallel import P2PTokenGather
-        try:  # peer stores over NVLink inside the graph; all ranks succeed or all fall back to the NCCL gather
-            token_gather = P2PTokenGather(rows)
-        except Exception as exc:
-            if rank == 0:
-                print(f"[bench] NVLink token gather unavailable ({exc!r}); using the NCCL all-gather", file=sys.stderr, flush=True)
     graph = DecodeStepGraph(meta, k_cache, v_cache, 0, SCALE, HQ // HKV, token_gather=token_gather)
     graph.query.copy_(q); graph.new_k.copy_(nk); graph.new_v.copy_(nv)
     graph_ready = [False]
@@ -438,7 +446,8 @@ def run_b200(args, w):
             "e2e": {"value": total_rows / (ms_e2e / K_steps * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e / K_steps,
                     "mode": "HostDecodePipeline: 2 steps in flight on copy/compute/copy streams; every step copies all operands "
-                            "from pinned host memory and its whole result back",
+                            "from pinned host memory and its whole result back; compute stage "
+                            + ("replayed from a CUDA graph per slot" if pipe_capture else "launched eagerly"),
                     "serial_value": total_rows / (ms_e2e_serial / K_steps * 1e-3), "serial_ms_per_step": ms_e2e_serial / K_steps},
             # per step of the timed pass: metadata advance, fused append+decode, token argmax (+ the NVLink token gather)
             "gpu_launches": (4 if token_gather is not None else 3) * K_steps,

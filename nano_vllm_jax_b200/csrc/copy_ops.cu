@@ -19,12 +19,12 @@ __device__ __forceinline__ void st_cs_u4(void* p, uint4 v) {
                : "memory");
 }
 
-// Copies `bytes` (multiple of 16, both pointers 16-byte aligned) with the CTAs
-// blockIdx.x, blockIdx.x + gridDim.x, ... each moving 16 KiB tiles.
-__device__ __forceinline__ void copy_span16(const char* src, char* dst, long long bytes) {
+// Copies `bytes` (multiple of 16, both pointers 16-byte aligned) with CTA `block` of `nblocks`
+// moving the 16 KiB tiles block, block + nblocks, ...
+__device__ __forceinline__ void copy_span16(const char* src, char* dst, long long bytes, int block, int nblocks) {
   const long long chunks = bytes >> 4;
-  for (long long base = (long long)blockIdx.x * kCopyThreads * kCopyUnroll; base < chunks;
-       base += (long long)gridDim.x * kCopyThreads * kCopyUnroll) {
+  for (long long base = (long long)block * kCopyThreads * kCopyUnroll; base < chunks;
+       base += (long long)nblocks * kCopyThreads * kCopyUnroll) {
     uint4 v[kCopyUnroll];
 #pragma unroll
     for (int u = 0; u < kCopyUnroll; ++u) {
@@ -39,27 +39,37 @@ __device__ __forceinline__ void copy_span16(const char* src, char* dst, long lon
   }
 }
 
-__device__ __forceinline__ void copy_span1(const char* src, char* dst, long long bytes) {
-  for (long long c = (long long)blockIdx.x * kCopyThreads + threadIdx.x; c < bytes;
-       c += (long long)gridDim.x * kCopyThreads)
+__device__ __forceinline__ void copy_span1(const char* src, char* dst, long long bytes, int block, int nblocks) {
+  for (long long c = (long long)block * kCopyThreads + threadIdx.x; c < bytes; c += (long long)nblocks * kCopyThreads)
     dst[c] = src[c];
 }
 
-// dst_base[dst_idx[i]] <- src_base[src_idx[i]], rows of row_bytes; grid.y = pair.
+// One table of rows that are copied by index: dst_base[dst_idx[i]] <- src_base[src_idx[i]].
+struct RowTable {
+  const char* src_base;
+  char* dst_base;
+  long long row_bytes;
+  int vec16;
+  int blocks;  // CTAs of grid.x that work on this table
+};
+
+// Both tables of a hybrid state (recurrent and conv) in one launch; grid.y = pair, grid.x = a.blocks + b.blocks.
 __global__ void __launch_bounds__(kCopyThreads)
-copy_rows_kernel(const char* src_base, long long src_rows, const int32_t* src_idx, char* dst_base,
-                 long long dst_rows, const int32_t* dst_idx, long long row_bytes, int vec16,
-                 int32_t* status) {
+copy_rows_kernel(RowTable a, RowTable b, long long src_rows, const int32_t* src_idx, long long dst_rows,
+                 const int32_t* dst_idx, int32_t* status) {
   const int i = blockIdx.y;
   const long long s = src_idx[i], d = dst_idx[i];
   if (s < 0 || s >= src_rows || d < 0 || d >= dst_rows) {
     if (threadIdx.x == 0 && blockIdx.x == 0 && status) atomicOr(status, NVJ_DEV_BAD_BLOCK_ID);
     return;
   }
-  const char* src = src_base + s * row_bytes;
-  char* dst = dst_base + d * row_bytes;
-  if (vec16) copy_span16(src, dst, row_bytes);
-  else copy_span1(src, dst, row_bytes);
+  const bool first = (int)blockIdx.x < a.blocks;
+  const RowTable& t = first ? a : b;
+  const int block = first ? blockIdx.x : blockIdx.x - a.blocks;
+  const char* src = t.src_base + s * t.row_bytes;
+  char* dst = t.dst_base + d * t.row_bytes;
+  if (t.vec16) copy_span16(src, dst, t.row_bytes, block, t.blocks);
+  else copy_span1(src, dst, t.row_bytes, block, t.blocks);
 }
 
 // Block copy across layers and K/V: grid.y = pair, grid.z = layer * 2 + (0: K, 1: V).
@@ -77,8 +87,8 @@ copy_blocks_kernel(char* k_cache, char* v_cache, long long num_blocks, long long
   if (s == d) return;
   char* base = (blockIdx.z & 1) ? v_cache : k_cache;
   base += (long long)(blockIdx.z >> 1) * layer_stride;
-  if (vec16) copy_span16(base + s * block_bytes, base + d * block_bytes, block_bytes);
-  else copy_span1(base + s * block_bytes, base + d * block_bytes, block_bytes);
+  if (vec16) copy_span16(base + s * block_bytes, base + d * block_bytes, block_bytes, blockIdx.x, gridDim.x);
+  else copy_span1(base + s * block_bytes, base + d * block_bytes, block_bytes, blockIdx.x, gridDim.x);
 }
 
 // One CTA per row; the first maximum wins, NaNs are never selected unless the
@@ -141,16 +151,15 @@ static int grid_x_for(long long bytes, int pairs) {
   return gx < 1 ? 1 : (int)gx;
 }
 
-static int launch_copy_rows(const void* src, long long src_rows, const int32_t* src_idx, void* dst,
-                            long long dst_rows, const int32_t* dst_idx, int n, long long row_bytes,
-                            int32_t* status, cudaStream_t stream) {
-  if (!src || !dst || row_bytes == 0) return NVJ_OK;
-  const int vec16 = aligned16(src) && aligned16(dst) && row_bytes % 16 == 0;
-  dim3 grid(grid_x_for(row_bytes, n), n, 1);
-  copy_rows_kernel<<<grid, kCopyThreads, 0, stream>>>(static_cast<const char*>(src), src_rows, src_idx,
-                                                      static_cast<char*>(dst), dst_rows, dst_idx,
-                                                      row_bytes, vec16, status);
-  return cudaGetLastError() == cudaSuccess ? NVJ_OK : NVJ_ERR_LAUNCH;
+static RowTable row_table(const void* src, void* dst, long long row_bytes, int pairs) {
+  RowTable t{};
+  if (!src || !dst || row_bytes == 0) return t;  // blocks = 0: no CTA works on it
+  t.src_base = static_cast<const char*>(src);
+  t.dst_base = static_cast<char*>(dst);
+  t.row_bytes = row_bytes;
+  t.vec16 = aligned16(src) && aligned16(dst) && row_bytes % 16 == 0;
+  t.blocks = grid_x_for(row_bytes, pairs);
+  return t;
 }
 
 // One decode step of the batch metadata, on the device: every active row (seq_len > 0) grows by
@@ -217,12 +226,13 @@ static int hybrid_copy(const void* conv_src, void* conv_dst, int64_t conv_row_by
   if (n > 65535) return NVJ_ERR_UNSUPPORTED;
   if ((conv_src == nullptr) != (conv_dst == nullptr) || (rec_src == nullptr) != (rec_dst == nullptr))
     return NVJ_ERR_INVALID_ARGUMENT;
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  int rc = launch_copy_rows(rec_src, src_rows, src_slots, rec_dst, dst_rows, dst_slots, n,
-                            rec_row_bytes, status, s);
-  if (rc != NVJ_OK) return rc;
-  return launch_copy_rows(conv_src, src_rows, src_slots, conv_dst, dst_rows, dst_slots, n,
-                          conv_row_bytes, status, s);
+  const RowTable rec = row_table(rec_src, rec_dst, rec_row_bytes, n);
+  const RowTable conv = row_table(conv_src, conv_dst, conv_row_bytes, n);
+  if (rec.blocks + conv.blocks == 0) return NVJ_OK;
+  dim3 grid(rec.blocks + conv.blocks, n, 1);
+  copy_rows_kernel<<<grid, kCopyThreads, 0, static_cast<cudaStream_t>(stream)>>>(rec, conv, src_rows, src_slots, dst_rows,
+                                                                                 dst_slots, status);
+  return cudaGetLastError() == cudaSuccess ? NVJ_OK : NVJ_ERR_LAUNCH;
 }
 
 extern "C" int nvj_hybrid_snapshot(const void* conv_table, void* conv_pool, int64_t conv_row_bytes,

@@ -16,12 +16,21 @@ back; steps are issued in order and the cache is only touched by the compute
 stream, so the cache contents are those of the serial execution.  The
 attention call itself is `B200Backend.write_kv_and_attention`
 (the reference's boundary, nanovllm_jax/backends.py:1252-1461).
+
+With `capture=True` the compute part of a slot (metadata, fused append +
+decode, `after_compute`) is captured into a CUDA graph the first time the slot
+is used for a layer and replayed afterwards.  The per-step host work of the
+attention call (argument checks, pointer marshalling, the launch itself: a few
+hundred microseconds of Python, more than the kernel takes) shrinks to one
+graph launch, and the pipeline becomes device-bound.  `after_compute` must then
+be capturable (no host synchronisation) and the same callable on every step.
 """
 
 from __future__ import annotations
 
-from dataclasses import dataclass
-from typing import Optional
+import os
+from dataclasses import dataclass, field
+from typing import Dict, Optional
 
 import torch
 
@@ -42,13 +51,16 @@ class _Slot:
     compute_done: torch.cuda.Event
     out_done: torch.cuda.Event
     busy: bool = False
+    graphs: Dict[int, torch.cuda.CUDAGraph] = field(default_factory=dict)  # per layer, with capture=True
+    graph_out: Dict[int, torch.Tensor] = field(default_factory=dict)
 
 
 class HostDecodePipeline:
     """`depth` decode steps in flight; operands from host tensors, results into pinned host tensors."""
 
     def __init__(self, backend: B200Backend, cache: KVCacheStorage, rows: int, table_width: int, block_size: int,
-                 scale: float, num_key_value_groups: int, depth: int = 2, query_dtype=torch.bfloat16):
+                 scale: float, num_key_value_groups: int, depth: int = 2, query_dtype=torch.bfloat16,
+                 capture: bool = False):
         if depth < 1:
             raise ValueError("depth must be at least 1")
         if not isinstance(backend, B200Backend):
@@ -56,7 +68,7 @@ class HostDecodePipeline:
         dev = cache.k_cache.device
         _, _, _, hkv, d = cache.k_cache.shape
         hq = hkv * num_key_value_groups
-        self.backend, self.cache = backend, cache
+        self.backend, self.cache, self.capture = backend, cache, bool(capture)
         self.rows, self.block_size, self.scale, self.groups = rows, block_size, scale, num_key_value_groups
         self.h2d, self.compute, self.d2h = (torch.cuda.Stream(dev) for _ in range(3))
         self.slots = []
@@ -98,20 +110,49 @@ class HostDecodePipeline:
             slot.in_done.record(self.h2d)
         with torch.cuda.stream(self.compute):
             self.compute.wait_event(slot.in_done)
-            md = self.backend.build_attention_metadata(slot.positions, slot.tables, slot.seq_lens, self.block_size, False)
-            _, out = self.backend.write_kv_and_attention(layer_id, slot.q, slot.k, slot.v, self.cache, md, self.block_size,
-                                                         self.scale, self.groups, False)
-            if after_compute is not None:
-                after_compute(out)
+            if not self.capture:
+                out = self._compute(slot, layer_id, after_compute)
+            elif layer_id in slot.graphs:
+                slot.graphs[layer_id].replay()
+                out = slot.graph_out[layer_id]
+            else:
+                out = self._capture(slot, layer_id, after_compute)
             slot.compute_done.record(self.compute)
         with torch.cuda.stream(self.d2h):
             self.d2h.wait_event(slot.compute_done)
             slot.host_out.copy_(out, non_blocking=True)
-            out.record_stream(self.d2h)
+            if out is not slot.graph_out.get(layer_id):  # a graph's output lives in the graph's own pool
+                out.record_stream(self.d2h)
             slot.out_done.record(self.d2h)
         slot.busy = True
         self.submitted += 1
         return ticket
+
+    def _compute(self, slot: _Slot, layer_id: int, after_compute):
+        md = self.backend.build_attention_metadata(slot.positions, slot.tables, slot.seq_lens, self.block_size, False)
+        _, out = self.backend.write_kv_and_attention(layer_id, slot.q, slot.k, slot.v, self.cache, md, self.block_size,
+                                                     self.scale, self.groups, False)
+        if after_compute is not None:
+            after_compute(out)
+        return out
+
+    def _capture(self, slot: _Slot, layer_id: int, after_compute):
+        """First use of (slot, layer): run the step once (this is the step's execution; it also warms kernels and
+        workspaces), then record the same calls for the replays.  Runs on the compute stream."""
+        first = self._compute(slot, layer_id, after_compute)
+        strict = os.environ.get("NVJ_CHECK_STATUS")
+        os.environ["NVJ_CHECK_STATUS"] = "0"  # reading the status word back is a host sync: not capturable
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=self.compute, capture_error_mode="thread_local"):
+                slot.graph_out[layer_id] = self._compute(slot, layer_id, after_compute)
+            slot.graphs[layer_id] = graph
+        finally:
+            if strict is None:
+                os.environ.pop("NVJ_CHECK_STATUS", None)
+            else:
+                os.environ["NVJ_CHECK_STATUS"] = strict
+        return first
 
     def result(self, ticket: int) -> torch.Tensor:
         """The step's attention output `[rows, 1, Hq*D]` fp32 in pinned host memory (valid until the slot is reused)."""

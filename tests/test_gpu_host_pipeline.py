@@ -1,4 +1,5 @@
-"""Decode steps submitted from host tensors through the three-stream pipeline equal the same steps run one by one."""
+"""Decode steps submitted from host tensors through the three-stream pipeline equal the same steps run one by one,
+with the compute stage launched eagerly and replayed from a CUDA graph per slot."""
 
 import numpy as np
 import pytest
@@ -10,7 +11,8 @@ from oracle import kv_cache_ref as R
 pytestmark = pytest.mark.gpu
 
 
-def test_pipelined_host_steps_equal_serial_steps_and_the_oracle():
+@pytest.mark.parametrize("capture", [False, True])
+def test_pipelined_host_steps_equal_serial_steps_and_the_oracle(capture):
     from nano_vllm_jax_b200.backends import B200Backend
     from nano_vllm_jax_b200.host_pipeline import HostDecodePipeline
     from nano_vllm_jax_b200.kv_cache import KVCacheStorage
@@ -33,7 +35,7 @@ def test_pipelined_host_steps_equal_serial_steps_and_the_oracle():
         host.append((q, nk, nv, pos, lens))
     tables = torch.from_numpy(c["tables"]).pin_memory()
 
-    pipe = HostDecodePipeline(backend, piped, rows, tables.shape[1], BS, SCALE, 4, depth=2)
+    pipe = HostDecodePipeline(backend, piped, rows, tables.shape[1], BS, SCALE, 4, depth=2, capture=capture)
     assert pipe.h2d_bytes_per_step == rows * (8 + 2 + 2) * 256 * 2 + tables.numel() * 4 + rows * 8
     outs = []
     for s, (q, nk, nv, pos, lens) in enumerate(host):
