@@ -40,6 +40,9 @@ struct DecodeParams {
   // writes out[i] and attends min(seq_lens[b], query_positions[i] + 1) keys.  Other rows are left
   // alone (no zero fill): the prefill kernel owns them.
   int packed_rows;
+  // query tokens per row of the wide kernel (2..4; 0 elsewhere): q is [batch, width, heads, dim], out
+  // [batch, width, heads * dim], positions (nullable) [batch, width]
+  int width;
   float* out;
   // workspace
   int32_t* status;

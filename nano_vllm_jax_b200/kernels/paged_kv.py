@@ -87,8 +87,9 @@ class _Workspace:
 
     def __init__(self, device: torch.device, max_batch: int):
         lib = _lib.load()
-        with torch.cuda.device(device):
-            nbytes = int(lib.nvj_paged_decode_workspace_bytes(int(max_batch)))
+        with torch.cuda.device(device):  # one buffer serves the width-1 and the wide kernel (never in flight together)
+            nbytes = max(int(lib.nvj_paged_decode_workspace_bytes(int(max_batch))),
+                         int(lib.nvj_paged_decode_wide_workspace_bytes(int(max_batch))))
         if nbytes <= 0:
             raise NvjError("nvj_paged_decode_workspace_bytes failed (no CUDA device?)")
         self.max_batch = int(max_batch)
@@ -348,6 +349,40 @@ def _decode_call(q3, k_layer, v_layer, block_tables, table_width, kv_indptr, kv_
     check(rc, what)
     if _strict():
         _check_word(ws.status_tensor(), what, ws)
+    return out
+
+
+WIDE_DECODE_MAX_WIDTH = 4
+
+
+def wide_decode_supported(q, k_layer) -> bool:
+    """Whether `paged_decode_attention_wide` takes this batch: 2..4 query tokens per row, the model's shape, bf16."""
+    return (q.ndim == 4 and 2 <= q.shape[1] <= WIDE_DECODE_MAX_WIDTH and q.dtype == torch.bfloat16
+            and k_layer.dtype == torch.bfloat16 and tuple(q.shape[2:]) == (8, 256) and tuple(k_layer.shape[1:]) == (16, 2, 256))
+
+
+def paged_decode_attention_wide(q, k_layer, v_layer, block_table, seq_lens, positions, scale):
+    """Decode attention for rows of 2..4 query tokens: q `[B, T, 8, 256]` bf16 -> `[B, T, 8 * 256]` fp32.
+
+    Token t of row b sees keys p < seq_lens[b] with p <= positions[b, t] (the reference's wide decode,
+    nanovllm_jax/kv_cache.py:852-998); K and V of a row are read once for all of its tokens.
+    """
+    if not wide_decode_supported(q, k_layer):
+        raise ValueError("paged_decode_attention_wide: 2..4 bf16 query tokens per row over the bf16 cache [NB, 16, 2, 256]")
+    lib = _lib.load()
+    batch, width = int(q.shape[0]), int(q.shape[1])
+    q = q.contiguous()
+    tables = block_table.to(torch.int32).contiguous()
+    lens = seq_lens.to(torch.int32).contiguous()
+    pos = None if positions is None else positions.to(torch.int32).reshape(batch, width).contiguous()
+    out = torch.empty((batch, width, 8 * 256), dtype=torch.float32, device=q.device)
+    ws = _workspace(q.device, batch)
+    _lib.check(lib.nvj_paged_decode_wide(q.data_ptr(), k_layer.data_ptr(), v_layer.data_ptr(), int(k_layer.shape[0]),
+                                         tables.data_ptr(), int(tables.shape[1]), lens.data_ptr(),
+                                         0 if pos is None else pos.data_ptr(), batch, width, float(scale), out.data_ptr(),
+                                         ws.buf.data_ptr(), ws.nbytes, _stream(q.device)), "nvj_paged_decode_wide")
+    if _strict():
+        _check_word(ws.status_tensor(), "paged decode (wide)", ws)
     return out
 
 

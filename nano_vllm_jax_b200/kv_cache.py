@@ -264,6 +264,10 @@ def paged_attention_decode(query, k_cache, v_cache, block_table, kv_lens, block_
         raise ValueError("num_key_value_groups does not match the head counts")
     lens = kv_lens.to(torch.int32).clamp(max=int(max_kv_len))
     tables = block_table.to(torch.int32)
+    if positions is not None and query_len > 1 and _k.wide_decode_supported(query, k_layer):
+        # 2..4 query tokens per row: the streaming kernel of the width-1 path with the products on the tensor cores
+        out = _k.paged_decode_attention_wide(query, k_layer, v_layer, tables, lens, positions, scale)
+        return out.to(_promoted(query, k_cache, out_dtype))
     if positions is not None and query_len > 1:
         # a rectangular batch is a packed batch with rows of equal width: K/V of a row are then read once for all
         # of its query tokens (tensor-core tiles for the model's shape) instead of once per token
