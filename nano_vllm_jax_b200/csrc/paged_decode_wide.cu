@@ -9,8 +9,9 @@
 // rows form one sequence cut into equal ranges, one per CTA (one CTA per SM here, the accumulators
 // need the registers); a ring of (K, V) blocks is kept in flight; a row that straddles CTAs is
 // finished by the CTA that arrives last, in two levels when it was cut into many partials.
-//   * Staging: TMA tiled copies with the 128-byte swizzle, one box per (K|V, kv head, 64-dim chunk)
-//     = [16 tokens][128 B], so that ldmatrix reads the tiles without bank conflicts.
+//   * Staging: one TMA tiled copy per 16 KiB block of K and of V, over a 4-D view of the cache whose box
+//     lands as [kv head][64-dim chunk][16 tokens][128 B] with the 128-byte swizzle, so that ldmatrix reads
+//     the tiles without bank conflicts.
 //   * Warp w = (block parity w & 1, kv head (w >> 1) & 1, dim half w >> 2).  The four warps of a
 //     parity take every other block: each computes the 16 x 16 scores of its KV head over all 256
 //     dims (the two dim halves repeat this; it is a quarter of the work) and accumulates its 128
@@ -27,7 +28,12 @@
 
 namespace nvj {
 
-constexpr int kWStages = 5;
+// An even number, so that a stage always holds blocks of the same parity and is read by the same four warps: a
+// parity wait can only tell two consecutive phases of an mbarrier apart, and a warp that waited for every other
+// phase of a stage's barrier could take an unfinished phase for the one after it, release the stage early and
+// leave a copy in flight when the CTA exits (seen as a launch failure with five stages).
+constexpr int kWStages = 4;
+static_assert(kWStages % 2 == 0, "each stage must belong to one block parity");
 constexpr int kWMaxWidth = 4;
 constexpr int kWSlotRows = kWMaxWidth * kHq;  // rows of one partial slot: [token][head]
 constexpr int kWPad = 136;                    // row pitch (floats) of the parity exchange buffer
@@ -47,10 +53,13 @@ struct WideSmem {
   int abort_flag;
 };
 
-__device__ __forceinline__ void w_tma_3d(uint32_t dst, const CUtensorMap* map, int x, int y, int z, uint32_t bar) {
+// One whole block (16 KiB) of the 4-D view {64 dims, token, 64-dim chunk, kv head} of a cache layer.
+__device__ __forceinline__ void w_tma_block(uint32_t dst, const CUtensorMap* map, int token, uint32_t bar) {
+  uint64_t policy;  // every block is read once: do not let it displace what the L2 is good for
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
   asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
-      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(bar)
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3, %4, %5}], [%6], %7;"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(0), "r"(token), "r"(0), "r"(0), "r"(bar), "l"(policy)
       : "memory");
 }
 
@@ -87,12 +96,8 @@ __device__ __forceinline__ void w_issue_block(const DecodeParams& p, WideSmem& s
   const int blk = sm.ring_blk[n & (kRing - 1)];
   if (sm.ring_rows[n & (kRing - 1)] > 0) {
     mbar_arrive_expect_tx(full, 2u * kTileBytes);
-    const uint32_t kdst = smem_u32(sm.tiles[stage][0]), vdst = smem_u32(sm.tiles[stage][1]);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {  // i = kv head * 4 + chunk
-      w_tma_3d(kdst + i * 2048, k_map, (i & 3) * 64, i >> 2, blk * kBlk, full);
-      w_tma_3d(vdst + i * 2048, v_map, (i & 3) * 64, i >> 2, blk * kBlk, full);
-    }
+    w_tma_block(smem_u32(sm.tiles[stage][0]), k_map, blk * kBlk, full);
+    w_tma_block(smem_u32(sm.tiles[stage][1]), v_map, blk * kBlk, full);
   } else {
     mbar_arrive(full);
   }
@@ -429,13 +434,15 @@ static WEncodeTiledFn w_encode_fn() {
   return fn;
 }
 
-// bf16 tensor [tokens of the pool, kv head, 256] (row pitch 512 B), boxes of [16 tokens, 1, 64 dims], 128-byte swizzle
+// A cache layer [token, kv head, 256] bf16 seen as {64 dims, token, 64-dim chunk, kv head}: one box of
+// {64, 16, 4, 2} is a whole block, and lands in shared memory as [kv head][chunk][16 tokens][128 B] with the
+// 128-byte swizzle inside every [token][128 B] panel.
 static bool w_make_map(CUtensorMap* map, const void* base, uint64_t tokens) {
-  const cuuint64_t dims[3] = {(cuuint64_t)kD, (cuuint64_t)kHkv, tokens};
-  const cuuint64_t strides[2] = {(cuuint64_t)kRowBytes, (cuuint64_t)kTokenBytes};
-  const cuuint32_t box[3] = {64, 1, (cuuint32_t)kBlk};
-  const cuuint32_t estr[3] = {1, 1, 1};
-  return w_encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+  const cuuint64_t dims[4] = {64, tokens, 4, (cuuint64_t)kHkv};
+  const cuuint64_t strides[3] = {(cuuint64_t)kTokenBytes, 128, (cuuint64_t)kRowBytes};
+  const cuuint32_t box[4] = {64, (cuuint32_t)kBlk, 4, (cuuint32_t)kHkv};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  return w_encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
