@@ -453,7 +453,7 @@ def run_b200(args, w):
             "gpu_launches": (4 if token_gather is not None else 3) * K_steps,
             "step_mode": step_mode,
             "eager_value": total_rows / (ms_eager / K_steps * 1e-3), "eager_ms_per_step": ms_eager / K_steps,
-            "roofline": {"bound": "hbm", "kernel": "decode_pipelined_kernel (fused append + paged GQA decode)",
+            "roofline": {"bound": "hbm", "kernel": "decode_wide_kernel at width 1 (fused append + paged GQA decode, TMA-staged, tensor-core tiles)",
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": peak_kind + " HBM copy bandwidth", "frac_of_8TBs_nominal": achieved / 8000.0,
                          "bytes_per_launch": bytes_per_launch, "us_per_launch": ms_kernel / K_steps * 1e3,

@@ -165,8 +165,11 @@ int nvj_paged_decode_workspace_init(void* workspace, size_t workspace_bytes,
  *   kv_last_page_len nullable [batch]; with kv_indptr it clips the length to
  *                (pages - 1) * P + last_page_len as paged_attention.py:171-178 does
  *   out          [batch, num_q_heads, head_dim] float32
- *   variant      0 = auto, 1 = generic kernel, 2 = bulk-copy pipelined kernel
- *                (bf16 cache, block_size 16, 2 kv heads x 4 q heads, head_dim 256)
+ *   variant      0 = auto, 1 = generic kernel; for the model's shape (bf16 cache, block_size 16,
+ *                2 kv heads x 4 q heads, head_dim 256): 2 = bulk-copy pipelined kernel on the CUDA
+ *                cores (bf16 or f32 queries), 3 = TMA-staged streaming kernel with the products on
+ *                tensor-core tiles (bf16 queries; what auto picks first).  NVJ_ERR_UNSUPPORTED when
+ *                2 or 3 is asked for another shape.
  */
 int nvj_paged_decode(const void* q, int q_dtype,
                      const void* k_cache_layer, const void* v_cache_layer, int kv_dtype,

@@ -32,7 +32,7 @@ static int run_decode(DecodeParams& p, void* workspace, size_t workspace_bytes, 
       p.num_kv_heads <= 0 || p.num_q_heads <= 0 || p.head_dim <= 0)
     return NVJ_ERR_INVALID_ARGUMENT;
   if (p.num_q_heads % p.num_kv_heads != 0) return NVJ_ERR_INVALID_ARGUMENT;
-  if (variant < 0 || variant > 2) return NVJ_ERR_INVALID_ARGUMENT;
+  if (variant < 0 || variant > 3) return NVJ_ERR_INVALID_ARGUMENT;
   if (p.batch == 0) return NVJ_OK;
   if (!p.q || !p.k_cache || !p.v_cache || !p.block_tables || !p.seq_lens || !p.out)
     return NVJ_ERR_INVALID_ARGUMENT;
@@ -42,7 +42,16 @@ static int run_decode(DecodeParams& p, void* workspace, size_t workspace_bytes, 
   const int rc = carve_workspace(p, workspace, workspace_bytes, num_ctas);
   if (rc != NVJ_OK) return rc;
   const bool fast_ok = pipelined_shape(p) && (!p.new_k || !p.kv_indptr);
-  if (variant == 2 && !fast_ok) return NVJ_ERR_UNSUPPORTED;
+  // The tensor-core streaming kernel (bf16 queries) first: one CTA per SM, whole blocks by TMA, products on
+  // mma.sync tiles; it needs a tensor-map encoder from the driver.  Then the CUDA-core pipelined kernel.
+  const bool mma_ok = fast_ok && p.q_dtype == NVJ_BF16;
+  if ((variant == 2 && !fast_ok) || (variant == 3 && !mma_ok)) return NVJ_ERR_UNSUPPORTED;
+  if (variant == 3 || (variant == 0 && mma_ok)) {
+    p.width = 1;
+    const int rc3 = launch_decode_wide(p, stream);
+    if (rc3 != NVJ_ERR_UNSUPPORTED || variant == 3) return rc3;
+    p.width = 0;
+  }
   if (variant == 2 || (variant == 0 && fast_ok)) return launch_decode_pipelined(p, num_ctas, stream);
   if (p.new_k) {
     if (p.kv_indptr) return NVJ_ERR_UNSUPPORTED;

@@ -115,6 +115,8 @@ inline size_t ws_acc_bytes(int num_ctas) { return ws_round(sizeof(float) * ws_sl
 int decode_num_ctas();  // 2 per SM of the current device
 int launch_decode_generic(const DecodeParams& p, cudaStream_t stream);
 int launch_decode_pipelined(const DecodeParams& p, int num_ctas, cudaStream_t stream);
+int decode_wide_num_ctas();  // 1 per SM of the current device
+int launch_decode_wide(const DecodeParams& p, cudaStream_t stream);  // tensor-core streaming kernel, width 1..4
 int append_decode_rows(const void* new_k, const void* new_v, const int32_t* positions,
                        const int32_t* seq_lens, void* k_cache, void* v_cache, int kv_dtype,
                        long long num_blocks, int block_size, int row_elems,

@@ -35,7 +35,6 @@ namespace nvj {
 constexpr int kWStages = 4;
 static_assert(kWStages % 2 == 0, "each stage must belong to one block parity");
 constexpr int kWMaxWidth = 4;
-constexpr int kWSlotRows = kWMaxWidth * kHq;  // rows of one partial slot: [token][head]
 constexpr int kWPad = 136;                    // row pitch (floats) of the parity exchange buffer
 
 struct WideSmem {
@@ -217,6 +216,7 @@ __device__ __forceinline__ void w_finish_segment(const DecodeParams& p, WideSmem
   const bool whole_row = (s.j0 == 0 && s.j1 == s.nb);
   const long long out_row = s.b;
   const int slot = partial_slot(blockIdx.x, s.j0 == 0);
+  const int slot_rows = p.width * kHq;  // rows of one partial slot: [token][head]
   if (par == 0) {
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
@@ -229,7 +229,7 @@ __device__ __forceinline__ void w_finish_segment(const DecodeParams& p, WideSmem
       const int head = kvh * kG + (row & 3);
       const float inv = whole_row ? (L > 0.f ? 1.f / L : 0.f) : 1.f;
       float* dst = whole_row ? p.out + ((out_row * p.width + tok) * kHq + head) * kD
-                             : p.part_acc + ((long long)slot * kWSlotRows + tok * kHq + head) * kD;
+                             : p.part_acc + ((long long)slot * slot_rows + tok * kHq + head) * kD;
       dst += dh * 128 + 2 * t;
 #pragma unroll
       for (int n = 0; n < 16; ++n) {
@@ -238,7 +238,7 @@ __device__ __forceinline__ void w_finish_segment(const DecodeParams& p, WideSmem
             make_float2((st.o[n][2 * r] * f0 + x.x * f1) * inv, (st.o[n][2 * r + 1] * f0 + x.y * f1) * inv);
       }
       if (!whole_row && dh == 0 && t == 0)
-        *reinterpret_cast<float2*>(p.part_ml + ((long long)slot * kWSlotRows + tok * kHq + head) * 2) = make_float2(M, L);
+        *reinterpret_cast<float2*>(p.part_ml + ((long long)slot * slot_rows + tok * kHq + head) * 2) = make_float2(M, L);
     }
   }
   if (whole_row) {
@@ -263,14 +263,14 @@ __device__ __forceinline__ void w_finish_segment(const DecodeParams& p, WideSmem
   __threadfence();
   if (!tree) {
     for (int tok = 0; tok < p.width; ++tok) {
-      fold_parts<true>(p, sm.red, tid, 0, c_lo, c_lo, c_hi - c_lo + 1, (out_row * p.width + tok) * kHq, kWSlotRows, tok * kHq);
+      fold_parts<true>(p, sm.red, tid, 0, c_lo, c_lo, c_hi - c_lo + 1, (out_row * p.width + tok) * kHq, slot_rows, tok * kHq);
       named_bar_sync(1, kDecodeThreads);
     }
     if (tid == 0) *counter = 0;
     return;
   }
   for (int tok = 0; tok < p.width; ++tok) {
-    fold_parts<false>(p, sm.red, tid, 0, first, c_lo, last - first + 1, 2LL * grid + 2 * cg + (cg == g_lo ? 1 : 0), kWSlotRows,
+    fold_parts<false>(p, sm.red, tid, 0, first, c_lo, last - first + 1, 2LL * grid + 2 * cg + (cg == g_lo ? 1 : 0), slot_rows,
                       tok * kHq);
     named_bar_sync(1, kDecodeThreads);
   }
@@ -282,7 +282,7 @@ __device__ __forceinline__ void w_finish_segment(const DecodeParams& p, WideSmem
   if (!sm.is_last) return;
   __threadfence();
   for (int tok = 0; tok < p.width; ++tok) {
-    fold_parts<true>(p, sm.red, tid, 2LL * grid, g_lo, g_lo, g_hi - g_lo + 1, (out_row * p.width + tok) * kHq, kWSlotRows,
+    fold_parts<true>(p, sm.red, tid, 2LL * grid, g_lo, g_lo, g_hi - g_lo + 1, (out_row * p.width + tok) * kHq, slot_rows,
                      tok * kHq);
     named_bar_sync(1, kDecodeThreads);
   }
@@ -370,7 +370,7 @@ decode_wide_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_const
         st.qa[ks][r] = real ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * ft) : 0u;
         st.qa[ks][r + 2] = real ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 8 + 2 * ft) : 0u;
       }
-      st.pos[r] = real ? (p.positions ? p.positions[(long long)s.b * p.width + tok] : 0x7fffffff) : -1;
+      st.pos[r] = real ? (p.positions && !p.new_k ? p.positions[(long long)s.b * p.width + tok] : 0x7fffffff) : -1;
       st.m[r] = kNegBig;
       st.l[r] = 0.f;
     }
@@ -379,6 +379,32 @@ decode_wide_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_const
 #pragma unroll
       for (int e = 0; e < 4; ++e) st.o[n][e] = 0.f;
 
+    // Fused append (width 1).  The CTA that owns block min(pos / 16, nb - 1) of the row writes the new K/V row
+    // (one warp per KV head); its copy of that block may race with the store, so every warp that reads the block
+    // overwrites the row in the staged tile, from the same source, once the copy has landed: no fence is needed
+    // and nothing waits for the store.
+    int patch_j = -1, patch_t = 0;
+    if (p.new_k) {
+      const int pos = p.positions[s.b];
+      const int jt = pos >> 4;
+      const int jw = jt < s.nb - 1 ? jt : s.nb - 1;
+      if (pos >= 0 && jw >= s.j0 && jw < s.j1) {
+        const long long tgt = jt < p.table_width ? (long long)p.block_tables[decode_table_base(p, s.b) + jt] : -1;
+        if (tgt >= 0 && tgt < p.num_blocks) {
+          if (par == 0 && dh == 0) {
+            const long long src = (long long)s.b * kTokenBytes + kvh * kRowBytes + lane * 16;
+            const long long dst = (tgt * kBlk + (pos & 15)) * kTokenBytes + kvh * kRowBytes + lane * 16;
+            *reinterpret_cast<uint4*>(const_cast<char*>(p.k_cache) + dst) =
+                *reinterpret_cast<const uint4*>(static_cast<const char*>(p.new_k) + src);
+            *reinterpret_cast<uint4*>(const_cast<char*>(p.v_cache) + dst) =
+                *reinterpret_cast<const uint4*>(static_cast<const char*>(p.new_v) + src);
+          }
+          if (jt == jw && pos < s.len) { patch_j = jw; patch_t = pos & 15; }
+        } else if (warp == 0 && lane == 0) {
+          atomicOr(p.status, NVJ_DEV_BAD_BLOCK_ID);
+        }
+      }
+    }
     for (int jb = s.j0; jb < s.j1; ++jb, ++it) {
       if ((it & (kRing / 2 - 1)) == 0 && it > 0) {
         named_bar_sync(1, kDecodeThreads);
@@ -390,6 +416,13 @@ decode_wide_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_const
       const int stage = it % kWStages;
       mbar_wait(smem_u32(&sm.full_bar[stage]), (uint32_t)(it / kWStages) & 1u, &sm.abort_flag, p.status);
       const int rows = sm.ring_rows[it & (kRing - 1)];
+      if (jb == patch_j) {  // lane l carries 16-byte piece l of the KV head's 512-byte row; the source is cache-hot
+        const long long src = (long long)s.b * kTokenBytes + kvh * kRowBytes + lane * 16;
+        const uint32_t off = kvh * 8192 + (lane >> 3) * 2048 + patch_t * 128 + (((lane & 7) ^ (patch_t & 7)) << 4);
+        *reinterpret_cast<uint4*>(sm.tiles[stage][0] + off) = *reinterpret_cast<const uint4*>(static_cast<const char*>(p.new_k) + src);
+        *reinterpret_cast<uint4*>(sm.tiles[stage][1] + off) = *reinterpret_cast<const uint4*>(static_cast<const char*>(p.new_v) + src);
+        __syncwarp();
+      }
       if (rows > 0)
         w_process_block(smem_u32(sm.tiles[stage][0]) + kvh * 8192, smem_u32(sm.tiles[stage][1]) + kvh * 8192, lane, dh, rows,
                         jb * kBlk, c, st);
@@ -449,7 +482,7 @@ static bool w_make_map(CUtensorMap* map, const void* base, uint64_t tokens) {
 
 static int g_wide_ctas[64];
 
-static int wide_num_ctas() {
+int decode_wide_num_ctas() {  // one per SM of the current device
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
   if (g_wide_ctas[dev] == 0) {
@@ -460,17 +493,40 @@ static int wide_num_ctas() {
   return g_wide_ctas[dev];
 }
 
-static size_t wide_ml_bytes(int n) { return ws_round(sizeof(float) * ws_slots(n) * kWSlotRows * 2); }
-static size_t wide_acc_bytes(int n) { return ws_round(sizeof(float) * ws_slots(n) * kWSlotRows * kD); }
+static size_t wide_ml_bytes(int n, int width) { return ws_round(sizeof(float) * ws_slots(n) * width * kHq * 2); }
+static size_t wide_acc_bytes(int n, int width) { return ws_round(sizeof(float) * ws_slots(n) * width * kHq * kD); }
+
+// p carries everything but the tensor maps: pointers, shapes, width (1..4) and the carved workspace, whose
+// partial area holds ws_slots(decode_wide_num_ctas()) slots of width * kHq rows.
+int launch_decode_wide(const DecodeParams& p, cudaStream_t stream) {
+  if (p.width < 1 || p.width > kWMaxWidth || p.num_blocks < 1 || p.num_blocks * kBlk > 0x7fffffffLL || !w_encode_fn())
+    return NVJ_ERR_UNSUPPORTED;
+  const int n = decode_wide_num_ctas();
+  if (n <= 0) return NVJ_ERR_LAUNCH;
+  CUtensorMap k_map, v_map;
+  if (!w_make_map(&k_map, p.k_cache, (uint64_t)p.num_blocks * kBlk) || !w_make_map(&v_map, p.v_cache, (uint64_t)p.num_blocks * kBlk))
+    return NVJ_ERR_UNSUPPORTED;
+  static bool smem_opted_in[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return NVJ_ERR_LAUNCH;
+  const int smem = (int)sizeof(WideSmem) + 1024;
+  if (!smem_opted_in[dev]) {
+    if (cudaFuncSetAttribute(decode_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+      return NVJ_ERR_LAUNCH;
+    smem_opted_in[dev] = true;
+  }
+  decode_wide_kernel<<<n, kDecodeThreads, smem, stream>>>(k_map, v_map, p);
+  return cudaGetLastError() == cudaSuccess ? NVJ_OK : NVJ_ERR_LAUNCH;
+}
 
 }  // namespace nvj
 
 extern "C" size_t nvj_paged_decode_wide_workspace_bytes(int max_batch) {
   using namespace nvj;
   if (max_batch < 0) return 0;
-  const int n = wide_num_ctas();
+  const int n = decode_wide_num_ctas();
   if (n <= 0) return 0;
-  return ws_header_bytes(max_batch) + wide_ml_bytes(n) + wide_acc_bytes(n);
+  return ws_header_bytes(max_batch) + wide_ml_bytes(n, kWMaxWidth) + wide_acc_bytes(n, kWMaxWidth);
 }
 
 extern "C" int nvj_paged_decode_wide(const void* q, const void* k_cache_layer, const void* v_cache_layer, int64_t num_blocks,
@@ -486,13 +542,10 @@ extern "C" int nvj_paged_decode_wide(const void* q, const void* k_cache_layer, c
                        reinterpret_cast<uintptr_t>(v_cache_layer) | reinterpret_cast<uintptr_t>(out) |
                        reinterpret_cast<uintptr_t>(workspace);
   if ((al & 15u) != 0) return NVJ_ERR_UNSUPPORTED;
-  if (num_blocks < 1 || num_blocks * kBlk > 0x7fffffffLL || !w_encode_fn()) return NVJ_ERR_UNSUPPORTED;
-  const int n = wide_num_ctas();
+  const int n = decode_wide_num_ctas();
   if (n <= 0) return NVJ_ERR_LAUNCH;
-  if (!workspace || workspace_bytes < ws_header_bytes(batch) + wide_ml_bytes(n) + wide_acc_bytes(n)) return NVJ_ERR_WORKSPACE;
-  CUtensorMap k_map, v_map;
-  if (!w_make_map(&k_map, k_cache_layer, (uint64_t)num_blocks * kBlk) || !w_make_map(&v_map, v_cache_layer, (uint64_t)num_blocks * kBlk))
-    return NVJ_ERR_UNSUPPORTED;
+  if (!workspace || workspace_bytes < ws_header_bytes(batch) + wide_ml_bytes(n, width) + wide_acc_bytes(n, width))
+    return NVJ_ERR_WORKSPACE;
   char* w = static_cast<char*>(workspace);
   DecodeParams p{};
   p.q = q;
@@ -506,7 +559,7 @@ extern "C" int nvj_paged_decode_wide(const void* q, const void* k_cache_layer, c
   p.status = reinterpret_cast<int32_t*>(w);
   p.counters = reinterpret_cast<int32_t*>(w + 64);
   p.part_ml = reinterpret_cast<float*>(w + ws_header_bytes(batch));
-  p.part_acc = reinterpret_cast<float*>(w + ws_header_bytes(batch) + wide_ml_bytes(n));
+  p.part_acc = reinterpret_cast<float*>(w + ws_header_bytes(batch) + wide_ml_bytes(n, width));
   p.num_blocks = num_blocks;
   p.batch = batch;
   p.table_width = table_width;
@@ -517,15 +570,5 @@ extern "C" int nvj_paged_decode_wide(const void* q, const void* k_cache_layer, c
   p.q_dtype = NVJ_BF16;
   p.kv_dtype = NVJ_BF16;
   p.scale = scale;
-  static bool smem_opted_in[64];
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return NVJ_ERR_LAUNCH;
-  const int smem = (int)sizeof(WideSmem) + 1024;
-  if (!smem_opted_in[dev]) {
-    if (cudaFuncSetAttribute(decode_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-      return NVJ_ERR_LAUNCH;
-    smem_opted_in[dev] = true;
-  }
-  decode_wide_kernel<<<n, kDecodeThreads, smem, static_cast<cudaStream_t>(stream)>>>(k_map, v_map, p);
-  return cudaGetLastError() == cudaSuccess ? NVJ_OK : NVJ_ERR_LAUNCH;
+  return launch_decode_wide(p, static_cast<cudaStream_t>(stream));
 }

@@ -18,7 +18,7 @@ pytestmark = pytest.mark.gpu
 
 CONTRACT = 2e-2
 TIGHT = 2e-3
-GENERIC, PIPELINED = 1, 2
+GENERIC, PIPELINED, TENSOR = 1, 2, 3
 
 
 def _K():
@@ -45,14 +45,14 @@ def _check(out, ref, active):
     assert err <= TIGHT, f"regression bound broken: max-abs {err}"
 
 
-@pytest.mark.parametrize("variant", [GENERIC, PIPELINED])
+@pytest.mark.parametrize("variant", [GENERIC, PIPELINED, TENSOR])
 def test_config1_single_layer_decode(variant):
     c = decode_case(1, 256, 4, 64, 512)
     out = _run(c, variant)
     _check(out, _oracle(c), np.ones(4, bool))
 
 
-@pytest.mark.parametrize("variant", [GENERIC, PIPELINED])
+@pytest.mark.parametrize("variant", [GENERIC, PIPELINED, TENSOR])
 def test_every_length_from_0_to_3_blocks_plus_1(variant):
     # one batch row per length 0 .. 3*bs+1: empty rows, partial last blocks of every size, exact multiples
     n = 3 * BS + 2
@@ -65,7 +65,7 @@ def test_every_length_from_0_to_3_blocks_plus_1(variant):
     assert not out[~active].any()  # rows with seq_len 0 are defined to be zeros
 
 
-@pytest.mark.parametrize("variant", [GENERIC, PIPELINED])
+@pytest.mark.parametrize("variant", [GENERIC, PIPELINED, TENSOR])
 def test_padded_rows_interleaved_and_layer_offset(variant):
     c = decode_case(3, 300, 9, 20, 200, layers=2, empty_rows=(0, 4, 8))
     out = _run(c, variant, layer=1)
@@ -75,17 +75,19 @@ def test_padded_rows_interleaved_and_layer_offset(variant):
     assert not out[~active].any()
 
 
-def test_rows_split_across_many_ctas():
-    # 3 rows of ~4000 keys = ~750 blocks over ~296 CTAs: every row is finished by a cross-CTA merge
+@pytest.mark.parametrize("variant", [PIPELINED, TENSOR])
+def test_rows_split_across_many_ctas(variant):
+    # 3 rows of ~4000 keys = ~750 blocks over the CTAs: every row is finished by a cross-CTA merge
     c = decode_case(4, 900, 3, 3900, 4095)
-    out = _run(c, PIPELINED)
+    out = _run(c, variant)
     _check(out, _oracle(c), np.ones(3, bool))
-    again = _run(c, PIPELINED)  # arrival counters were left at zero: a second launch gives the same bits
+    again = _run(c, variant)  # arrival counters were left at zero: a second launch gives the same bits
     np.testing.assert_array_equal(bits(out), bits(again))
 
 
+@pytest.mark.parametrize("variant", [PIPELINED, TENSOR])
 @pytest.mark.parametrize("lens", [(20000,), (9000, 30, 9000, 700, 5), (3000, 12000, 1, 6000)])
-def test_few_long_rows_are_merged_in_two_levels(lens):
+def test_few_long_rows_are_merged_in_two_levels(lens, variant):
     # rows cut into more than 32 partials: groups of 16 CTAs fold first, the last group folds the groups;
     # short rows between them share CTAs and groups with the long ones
     c = decode_case(9, 2600, len(lens), 1, 1)
@@ -97,15 +99,16 @@ def test_few_long_rows_are_merged_in_two_levels(lens):
     for b in range(len(lens)):
         c["tables"][b, :need[b]] = perm[o:o + need[b]]
         o += need[b]
-    out = _run(c, PIPELINED)
+    out = _run(c, variant)
     _check(out, _oracle(c), np.ones(len(lens), bool))
-    again = _run(c, PIPELINED)  # row and group counters were left at zero
+    again = _run(c, variant)  # row and group counters were left at zero
     np.testing.assert_array_equal(bits(out), bits(again))
 
 
-def test_mixed_short_and_long_rows():
+@pytest.mark.parametrize("variant", [PIPELINED, TENSOR])
+def test_mixed_short_and_long_rows(variant):
     c = decode_case(5, 4096, 40, 1, 1500)
-    out = _run(c, PIPELINED)
+    out = _run(c, variant)
     ref = _oracle(c)
     _check(out, ref, np.ones(40, bool))
     gen = _run(c, GENERIC)
@@ -135,9 +138,11 @@ def test_long_ranges_refill_the_block_id_ring():
     K = _K()
     t_tables, t_lens = to_torch(tables), to_torch(lens)
     fast = K.paged_decode_attention(q, kc, vc, t_tables, t_lens, SCALE, variant=PIPELINED)
+    tensor = K.paged_decode_attention(q, kc, vc, t_tables, t_lens, SCALE, variant=TENSOR)
     slow = K.paged_decode_attention(q, kc, vc, t_tables, t_lens, SCALE, variant=GENERIC)
     torch.cuda.synchronize()
     assert float((fast - slow).abs().max()) <= TIGHT
+    assert float((tensor - slow).abs().max()) <= TIGHT
     # two rows against the CPU oracle (the gather of all rows would need tens of GB on the host)
     for b in (0, rows - 1):
         blocks = tables[b, :need[b]]
@@ -148,7 +153,7 @@ def test_long_ranges_refill_the_block_id_ring():
         assert np.abs(to_numpy(fast[b]).reshape(-1) - ref).max() <= TIGHT
 
 
-@pytest.mark.parametrize("variant", [GENERIC, PIPELINED])
+@pytest.mark.parametrize("variant", [GENERIC, PIPELINED, TENSOR])
 def test_fused_append_cache_bit_exact_and_attention(variant):
     K = _K()
     c = decode_case(7, 2048, 33, 1, 900, layers=2, empty_rows=(5,))
@@ -170,7 +175,8 @@ def test_fused_append_cache_bit_exact_and_attention(variant):
     assert not to_numpy(out)[~active].any()
 
 
-def test_fused_equals_append_then_decode_bitwise():
+@pytest.mark.parametrize("variant", [PIPELINED, TENSOR])
+def test_fused_equals_append_then_decode_bitwise(variant):
     K = _K()
     from nano_vllm_jax_b200 import kv_cache as kv
     c = decode_case(8, 2048, 64, 100, 400)
@@ -178,17 +184,17 @@ def test_fused_equals_append_then_decode_bitwise():
     kc2, vc2 = to_torch(c["k_cache"]), to_torch(c["v_cache"])
     out1, _, _ = K.paged_decode_attention_with_kv_append(
         to_torch(c["q"]), to_torch(c["new_k"]), to_torch(c["new_v"]), kc1, vc1, to_torch(c["tables"]),
-        to_torch(c["seq_lens"]), to_torch(c["positions"]), 0, BS, SCALE, 4, variant=PIPELINED)
+        to_torch(c["seq_lens"]), to_torch(c["positions"]), 0, BS, SCALE, 4, variant=variant)
     s = kv.compute_slot_mapping(to_torch(c["positions"]), to_torch(c["tables"]), BS)
     kv.update_kv_cache(kc2, vc2, s, to_torch(c["new_k"]), to_torch(c["new_v"]), 0)
     out2 = K.paged_decode_attention(to_torch(c["q"][:, 0]), kc2[0], vc2[0], to_torch(c["tables"]),
-                                    to_torch(c["seq_lens"]), SCALE, variant=PIPELINED)
+                                    to_torch(c["seq_lens"]), SCALE, variant=variant)
     torch.cuda.synchronize()
     assert torch.equal(kc1, kc2) and torch.equal(vc1, vc2)
     assert torch.equal(out1.reshape(64, 8, 256), out2)
 
 
-@pytest.mark.parametrize("variant", [GENERIC, PIPELINED])
+@pytest.mark.parametrize("variant", [GENERIC, PIPELINED, TENSOR])
 def test_csr_page_table_form(variant):
     # reference tests/test_paged_attention_abi.py:100-151 shape: P16, Hq8/Hkv2, D256, lens [17, 31]
     K = _K()
@@ -284,7 +290,7 @@ def test_rectangular_prefill_with_rows_padded_at_position_zero():
     assert np.abs(to_numpy(out) - ref).max() <= TIGHT
 
 
-@pytest.mark.parametrize("variant", [GENERIC, PIPELINED])
+@pytest.mark.parametrize("variant", [GENERIC, PIPELINED, TENSOR])
 def test_block_id_outside_the_pool_is_flagged_not_read(variant):
     K = _K()
     c = decode_case(12, 64, 2, 30, 60)
