@@ -40,10 +40,10 @@ BS, HQ, HKV, D = 16, 8, 2, 256
 SCALE = 1.0 / 16.0
 TOKEN_BYTES = 2 * HKV * D * 2  # K + V row of one token, bf16
 FALLBACK_HBM_GBS = 6650.0
-# dram__bytes_read.sum + dram__bytes_write.sum of decode_pipelined_kernel over its algorithmic bytes, from the
-# ncu capture of `--workload c2small` (profiles/decode_pipelined_c2small_ncu_full.md): 316-320 MB moved for
-# 311.2 MB algorithmic.  K/V traffic grows in proportion to the tokens read, so the ratio carries over to c2.
-DRAM_TRAFFIC_RATIO = 1.02
+# dram__bytes_read.sum + dram__bytes_write.sum of decode_wide_kernel over its algorithmic bytes, from the
+# ncu capture of `--workload c2small` (profiles/decode_wide_c2small_ncu_full.md): 314.2-314.7 MB moved for
+# 310.5 MB algorithmic.  K/V traffic grows in proportion to the tokens read, so the ratio carries over to c2.
+DRAM_TRAFFIC_RATIO = 1.012
 
 WORKLOADS = {
     # name: (total rows at N=1 or overall, ctx_lo, ctx_hi, pool blocks per rank or None = sized to fit, scaling)
@@ -458,7 +458,7 @@ def run_b200(args, w):
                          "peak_source": peak_kind + " HBM copy bandwidth", "frac_of_8TBs_nominal": achieved / 8000.0,
                          "bytes_per_launch": bytes_per_launch, "us_per_launch": ms_kernel / K_steps * 1e3,
                          "traffic": DRAM_TRAFFIC_RATIO * bytes_per_launch,
-                         "traffic_source": "ncu dram bytes of the c2small capture scaled by algorithmic bytes (ratio 1.02)"},
+                         "traffic_source": "ncu dram bytes of the c2small capture scaled by algorithmic bytes (ratio 1.012)"},
             "cpu_baseline": cpu,
             "clocks": clocks,
         }
