@@ -106,9 +106,14 @@ def decode_cases(dev, iters):
            2 * rows * TOKEN_BYTES + rows * 4, {"workload": "c2"})
     report("compute_slot_mapping (256 tokens)", small.run(lambda: K.compute_slot_mapping(pos, tables, BS)),
            rows * 12, {"workload": "c2"})
-    report("paged_decode (pipelined)", big.run(lambda: K.paged_decode_attention(q[:, 0], k[0], v[0], tables, t_lens, SCALE, variant=2)),
+    report("paged_decode (tensor-core streaming kernel, variant 3: the default for bf16 queries)", big.run(lambda: K.paged_decode_attention(q[:, 0], k[0], v[0], tables, t_lens, SCALE, variant=3)),
            kv_bytes + io, {"workload": "c2", "tok/s": None})
-    report("paged_decode + fused append (pipelined)",
+    report("paged_decode + fused append (tensor-core streaming kernel)",
+           big.run(lambda: K.paged_decode_attention_with_kv_append(q, nk, nv, k, v, tables, t_lens, pos, 0, BS, SCALE, 4, variant=3)),
+           kv_bytes + io + 2 * rows * TOKEN_BYTES, {"workload": "c2"})
+    report("paged_decode (CUDA-core pipelined kernel, variant 2)", big.run(lambda: K.paged_decode_attention(q[:, 0], k[0], v[0], tables, t_lens, SCALE, variant=2)),
+           kv_bytes + io, {"workload": "c2", "tok/s": None})
+    report("paged_decode + fused append (CUDA-core pipelined kernel)",
            big.run(lambda: K.paged_decode_attention_with_kv_append(q, nk, nv, k, v, tables, t_lens, pos, 0, BS, SCALE, 4, variant=2)),
            kv_bytes + io + 2 * rows * TOKEN_BYTES, {"workload": "c2"})
     sub = 16  # the generic kernel re-reads K/V once per query head: time a 16-row slice
@@ -122,8 +127,13 @@ def decode_cases(dev, iters):
     qw = _randn_bf16((rows, width, HQ, D), 6, dev)
     wpos = (t_lens[:, None] - width + torch.arange(width, device=dev, dtype=torch.int32)[None, :]).contiguous()
     wbytes = kv_bytes + table_bytes + rows * width * (HQ * D * 2 + HQ * D * 4)
-    report("wide decode, 4 query tokens per row (packed tensor-core route)",
+    report("wide decode, 4 query tokens per row (tensor-core streaming kernel)",
            big.run(lambda: kvc.paged_attention_decode(qw, k, v, tables, t_lens, BS, SCALE, 4, positions=wpos, out_dtype=torch.float32)),
+           wbytes, {"workload": "c2, width 4"})
+    qsl_w = torch.arange(rows + 1, dtype=torch.int32, device=dev) * width
+    report("wide decode as a packed batch of equal-width rows (tcgen05 prefill tiles; what widths above 4 take)",
+           big.run(lambda: K.packed_paged_prefill_attention(qw.reshape(1, rows * width, HQ, D), k[0], v[0], tables, t_lens,
+                                                            wpos.reshape(1, -1), qsl_w, BS, SCALE, 4, num_decode_rows=0)),
            wbytes, {"workload": "c2, width 4"})
     rep_tables = tables.repeat_interleave(width, dim=0)
     rep_lens = torch.minimum(t_lens[:, None], wpos + 1).reshape(-1).contiguous()

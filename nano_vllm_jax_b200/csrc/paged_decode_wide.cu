@@ -24,7 +24,10 @@
 
 #include <cuda.h>
 
+#include <mutex>
+
 #include "decode_parts.cuh"
+#include "umma.cuh"
 
 namespace nvj {
 
@@ -214,7 +217,7 @@ __device__ __forceinline__ void w_finish_segment(const DecodeParams& p, WideSmem
   }
   named_bar_sync(1, kDecodeThreads);
   const bool whole_row = (s.j0 == 0 && s.j1 == s.nb);
-  const long long out_row = s.b;
+  const long long qbase = p.packed_rows ? (long long)p.query_start_loc[s.b] : (long long)s.b * p.width;  // first query token
   const int slot = partial_slot(blockIdx.x, s.j0 == 0);
   const int slot_rows = p.width * kHq;  // rows of one partial slot: [token][head]
   if (par == 0) {
@@ -228,7 +231,7 @@ __device__ __forceinline__ void w_finish_segment(const DecodeParams& p, WideSmem
       if (tok >= p.width) continue;
       const int head = kvh * kG + (row & 3);
       const float inv = whole_row ? (L > 0.f ? 1.f / L : 0.f) : 1.f;
-      float* dst = whole_row ? p.out + ((out_row * p.width + tok) * kHq + head) * kD
+      float* dst = whole_row ? p.out + ((qbase + tok) * kHq + head) * kD
                              : p.part_acc + ((long long)slot * slot_rows + tok * kHq + head) * kD;
       dst += dh * 128 + 2 * t;
 #pragma unroll
@@ -263,7 +266,7 @@ __device__ __forceinline__ void w_finish_segment(const DecodeParams& p, WideSmem
   __threadfence();
   if (!tree) {
     for (int tok = 0; tok < p.width; ++tok) {
-      fold_parts<true>(p, sm.red, tid, 0, c_lo, c_lo, c_hi - c_lo + 1, (out_row * p.width + tok) * kHq, slot_rows, tok * kHq);
+      fold_parts<true>(p, sm.red, tid, 0, c_lo, c_lo, c_hi - c_lo + 1, (qbase + tok) * kHq, slot_rows, tok * kHq);
       named_bar_sync(1, kDecodeThreads);
     }
     if (tid == 0) *counter = 0;
@@ -282,7 +285,7 @@ __device__ __forceinline__ void w_finish_segment(const DecodeParams& p, WideSmem
   if (!sm.is_last) return;
   __threadfence();
   for (int tok = 0; tok < p.width; ++tok) {
-    fold_parts<true>(p, sm.red, tid, 2LL * grid, g_lo, g_lo, g_hi - g_lo + 1, (out_row * p.width + tok) * kHq, slot_rows,
+    fold_parts<true>(p, sm.red, tid, 2LL * grid, g_lo, g_lo, g_hi - g_lo + 1, (qbase + tok) * kHq, slot_rows,
                      tok * kHq);
     named_bar_sync(1, kDecodeThreads);
   }
@@ -303,7 +306,7 @@ decode_wide_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_const
     int len = 0;
     if (b < p.batch) len = decode_row_len(p, b);
     mine += (len + kBlk - 1) / kBlk;
-    const unsigned idle = __ballot_sync(kFullMask, b < p.batch && len <= 0 && (b % grid) == (int)blockIdx.x);
+    const unsigned idle = __ballot_sync(kFullMask, !p.packed_rows && b < p.batch && len <= 0 && (b % grid) == (int)blockIdx.x);
     for (unsigned m = idle; m; m &= m - 1) {
       const int bb = base + (warp << 5) + (__ffs(m) - 1);
       float4* o = reinterpret_cast<float4*>(p.out + (long long)bb * p.width * kHq * kD);
@@ -359,18 +362,20 @@ decode_wide_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_const
   WideState st;
   while (next_seg(p, b, j, g, g1, s)) {
     // query rows of this KV head as A fragments: row = token * 4 + head of the group; rows past the width are zero
+    // (packed_rows: the row's single query token sits at query_start_loc[b]; its length is already capped by its position)
+    const long long qbase = p.packed_rows ? (long long)p.query_start_loc[s.b] : (long long)s.b * p.width;
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
       const int row = fg + 8 * r, tok = row >> 2;
       const bool real = tok < p.width;
       const __nv_bfloat16* qrow =
-          static_cast<const __nv_bfloat16*>(p.q) + (((long long)s.b * p.width + (real ? tok : 0)) * kHq + kvh * kG + (row & 3)) * kD;
+          static_cast<const __nv_bfloat16*>(p.q) + ((qbase + (real ? tok : 0)) * kHq + kvh * kG + (row & 3)) * kD;
 #pragma unroll
       for (int ks = 0; ks < 16; ++ks) {
         st.qa[ks][r] = real ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 2 * ft) : 0u;
         st.qa[ks][r + 2] = real ? *reinterpret_cast<const uint32_t*>(qrow + ks * 16 + 8 + 2 * ft) : 0u;
       }
-      st.pos[r] = real ? (p.positions && !p.new_k ? p.positions[(long long)s.b * p.width + tok] : 0x7fffffff) : -1;
+      st.pos[r] = real ? (p.positions && !p.new_k ? p.positions[qbase + tok] : 0x7fffffff) : -1;
       st.m[r] = kNegBig;
       st.l[r] = 0.f;
     }
@@ -480,6 +485,32 @@ static bool w_make_map(CUtensorMap* map, const void* base, uint64_t tokens) {
                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+struct MapEntry {
+  int kind;
+  const void* base;
+  uint64_t extent;
+  CUtensorMap map;
+};
+static std::mutex g_map_mutex;
+static MapEntry g_map_cache[128];
+static unsigned g_map_next;
+
+bool tensor_map_cached(CUtensorMap* map, int kind, const void* base, uint64_t extent, TensorMapMaker make) {
+  std::lock_guard<std::mutex> lock(g_map_mutex);
+  for (const MapEntry& e : g_map_cache)
+    if (e.base == base && e.extent == extent && e.kind == kind && e.base != nullptr) {
+      *map = e.map;
+      return true;
+    }
+  if (!make(map, base, extent)) return false;
+  MapEntry& e = g_map_cache[g_map_next++ % 128];
+  e.kind = kind;
+  e.base = base;
+  e.extent = extent;
+  e.map = *map;
+  return true;
+}
+
 static int g_wide_ctas[64];
 
 int decode_wide_num_ctas() {  // one per SM of the current device
@@ -504,7 +535,8 @@ int launch_decode_wide(const DecodeParams& p, cudaStream_t stream) {
   const int n = decode_wide_num_ctas();
   if (n <= 0) return NVJ_ERR_LAUNCH;
   CUtensorMap k_map, v_map;
-  if (!w_make_map(&k_map, p.k_cache, (uint64_t)p.num_blocks * kBlk) || !w_make_map(&v_map, p.v_cache, (uint64_t)p.num_blocks * kBlk))
+  if (!tensor_map_cached(&k_map, 0, p.k_cache, (uint64_t)p.num_blocks * kBlk, w_make_map) ||
+      !tensor_map_cached(&v_map, 0, p.v_cache, (uint64_t)p.num_blocks * kBlk, w_make_map))
     return NVJ_ERR_UNSUPPORTED;
   static bool smem_opted_in[64];
   int dev = 0;

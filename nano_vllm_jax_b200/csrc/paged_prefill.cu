@@ -88,7 +88,14 @@ extern "C" int nvj_paged_prefill_packed(const void* q, int q_dtype, const void* 
       d.q_dtype = q_dtype;
       d.kv_dtype = kv_dtype;
       d.scale = scale;
-      const int rc = launch_decode_pipelined(d, num_ctas, s);
+      // bf16 queries: the tensor-core streaming kernel (it declines without a tensor-map encoder); else the CUDA-core one
+      int rc = NVJ_ERR_UNSUPPORTED;
+      if (q_dtype == NVJ_BF16) {
+        d.width = 1;
+        rc = launch_decode_wide(d, s);
+        d.width = 0;
+      }
+      if (rc == NVJ_ERR_UNSUPPORTED) rc = launch_decode_pipelined(d, num_ctas, s);
       if (rc != NVJ_OK) return rc;
       skip_single = 1;
     }

@@ -439,8 +439,9 @@ int launch_prefill_umma(const void* q, int q_dtype, const char* k_cache, const c
     opted_in[dev] = true;
   }
   CUtensorMap k_map, v_map;
-  if (!um_make_map(&k_map, k_cache, kHkv, (uint64_t)num_blocks * kBlk, kBlk) ||
-      !um_make_map(&v_map, v_cache, kHkv, (uint64_t)num_blocks * kBlk, kBlk))
+  const TensorMapMaker make = [](CUtensorMap* m, const void* base, uint64_t tokens) { return um_make_map(m, base, kHkv, tokens, kBlk); };
+  if (!tensor_map_cached(&k_map, 1, k_cache, (uint64_t)num_blocks * kBlk, make) ||
+      !tensor_map_cached(&v_map, 1, v_cache, (uint64_t)num_blocks * kBlk, make))
     return NVJ_ERR_UNSUPPORTED;
   if (!skip_single &&
       cudaMemsetAsync(out, 0, sizeof(float) * (size_t)token_bucket * kHq * kD, stream) != cudaSuccess)

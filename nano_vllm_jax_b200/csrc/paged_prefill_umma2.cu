@@ -491,7 +491,8 @@ int launch_prefill_umma2(const void* q, int q_dtype, const char* k_cache, const 
     opted_in[dev] = true;
   }
   CUtensorMap k_map, v_map;
-  if (!u2_make_map(&k_map, k_cache, (uint64_t)num_blocks * kBlk) || !u2_make_map(&v_map, v_cache, (uint64_t)num_blocks * kBlk))
+  if (!tensor_map_cached(&k_map, 2, k_cache, (uint64_t)num_blocks * kBlk, u2_make_map) ||
+      !tensor_map_cached(&v_map, 2, v_cache, (uint64_t)num_blocks * kBlk, u2_make_map))
     return NVJ_ERR_UNSUPPORTED;
   // With skip_single the caller has zeroed `out` before its decode-row pass; otherwise the kernel zeroes what no
   // tile writes itself, which spares a memset launch in front of every pure prefill batch.

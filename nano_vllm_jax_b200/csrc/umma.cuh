@@ -139,4 +139,10 @@ __device__ __forceinline__ bool um_elect_one() {
 }
 
 
+// Host side.  Encoding a tensor map is a driver call of several microseconds and a serving loop presents the same few
+// cache layers over and over: `tensor_map_cached` keeps the last maps per kind of view (`kind` names the encoder),
+// keyed by base address and extent (a map holds nothing else), and calls `make` only on a miss.
+typedef bool (*TensorMapMaker)(CUtensorMap* map, const void* base, uint64_t extent);
+bool tensor_map_cached(CUtensorMap* map, int kind, const void* base, uint64_t extent, TensorMapMaker make);
+
 }  // namespace nvj
