@@ -111,7 +111,14 @@ extern "C" int nvj_paged_decode_static_scratch(const void* q, int q_dtype, const
   const bool fast = kv_dtype == NVJ_BF16 && block_size == kBlk && num_kv_heads == kHkv &&
                     num_q_heads == kHq && head_dim == kD && (q_dtype == NVJ_BF16 || q_dtype == NVJ_F32) &&
                     ptr16(q) && ptr16(k_cache_layer) && ptr16(v_cache_layer) && ptr16(out);
-  const int rc = fast ? launch_decode_pipelined(p, num_ctas, s) : launch_decode_generic(p, s);
+  int rc = NVJ_ERR_UNSUPPORTED;
+  // tensor-core streaming kernel, one CTA per SM: its partials fit the slots as long as the device has at most 320 SMs
+  if (fast && q_dtype == NVJ_BF16 && decode_wide_num_ctas() <= kStaticMaxCtas) {
+    p.width = 1;
+    rc = launch_decode_wide(p, s);
+    p.width = 0;
+  }
+  if (rc == NVJ_ERR_UNSUPPORTED) rc = fast ? launch_decode_pipelined(p, num_ctas, s) : launch_decode_generic(p, s);
   if (rc != NVJ_OK) return rc;
   if (status_out &&
       cudaMemcpyAsync(status_out, scratch, sizeof(int32_t), cudaMemcpyDeviceToDevice, s) != cudaSuccess)
