@@ -1,11 +1,13 @@
-// Paged GQA decode attention for rows that carry 2..4 query tokens (verification of speculated
-// tokens, multi-token prediction), same cache shape as the width-1 kernel: bf16, 16-token blocks,
-// 2 KV heads x 4 query heads, head_dim 256.
+// Paged GQA decode attention with the products on tensor-core tiles, for rows of 1..4 query tokens:
+// the decode step proper (width 1, with the optional fused append of the step's new K/V row) and
+// the verification of speculated tokens / multi-token prediction (width 2..4).  Cache shape of the
+// model's full-attention layer: bf16, 16-token blocks, 2 KV heads x 4 query heads, head_dim 256.
 //
-// With several query tokens per row the CUDA-core dot products of the width-1 kernel would make
-// the kernel compute-bound, so the scores and the weighted sums run on the tensor cores
-// (mma.sync m16n8k16, bf16 in, fp32 accumulate): the width * 4 query rows of one KV head fill one
-// 16-row tile.  Everything around the arithmetic is the width-1 kernel's scheme: all blocks of all
+// The kernel is HBM-bound: every K/V byte is read from HBM exactly once.  On the CUDA cores the dot
+// products take half of the issue slots at width 1 and would make the kernel compute-bound beyond
+// it, so the scores and the weighted sums run on the tensor cores (mma.sync m16n8k16, bf16 in, fp32
+// accumulate): the width * 4 query rows of one KV head fill one 16-row tile.  Around the arithmetic
+// the scheme is the CUDA-core kernel's (paged_decode.cu, decode_parts.cuh): all blocks of all
 // rows form one sequence cut into equal ranges, one per CTA (one CTA per SM here, the accumulators
 // need the registers); a ring of (K, V) blocks is kept in flight; a row that straddles CTAs is
 // finished by the CTA that arrives last, in two levels when it was cut into many partials.
@@ -19,8 +21,10 @@
 //     keeps the result within 2e-3 of an fp32 evaluation.
 //   * The two parities of a (kv head, dim half) merge through shared memory at the end of a row
 //     segment.
-// Semantics: nanovllm_jax/kv_cache.py:852-998 (query width T > 1: key p of row b is visible to
-// token t when p < seq_lens[b] and, with positions given, p <= positions[b, t]).
+// Semantics: nanovllm_jax/kv_cache.py:852-998 (key p of row b is visible to token t when
+// p < seq_lens[b] and, at width > 1 with positions given, p <= positions[b, t]); the fused append
+// follows nanovllm_jax/kernels/full_attention_triton.py:373-485 (positions are then the slots the
+// new rows go to).
 
 #include <cuda.h>
 
