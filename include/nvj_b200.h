@@ -272,7 +272,7 @@ int nvj_paged_decode_wide(const void* q, const void* k_cache_layer, const void* 
  *   out        [token_bucket, num_q_heads, head_dim] float32
  *   workspace  nullable decode workspace (nvj_paged_decode_workspace_bytes(rows)); when given,
  *              rows that hold exactly one query token (the decode rows of a mixed batch,
- *              nanovllm_jax/engine/scheduler.py:956-1032) are served by the pipelined decode
+ *              nanovllm_jax/engine/scheduler.py:956-1032) are served by the streaming decode
  *              kernel instead of a query tile
  *   variant    0 = automatic; 1 = generic CUDA-core kernel (any shape or dtype); for the model's
  *              shape (bf16 cache, block 16, 2 KV x 4 query heads, head_dim 256): 2 = mma.sync
