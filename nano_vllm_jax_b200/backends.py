@@ -16,6 +16,7 @@ In the reference a new implementation is chosen with one string per operation
 
 from __future__ import annotations
 
+import os
 from dataclasses import replace
 from typing import Optional
 
@@ -40,12 +41,28 @@ def normalize_full_attention_impl(value: Optional[str]) -> str:
     return v
 
 
+_CACHE_DTYPE_ENV = "NANO_VLLM_JAX_FULL_ATTN_KV_CACHE_DTYPE"
+_OFF_VALUES = {"", "0", "false", "no", "off", "none"}
+
+
 def full_attention_kv_cache_dtype(default_dtype, config=None):
-    """`full_attention_kv_cache_dtype` override (backends.py:100-118): default | bf16 | fp16 | fp32."""
-    name = str(getattr(config, "full_attention_kv_cache_dtype", "default") or "default").lower()
+    """`full_attention_kv_cache_dtype` override (backends.py:100-118): default | bf16 | fp16 | fp32 | off.
+
+    As in the reference (backends.py:74-80) the environment variable
+    NANO_VLLM_JAX_FULL_ATTN_KV_CACHE_DTYPE wins over the config attribute.
+    """
+    env = os.environ.get(_CACHE_DTYPE_ENV)
+    if env is not None:
+        name = env.strip().lower()
+    elif config is not None and hasattr(config, "full_attention_kv_cache_dtype"):
+        name = str(getattr(config, "full_attention_kv_cache_dtype") or "default").strip().lower()
+    else:
+        name = "default"
+    if name == "default" or name in _OFF_VALUES:
+        return default_dtype
     if name not in _CACHE_DTYPES:
-        raise ValueError(f"unsupported full_attention_kv_cache_dtype {name!r}")
-    return _CACHE_DTYPES[name] or default_dtype
+        raise ValueError(f"Unknown {_CACHE_DTYPE_ENV}={name!r}; expected fp32, bf16, fp16, default, or off")
+    return _CACHE_DTYPES[name]
 
 
 class B200Backend:
