@@ -123,9 +123,14 @@ slot_mapping_kernel(const int32_t* positions, const int32_t* block_tables, const
   int row = token_row_ids ? token_row_ids[i] : i / n_cols;
   row = row < 0 ? 0 : (row >= table_rows ? table_rows - 1 : row);
   const int pos = positions[i];
-  int col = pos / block_size;
-  col = col < 0 ? 0 : (col >= table_width ? table_width - 1 : col);  // clamped like an XLA gather
-  slots[i] = block_tables[(long long)row * table_width + col] * block_size + pos % block_size;
+  // floor division and a non-negative remainder, as jnp's // and % give for a negative position
+  // (nanovllm_jax/kv_cache.py:432-435); C's / and % would round toward zero
+  int col = pos / block_size, off = pos % block_size;
+  if (off < 0) { off += block_size; --col; }
+  // a negative block index wraps around once as NumPy / jnp indexing does, then the gather clamps
+  if (col < 0) col += table_width;
+  col = col < 0 ? 0 : (col >= table_width ? table_width - 1 : col);
+  slots[i] = block_tables[(long long)row * table_width + col] * block_size + off;
 }
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }

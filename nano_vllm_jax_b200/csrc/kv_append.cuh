@@ -62,9 +62,12 @@ __device__ __forceinline__ long long resolve_slot(const AppendParams& p, int i) 
       return -1;
     }
     if (p.seq_lens && p.seq_lens[b] <= 0) return -1;
-    const long long e =
-        (p.kv_indptr ? (long long)p.kv_indptr[b] : (long long)b * p.table_width) + pos / p.page_size;
-    if (e < 0 || e >= p.kv_indices_len) {
+    // the page index is bounded by the row's own page list, so a position past it cannot reach the next row's pages
+    const int page = pos / p.page_size;
+    const long long first = p.kv_indptr ? (long long)p.kv_indptr[b] : (long long)b * p.table_width;
+    const long long pages = p.kv_indptr ? (long long)p.kv_indptr[b + 1] - first : (long long)p.table_width;
+    const long long e = first + page;
+    if (page >= pages || e < 0 || e >= p.kv_indices_len) {
       if (p.status) atomicOr(p.status, NVJ_DEV_BAD_BLOCK_ID);
       return -1;
     }

@@ -19,7 +19,13 @@ an unbounded dict of arrays); snapshot and restore are index-list copy kernels
 (nvj_hybrid_snapshot / nvj_hybrid_restore), batched over all sequences of a
 step.  When the pool is full the least recently used entry is dropped and its
 hash leaves `cacheable_hashes`, so the block manager stops offering that prefix
-to hybrid models.
+to hybrid models.  Two kinds of entry are never dropped: one that was assigned
+earlier in the same `snapshot()` batch (its pool row is a destination of the
+copy kernel about to be launched), and one that a sequence has been allocated
+against but not yet seeded from (`pin` / `install_cached_prefix_hybrid_states`).
+When nothing can be dropped the snapshot of that sequence is skipped and its
+prefix is not published: a later request recomputes it, as it would after an
+eviction.
 """
 
 from __future__ import annotations
@@ -102,6 +108,7 @@ class PrefixStateCache:
         self.rec_pool = None if table.rec is None else torch.zeros((capacity, *table.rec.shape[1:]), dtype=torch.float32, device=dev)
         self._entry: "OrderedDict[int, int]" = OrderedDict()  # hash -> pool row, LRU order
         self._free = list(range(capacity - 1, -1, -1))
+        self._pins: Dict[int, int] = {}  # hash -> sequences allocated against it and not yet seeded
 
     def __contains__(self, prefix_hash: int) -> bool:
         return int(prefix_hash) in self._entry
@@ -114,13 +121,40 @@ class PrefixStateCache:
         """Hashes a hybrid model may reuse (`Scheduler._prefix_cacheable_hashes`)."""
         return set(self._entry)
 
-    def _row_for(self, prefix_hash: int) -> int:
+    # ---- pins: a hash a sequence was allocated against stays until that sequence has been seeded
+    def pin(self, prefix_hash: int) -> None:
+        h = int(prefix_hash)
+        self._pins[h] = self._pins.get(h, 0) + 1
+
+    def unpin(self, prefix_hash: int) -> None:
+        h = int(prefix_hash)
+        n = self._pins.get(h, 0) - 1
+        if n > 0:
+            self._pins[h] = n
+        else:
+            self._pins.pop(h, None)
+
+    def pin_for(self, seqs) -> None:
+        """Call after `BlockManager.allocate`: protects the state of every prefix a new sequence will start from."""
+        for seq in seqs:
+            h = getattr(seq, "cached_prefix_hash", None)
+            if (h is not None and int(getattr(seq, "num_cached_tokens", 0)) > 0
+                    and not getattr(seq, "cached_prefix_hybrid_seeded", False)
+                    and not getattr(seq, "_prefix_state_pinned", False)):
+                self.pin(h)
+                seq._prefix_state_pinned = True
+
+    def _row_for(self, prefix_hash: int, in_batch: set) -> Optional[int]:
+        """Pool row for a new snapshot of `prefix_hash`; None when the pool is full of rows that must stay."""
         row = self._entry.pop(prefix_hash, None)
         if row is None:
-            if not self._free:
-                _, row = self._entry.popitem(last=False)  # drop the least recently used snapshot
-            else:
+            if self._free:
                 row = self._free.pop()
+            else:
+                victim = next((h for h in self._entry if h not in in_batch and h not in self._pins), None)
+                if victim is None:
+                    return None
+                row = self._entry.pop(victim)  # the least recently used snapshot that may go
         self._entry[prefix_hash] = row
         return row
 
@@ -128,14 +162,28 @@ class PrefixStateCache:
         t = torch.tensor(values, dtype=torch.int32)
         return t.pin_memory().to(self.table.device, non_blocking=True) if self.table.device.type == "cuda" else t
 
-    def snapshot(self, seq_ids: Seq[int], prefix_hashes: Seq[int]) -> None:
-        """pool[hash] <- table[slot(seq)] for every pair, one batched copy."""
-        if not seq_ids:
-            return
-        slots = [self.table.slot(int(s)) for s in seq_ids]
-        rows = [self._row_for(int(h)) for h in prefix_hashes]
-        _k.hybrid_copy(self.table.conv, self.table.rec, self.conv_pool, self.rec_pool,
-                       self._idx(slots), self._idx(rows), restore=False)
+    def snapshot(self, seq_ids: Seq[int], prefix_hashes: Seq[int]) -> List[bool]:
+        """pool[hash] <- table[slot(seq)] for every pair, one batched copy.  Returns, per pair, whether the state is
+        stored now (False: the pool had no row that could be given up)."""
+        stored: List[bool] = []
+        slots, rows, in_batch = [], [], set()
+        for s, h in zip(seq_ids, prefix_hashes):
+            h = int(h)
+            if h in in_batch:  # the same prefix twice in one step: one copy is enough (the states are identical)
+                stored.append(True)
+                continue
+            row = self._row_for(h, in_batch)
+            if row is None:
+                stored.append(False)
+                continue
+            in_batch.add(h)
+            slots.append(self.table.slot(int(s)))
+            rows.append(row)
+            stored.append(True)
+        if rows:
+            _k.hybrid_copy(self.table.conv, self.table.rec, self.conv_pool, self.rec_pool,
+                           self._idx(slots), self._idx(rows), restore=False)
+        return stored
 
     def restore(self, seq_ids: Seq[int], prefix_hashes: Seq[int]) -> None:
         """table[slot(seq)] <- pool[hash]; a hash without a snapshot is a RuntimeError."""
@@ -167,6 +215,9 @@ class PrefixStateCache:
         self.restore(ids, hashes)
         for seq in todo:
             seq.cached_prefix_hybrid_seeded = True
+            if getattr(seq, "_prefix_state_pinned", False):
+                self.unpin(seq.cached_prefix_hash)
+                seq._prefix_state_pinned = False
 
     def record_computed_prefix_states(self, block_manager, seqs, prefill_chunk_lengths) -> None:
         """After a prefill step: snapshot block-aligned prefixes, then publish them (scheduler.py:239-279)."""
@@ -184,6 +235,7 @@ class PrefixStateCache:
             if h is None or not self.table.has(int(seq.seq_id)):
                 continue
             ids.append(int(seq.seq_id)); hashes.append(int(h)); publish.append((seq, computed))
-        self.snapshot(ids, hashes)
-        for seq, computed in publish:
-            block_manager.publish_computed_prefix(seq, computed)
+        stored = self.snapshot(ids, hashes)
+        for (seq, computed), ok in zip(publish, stored):
+            if ok:  # a prefix without a stored state must not be offered to later requests
+                block_manager.publish_computed_prefix(seq, computed)

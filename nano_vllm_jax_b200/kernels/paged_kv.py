@@ -101,6 +101,10 @@ class _Workspace:
 
 
 _workspaces: dict[tuple[int, int], _Workspace] = {}
+# Workspaces that a larger one has replaced.  They are kept until the process ends: a CUDA graph captured on
+# the stream while the smaller buffer was current still holds its address, and a freed buffer could be handed
+# to another tensor by the caching allocator before that graph is replayed.
+_retired_workspaces: list[_Workspace] = []
 _status_words: dict[tuple[int, int], torch.Tensor] = {}
 
 
@@ -108,6 +112,8 @@ def _workspace(device: torch.device, batch: int) -> _Workspace:
     key = (device.index if device.index is not None else torch.cuda.current_device(), _stream(device))
     ws = _workspaces.get(key)
     if ws is None or ws.max_batch < batch:
+        if ws is not None:
+            _retired_workspaces.append(ws)
         ws = _Workspace(device, max(batch, 256, 2 * (ws.max_batch if ws else 0)))
         _workspaces[key] = ws
     return ws
@@ -415,13 +421,32 @@ def paged_decode_attention_no_alloc(q, k_layer, v_layer, block_table, seq_lens, 
     if q.ndim != 3 or block_table.ndim != 2 or block_table.shape[0] != q.shape[0]:
         raise ValueError("q must be [batch, heads, head_dim] and block_table [batch, width]")
     batch, hq, d = q.shape
+    pages, page_size, hkv, dk = k_layer.shape
+    if d != dk:
+        raise ValueError("q and cache head_dim must match")
+    if hq % hkv != 0:
+        raise ValueError("num_q_heads must be divisible by num_kv_heads")
+    if q.dtype not in _DTYPES:
+        raise ValueError(f"unsupported q dtype {q.dtype}")
     if tuple(out.shape) != (batch, hq, d) or out.dtype != torch.float32 or not out.is_cuda or not out.is_contiguous():
         raise ValueError("out must be a contiguous float32 CUDA tensor [batch, heads, head_dim]")
     if not q.is_contiguous():
         raise ValueError("q must be contiguous (this call makes no copies)")
-    block_table = _i32("block_table", block_table)
-    seq_lens = _i32("seq_lens", seq_lens)
-    pages, page_size, hkv, _ = k_layer.shape
+    # nothing may be copied or converted here: the operands are used where they lie
+    for name, t in (("block_table", block_table), ("seq_lens", seq_lens)):
+        _cuda(name, t)
+        if t.dtype != torch.int32 or not t.is_contiguous():
+            raise ValueError(f"{name} must be a contiguous int32 tensor (this call makes no copies)")
+    if tuple(seq_lens.shape) != (batch,):
+        raise ValueError("seq_lens must have shape [batch]")
+    tensors = [k_layer, v_layer, out, block_table, seq_lens]
+    if status_out is not None:
+        if (not isinstance(status_out, torch.Tensor) or not status_out.is_cuda or status_out.dtype != torch.int32
+                or status_out.numel() < 1 or not status_out.is_contiguous()):
+            raise ValueError("status_out must be a CUDA int32 tensor with at least one element")
+        tensors.append(status_out)
+    if any(t.device != q.device for t in tensors):
+        raise ValueError("all tensors must live on the device of q")
     rc = lib.nvj_paged_decode_static_scratch(_ptr(q), _dt(q), _ptr(k_layer), _ptr(v_layer), _dt(k_layer), pages,
                                              page_size, hkv, d, hq, _ptr(block_table), block_table.shape[1],
                                              _ptr(seq_lens), batch, float(scale), _ptr(out), _ptr(status_out),

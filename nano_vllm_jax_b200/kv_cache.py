@@ -296,8 +296,9 @@ def paged_attention(query, k_cache, v_cache, slot_mapping, kv_lens, scale, num_k
                     layer_idx: int = 0, out_dtype=None):
     """Legacy prefill (kv_cache.py:567-647): keys of row b are the slots slot_mapping[b, :], causal mask.
 
-    Each row's slot list is read as a table of one-token pages, so token t of row
-    b attends slot_mapping[b, 0..t].
+    Each row's slot list is read as a block table of one-token pages and the batch travels the packed
+    prefill route as `batch` rows of `seq_len` tokens, so token t of row b attends slot_mapping[b, 0..t];
+    the metadata built for it is O(batch * seq_len).
     """
     batch, seq_len, num_heads, head_dim = query.shape
     k_layer, _ = _resolve_kv_layer(k_cache, layer_idx)
@@ -305,10 +306,13 @@ def paged_attention(query, k_cache, v_cache, slot_mapping, kv_lens, scale, num_k
     hkv = k_layer.shape[-2]
     k1 = k_layer.reshape(-1, 1, hkv, head_dim)
     v1 = v_layer.reshape(-1, 1, hkv, head_dim)
-    tables = slot_mapping.to(torch.int32).repeat_interleave(seq_len, dim=0)
-    lens = (torch.arange(seq_len, dtype=torch.int32, device=query.device) + 1).repeat(batch)
-    out = _k.paged_decode_attention(query.reshape(batch * seq_len, num_heads, head_dim), k1, v1, tables,
-                                    lens, scale)
+    dev = query.device
+    positions = torch.arange(seq_len, dtype=torch.int32, device=dev).repeat(batch)[None]
+    qsl = torch.arange(batch + 1, dtype=torch.int32, device=dev) * seq_len
+    lens = torch.full((batch,), seq_len, dtype=torch.int32, device=dev)
+    out = _k.packed_paged_prefill_attention(query.reshape(1, batch * seq_len, num_heads, head_dim), k1, v1,
+                                            slot_mapping.to(torch.int32), lens, positions, qsl, 1, scale,
+                                            num_key_value_groups, seq_len, num_decode_rows=0)
     return out.reshape(batch, seq_len, num_heads * head_dim).to(_promoted(query, k_cache, out_dtype))
 
 

@@ -162,3 +162,36 @@ def test_empty_and_out_of_range():
     assert float(kc.float().abs().max()) == 0.0
     K.kv_append_slots(one, one, torch.tensor([[31]], dtype=torch.int32, device="cuda"), kc[0], vc[0])
     assert float(kc[0, 1, 15].float().min()) == 1.0
+
+
+def test_slot_mapping_of_negative_positions_floors_like_the_reference():
+    # jnp's // and % floor (nanovllm_jax/kv_cache.py:432-435): position -1 is offset bs - 1 of block index -1,
+    # which indexes the table's last column; C's / and % would give column 0, offset -1
+    tables = np.array([[3, 1, 7], [2, 4, 6]], np.int32)
+    positions = np.array([[-1, 0, 17], [-16, -17, 33]], np.int32)
+    want = R.compute_slot_mapping(positions, tables, 16)
+    np.testing.assert_array_equal(want, [[7 * 16 + 15, 48, 17], [6 * 16, 4 * 16 + 15, 6 * 16 + 1]])
+    got = _kv().compute_slot_mapping(to_torch(positions), to_torch(tables), 16)
+    np.testing.assert_array_equal(to_numpy(got), want)
+    rid = np.array([[1, 1, 0, 0, 1, 0]], np.int32)
+    ppos = positions.reshape(1, -1)
+    np.testing.assert_array_equal(to_numpy(_kv().compute_packed_slot_mapping(to_torch(ppos), to_torch(tables), to_torch(rid), 16)),
+                                  R.compute_packed_slot_mapping(ppos, tables, rid, 16))
+
+
+def test_page_table_append_does_not_reach_into_the_next_rows_pages():
+    # row 0 owns 2 pages; a position in "page 2" must be flagged and dropped, not written into row 1's first page
+    from nano_vllm_jax_b200.kernels import paged_kv as K
+    k0 = np.zeros((6, 4, 1, 8), np.float32)
+    kc, vc = to_torch(k0), to_torch(k0.copy())
+    one = torch.ones((1, 1, 8), dtype=torch.float32, device="cuda")
+    indices = to_torch(np.array([0, 1, 2, 3], np.int32))
+    indptr = to_torch(np.array([0, 2, 4], np.int32))
+    last = to_torch(np.array([4, 4], np.int32))
+    with pytest.raises(K.DeviceStatusError):
+        K.kv_append_paged_nhd(one, one, to_torch(np.array([0], np.int32)), to_torch(np.array([8], np.int32)), kc, vc,
+                              indices, indptr, last)
+    assert float(kc.abs().max()) == 0.0 and float(vc.abs().max()) == 0.0
+    K.kv_append_paged_nhd(one, one, to_torch(np.array([0], np.int32)), to_torch(np.array([7], np.int32)), kc, vc,
+                          indices, indptr, last)
+    assert float(kc[1, 3].min()) == 1.0 and float(kc.sum()) == 8.0

@@ -316,3 +316,23 @@ def test_validation_errors_match_the_reference_messages():
         kv.paged_attention_decode(*args, BS, SCALE, 4, max_kv_len=10 ** 6)
     with pytest.raises(ValueError, match="CUDA tensor"):
         kv.paged_attention_decode(args[0].cpu(), *args[1:], BS, SCALE, 4)
+
+
+def test_fused_append_position_beyond_the_table_is_flagged_on_the_generic_route_too():
+    # a shape only the generic kernel serves (fp32, block 4): the append in front of it must treat a position past
+    # the row's table as the fused kernels do (flag, no write), not write into the next row's block
+    K = _K()
+    rng = np.random.default_rng(14)
+    L, nb, bs, hkv, d = 1, 8, 4, 1, 8
+    k0 = np.zeros((L, nb, bs, hkv, d), np.float32)
+    kc, vc = to_torch(k0), to_torch(k0.copy())
+    q = to_torch(rng.standard_normal((2, 1, 2, d)).astype(np.float32))
+    nk = torch.ones((2, 1, hkv, d), dtype=torch.float32, device="cuda")
+    tables = to_torch(np.array([[1, 2], [3, 4]], np.int32))
+    lens = to_torch(np.array([5, 5], np.int32))
+    bad_pos = to_torch(np.array([[8], [4]], np.int32))   # row 0: block index 2 of a 2-wide table
+    with pytest.raises(K.DeviceStatusError):
+        K.paged_decode_attention_with_kv_append(q, nk, nk, kc, vc, tables, lens, bad_pos, 0, bs, 0.3, 2)
+    torch.cuda.synchronize()
+    assert float(kc[0, 3].abs().max()) == 0.0            # row 1's first block untouched by row 0
+    assert float(kc[0, 4, 0].min()) == 1.0               # row 1's own token landed
