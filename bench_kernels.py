@@ -1,6 +1,6 @@
 """Per-kernel timings of the path on one GPU (one JSON line per kernel).
 
-    python -m nano_vllm_jax_b200.bench_kernels [--iters N]
+    python bench_kernels.py [--iters N] [--only decode|prefill|...]
 
 Every case uses seeded synthetic inputs with the shapes of the baseline
 configurations (append and decode: 256 rows, contexts U[1024, 4096]; prefill and
@@ -15,13 +15,17 @@ from __future__ import annotations
 
 import argparse
 import json
+import os
 import statistics
+import sys
 
 import numpy as np
 import torch
 
-from .engine.prefix_state import HybridStateTable, PrefixStateCache
-from .kernels import paged_kv as K
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+from nano_vllm_jax_b200.engine.prefix_state import HybridStateTable, PrefixStateCache  # noqa: E402
+from nano_vllm_jax_b200.kernels import paged_kv as K  # noqa: E402
 
 BS, HQ, HKV, D = 16, 8, 2, 256
 SCALE = 1.0 / 16.0
@@ -122,7 +126,7 @@ def decode_cases(dev, iters):
                lambda: K.paged_decode_attention(q[:sub, 0], k[0], v[0], tables[:sub], t_lens[:sub], SCALE, variant=1)),
            int(lens[:sub].sum()) * TOKEN_BYTES, {"workload": "c2, first 16 rows"})
     # speculative-verify decode: 4 query tokens per row at the last 4 positions (rows already appended)
-    from . import kv_cache as kvc
+    from nano_vllm_jax_b200 import kv_cache as kvc
     width = 4
     qw = _randn_bf16((rows, width, HQ, D), 6, dev)
     wpos = (t_lens[:, None] - width + torch.arange(width, device=dev, dtype=torch.int32)[None, :]).contiguous()
@@ -320,8 +324,8 @@ def comparator_case(dev, iters):
 def mixed_step_case(dev, iters):
     """The KV path of one mixed continuous-batching step over 6 layers: 32 decode rows (contexts in
     [128, 2048]) plus 2 prefill chunks of 256 tokens, packed; per layer one append and one attention."""
-    from .backends import B200Backend
-    from .kv_cache import KVCacheStorage
+    from nano_vllm_jax_b200.backends import B200Backend
+    from nano_vllm_jax_b200.kv_cache import KVCacheStorage
     rng = np.random.default_rng(4)
     layers, pool = 6, 8192
     ctx = rng.integers(128, 2049, size=32)

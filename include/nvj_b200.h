@@ -13,6 +13,13 @@
  *   flat slot     slot = block_id * block_size + position % block_size
  *   block tables  [rows, table_width] int32, unused entries 0
  *
+ * Process state.  The compute entry points allocate nothing and keep no per-call state; what the library keeps
+ * per process is (a) a cache of encoded TMA tensor maps keyed by (base address, extent), behind a mutex,
+ * (b) once-per-device kernel attributes set on first use (guarded), (c) the wait limit of nvj_set_wait_limit_ns,
+ * (d) the device address of the static scratch of nvj_paged_decode_static_scratch.  All entry points may be called
+ * from several host threads.  The set-up calls nvj_p2p_buffer_create / open / close / destroy allocate, map and
+ * synchronise by design; nothing else does.
+ *
  * Device-side problems (a block id outside the pool, a wait that ran out) never
  * trap: the kernel skips the access, ORs a NVJ_DEV_* bit into a status word and
  * returns.  The status word is `int32_t* status` where a function takes one, or
@@ -362,11 +369,24 @@ int nvj_advance_decode_metadata(int32_t* seq_lens, int32_t* positions, int batch
  *   nvj_p2p_buffer_create         cudaMalloc + zero + IPC handle (64 bytes) of this rank's buffer
  *   nvj_p2p_buffer_open / close   map / unmap a peer's buffer from its handle
  *   nvj_p2p_buffer_destroy        free this rank's buffer (after every peer has closed it)
- *   nvj_p2p_allgather_i32         one step: out[r * n + i] = rank r's local[i].  `peer_buffers` is a HOST array of
+ *   nvj_p2p_allgather_i32         one step, blocking: out[r * n + i] = rank r's local[i].  `peer_buffers` is a HOST array of
  *                                 `world` device pointers ([rank] = this rank's own buffer); `epoch` starts at 1 and
  *                                 grows by 1 per call on every rank, or is 0 on every call: the kernel then keeps
- *                                 the count in the rank's buffer (a launch that can be replayed from a CUDA graph).  The kernel waits at most 1 s for its peers and
- *                                 then flags NVJ_DEV_TIMEOUT in *status.
+ *                                 the count in the rank's buffer (a launch that can be replayed from a CUDA graph).
+ *                                 The kernel waits for its peers up to the wait limit (below) and then flags
+ *                                 NVJ_DEV_TIMEOUT in *status and returns; with host-passed epochs the same call can
+ *                                 simply be issued again.
+ *
+ * The split form keeps the wait out of the decode step (device-kept epochs only; do not mix with the blocking form
+ * on one buffer):
+ *   nvj_p2p_argmax_publish        tokens[r] = argmax of row r of x [rows, row_len] (as nvj_row_argmax), stored locally
+ *                                 and into every peer's buffer, then this rank's next epoch is published.  Waits for
+ *                                 nobody.  rows must equal the n the buffers were sized for.
+ *   nvj_p2p_collect               waits (up to the wait limit) for the oldest published epoch not collected yet and
+ *                                 writes out[r * n + i]; returns at once when there is none.  A step k + 1 runs it beside
+ *                                 its append + decode and in front of its own publish, so that a rank late by less than a
+ *                                 step costs nothing; after the last step one more call fetches the last tokens.  On a
+ *                                 timeout NVJ_DEV_TIMEOUT is flagged, nothing is consumed and the call can be repeated.
  */
 size_t nvj_p2p_gather_buffer_bytes(int world, int n);
 int nvj_p2p_buffer_create(size_t bytes, void** dev_ptr, unsigned char* handle64);
@@ -375,6 +395,23 @@ int nvj_p2p_buffer_close(void* dev_ptr);
 int nvj_p2p_buffer_destroy(void* dev_ptr);
 int nvj_p2p_allgather_i32(const int32_t* local, int n, int rank, int world, void* const* peer_buffers,
                           uint32_t epoch, int32_t* out, int32_t* status, nvj_stream_t stream);
+int nvj_p2p_argmax_publish(const float* x, int rows, int row_len, int32_t* tokens, int rank, int world,
+                           void* const* peer_buffers, nvj_stream_t stream);
+int nvj_p2p_collect(void* own_buffer, int n, int world, int32_t* out, int32_t* status, nvj_stream_t stream);
+
+/* ------------------------------------------------------------- bounded waits */
+
+/*
+ * No kernel of this library waits without a limit.  A wait on a CTA's own copies is bounded by a fixed 1 s; a wait
+ * on another GPU (the token gather above) by the process-wide limit set here (default 1 s; 0 restores the default).
+ * When a limit runs out the kernel ORs NVJ_DEV_TIMEOUT into its status word and returns; the context stays usable.
+ * nvj_selftest_bounded_wait runs the mbarrier wait of the pipelined kernels on a barrier that nobody arrives on,
+ * with the current limit: *status receives NVJ_DEV_TIMEOUT and *returned the number of threads that came back (64).
+ * The reference has no device-side waits and no counterpart.
+ */
+void nvj_set_wait_limit_ns(uint64_t ns);
+uint64_t nvj_get_wait_limit_ns(void);
+int nvj_selftest_bounded_wait(int32_t* status, int32_t* returned, nvj_stream_t stream);
 
 /* ------------------------------------------------------------------ tokens */
 

@@ -10,7 +10,7 @@ from __future__ import annotations
 import ctypes
 import os
 import threading
-from ctypes import c_char_p, c_float, c_int, c_int64, c_size_t, c_uint32, c_void_p
+from ctypes import c_char_p, c_float, c_int, c_int64, c_size_t, c_uint32, c_uint64, c_void_p
 
 from . import build as _build
 
@@ -67,6 +67,11 @@ SIGNATURES = {
     "nvj_p2p_buffer_close": (c_int, [c_void_p]),
     "nvj_p2p_buffer_destroy": (c_int, [c_void_p]),
     "nvj_p2p_allgather_i32": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_uint32, c_void_p, c_void_p, c_void_p]),
+    "nvj_p2p_argmax_publish": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p]),
+    "nvj_p2p_collect": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "nvj_set_wait_limit_ns": (None, [c_uint64]),
+    "nvj_get_wait_limit_ns": (c_uint64, []),
+    "nvj_selftest_bounded_wait": (c_int, [c_void_p, c_void_p, c_void_p]),
     "nvj_row_argmax": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p]),
 }
 

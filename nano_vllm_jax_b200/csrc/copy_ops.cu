@@ -7,6 +7,7 @@
 // algorithmic traffic is 2 x bytes moved (one read, one write).
 
 #include "nvj_common.cuh"
+#include "row_argmax.cuh"
 
 namespace nvj {
 
@@ -91,54 +92,11 @@ copy_blocks_kernel(char* k_cache, char* v_cache, long long num_blocks, long long
   else copy_span1(base + s * block_bytes, base + d * block_bytes, block_bytes, blockIdx.x, gridDim.x);
 }
 
-// One CTA per row; the first maximum wins, NaNs are never selected unless the
-// whole row is NaN (then index 0).
-__global__ void __launch_bounds__(128)
+// One CTA per row.
+__global__ void __launch_bounds__(kArgmaxThreads)
 row_argmax_kernel(const float* x, int row_len, int32_t* tokens) {
-  const float* row = x + (long long)blockIdx.x * row_len;
-  float best = -INFINITY;
-  int best_i = 0x7fffffff;
-  if ((row_len & 3) == 0 && (reinterpret_cast<uintptr_t>(row) & 15u) == 0) {
-    // 16-byte loads, four in flight per thread: the row is read in one or two round trips instead of row_len / 128
-    const float4* row4 = reinterpret_cast<const float4*>(row);
-    const int n4 = row_len >> 2;
-    for (int base = threadIdx.x; base < n4; base += 4 * blockDim.x) {
-      float4 v[4];
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int j = base + u * blockDim.x;
-        v[u] = j < n4 ? row4[j] : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
-      }
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int i0 = (base + u * blockDim.x) * 4;
-        const float e[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
-#pragma unroll
-        for (int c = 0; c < 4; ++c)
-          if (e[c] > best || (e[c] == best && i0 + c < best_i)) { best = e[c]; best_i = i0 + c; }
-      }
-    }
-  } else {
-    for (int i = threadIdx.x; i < row_len; i += blockDim.x) {
-      const float v = row[i];
-      if (v > best || (v == best && i < best_i)) { best = v; best_i = i; }
-    }
-  }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    const float ov = __shfl_xor_sync(kFullMask, best, o);
-    const int oi = __shfl_xor_sync(kFullMask, best_i, o);
-    if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
-  }
-  __shared__ float sv[4];
-  __shared__ int si[4];
-  if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = best; si[threadIdx.x >> 5] = best_i; }
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    for (int w = 1; w < 4; ++w)
-      if (sv[w] > best || (sv[w] == best && si[w] < best_i)) { best = sv[w]; best_i = si[w]; }
-    tokens[blockIdx.x] = best_i == 0x7fffffff ? 0 : best_i;
-  }
+  const int token = row_argmax_cta(x + (long long)blockIdx.x * row_len, row_len);
+  if (threadIdx.x == 0) tokens[blockIdx.x] = token;
 }
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -271,6 +229,6 @@ extern "C" int nvj_row_argmax(const float* x, int rows, int row_len, int32_t* to
   if (rows < 0 || row_len <= 0) return NVJ_ERR_INVALID_ARGUMENT;
   if (rows == 0) return NVJ_OK;
   if (!x || !tokens) return NVJ_ERR_INVALID_ARGUMENT;
-  row_argmax_kernel<<<rows, 128, 0, static_cast<cudaStream_t>(stream)>>>(x, row_len, tokens);
+  row_argmax_kernel<<<rows, kArgmaxThreads, 0, static_cast<cudaStream_t>(stream)>>>(x, row_len, tokens);
   return cudaGetLastError() == cudaSuccess ? NVJ_OK : NVJ_ERR_LAUNCH;
 }

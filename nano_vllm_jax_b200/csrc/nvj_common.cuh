@@ -7,6 +7,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
+
 #include "../../include/nvj_b200.h"
 
 namespace nvj {
@@ -14,8 +16,11 @@ namespace nvj {
 constexpr unsigned kFullMask = 0xffffffffu;
 
 // Longest time any device-side wait may poll before the kernel gives up, flags
-// NVJ_DEV_TIMEOUT and runs to its end without waiting any more.
+// NVJ_DEV_TIMEOUT and runs to its end without waiting any more.  Waits on a CTA's own copies use this
+// fixed bound; waits on another GPU (the token gather) take the process-wide limit set by
+// nvj_set_wait_limit_ns, whose default is this value.
 constexpr unsigned long long kWaitLimitNs = 1000ull * 1000ull * 1000ull;
+unsigned long long wait_limit_ns();  // host: the current process-wide limit
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -83,13 +88,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // so that all warps reach the end of the kernel (results are then invalid and
 // the status word says so).
 static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity,
-                                            volatile int* abort_flag, int32_t* status) {
+                                            volatile int* abort_flag, int32_t* status,
+                                            unsigned long long limit_ns) {
   const unsigned long long t0 = global_timer_ns();
   for (uint32_t i = 0;; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((i & 31u) == 31u) {
       if (*abort_flag) return false;
-      if (global_timer_ns() - t0 > kWaitLimitNs) {
+      if (global_timer_ns() - t0 > limit_ns) {
         *abort_flag = 1;
         if (status) atomicOr(status, NVJ_DEV_TIMEOUT);
         return false;
@@ -99,10 +105,11 @@ static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity
 }
 
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity,
-                                          volatile int* abort_flag, int32_t* status) {
+                                          volatile int* abort_flag, int32_t* status,
+                                          unsigned long long limit_ns = kWaitLimitNs) {
   if (mbar_try_wait(bar, parity)) return true;
   if (*abort_flag) return false;
-  return mbar_wait_slow(bar, parity, abort_flag, status);
+  return mbar_wait_slow(bar, parity, abort_flag, status, limit_ns);
 }
 
 // ---- 1-D bulk async copy global -> this CTA's shared memory -----------------
@@ -149,6 +156,29 @@ __device__ __forceinline__ uint4 ld_nc_u4(const void* p) {
                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
                : "l"(p));
   return v;
+}
+
+// Once-per-device set-up on the host (a kernel attribute, a cached device property), safe when several host
+// threads make their first call together: the set-up itself must be idempotent (two threads may both run it),
+// the flag is published with release / acquire.
+constexpr int kMaxDevices = 64;
+struct PerDeviceFlags {
+  std::atomic<int> v[kMaxDevices];
+};
+// Returns the current device ordinal, or -1.
+inline int current_device() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return -1;
+  return dev;
+}
+template <class F>
+inline bool once_per_device(PerDeviceFlags& flags, F&& setup) {
+  const int dev = current_device();
+  if (dev < 0) return false;
+  if (flags.v[dev].load(std::memory_order_acquire) != 0) return true;
+  if (!setup(dev)) return false;
+  flags.v[dev].store(1, std::memory_order_release);
+  return true;
 }
 
 __host__ __device__ __forceinline__ int dtype_size(int dt) {

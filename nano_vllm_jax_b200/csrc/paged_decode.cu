@@ -445,31 +445,30 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_pipelined_kernel(Dec
   __syncthreads();
 }
 
-static int g_num_ctas[64];
+static PerDeviceFlags g_num_ctas;  // 0 = not queried yet
 
 int decode_num_ctas() {
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
-  if (g_num_ctas[dev] == 0) {
+  const int dev = current_device();
+  if (dev < 0) return 0;
+  int n = g_num_ctas.v[dev].load(std::memory_order_acquire);
+  if (n == 0) {
     int sms = 0;
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
     // no more CTAs than the group counters of the workspace header cover
-    g_num_ctas[dev] = 2 * sms < kMergeGroup * kGroupCounters / 2 ? 2 * sms : kMergeGroup * kGroupCounters / 2;
+    n = 2 * sms < kMergeGroup * kGroupCounters / 2 ? 2 * sms : kMergeGroup * kGroupCounters / 2;
+    g_num_ctas.v[dev].store(n, std::memory_order_release);
   }
-  return g_num_ctas[dev];
+  return n;
 }
 
 int launch_decode_pipelined(const DecodeParams& p, int num_ctas, cudaStream_t stream) {
   static_assert(sizeof(DecodeSmem) <= 113 * 1024, "two CTAs must fit one SM");
-  static bool smem_opted_in[64];
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return NVJ_ERR_LAUNCH;
-  if (!smem_opted_in[dev]) {
-    if (cudaFuncSetAttribute(decode_pipelined_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)sizeof(DecodeSmem)) != cudaSuccess)
-      return NVJ_ERR_LAUNCH;
-    smem_opted_in[dev] = true;
-  }
+  static PerDeviceFlags smem_opted_in;
+  if (!once_per_device(smem_opted_in, [](int) {
+        return cudaFuncSetAttribute(decode_pipelined_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    (int)sizeof(DecodeSmem)) == cudaSuccess;
+      }))
+    return NVJ_ERR_LAUNCH;
   decode_pipelined_kernel<<<num_ctas, kDecodeThreads, sizeof(DecodeSmem), stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? NVJ_OK : NVJ_ERR_LAUNCH;
 }

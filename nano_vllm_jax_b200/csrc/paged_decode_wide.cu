@@ -515,17 +515,19 @@ bool tensor_map_cached(CUtensorMap* map, int kind, const void* base, uint64_t ex
   return true;
 }
 
-static int g_wide_ctas[64];
+static PerDeviceFlags g_wide_ctas;  // 0 = not queried yet
 
 int decode_wide_num_ctas() {  // one per SM of the current device
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
-  if (g_wide_ctas[dev] == 0) {
+  const int dev = current_device();
+  if (dev < 0) return 0;
+  int n = g_wide_ctas.v[dev].load(std::memory_order_acquire);
+  if (n == 0) {
     int sms = 0;
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
-    g_wide_ctas[dev] = sms < kMergeGroup * kGroupCounters / 2 ? sms : kMergeGroup * kGroupCounters / 2;
+    n = sms < kMergeGroup * kGroupCounters / 2 ? sms : kMergeGroup * kGroupCounters / 2;
+    g_wide_ctas.v[dev].store(n, std::memory_order_release);
   }
-  return g_wide_ctas[dev];
+  return n;
 }
 
 static size_t wide_ml_bytes(int n, int width) { return ws_round(sizeof(float) * ws_slots(n) * width * kHq * 2); }
@@ -542,15 +544,12 @@ int launch_decode_wide(const DecodeParams& p, cudaStream_t stream) {
   if (!tensor_map_cached(&k_map, 0, p.k_cache, (uint64_t)p.num_blocks * kBlk, w_make_map) ||
       !tensor_map_cached(&v_map, 0, p.v_cache, (uint64_t)p.num_blocks * kBlk, w_make_map))
     return NVJ_ERR_UNSUPPORTED;
-  static bool smem_opted_in[64];
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return NVJ_ERR_LAUNCH;
+  static PerDeviceFlags smem_opted_in;
   const int smem = (int)sizeof(WideSmem) + 1024;
-  if (!smem_opted_in[dev]) {
-    if (cudaFuncSetAttribute(decode_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
-      return NVJ_ERR_LAUNCH;
-    smem_opted_in[dev] = true;
-  }
+  if (!once_per_device(smem_opted_in, [smem](int) {
+        return cudaFuncSetAttribute(decode_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) == cudaSuccess;
+      }))
+    return NVJ_ERR_LAUNCH;
   decode_wide_kernel<<<n, kDecodeThreads, smem, stream>>>(k_map, v_map, p);
   return cudaGetLastError() == cudaSuccess ? NVJ_OK : NVJ_ERR_LAUNCH;
 }

@@ -275,15 +275,12 @@ int launch_prefill_mma(const void* q, int q_dtype, const char* k_cache, const ch
                        const int32_t* kv_lens, const int32_t* positions, const int32_t* query_start_loc,
                        int rows, int token_bucket, float scale, float* out, int32_t* status,
                        int skip_single, cudaStream_t stream) {
-  static bool opted_in[64];
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return NVJ_ERR_LAUNCH;
-  if (!opted_in[dev]) {
-    if (cudaFuncSetAttribute(prefill_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)sizeof(PrefillSmem)) != cudaSuccess)
-      return NVJ_ERR_LAUNCH;
-    opted_in[dev] = true;
-  }
+  static PerDeviceFlags opted_in;
+  if (!once_per_device(opted_in, [](int) {
+        return cudaFuncSetAttribute(prefill_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    (int)sizeof(PrefillSmem)) == cudaSuccess;
+      }))
+    return NVJ_ERR_LAUNCH;
   // padded tokens (and rows that see no key) are defined to be zero; with skip_single the caller
   // has already cleared the output and the decode kernel has written the single-token rows
   if (!skip_single &&

@@ -427,17 +427,14 @@ int launch_prefill_umma(const void* q, int q_dtype, const char* k_cache, const c
                         const int32_t* kv_lens, const int32_t* positions, const int32_t* query_start_loc,
                         int rows, int token_bucket, float scale, float* out, int32_t* status,
                         int skip_single, cudaStream_t stream) {
-  static bool opted_in[64];
+  static PerDeviceFlags opted_in;
   constexpr int kSmemBytes = (int)sizeof(UmmaSmem) + 1024;
   static_assert(kSmemBytes <= 232448, "tiles exceed the shared memory of one CTA");
   if (!(scale > 0.f) || num_blocks < 1 || !um_encode_fn()) return NVJ_ERR_UNSUPPORTED;
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return NVJ_ERR_LAUNCH;
-  if (!opted_in[dev]) {
-    if (cudaFuncSetAttribute(prefill_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
-      return NVJ_ERR_LAUNCH;
-    opted_in[dev] = true;
-  }
+  if (!once_per_device(opted_in, [](int) {
+        return cudaFuncSetAttribute(prefill_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) == cudaSuccess;
+      }))
+    return NVJ_ERR_LAUNCH;
   CUtensorMap k_map, v_map;
   const TensorMapMaker make = [](CUtensorMap* m, const void* base, uint64_t tokens) { return um_make_map(m, base, kHkv, tokens, kBlk); };
   if (!tensor_map_cached(&k_map, 1, k_cache, (uint64_t)num_blocks * kBlk, make) ||

@@ -12,9 +12,13 @@ costs no host-to-device traffic for metadata.  Here the same arrays are torch CU
                            (the only per-step host work, and only when a row crosses a block
                            boundary), `load()` (re)installs a batch.
   DecodeStepGraph          captures  advance -> fused append + paged decode -> token pick
-                           (-> all-gather of the tokens over NVLink, on several GPUs)
                            once and replays it: one graph launch per step, the kernels run
-                           back to back, and nothing is allocated or copied per step.
+                           back to back, and nothing is allocated or copied per step.  On
+                           several GPUs the token pick also publishes the tokens to every
+                           peer over NVLink, and the graph holds a second branch beside the
+                           attention that collects the PREVIOUS step's tokens: the wait for
+                           the slowest rank never sits between two steps (`gathered` lags one
+                           step; `flush()` fetches the last one).
 
 The query and the new K/V rows are static buffers the caller fills before `replay()` (in a
 model they are produced by the projections that run in front of this path).
@@ -81,8 +85,9 @@ class DecodeStepGraph:
 
     def __init__(self, meta: ResidentDecodeMetadata, k_cache: torch.Tensor, v_cache: torch.Tensor, layer_id: int,
                  scale: float, num_key_value_groups: int, query_dtype=torch.bfloat16, token_gather=None):
-        """`token_gather` (a `parallel.P2PTokenGather` over `meta.rows` tokens) appends the all-gather of the step's
-        tokens over NVLink to the captured step; `gathered` then holds every rank's tokens after each replay."""
+        """`token_gather` (a `parallel.P2PTokenGather` over `meta.rows` tokens) makes the token pick publish the step's
+        tokens to every rank over NVLink; `gathered` holds every rank's tokens of the step BEFORE the one just replayed
+        (the collect runs beside the attention), and `flush()` brings it up to date."""
         if k_cache.ndim != 5:
             raise ValueError("k_cache must be the 5-D cache [L, NB, bs, Hkv, D]")
         self.meta, self.k_cache, self.v_cache = meta, k_cache, v_cache
@@ -101,16 +106,29 @@ class DecodeStepGraph:
                          if token_gather is not None else None)
         self._graph: Optional[torch.cuda.CUDAGraph] = None
         self._stream = torch.cuda.Stream(dev)
+        self._side = torch.cuda.Stream(dev)
+        self._tokens = torch.empty(meta.rows, dtype=torch.int32, device=dev)
 
     def _step(self):
+        cur = torch.cuda.current_stream(self.meta.device)
+        if self.token_gather is not None:  # the previous step's tokens arrive while this step's attention runs
+            self._side.wait_stream(cur)
+            with torch.cuda.stream(self._side):
+                self.token_gather.collect(out=self.gathered)
         self.meta.advance()
         out, _, _ = _k.paged_decode_attention_with_kv_append(self.query, self.new_k, self.new_v, self.k_cache, self.v_cache,
                                                              self.meta.block_tables, self.meta.seq_lens, self.meta.positions,
                                                              self.layer_id, self.meta.block_size, self.scale, self.groups)
-        tokens = _k.row_argmax(out.view(self.meta.rows, -1))
+        if self.token_gather is None:
+            return out, _k.row_argmax(out.view(self.meta.rows, -1))
+        cur.wait_stream(self._side)  # this rank has read step k - 1 before it publishes step k
+        return out, self.token_gather.publish_argmax(out.view(self.meta.rows, -1), self._tokens)
+
+    def flush(self) -> Optional[torch.Tensor]:
+        """Collect the tokens of the last replayed step into `gathered` (several GPUs only)."""
         if self.token_gather is not None:
-            self.token_gather.gather(tokens, out=self.gathered)
-        return out, tokens
+            self.token_gather.collect(out=self.gathered)
+        return self.gathered
 
     def capture(self):
         """Run one real step from the current `query`, `new_k`, `new_v` (on a side stream: capture needs warm kernels

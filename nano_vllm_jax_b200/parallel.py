@@ -7,8 +7,18 @@ output tokens (int32 per row): `gather_tokens` does it with `torch.distributed`
 (NCCL on GPUs; the same code runs on the gloo backend in CPU tests), and
 `P2PTokenGather` with one small kernel per rank that stores the tokens straight
 into its peers' memory over NVLink (one node, one process per GPU), which takes
-a few microseconds where the library call takes 7-20.  The reference is
+a few microseconds where the library call takes 7-20.  Its split form
+(`publish_argmax` / `collect`) fuses the publish with the step's token pick and
+moves the wait for the peers beside the next step's attention, so that a rank
+which is late by less than one step delays nobody.  The reference is
 single-device and has no counterpart of this module.
+
+Failures.  A rank that dies or never joins shows up here in one of two ways:
+the library collective raises when the process group's timeout runs out
+(`gather_tokens` re-raises it as `TokenGatherError` naming the rank), or a
+device-side wait of the peer-store gather runs out (`nvj_set_wait_limit_ns`),
+the kernel returns, and `P2PTokenGather.check()` raises `DeviceStatusError`.
+Nothing waits without a limit.
 
 Prefix reuse and GDN snapshots stay rank-local: a request can only hit a prefix
 that an earlier request of the same rank computed.
@@ -35,6 +45,16 @@ def max_local_rows(num_requests: int, world: int) -> int:
     return -(-num_requests // world)
 
 
+class TokenGatherError(RuntimeError):
+    """The per-step token all-gather failed (a peer left, or the process group's timeout ran out)."""
+
+
+def set_wait_limit(seconds: float) -> None:
+    """Limit of every device-side wait on another GPU (default 1 s)."""
+    from . import _lib
+    _lib.load().nvj_set_wait_limit_ns(int(max(0.0, float(seconds)) * 1e9))
+
+
 def gather_tokens(local_tokens: torch.Tensor, num_requests: int, group: Optional[dist.ProcessGroup] = None,
                   pad_value: int = -1) -> torch.Tensor:
     """All-gather one int32 token per local row and return them in global request order.
@@ -49,7 +69,10 @@ def gather_tokens(local_tokens: torch.Tensor, num_requests: int, group: Optional
     send = torch.full((rows,), pad_value, dtype=torch.int32, device=local_tokens.device)
     send[: local_tokens.numel()] = local_tokens.to(torch.int32)
     recv = torch.empty(world * rows, dtype=torch.int32, device=local_tokens.device)
-    dist.all_gather_into_tensor(recv, send, group=group)
+    try:
+        dist.all_gather_into_tensor(recv, send, group=group)
+    except (RuntimeError, dist.DistBackendError) as exc:  # a peer that left, or the group's timeout
+        raise TokenGatherError(f"rank {dist.get_rank(group)} of {world}: token all-gather failed: {exc}") from exc
     # rank r's row j is request j * world + r: transpose [world, rows] -> [rows, world]
     return recv.view(world, rows).t().reshape(-1)[:num_requests].contiguous()
 
@@ -129,6 +152,28 @@ class P2PTokenGather:
                                              0, out.data_ptr(), self._status.data_ptr(),
                                              torch.cuda.current_stream(self.device).cuda_stream)
         self._check(rc, "nvj_p2p_allgather_i32")
+        return out
+
+    def publish_argmax(self, x: torch.Tensor, tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """tokens[r] = argmax of row r of the float32 `[n, row_len]` tensor, and the same tokens stored into every peer's
+        buffer and published as this rank's next epoch.  Waits for nobody.  Returns the local tokens."""
+        if x.dtype != torch.float32 or x.ndim != 2 or x.shape[0] != self.n or not x.is_cuda or not x.is_contiguous():
+            raise ValueError("x must be a contiguous CUDA float32 tensor [n, row_len]")
+        if tokens is None:
+            tokens = torch.empty(self.n, dtype=torch.int32, device=self.device)
+        rc = self._lib.nvj_p2p_argmax_publish(x.data_ptr(), self.n, int(x.shape[1]), tokens.data_ptr(), self.rank, self.world,
+                                              self._ptr_array, torch.cuda.current_stream(self.device).cuda_stream)
+        self._check(rc, "nvj_p2p_argmax_publish")
+        return tokens
+
+    def collect(self, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Fetch the oldest published step that has not been collected: `[world * n]` int32, rank r's tokens at
+        `[r * n, (r + 1) * n)`.  Leaves `out` untouched when every published step has been collected already."""
+        if out is None:
+            out = torch.empty(self.world * self.n, dtype=torch.int32, device=self.device)
+        rc = self._lib.nvj_p2p_collect(self._own, self.n, self.world, out.data_ptr(), self._status.data_ptr(),
+                                       torch.cuda.current_stream(self.device).cuda_stream)
+        self._check(rc, "nvj_p2p_collect")
         return out
 
     def check(self) -> None:

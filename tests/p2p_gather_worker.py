@@ -28,6 +28,26 @@ def main():
         dist.all_gather_into_tensor(ref, tok)
         assert torch.equal(out, ref), f"rank {rank} step {s}: peer-store gather differs from the NCCL gather"
     g.check()
+    # split form on a second set of buffers: the token pick publishes, the collect of step s - 1 runs one step later
+    g2 = P2PTokenGather(n)
+    gen = torch.Generator(device=dev).manual_seed(1234 + rank)
+    got = torch.full((world * n,), -1, dtype=torch.int32, device=dev)
+    prev_ref = None
+    for s in range(steps):
+        x = torch.randn((n, 512), generator=gen, device=dev)
+        if s % 5 == rank % 5:
+            torch.cuda._sleep(3_000_000)  # a late rank: the others' collect of its step waits, their publish does not
+        g2.collect(out=got)
+        if prev_ref is not None:
+            assert torch.equal(got, prev_ref), f"rank {rank} step {s}: collected tokens differ from the NCCL gather of step {s - 1}"
+        tok = g2.publish_argmax(x)
+        assert torch.equal(tok.long(), x.argmax(dim=1))
+        dist.all_gather_into_tensor(ref, tok)
+        prev_ref = ref.clone()
+    g2.collect(out=got)
+    assert torch.equal(got, prev_ref)
+    g2.check()
+    g2.close()
     # timing, both ways, 200 steps each
     tok = base.clone()
     for fn, name in ((lambda: g.gather(tok, out=ref), "p2p"), (lambda: dist.all_gather_into_tensor(ref, tok), "nccl")):

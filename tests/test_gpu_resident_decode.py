@@ -1,10 +1,12 @@
-"""Device-resident decode metadata and the decode step replayed from a CUDA graph equal eager steps."""
+"""Device-resident decode metadata and the decode step replayed from a CUDA graph: equal to eager steps bit for bit,
+and to the CPU oracle's append + paged attention step by step."""
 
 import numpy as np
 import pytest
 import torch
 
 from helpers import BS, SCALE, bits, decode_case, to_numpy, to_torch
+from oracle import kv_cache_ref as R
 
 pytestmark = pytest.mark.gpu
 
@@ -68,3 +70,18 @@ def test_graph_replayed_steps_equal_eager_steps():
         assert torch.equal(got[s][1][active], K.row_argmax(ref.view(rows, -1))[active])
     np.testing.assert_array_equal(bits(to_numpy(k_g)), bits(to_numpy(k_e)))
     np.testing.assert_array_equal(bits(to_numpy(v_g)), bits(to_numpy(v_e)))
+
+    # the same steps in the CPU oracle: slot mapping -> masked append -> paged attention (the reference's pure path)
+    ok, ov = c["k_cache"], c["v_cache"]
+    for s in range(steps):
+        lens = np.where(lens0 > 0, lens0 + s + 1, 0).astype(np.int32)
+        pos = np.maximum(lens - 1, 0)[:, None]
+        slots = R.compute_slot_mapping(pos, c["tables"], BS)
+        ok, ov = R.update_kv_cache(ok, ov, slots, to_numpy(ks[s]), to_numpy(vs[s]), 0, valid_mask=(lens > 0)[:, None])
+        ref = R.paged_attention_decode(to_numpy(qs[s]), ok, ov, c["tables"], lens, BS, SCALE, 4)
+        active = lens > 0
+        err = np.abs(to_numpy(got[s][0])[active] - ref[active]).max()
+        assert err <= 2e-3, f"step {s}: graph output vs oracle max-abs {err}"
+        assert not to_numpy(got[s][0])[~active].any()
+    np.testing.assert_array_equal(bits(to_numpy(k_g)), bits(ok))
+    np.testing.assert_array_equal(bits(to_numpy(v_g)), bits(ov))

@@ -48,3 +48,36 @@ def test_two_rank_gather_restores_global_request_order(tmp_path):
 def test_single_process_gather_is_identity():
     t = torch.arange(5, dtype=torch.int32)
     assert torch.equal(parallel.gather_tokens(t, 5), t)
+
+
+def _leaver(rank, world, port, out_dir):
+    """Rank 1 leaves between two steps (no collective in flight); rank 0's next gather must end with an error after
+    the process group's timeout instead of waiting for ever."""
+    import datetime
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=3))
+    local = torch.tensor([rank], dtype=torch.int32)
+    parallel.gather_tokens(local, world)  # one healthy step
+    if rank == 1:
+        os._exit(0)  # gone, without a goodbye
+    try:
+        parallel.gather_tokens(local, world)
+        verdict = "no error"
+    except parallel.TokenGatherError as exc:
+        verdict = "TokenGatherError: " + str(exc)[:80]
+    with open(os.path.join(out_dir, "verdict.txt"), "w") as f:
+        f.write(verdict)
+    os._exit(0)  # the group cannot be torn down collectively any more
+
+
+def test_a_rank_that_leaves_between_steps_ends_the_next_gather_with_an_error(tmp_path):
+    ctx = mp.get_context("spawn")
+    procs = [ctx.Process(target=_leaver, args=(r, 2, port, str(tmp_path))) for port in [_free_port()] for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=60)
+        assert not p.is_alive(), "a rank is still waiting: the gather did not time out"
+    verdict = (tmp_path / "verdict.txt").read_text()
+    assert verdict.startswith("TokenGatherError"), verdict
