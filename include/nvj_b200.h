@@ -149,10 +149,12 @@ int nvj_qk_norm_rope_kv_append(const void* q, int64_t q_token_stride, int64_t q_
 
 /*
  * Bytes of caller-owned scratch the decode entry points need for `max_batch`
- * rows on the current device.  Its leading header (64 bytes + 4 bytes per row) holds the
- * status word and the per-row arrival counters and must be zero before the
- * first use (nvj_paged_decode_workspace_init does that); the kernels leave
- * them zero again on success.  One workspace serves one stream at a time.
+ * rows on the current device.  The front of the buffer (64 bytes of status, 256 bytes of group
+ * counters, 4 bytes per row) holds the status word and the arrival counters and must be zero before the
+ * first use (nvj_paged_decode_workspace_init does that); the kernels leave them zero again on success.
+ * The partial results live at the END of the buffer, so one buffer serves calls of any batch size up to
+ * `max_batch`, of either decode entry point and of any width, one after another: pass the same
+ * `workspace_bytes` (the buffer's size) on every call.  One workspace serves one stream at a time.
  */
 size_t nvj_paged_decode_workspace_bytes(int max_batch);
 int nvj_paged_decode_workspace_init(void* workspace, size_t workspace_bytes,

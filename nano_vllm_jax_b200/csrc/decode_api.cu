@@ -15,15 +15,7 @@ static bool pipelined_shape(const DecodeParams& p) {
 }
 
 static int carve_workspace(DecodeParams& p, void* workspace, size_t bytes, int num_ctas) {
-  if (!workspace || !aligned16(workspace)) return NVJ_ERR_WORKSPACE;
-  const size_t need = ws_header_bytes(p.batch) + ws_ml_bytes(num_ctas) + ws_acc_bytes(num_ctas);
-  if (bytes < need) return NVJ_ERR_WORKSPACE;
-  char* w = static_cast<char*>(workspace);
-  p.status = reinterpret_cast<int32_t*>(w);
-  p.counters = reinterpret_cast<int32_t*>(w + 64);
-  p.part_ml = reinterpret_cast<float*>(w + ws_header_bytes(p.batch));
-  p.part_acc = reinterpret_cast<float*>(w + ws_header_bytes(p.batch) + ws_ml_bytes(num_ctas));
-  return NVJ_OK;
+  return carve_decode_workspace(p, workspace, bytes, ws_ml_bytes(num_ctas), ws_acc_bytes(num_ctas));
 }
 
 static int run_decode(DecodeParams& p, void* workspace, size_t workspace_bytes, int variant,

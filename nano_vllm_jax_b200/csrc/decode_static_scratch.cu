@@ -84,7 +84,8 @@ extern "C" int nvj_paged_decode_static_scratch(const void* q, int q_dtype, const
   p.seq_lens = seq_lens;
   p.out = out;
   p.status = reinterpret_cast<int32_t*>(scratch);
-  p.counters = reinterpret_cast<int32_t*>(scratch + 64);
+  p.group_counters = reinterpret_cast<int32_t*>(scratch + 64);
+  p.counters = reinterpret_cast<int32_t*>(scratch + 64 + sizeof(int32_t) * kGroupCounters);
   p.part_ml = reinterpret_cast<float*>(scratch + kStaticHeaderBytes);
   p.part_acc = reinterpret_cast<float*>(scratch + kStaticHeaderBytes + kStaticMlBytes);
   p.num_blocks = num_blocks;

@@ -278,7 +278,7 @@ __device__ __forceinline__ void finish_segment(const DecodeParams& p, DecodeSmem
   const int grp = blockIdx.x / kMergeGroup, g_lo = c_lo / kMergeGroup, g_hi = c_hi / kMergeGroup;
   const int first = tree ? max(c_lo, grp * kMergeGroup) : c_lo;
   const int last = tree ? min(c_hi, grp * kMergeGroup + kMergeGroup - 1) : c_hi;
-  int32_t* counter = tree ? p.counters + p.batch + 2 * grp + (grp == g_lo ? 1 : 0) : p.counters + s.b;
+  int32_t* counter = tree ? p.group_counters + 2 * grp + (grp == g_lo ? 1 : 0) : p.counters + s.b;
   __threadfence();
   named_bar_sync(1, kConsumerThreads);
   if (tid == 0) sm.is_last = (atomicAdd(counter, 1) == last - first) ? 1 : 0;

@@ -46,7 +46,8 @@ struct DecodeParams {
   float* out;
   // workspace
   int32_t* status;
-  int32_t* counters;  // [batch + kGroupCounters], zero between launches
+  int32_t* counters;        // [batch] row arrival counters, zero between launches
+  int32_t* group_counters;  // [kGroupCounters] group arrival counters, zero between launches
   float* part_ml;     // [ws_slots(num_ctas)][kHq][2]  (running max in log2 units, sum)
   float* part_acc;    // [ws_slots(num_ctas)][kHq][kD] un-normalised accumulators
   long long num_blocks;
@@ -107,10 +108,36 @@ constexpr int kGroupCounters = 64;
 __host__ __device__ inline int ws_groups(int num_ctas) { return (num_ctas + kMergeGroup - 1) / kMergeGroup; }
 // Partial slots: two per CTA, then two per group.
 __host__ __device__ inline size_t ws_slots(int num_ctas) { return 2ull * num_ctas + 2ull * ws_groups(num_ctas); }
-// Header = status word (64 B) + one int32 counter per row + the group counters.
+// Header = status word (64 B) + the group counters + one int32 counter per row.
 inline size_t ws_header_bytes(int max_batch) { return ws_round(64 + sizeof(int32_t) * ((size_t)max_batch + kGroupCounters)); }
 inline size_t ws_ml_bytes(int num_ctas) { return ws_round(sizeof(float) * ws_slots(num_ctas) * kHq * 2); }
 inline size_t ws_acc_bytes(int num_ctas) { return ws_round(sizeof(float) * ws_slots(num_ctas) * kHq * kD); }
+
+// Carves a decode workspace of `bytes` bytes for a call with p.batch rows whose partial results need `ml_bytes` and
+// `acc_bytes`.  One buffer serves calls of any batch size, width and kernel one after another, so nothing a call
+// writes may land where a later call keeps state that must start at zero:
+//   [0, 64)              status word
+//   [64, 320)            group arrival counters
+//   [320, 320 + 4 rows)  row arrival counters
+//   ... unused ...
+//   the last ml_bytes + acc_bytes of the buffer: partial (max, sum) pairs and accumulators
+// The counters are zero before the first use and every launch leaves them zero again; the partials are always
+// written before they are read.  Because the partials are anchored at the END of the buffer, a call with few rows
+// cannot leave them inside the counter area of a later call with more rows (anchored behind the call's own
+// counters they would: a 256-row call after a 4-row call then found garbage in its counters and never merged
+// its split rows).  Callers pass the same `bytes` for every call on one buffer.
+inline int carve_decode_workspace(DecodeParams& p, void* workspace, size_t bytes, size_t ml_bytes, size_t acc_bytes) {
+  if (!workspace || (reinterpret_cast<uintptr_t>(workspace) & 15u) != 0) return NVJ_ERR_WORKSPACE;
+  const size_t end = bytes / kWsAlign * kWsAlign;
+  if (end < ws_header_bytes(p.batch) + ml_bytes + acc_bytes) return NVJ_ERR_WORKSPACE;
+  char* w = static_cast<char*>(workspace);
+  p.status = reinterpret_cast<int32_t*>(w);
+  p.group_counters = reinterpret_cast<int32_t*>(w + 64);
+  p.counters = reinterpret_cast<int32_t*>(w + 64 + sizeof(int32_t) * kGroupCounters);
+  p.part_acc = reinterpret_cast<float*>(w + end - acc_bytes);
+  p.part_ml = reinterpret_cast<float*>(w + end - acc_bytes - ml_bytes);
+  return NVJ_OK;
+}
 
 int decode_num_ctas();  // 2 per SM of the current device
 int launch_decode_generic(const DecodeParams& p, cudaStream_t stream);

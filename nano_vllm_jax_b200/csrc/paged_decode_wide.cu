@@ -261,7 +261,7 @@ __device__ __forceinline__ void w_finish_segment(const DecodeParams& p, WideSmem
   const int cg = blockIdx.x / kMergeGroup, g_lo = c_lo / kMergeGroup, g_hi = c_hi / kMergeGroup;
   const int first = tree ? max(c_lo, cg * kMergeGroup) : c_lo;
   const int last = tree ? min(c_hi, cg * kMergeGroup + kMergeGroup - 1) : c_hi;
-  int32_t* counter = tree ? p.counters + p.batch + 2 * cg + (cg == g_lo ? 1 : 0) : p.counters + s.b;
+  int32_t* counter = tree ? p.group_counters + 2 * cg + (cg == g_lo ? 1 : 0) : p.counters + s.b;
   __threadfence();
   named_bar_sync(1, kDecodeThreads);
   if (tid == 0) sm.is_last = (atomicAdd(counter, 1) == last - first) ? 1 : 0;
@@ -579,10 +579,10 @@ extern "C" int nvj_paged_decode_wide(const void* q, const void* k_cache_layer, c
   if ((al & 15u) != 0) return NVJ_ERR_UNSUPPORTED;
   const int n = decode_wide_num_ctas();
   if (n <= 0) return NVJ_ERR_LAUNCH;
-  if (!workspace || workspace_bytes < ws_header_bytes(batch) + wide_ml_bytes(n, width) + wide_acc_bytes(n, width))
-    return NVJ_ERR_WORKSPACE;
-  char* w = static_cast<char*>(workspace);
   DecodeParams p{};
+  p.batch = batch;
+  const int carved = carve_decode_workspace(p, workspace, workspace_bytes, wide_ml_bytes(n, width), wide_acc_bytes(n, width));
+  if (carved != NVJ_OK) return carved;
   p.q = q;
   p.k_cache = static_cast<const char*>(k_cache_layer);
   p.v_cache = static_cast<const char*>(v_cache_layer);
@@ -591,12 +591,7 @@ extern "C" int nvj_paged_decode_wide(const void* q, const void* k_cache_layer, c
   p.positions = positions;
   p.width = width;
   p.out = out;
-  p.status = reinterpret_cast<int32_t*>(w);
-  p.counters = reinterpret_cast<int32_t*>(w + 64);
-  p.part_ml = reinterpret_cast<float*>(w + ws_header_bytes(batch));
-  p.part_acc = reinterpret_cast<float*>(w + ws_header_bytes(batch) + wide_ml_bytes(n, width));
   p.num_blocks = num_blocks;
-  p.batch = batch;
   p.table_width = table_width;
   p.block_size = kBlk;
   p.num_kv_heads = kHkv;

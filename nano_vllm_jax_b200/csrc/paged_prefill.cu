@@ -57,13 +57,12 @@ extern "C" int nvj_paged_prefill_packed(const void* q, int q_dtype, const void* 
     // decode kernel when the caller lends it a decode workspace; everything else goes to the tile kernel.
     int skip_single = 0;
     const int num_ctas = decode_num_ctas();
-    const size_t need = ws_header_bytes(rows) + ws_ml_bytes(num_ctas) + ws_acc_bytes(num_ctas);
-    if (workspace && num_ctas > 0 && workspace_bytes >= need && rows > 0 &&
-        (reinterpret_cast<uintptr_t>(workspace) & 15u) == 0) {
+    DecodeParams d{};
+    d.batch = rows;
+    if (workspace && num_ctas > 0 && rows > 0 &&
+        carve_decode_workspace(d, workspace, workspace_bytes, ws_ml_bytes(num_ctas), ws_acc_bytes(num_ctas)) == NVJ_OK) {
       if (cudaMemsetAsync(out, 0, sizeof(float) * (size_t)token_bucket * kHq * kD, s) != cudaSuccess)
         return NVJ_ERR_LAUNCH;
-      char* w = static_cast<char*>(workspace);
-      DecodeParams d{};
       d.q = q;
       d.k_cache = static_cast<const char*>(k_cache_layer);
       d.v_cache = static_cast<const char*>(v_cache_layer);
@@ -74,12 +73,7 @@ extern "C" int nvj_paged_prefill_packed(const void* q, int q_dtype, const void* 
       d.qsl_rows = rows;
       d.packed_rows = 1;
       d.out = out;
-      d.status = reinterpret_cast<int32_t*>(w);
-      d.counters = reinterpret_cast<int32_t*>(w + 64);
-      d.part_ml = reinterpret_cast<float*>(w + ws_header_bytes(rows));
-      d.part_acc = reinterpret_cast<float*>(w + ws_header_bytes(rows) + ws_ml_bytes(num_ctas));
       d.num_blocks = num_blocks;
-      d.batch = rows;
       d.table_width = table_width;
       d.block_size = block_size;
       d.num_kv_heads = num_kv_heads;

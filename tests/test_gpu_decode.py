@@ -336,3 +336,20 @@ def test_fused_append_position_beyond_the_table_is_flagged_on_the_generic_route_
     torch.cuda.synchronize()
     assert float(kc[0, 3].abs().max()) == 0.0            # row 1's first block untouched by row 0
     assert float(kc[0, 4, 0].min()) == 1.0               # row 1's own token landed
+
+
+@pytest.mark.parametrize("variant", [PIPELINED, TENSOR])
+def test_one_workspace_serves_small_and_large_batches_in_turn(variant):
+    # A call with few rows leaves partial results in the workspace; they must not sit where a later call with more
+    # rows keeps its arrival counters (that once left every split row beyond ~110 of a 256-row call unwritten).
+    K = _K()
+    small = decode_case(15, 3000, 4, 9000, 10000)       # 4 long rows: every CTA writes partials
+    large = decode_case(16, 9000, 256, 300, 500)        # 256 rows, most of them split over two CTAs
+    wide_q = np.random.default_rng(17).standard_normal((4, 3, 8, 256), dtype=np.float32).astype(bfloat16)
+    for _ in range(2):
+        _check(_run(small, variant), _oracle(small), np.ones(4, bool))
+        _check(_run(large, variant), _oracle(large), np.ones(256, bool))
+        # a wide call (larger partial area) in between, then the large batch again
+        K.paged_decode_attention_wide(to_torch(wide_q), to_torch(small["k_cache"][0]), to_torch(small["v_cache"][0]),
+                                      to_torch(small["tables"]), to_torch(small["seq_lens"]), None, SCALE)
+        _check(_run(large, variant), _oracle(large), np.ones(256, bool))
