@@ -415,8 +415,7 @@ def run_b200(args, w):
     def gather_tokens(out):
         if world > 1:
             if token_gather is not None:  # the step before arrives (it has had a whole step to do so), then this one leaves
-                token_gather.collect(out=gathered_p2p)
-                token_gather.publish_argmax(out.view(rows, HQ * D), pipe_tokens)
+                token_gather.publish_argmax(out.view(rows, HQ * D), pipe_tokens, collect_out=gathered_p2p)
             else:
                 dist.all_gather_into_tensor(gathered, K.row_argmax(out.view(rows, HQ * D)))
 
@@ -490,7 +489,7 @@ def run_b200(args, w):
         if token_gather is not None:
             graph.flush()
             token_gather.check()
-            step_mode += "; the argmax publishes the tokens over NVLink peer stores, the collect of the step before runs beside the attention, all in the graph"
+            step_mode += "; the argmax launch collects the tokens of the step before and publishes this step's over NVLink peer stores, all in the graph"
             ok = torch.equal(graph.gathered.view(world, rows)[rank], graph.tokens)
             if not ok:
                 raise SystemExit("token all-gather returned something else than this rank's own tokens")
@@ -585,9 +584,9 @@ def run_b200(args, w):
                             "from pinned host memory and its whole result back; compute stage "
                             + ("replayed from a CUDA graph per slot" if pipe_capture else "launched eagerly"),
                     "serial_value": total_rows / (ms_e2e_serial / K_steps * 1e-3), "serial_ms_per_step": ms_e2e_serial / K_steps},
-            # per step of the timed pass: metadata advance, fused append+decode, token argmax (N > 1: the argmax also
-            # publishes, plus the collect kernel)
-            "gpu_launches": (4 if token_gather is not None else 3) * K_steps,
+            # per step of the timed pass: metadata advance, fused append+decode, token argmax (N > 1: the same launch
+            # also collects and publishes)
+            "gpu_launches": 3 * K_steps,
             "step_mode": step_mode,
             "eager_value": total_rows / (ms_eager / K_steps * 1e-3), "eager_ms_per_step": ms_eager / K_steps,
             "roofline": {"bound": "hbm", "kernel": "decode_wide_kernel at width 1 (fused append + paged GQA decode, TMA-staged, tensor-core tiles)",

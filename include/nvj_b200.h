@@ -379,16 +379,18 @@ int nvj_advance_decode_metadata(int32_t* seq_lens, int32_t* positions, int batch
  *                                 NVJ_DEV_TIMEOUT in *status and returns; with host-passed epochs the same call can
  *                                 simply be issued again.
  *
- * The split form keeps the wait out of the decode step (device-kept epochs only; do not mix with the blocking form
- * on one buffer):
+ * The split form keeps the wait out of the decode step (device-kept epochs only):
  *   nvj_p2p_argmax_publish        tokens[r] = argmax of row r of x [rows, row_len] (as nvj_row_argmax), stored locally
- *                                 and into every peer's buffer, then this rank's next epoch is published.  Waits for
- *                                 nobody.  rows must equal the n the buffers were sized for.
+ *                                 and into every peer's buffer, then this rank's next epoch is published.  The publish
+ *                                 waits for nobody.  rows must equal the n the buffers were sized for.  With
+ *                                 `collect_out` (nullable) the same launch first collects the step before, as
+ *                                 nvj_p2p_collect does: the usual form of a step, whose gathered tokens then lag by one.
  *   nvj_p2p_collect               waits (up to the wait limit) for the oldest published epoch not collected yet and
- *                                 writes out[r * n + i]; returns at once when there is none.  A step k + 1 runs it beside
- *                                 its append + decode and in front of its own publish, so that a rank late by less than a
- *                                 step costs nothing; after the last step one more call fetches the last tokens.  On a
- *                                 timeout NVJ_DEV_TIMEOUT is flagged, nothing is consumed and the call can be repeated.
+ *                                 writes out[r * n + i]; returns at once when there is none.  After the last step one
+ *                                 call fetches the last tokens.  On a timeout NVJ_DEV_TIMEOUT is flagged in *status,
+ *                                 nothing is consumed and the call can be repeated.
+ * A rank must collect step k before it publishes step k + 1 (the fused form does); switch between the blocking and
+ * the split form only when every published step has been collected.
  */
 size_t nvj_p2p_gather_buffer_bytes(int world, int n);
 int nvj_p2p_buffer_create(size_t bytes, void** dev_ptr, unsigned char* handle64);
@@ -398,7 +400,7 @@ int nvj_p2p_buffer_destroy(void* dev_ptr);
 int nvj_p2p_allgather_i32(const int32_t* local, int n, int rank, int world, void* const* peer_buffers,
                           uint32_t epoch, int32_t* out, int32_t* status, nvj_stream_t stream);
 int nvj_p2p_argmax_publish(const float* x, int rows, int row_len, int32_t* tokens, int rank, int world,
-                           void* const* peer_buffers, nvj_stream_t stream);
+                           void* const* peer_buffers, int32_t* collect_out, int32_t* status, nvj_stream_t stream);
 int nvj_p2p_collect(void* own_buffer, int n, int world, int32_t* out, int32_t* status, nvj_stream_t stream);
 
 /* ------------------------------------------------------------- bounded waits */

@@ -16,12 +16,15 @@
 //
 // (2) the split form for a pipelined decode step, where the wait must not sit between two steps:
 //     nvj_p2p_argmax_publish   token pick of the step fused with the publish: every CTA takes a row's
-//                              argmax, stores the token locally and into every peer's set; the CTA that
-//                              finishes last publishes the epoch.  It waits for nobody.
+//                              argmax; the CTA that finishes last copies the tokens into every peer's set
+//                              and publishes the epoch.  One more CTA of the same launch can collect the
+//                              step before (below).  The publish waits for nobody.
 //     nvj_p2p_collect          waits (bounded) for the oldest published epoch that has not been collected
 //                              yet and copies its set out; does nothing when there is none.
-//     A step k + 1 runs  { append + decode }  beside  { collect of step k }  and then its own publish, so
-//     a peer that is late by less than one decode costs nothing.  Because every rank collects epoch k
+//     A step k + 1 runs  append + decode,  then one launch that collects step k and publishes step k + 1:
+//     step k's tokens have had a whole step to arrive, so a peer that is late by less than one step costs
+//     nothing, and no launch of the step waits beside the attention kernel (which fills every SM's register
+//     file: a waiting kernel that got an SM first delayed the attention's last CTA).  Because every rank collects epoch k
 //     before it publishes k + 1, and a peer publishes k + 2 only after it has seen this rank's flag k + 1
 //     (it collects k + 1 first), nobody overwrites set (k & 1) before everyone has read it: two sets are
 //     enough and a flag is either the awaited epoch or an older one.
@@ -114,29 +117,58 @@ __global__ void __launch_bounds__(256) p2p_allgather_kernel(P2pPeers peers, cons
   for (int i = threadIdx.x; i < world * n; i += blockDim.x) out[i] = gathered[i];
 }
 
-// Argmax of one row per CTA (first maximum wins, as row_argmax_kernel), the token stored locally and into
-// every peer's data set; the last CTA to finish publishes the epoch.
-__global__ void __launch_bounds__(kArgmaxThreads) p2p_argmax_publish_kernel(P2pPeers peers, const float* x, int row_len, int rank, int world,
-                                                                int32_t* tokens) {
-  const int n = gridDim.x;
-  P2pHeader* own = p2p_header(peers.base[rank]);
-  // advanced only by the last CTA, after every CTA has read it
-  const unsigned long long epoch = *reinterpret_cast<volatile unsigned long long*>(&own->published) + 1;
+// Waits (bounded) for the oldest published epoch this rank has not collected and copies its data set out.
+// Called by all threads of one CTA.  Returns without doing anything when there is no such epoch; on a timeout the
+// status word is flagged, nothing is consumed, and a later call tries the same epoch again.
+__device__ __forceinline__ void p2p_collect_cta(char* own_base, int n, int world, unsigned long long wait_ns, int32_t* out,
+                                                int32_t* status) {
+  __shared__ int failed;
+  P2pHeader* own = p2p_header(own_base);
+  const unsigned long long epoch = *reinterpret_cast<volatile unsigned long long*>(&own->consumed) + 1;
+  if (epoch > *reinterpret_cast<volatile unsigned long long*>(&own->published)) return;
+  if (threadIdx.x == 0) failed = 0;
+  __syncthreads();
   const int parity = (int)(epoch & 1u);
-  __shared__ int token_sh, last_sh;
-  const int token = row_argmax_cta(x + (long long)blockIdx.x * row_len, row_len);
-  if (threadIdx.x == 0) {
-    token_sh = token;
-    tokens[blockIdx.x] = token;
+  if ((int)threadIdx.x < world && !p2p_wait_flag(&own->flags[parity][threadIdx.x], epoch, wait_ns, status)) failed = 1;
+  __syncthreads();
+  if (failed) return;
+  const int32_t* gathered = p2p_data(own_base, parity, world, n);
+  for (int i = threadIdx.x; i < world * n; i += blockDim.x) out[i] = gathered[i];
+  __syncthreads();
+  if (threadIdx.x == 0) own->consumed = epoch;
+}
+
+// Token pick fused with the publish (and, optionally, with the collect of the step before).  CTA r < n takes the
+// argmax of row r (first maximum wins, as row_argmax_kernel) and stores the token locally; CTA n, present when
+// collect_out is given, collects the previous epoch.  The CTA that finishes last copies the n tokens into every
+// peer's data set with coalesced stores and then publishes the epoch: one system-scope fence per launch, and the
+// publish comes after this rank's own collect, which is what lets two data sets suffice.
+__global__ void __launch_bounds__(kArgmaxThreads) p2p_argmax_publish_kernel(P2pPeers peers, const float* x, int row_len, int n, int rank,
+                                                                            int world, int32_t* tokens, int32_t* collect_out,
+                                                                            unsigned long long wait_ns, int32_t* status) {
+  P2pHeader* own = p2p_header(peers.base[rank]);
+  __shared__ int last_sh;
+  if ((int)blockIdx.x < n) {
+    const int token = row_argmax_cta(x + (long long)blockIdx.x * row_len, row_len);
+    if (threadIdx.x == 0) tokens[blockIdx.x] = token;
+  } else {
+    p2p_collect_cta(peers.base[rank], n, world, wait_ns, collect_out, status);
   }
+  __threadfence();
   __syncthreads();
-  if ((int)threadIdx.x < world) p2p_data(peers.base[threadIdx.x], parity, world, n)[rank * n + blockIdx.x] = token_sh;
-  __threadfence_system();
-  __syncthreads();
-  if (threadIdx.x == 0) last_sh = (atomicAdd(&own->arrivals, 1u) == (unsigned)n - 1u) ? 1 : 0;
+  if (threadIdx.x == 0) last_sh = (atomicAdd(&own->arrivals, 1u) == gridDim.x - 1u) ? 1 : 0;
   __syncthreads();
   if (!last_sh) return;
+  __threadfence();
+  // `published` is advanced here and nowhere else, after every CTA of the launch is done with it
+  const unsigned long long epoch = *reinterpret_cast<volatile unsigned long long*>(&own->published) + 1;
+  const int parity = (int)(epoch & 1u);
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int32_t v = __ldcg(tokens + i);
+    for (int r = 0; r < world; ++r) p2p_data(peers.base[r], parity, world, n)[rank * n + i] = v;
+  }
   __threadfence_system();
+  __syncthreads();
   if ((int)threadIdx.x < world) st_release_sys(&p2p_header(peers.base[threadIdx.x])->flags[parity][rank], epoch);
   if (threadIdx.x == 0) {
     own->arrivals = 0;
@@ -144,22 +176,9 @@ __global__ void __launch_bounds__(kArgmaxThreads) p2p_argmax_publish_kernel(P2pP
   }
 }
 
-__global__ void __launch_bounds__(256) p2p_collect_kernel(char* own_base, int n, int world, unsigned long long wait_ns, int32_t* out,
-                                                         int32_t* status) {
-  __shared__ int failed;
-  P2pHeader* own = p2p_header(own_base);
-  const unsigned long long epoch = *reinterpret_cast<volatile unsigned long long*>(&own->consumed) + 1;
-  if (epoch > *reinterpret_cast<volatile unsigned long long*>(&own->published)) return;  // nothing published that has not been collected
-  if (threadIdx.x == 0) failed = 0;
-  __syncthreads();
-  const int parity = (int)(epoch & 1u);
-  if ((int)threadIdx.x < world && !p2p_wait_flag(&own->flags[parity][threadIdx.x], epoch, wait_ns, status)) failed = 1;
-  __syncthreads();
-  if (failed) return;  // `consumed` stays: the next collect tries the same epoch again
-  const int32_t* gathered = p2p_data(own_base, parity, world, n);
-  for (int i = threadIdx.x; i < world * n; i += blockDim.x) out[i] = gathered[i];
-  __syncthreads();
-  if (threadIdx.x == 0) own->consumed = epoch;
+__global__ void __launch_bounds__(kArgmaxThreads) p2p_collect_kernel(char* own_base, int n, int world, unsigned long long wait_ns,
+                                                                     int32_t* out, int32_t* status) {
+  p2p_collect_cta(own_base, n, world, wait_ns, out, status);
 }
 
 static std::atomic<unsigned long long> g_wait_limit_ns{kWaitLimitNs};
@@ -255,14 +274,15 @@ extern "C" int nvj_p2p_allgather_i32(const int32_t* local, int n, int rank, int 
 }
 
 extern "C" int nvj_p2p_argmax_publish(const float* x, int rows, int row_len, int32_t* tokens, int rank, int world,
-                                      void* const* peer_buffers, nvj_stream_t stream) {
+                                      void* const* peer_buffers, int32_t* collect_out, int32_t* status, nvj_stream_t stream) {
   using namespace nvj;
   if (rows < 0 || row_len <= 0) return NVJ_ERR_INVALID_ARGUMENT;
   P2pPeers peers{};
   if (!p2p_args_ok(rank, world, peer_buffers, peers)) return NVJ_ERR_INVALID_ARGUMENT;
   if (rows == 0) return NVJ_OK;
   if (!x || !tokens) return NVJ_ERR_INVALID_ARGUMENT;
-  p2p_argmax_publish_kernel<<<rows, kArgmaxThreads, 0, static_cast<cudaStream_t>(stream)>>>(peers, x, row_len, rank, world, tokens);
+  p2p_argmax_publish_kernel<<<rows + (collect_out ? 1 : 0), kArgmaxThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      peers, x, row_len, rows, rank, world, tokens, collect_out, wait_limit_ns(), status);
   return cudaGetLastError() == cudaSuccess ? NVJ_OK : NVJ_ERR_LAUNCH;
 }
 
@@ -271,7 +291,7 @@ extern "C" int nvj_p2p_collect(void* own_buffer, int n, int world, int32_t* out,
   if (world <= 0 || world > kP2pMaxWorld || n < 0 || !own_buffer) return NVJ_ERR_INVALID_ARGUMENT;
   if (n == 0) return NVJ_OK;
   if (!out) return NVJ_ERR_INVALID_ARGUMENT;
-  p2p_collect_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<char*>(own_buffer), n, world, wait_limit_ns(), out,
-                                                                       status);
+  p2p_collect_kernel<<<1, kArgmaxThreads, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<char*>(own_buffer), n, world,
+                                                                                 wait_limit_ns(), out, status);
   return cudaGetLastError() == cudaSuccess ? NVJ_OK : NVJ_ERR_LAUNCH;
 }

@@ -15,8 +15,8 @@ costs no host-to-device traffic for metadata.  Here the same arrays are torch CU
                            once and replays it: one graph launch per step, the kernels run
                            back to back, and nothing is allocated or copied per step.  On
                            several GPUs the token pick also publishes the tokens to every
-                           peer over NVLink, and the graph holds a second branch beside the
-                           attention that collects the PREVIOUS step's tokens: the wait for
+                           peer over NVLink and, in the same launch, collects the PREVIOUS
+                           step's tokens, which have had a whole step to arrive: the wait for
                            the slowest rank never sits between two steps (`gathered` lags one
                            step; `flush()` fetches the last one).
 
@@ -87,7 +87,7 @@ class DecodeStepGraph:
                  scale: float, num_key_value_groups: int, query_dtype=torch.bfloat16, token_gather=None):
         """`token_gather` (a `parallel.P2PTokenGather` over `meta.rows` tokens) makes the token pick publish the step's
         tokens to every rank over NVLink; `gathered` holds every rank's tokens of the step BEFORE the one just replayed
-        (the collect runs beside the attention), and `flush()` brings it up to date."""
+        (each step's launch collects the step before), and `flush()` brings it up to date."""
         if k_cache.ndim != 5:
             raise ValueError("k_cache must be the 5-D cache [L, NB, bs, Hkv, D]")
         self.meta, self.k_cache, self.v_cache = meta, k_cache, v_cache
@@ -106,23 +106,17 @@ class DecodeStepGraph:
                          if token_gather is not None else None)
         self._graph: Optional[torch.cuda.CUDAGraph] = None
         self._stream = torch.cuda.Stream(dev)
-        self._side = torch.cuda.Stream(dev)
         self._tokens = torch.empty(meta.rows, dtype=torch.int32, device=dev)
 
     def _step(self):
-        cur = torch.cuda.current_stream(self.meta.device)
-        if self.token_gather is not None:  # the previous step's tokens arrive while this step's attention runs
-            self._side.wait_stream(cur)
-            with torch.cuda.stream(self._side):
-                self.token_gather.collect(out=self.gathered)
         self.meta.advance()
         out, _, _ = _k.paged_decode_attention_with_kv_append(self.query, self.new_k, self.new_v, self.k_cache, self.v_cache,
                                                              self.meta.block_tables, self.meta.seq_lens, self.meta.positions,
                                                              self.layer_id, self.meta.block_size, self.scale, self.groups)
         if self.token_gather is None:
             return out, _k.row_argmax(out.view(self.meta.rows, -1))
-        cur.wait_stream(self._side)  # this rank has read step k - 1 before it publishes step k
-        return out, self.token_gather.publish_argmax(out.view(self.meta.rows, -1), self._tokens)
+        # one launch: collect the step before, pick this step's tokens, publish them
+        return out, self.token_gather.publish_argmax(out.view(self.meta.rows, -1), self._tokens, collect_out=self.gathered)
 
     def flush(self) -> Optional[torch.Tensor]:
         """Collect the tokens of the last replayed step into `gathered` (several GPUs only)."""

@@ -9,8 +9,8 @@ output tokens (int32 per row): `gather_tokens` does it with `torch.distributed`
 into its peers' memory over NVLink (one node, one process per GPU), which takes
 a few microseconds where the library call takes 7-20.  Its split form
 (`publish_argmax` / `collect`) fuses the publish with the step's token pick and
-moves the wait for the peers beside the next step's attention, so that a rank
-which is late by less than one step delays nobody.  The reference is
+collects a step's tokens one step later, so that a rank which is late by less
+than one step delays nobody.  The reference is
 single-device and has no counterpart of this module.
 
 Failures.  A rank that dies or never joins shows up here in one of two ways:
@@ -154,15 +154,22 @@ class P2PTokenGather:
         self._check(rc, "nvj_p2p_allgather_i32")
         return out
 
-    def publish_argmax(self, x: torch.Tensor, tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def publish_argmax(self, x: torch.Tensor, tokens: Optional[torch.Tensor] = None,
+                       collect_out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """tokens[r] = argmax of row r of the float32 `[n, row_len]` tensor, and the same tokens stored into every peer's
-        buffer and published as this rank's next epoch.  Waits for nobody.  Returns the local tokens."""
+        buffer and published as this rank's next epoch.  The publish waits for nobody.  With `collect_out` (`[world * n]`
+        int32) the same launch first collects the step before into it, as `collect` would: one launch per step, and the
+        gathered tokens lag the step by one.  Returns the local tokens."""
         if x.dtype != torch.float32 or x.ndim != 2 or x.shape[0] != self.n or not x.is_cuda or not x.is_contiguous():
             raise ValueError("x must be a contiguous CUDA float32 tensor [n, row_len]")
         if tokens is None:
             tokens = torch.empty(self.n, dtype=torch.int32, device=self.device)
+        if collect_out is not None and (collect_out.dtype != torch.int32 or collect_out.numel() != self.world * self.n
+                                        or not collect_out.is_cuda or not collect_out.is_contiguous()):
+            raise ValueError("collect_out must be a contiguous CUDA int32 tensor of world * n elements")
         rc = self._lib.nvj_p2p_argmax_publish(x.data_ptr(), self.n, int(x.shape[1]), tokens.data_ptr(), self.rank, self.world,
-                                              self._ptr_array, torch.cuda.current_stream(self.device).cuda_stream)
+                                              self._ptr_array, None if collect_out is None else collect_out.data_ptr(),
+                                              self._status.data_ptr(), torch.cuda.current_stream(self.device).cuda_stream)
         self._check(rc, "nvj_p2p_argmax_publish")
         return tokens
 

@@ -37,10 +37,13 @@ def main():
         x = torch.randn((n, 512), generator=gen, device=dev)
         if s % 5 == rank % 5:
             torch.cuda._sleep(3_000_000)  # a late rank: the others' collect of its step waits, their publish does not
-        g2.collect(out=got)
+        if s % 2 == 0:   # the two-launch form and the fused form take turns
+            g2.collect(out=got)
+            tok = g2.publish_argmax(x)
+        else:
+            tok = g2.publish_argmax(x, collect_out=got)
         if prev_ref is not None:
             assert torch.equal(got, prev_ref), f"rank {rank} step {s}: collected tokens differ from the NCCL gather of step {s - 1}"
-        tok = g2.publish_argmax(x)
         assert torch.equal(tok.long(), x.argmax(dim=1))
         dist.all_gather_into_tensor(ref, tok)
         prev_ref = ref.clone()

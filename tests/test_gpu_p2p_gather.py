@@ -49,6 +49,21 @@ def test_split_form_publishes_with_the_token_pick_and_collects_one_step_later():
     g.collect(out=out)                                      # a second collect of the same step changes nothing
     torch.cuda.synchronize()
     assert torch.equal(out, prev)
+    # the fused form: one launch collects the step before and publishes this one
+    for step in range(4):
+        x = torch.randn((n, row_len), generator=gen, device="cuda")
+        out.fill_(-7)
+        tok = g.publish_argmax(x, collect_out=out)
+        torch.cuda.synchronize()
+        assert torch.equal(tok.long(), x.argmax(dim=1))
+        if step == 0:
+            assert int(out.max()) == -7                     # everything published before had been collected
+        else:
+            assert torch.equal(out, prev)
+        prev = tok.clone()
+    g.collect(out=out)
+    torch.cuda.synchronize()
+    assert torch.equal(out, prev)
     g.check()
     g.close()
 
@@ -110,12 +125,12 @@ def test_a_peer_that_never_publishes_runs_the_wait_out_and_the_gather_recovers()
         x1 = torch.zeros((n, 8), device="cuda"); x1[:, 5] = 1.0
         t = torch.empty(n, dtype=torch.int32, device="cuda")
         got = torch.full((2 * n,), -1, dtype=torch.int32, device="cuda")
-        _lib.check(lib.nvj_p2p_argmax_publish(x0.data_ptr(), n, 8, t.data_ptr(), 0, 2, ptrs2, stream), "publish 0")
+        _lib.check(lib.nvj_p2p_argmax_publish(x0.data_ptr(), n, 8, t.data_ptr(), 0, 2, ptrs2, None, status.data_ptr(), stream), "publish 0")
         _lib.check(lib.nvj_p2p_collect(bufs2[0], n, 2, got.data_ptr(), status.data_ptr(), stream), "collect 0")
         torch.cuda.synchronize()
         assert int(status.item()) == _lib.NVJ_DEV_TIMEOUT and int(got.max()) == -1
         status.zero_()
-        _lib.check(lib.nvj_p2p_argmax_publish(x1.data_ptr(), n, 8, t.data_ptr(), 1, 2, ptrs2, stream), "publish 1")
+        _lib.check(lib.nvj_p2p_argmax_publish(x1.data_ptr(), n, 8, t.data_ptr(), 1, 2, ptrs2, None, status.data_ptr(), stream), "publish 1")
         _lib.check(lib.nvj_p2p_collect(bufs2[0], n, 2, got.data_ptr(), status.data_ptr(), stream), "collect 0 again")
         torch.cuda.synchronize()
         assert int(status.item()) == 0
