@@ -373,6 +373,11 @@ def hybrid_cases(dev, iters):
                2 * n * row, {"workload": "c4 state", "note": "includes the host-side index upload"})
         report("hybrid restore (%d sequences)" % n, tm.run(lambda: cache.restore(ids, [100 + i for i in ids])),
                2 * n * row, {"workload": "c4 state", "note": "includes the host-side index upload"})
+        slots = torch.tensor([table.slot(i) for i in ids], dtype=torch.int32, device=dev)
+        rows = torch.arange(n, dtype=torch.int32, device=dev)
+        report("hybrid state copy kernel alone (%d sequences)" % n,
+               tm.run(lambda: K.hybrid_copy(table.conv, table.rec, cache.conv_pool, cache.rec_pool, slots, rows, restore=False)),
+               2 * n * row, {"workload": "c4 state", "note": "indices already on the device"})
         del table, cache
     K.check_device_status(dev)
 

@@ -128,7 +128,10 @@ int nvj_kv_append_nhd(const void* append_key, const void* append_value, int src_
  *            needs no copy; k, v rows [num_kv_heads, head_dim] at token strides
  *   weights  q_norm, k_norm [head_dim], bf16 or f32
  *   inv_freq [rotary_dim / 2] f32, the framework's own 1 / theta^(2 i / rotary_dim) table
- *   rope_positions [tokens] (text positions; multimodal 3-row positions are not handled)
+ *   rope_positions [position_rows, tokens]: one row (text) or three rows (temporal, height, width) of a
+ *            multimodal position id; with three rows `mrope_section` (HOST array of 3 ints, e.g. 11 / 11 / 10)
+ *            selects the row per frequency as nanovllm_jax/layers.py:79-139 does (positions are stacked x3
+ *            at nanovllm_jax/model.py:3955; equal rows give the text result)
  *   slots and masks as in nvj_kv_append; q_out [tokens, num_q_heads, head_dim] bf16
  * bf16 activations and cache, head_dim 64 / 128 / 256; otherwise NVJ_ERR_UNSUPPORTED.
  */
@@ -137,7 +140,8 @@ int nvj_qk_norm_rope_kv_append(const void* q, int64_t q_token_stride, int64_t q_
                                const void* v, int64_t v_token_stride, int act_dtype,
                                const void* q_norm_weight, const void* k_norm_weight, int weight_dtype,
                                float eps, const float* inv_freq, int rotary_dim,
-                               const int32_t* rope_positions,
+                               const int32_t* rope_positions, int position_rows,
+                               const int32_t* mrope_section,
                                const int32_t* slot_mapping, const int32_t* valid_mask,
                                const int32_t* query_start_loc, int qsl_rows, int packed,
                                int n_rows, int n_cols,

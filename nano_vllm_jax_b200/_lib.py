@@ -27,7 +27,7 @@ SIGNATURES = {
                               c_int, c_int, c_void_p, c_void_p, c_int, c_int64, c_int, c_int,
                               c_void_p, c_void_p]),
     "nvj_qk_norm_rope_kv_append": (c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int,
-                                           c_void_p, c_void_p, c_int, c_float, c_void_p, c_int, c_void_p,
+                                           c_void_p, c_void_p, c_int, c_float, c_void_p, c_int, c_void_p, c_int, c_void_p,
                                            c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                            c_void_p, c_void_p, c_int, c_int64, c_int, c_int, c_int,
                                            c_void_p, c_void_p, c_void_p]),

@@ -73,6 +73,102 @@ copy_rows_kernel(RowTable a, RowTable b, long long src_rows, const int32_t* src_
   else copy_span1(src, dst, t.row_bytes, block, t.blocks);
 }
 
+// The same row copy for rows whose size is a multiple of 16 bytes, moved by the bulk-copy engine: one warp per
+// CTA, a ring of kBulkStages chunks of kBulkChunk bytes in shared memory, every chunk loaded by one
+// cp.async.bulk (global -> shared, completion on an mbarrier) and written back by one cp.async.bulk
+// (shared -> global, tracked by a bulk group).  A thread keeps 64 KiB in flight instead of 64 bytes, which is
+// what a copy of one 19 MB state row needs to reach the memory system's bandwidth: with 16-byte vector loads
+// the same copy is bound by the latency of its few loads per thread.  Chunks of all (pair, table) combinations
+// form one sequence dealt round-robin to the CTAs.
+constexpr int kBulkChunk = 16 * 1024;
+constexpr int kBulkStages = 4;
+
+struct BulkSmem {
+  alignas(128) unsigned char stage[kBulkStages][kBulkChunk];
+  alignas(8) unsigned long long full[kBulkStages];
+  int abort_flag;
+};
+
+__device__ __forceinline__ void bulk_s2g(void* gmem_dst, uint32_t smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gmem_dst), "r"(smem_src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+template <int N>
+__device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory"); }
+
+__global__ void __launch_bounds__(32)
+copy_rows_bulk_kernel(RowTable a, RowTable b, long long src_rows, const int32_t* src_idx, long long dst_rows,
+                      const int32_t* dst_idx, int n_pairs, int32_t* status) {
+  extern __shared__ unsigned char bulk_smem_raw[];
+  BulkSmem& sm = *reinterpret_cast<BulkSmem*>((reinterpret_cast<uintptr_t>(bulk_smem_raw) + 127) & ~(uintptr_t)127);
+  if (threadIdx.x != 0) return;  // one thread drives the copy engine; the warp exists only to own the shared memory
+  const long long chunks_a = (a.row_bytes + kBulkChunk - 1) / kBulkChunk, chunks_b = (b.row_bytes + kBulkChunk - 1) / kBulkChunk;
+  const long long per_pair = chunks_a + chunks_b, total = per_pair * n_pairs;
+  sm.abort_flag = 0;
+  for (int s = 0; s < kBulkStages; ++s) mbar_init(smem_u32(&sm.full[s]), 1);
+  mbar_fence_init();
+
+  // chunk c of this CTA's subsequence -> (source, destination, bytes); bytes = 0 for a pair with a bad index
+  auto locate = [&](long long c, const char*& src, char*& dst) -> uint32_t {
+    const int pair = (int)(c / per_pair);
+    long long r = c - (long long)pair * per_pair;
+    const long long si = src_idx[pair], di = dst_idx[pair];
+    if (si < 0 || si >= src_rows || di < 0 || di >= dst_rows) {
+      if (status) atomicOr(status, NVJ_DEV_BAD_BLOCK_ID);
+      return 0;
+    }
+    const RowTable& t = r < chunks_a ? a : b;
+    if (r >= chunks_a) r -= chunks_a;
+    const long long off = r * kBulkChunk;
+    src = t.src_base + si * t.row_bytes + off;
+    dst = t.dst_base + di * t.row_bytes + off;
+    const long long left = t.row_bytes - off;
+    return (uint32_t)(left < kBulkChunk ? left : kBulkChunk);
+  };
+
+  const long long first = blockIdx.x, stride = gridDim.x;
+  const long long mine = first < total ? (total - first + stride - 1) / stride : 0;
+  char* dsts[kBulkStages];
+  uint32_t sizes[kBulkStages];
+  auto issue_load = [&](long long k) {
+    const int s = (int)(k % kBulkStages);
+    const char* src = nullptr;
+    sizes[s] = locate(first + k * stride, src, dsts[s]);
+    const uint32_t bar = smem_u32(&sm.full[s]);
+    if (sizes[s] > 0) {
+      mbar_arrive_expect_tx(bar, sizes[s]);
+      bulk_g2s(smem_u32(sm.stage[s]), src, sizes[s], bar);
+    } else {
+      mbar_arrive(bar);
+    }
+  };
+  long long issued = 0;
+  for (; issued < mine && issued < kBulkStages; ++issued) issue_load(issued);
+  for (long long k = 0; k < mine; ++k) {
+    const int s = (int)(k % kBulkStages);
+    if (!mbar_wait(smem_u32(&sm.full[s]), (uint32_t)(k / kBulkStages) & 1u, &sm.abort_flag, status)) break;
+    if (sizes[s] > 0) {
+      fence_proxy_async_all();
+      bulk_s2g(dsts[s], smem_u32(sm.stage[s]), sizes[s]);
+    }
+    bulk_commit();
+    if (issued < mine) {
+      bulk_wait_read<0>();  // the store has read the stage: it can take the next chunk
+      issue_load(issued++);
+    }
+  }
+  bulk_wait_all<0>();
+  if (sm.abort_flag) {  // only after a timeout can loads still be in flight: hold the shared memory until they have landed
+    const unsigned long long t0 = global_timer_ns();
+    for (long long k = issued > kBulkStages ? issued - kBulkStages : 0; k < issued; ++k)
+      while (!mbar_try_wait(smem_u32(&sm.full[k % kBulkStages]), (uint32_t)(k / kBulkStages) & 1u) &&
+             global_timer_ns() - t0 < kWaitLimitNs) {
+      }
+  }
+}
+
 // Block copy across layers and K/V: grid.y = pair, grid.z = layer * 2 + (0: K, 1: V).
 __global__ void __launch_bounds__(kCopyThreads)
 copy_blocks_kernel(char* k_cache, char* v_cache, long long num_blocks, long long block_bytes,
@@ -100,6 +196,27 @@ row_argmax_kernel(const float* x, int row_len, int32_t* tokens) {
 }
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Opt the bulk row-copy kernel into its 64 KiB of dynamic shared memory, once per device.
+static bool bulk_copy_ready() {
+  static PerDeviceFlags opted_in;
+  return once_per_device(opted_in, [](int) {
+    return cudaFuncSetAttribute(copy_rows_bulk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                (int)sizeof(BulkSmem) + 128) == cudaSuccess;
+  });
+}
+
+static int sm_count() {
+  static PerDeviceFlags cached;  // 0 = not queried yet
+  const int dev = current_device();
+  if (dev < 0) return 0;
+  int n = cached.v[dev].load(std::memory_order_acquire);
+  if (n == 0) {
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    cached.v[dev].store(n, std::memory_order_release);
+  }
+  return n;
+}
 
 static int grid_x_for(long long bytes, int pairs) {
   // Enough CTAs to fill the machine a few times over, never more than one per tile.
@@ -187,6 +304,17 @@ static int hybrid_copy(const void* conv_src, void* conv_dst, int64_t conv_row_by
   const RowTable rec = row_table(rec_src, rec_dst, rec_row_bytes, n);
   const RowTable conv = row_table(conv_src, conv_dst, conv_row_bytes, n);
   if (rec.blocks + conv.blocks == 0) return NVJ_OK;
+  // rows that the bulk-copy engine can move (16-byte aligned, sizes multiples of 16 bytes) go through it
+  const bool bulk_ok = (rec.blocks == 0 || rec.vec16) && (conv.blocks == 0 || conv.vec16) && bulk_copy_ready();
+  if (bulk_ok) {
+    const long long chunks = ((rec.row_bytes + kBulkChunk - 1) / kBulkChunk + (conv.row_bytes + kBulkChunk - 1) / kBulkChunk) * n;
+    const int sms = sm_count();
+    const long long cap = (long long)(sms > 0 ? sms : 148) * 3;  // three CTAs of 64 KiB shared memory per SM
+    const int ctas = (int)(chunks < cap ? chunks : cap);
+    copy_rows_bulk_kernel<<<ctas, 32, sizeof(BulkSmem) + 128, static_cast<cudaStream_t>(stream)>>>(
+        rec, conv, src_rows, src_slots, dst_rows, dst_slots, n, status);
+    return cudaGetLastError() == cudaSuccess ? NVJ_OK : NVJ_ERR_LAUNCH;
+  }
   dim3 grid(rec.blocks + conv.blocks, n, 1);
   copy_rows_kernel<<<grid, kCopyThreads, 0, static_cast<cudaStream_t>(stream)>>>(rec, conv, src_rows, src_slots, dst_rows,
                                                                                  dst_slots, status);

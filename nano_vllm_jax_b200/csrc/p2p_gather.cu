@@ -4,30 +4,30 @@
 // spends 7-20 us on it (launch + protocol).  Here every rank owns an exchange buffer that its
 // peers map through CUDA IPC:
 //
-//   header   flags[2][16] (uint64: the epoch each rank last published into data set 0 / 1),
-//            published, consumed (uint64 epoch counters of this rank), arrivals (uint32)
-//   data     [2][world][n] int32, two sets that alternate by epoch parity
+//   header   published, consumed (uint64 epoch counters of this rank), arrivals (uint32)
+//   data     [3][world][n] words of 64 bits = (epoch << 32 | token), three sets used in turn (epoch % 3)
+//
+// A token travels together with the epoch it belongs to in ONE 8-byte store, so the receiver needs no flag and the
+// sender no fence: a word whose upper half carries the awaited epoch is the awaited token (the aligned 8-byte store
+// is indivisible).  No step of the protocol waits for an NVLink round trip before it can go on.
 //
 // Two forms use it.
 //
-// (1) nvj_p2p_allgather_i32, one blocking kernel per rank and step: store the tokens into slot `rank` of
-//     every peer's set, publish the epoch into every peer's flag (system-scope release), wait (bounded)
-//     until all flags in the own buffer carry the epoch, copy the set out.
+// (1) nvj_p2p_allgather_i32, one blocking kernel per rank and step: store the words into slot `rank` of every
+//     peer's set, wait (bounded) until all words of the own set carry the epoch, copy the tokens out.
 //
 // (2) the split form for a pipelined decode step, where the wait must not sit between two steps:
-//     nvj_p2p_argmax_publish   token pick of the step fused with the publish: every CTA takes a row's
-//                              argmax; the CTA that finishes last copies the tokens into every peer's set
-//                              and publishes the epoch.  One more CTA of the same launch can collect the
-//                              step before (below).  The publish waits for nobody.
-//     nvj_p2p_collect          waits (bounded) for the oldest published epoch that has not been collected
-//                              yet and copies its set out; does nothing when there is none.
-//     A step k + 1 runs  append + decode,  then one launch that collects step k and publishes step k + 1:
-//     step k's tokens have had a whole step to arrive, so a peer that is late by less than one step costs
-//     nothing, and no launch of the step waits beside the attention kernel (which fills every SM's register
-//     file: a waiting kernel that got an SM first delayed the attention's last CTA).  Because every rank collects epoch k
-//     before it publishes k + 1, and a peer publishes k + 2 only after it has seen this rank's flag k + 1
-//     (it collects k + 1 first), nobody overwrites set (k & 1) before everyone has read it: two sets are
-//     enough and a flag is either the awaited epoch or an older one.
+//     nvj_p2p_argmax_publish   token pick of the step fused with the publish: every CTA takes a row's argmax and
+//                              stores the word into every peer's set.  One more CTA of the same launch can collect
+//                              the step before (below).  The publish waits for nobody.
+//     nvj_p2p_collect          waits (bounded) for the oldest published epoch that has not been collected yet and
+//                              copies its tokens out; does nothing when there is none.
+//     A step k + 1 runs  append + decode,  then one launch that collects step k and publishes step k + 1: step k's
+//     tokens have had a whole step to arrive, so a peer that is late by less than one step costs nothing, and no
+//     launch of the step waits beside the attention kernel (which fills every SM's register file: a waiting kernel
+//     that got an SM first delayed the attention's last CTA).  Three sets suffice: a peer overwrites set k % 3 when it
+//     publishes k + 3, which it does after collecting k + 2, hence after this rank's launch k + 2 has started, hence
+//     (stream order) after this rank's launch k + 1, the one that collects k, has finished.
 //
 // Every wait has a time limit (nvj_set_wait_limit_ns, default 1 s); on a timeout the kernel flags
 // NVJ_DEV_TIMEOUT and returns, and the call can be issued again.  Plain peer stores only: no multicast.
@@ -42,9 +42,9 @@
 namespace nvj {
 
 constexpr int kP2pMaxWorld = 16;
+constexpr int kP2pSets = 3;
 
 struct P2pHeader {
-  unsigned long long flags[2][kP2pMaxWorld];
   unsigned long long published;  // last epoch this rank published (device-kept epochs)
   unsigned long long consumed;   // last epoch this rank collected
   unsigned int arrivals;         // CTAs of the running publish kernel that are done
@@ -57,30 +57,46 @@ struct P2pPeers {
 };
 
 __device__ __forceinline__ P2pHeader* p2p_header(char* base) { return reinterpret_cast<P2pHeader*>(base); }
-__device__ __forceinline__ int32_t* p2p_data(char* base, int parity, int world, int n) {
-  return reinterpret_cast<int32_t*>(base + sizeof(P2pHeader)) + (long long)parity * world * n;
+__device__ __forceinline__ unsigned long long* p2p_set(char* base, unsigned long long epoch, int world, int n) {
+  return reinterpret_cast<unsigned long long*>(base + sizeof(P2pHeader)) + (long long)(epoch % kP2pSets) * world * n;
 }
-__device__ __forceinline__ void st_release_sys(unsigned long long* p, unsigned long long v) {
-  asm volatile("st.release.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+__device__ __forceinline__ unsigned long long p2p_word(int32_t token, unsigned long long epoch) {
+  return (epoch << 32) | (unsigned long long)(uint32_t)token;
 }
-__device__ __forceinline__ unsigned long long ld_acquire_sys(const unsigned long long* p) {
+__device__ __forceinline__ void st_word(unsigned long long* p, unsigned long long v) {
+  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_word(const unsigned long long* p) {
   unsigned long long v;
-  asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
   return v;
 }
 
-// Thread r < world waits until rank r's flag of `parity` in the own buffer reaches `epoch`.  Returns false
-// (and flags the status word) when the limit ran out.
-__device__ __forceinline__ bool p2p_wait_flag(const unsigned long long* flag, unsigned long long epoch,
-                                              unsigned long long wait_ns, int32_t* status) {
+// All threads of a CTA: wait (bounded) until the world * n words of `set` carry `epoch`, writing each token to `out` as
+// it arrives.  Returns false in every thread (and flags the status word) when the limit ran out.
+__device__ __forceinline__ bool p2p_gather_words(const unsigned long long* set, unsigned long long epoch, int count,
+                                                 unsigned long long wait_ns, int32_t* out, int32_t* status, int* failed_sh) {
+  if (threadIdx.x == 0) *failed_sh = 0;
+  __syncthreads();
+  const unsigned long long want = epoch & 0xffffffffull;
   const unsigned long long t0 = global_timer_ns();
-  for (uint32_t spins = 0;; ++spins) {
-    if (ld_acquire_sys(flag) >= epoch) return true;
-    if ((spins & 63u) == 63u && global_timer_ns() - t0 > wait_ns) {
-      if (status) atomicOr(status, NVJ_DEV_TIMEOUT);
-      return false;
+  for (int i = threadIdx.x; i < count; i += blockDim.x) {
+    for (uint32_t spins = 0;; ++spins) {
+      const unsigned long long w = ld_word(set + i);
+      if ((w >> 32) == want) {
+        out[i] = (int32_t)(uint32_t)w;
+        break;
+      }
+      if ((spins & 63u) == 63u && (*reinterpret_cast<volatile int*>(failed_sh) || global_timer_ns() - t0 > wait_ns)) {
+        *failed_sh = 1;
+        break;
+      }
     }
   }
+  __syncthreads();
+  const bool ok = *failed_sh == 0;
+  if (!ok && threadIdx.x == 0 && status) atomicOr(status, NVJ_DEV_TIMEOUT);
+  return ok;
 }
 
 __global__ void __launch_bounds__(256) p2p_allgather_kernel(P2pPeers peers, const int32_t* local, int n, int rank, int world,
@@ -90,7 +106,6 @@ __global__ void __launch_bounds__(256) p2p_allgather_kernel(P2pPeers peers, cons
   __shared__ int failed;
   P2pHeader* own = p2p_header(peers.base[rank]);
   if (threadIdx.x == 0) {
-    failed = 0;
     if (epoch == 0) {  // epoch kept on the device: the same launch can then be replayed from a CUDA graph
       epoch = own->published + 1;
       own->published = epoch;
@@ -100,24 +115,14 @@ __global__ void __launch_bounds__(256) p2p_allgather_kernel(P2pPeers peers, cons
   }
   __syncthreads();
   epoch = epoch_sh;
-  const int parity = (int)(epoch & 1u);
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const int32_t v = local[i];
-    for (int r = 0; r < world; ++r) p2p_data(peers.base[r], parity, world, n)[rank * n + i] = v;
+    const unsigned long long w = p2p_word(local[i], epoch);
+    for (int r = 0; r < world; ++r) st_word(p2p_set(peers.base[r], epoch, world, n) + rank * n + i, w);
   }
-  __threadfence_system();
-  __syncthreads();
-  if (threadIdx.x < world) {
-    st_release_sys(&p2p_header(peers.base[threadIdx.x])->flags[parity][rank], epoch);
-    if (!p2p_wait_flag(&own->flags[parity][threadIdx.x], epoch, wait_ns, status)) failed = 1;
-  }
-  __syncthreads();
-  if (failed) return;
-  const int32_t* gathered = p2p_data(peers.base[rank], parity, world, n);
-  for (int i = threadIdx.x; i < world * n; i += blockDim.x) out[i] = gathered[i];
+  p2p_gather_words(p2p_set(peers.base[rank], epoch, world, n), epoch, world * n, wait_ns, out, status, &failed);
 }
 
-// Waits (bounded) for the oldest published epoch this rank has not collected and copies its data set out.
+// Waits (bounded) for the oldest published epoch this rank has not collected and copies its tokens out.
 // Called by all threads of one CTA.  Returns without doing anything when there is no such epoch; on a timeout the
 // status word is flagged, nothing is consumed, and a later call tries the same epoch again.
 __device__ __forceinline__ void p2p_collect_cta(char* own_base, int n, int world, unsigned long long wait_ns, int32_t* out,
@@ -126,53 +131,41 @@ __device__ __forceinline__ void p2p_collect_cta(char* own_base, int n, int world
   P2pHeader* own = p2p_header(own_base);
   const unsigned long long epoch = *reinterpret_cast<volatile unsigned long long*>(&own->consumed) + 1;
   if (epoch > *reinterpret_cast<volatile unsigned long long*>(&own->published)) return;
-  if (threadIdx.x == 0) failed = 0;
-  __syncthreads();
-  const int parity = (int)(epoch & 1u);
-  if ((int)threadIdx.x < world && !p2p_wait_flag(&own->flags[parity][threadIdx.x], epoch, wait_ns, status)) failed = 1;
-  __syncthreads();
-  if (failed) return;
-  const int32_t* gathered = p2p_data(own_base, parity, world, n);
-  for (int i = threadIdx.x; i < world * n; i += blockDim.x) out[i] = gathered[i];
-  __syncthreads();
+  if (!p2p_gather_words(p2p_set(own_base, epoch, world, n), epoch, world * n, wait_ns, out, status, &failed)) return;
   if (threadIdx.x == 0) own->consumed = epoch;
 }
 
 // Token pick fused with the publish (and, optionally, with the collect of the step before).  CTA r < n takes the
-// argmax of row r (first maximum wins, as row_argmax_kernel) and stores the token locally; CTA n, present when
-// collect_out is given, collects the previous epoch.  The CTA that finishes last copies the n tokens into every
-// peer's data set with coalesced stores and then publishes the epoch: one system-scope fence per launch, and the
-// publish comes after this rank's own collect, which is what lets two data sets suffice.
+// argmax of row r (first maximum wins, as row_argmax_kernel), stores the token locally and sends its word to every
+// peer; CTA n, present when collect_out is given, collects the previous epoch.  The CTA that finishes last advances
+// this rank's epoch counter (a local store: nothing here waits for the links).
 __global__ void __launch_bounds__(kArgmaxThreads) p2p_argmax_publish_kernel(P2pPeers peers, const float* x, int row_len, int n, int rank,
                                                                             int world, int32_t* tokens, int32_t* collect_out,
                                                                             unsigned long long wait_ns, int32_t* status) {
   P2pHeader* own = p2p_header(peers.base[rank]);
-  __shared__ int last_sh;
+  // `published` is advanced by the last CTA only, after every CTA of the launch has read it
+  const unsigned long long epoch = *reinterpret_cast<volatile unsigned long long*>(&own->published) + 1;
+  __shared__ int token_sh, last_sh;
   if ((int)blockIdx.x < n) {
     const int token = row_argmax_cta(x + (long long)blockIdx.x * row_len, row_len);
-    if (threadIdx.x == 0) tokens[blockIdx.x] = token;
+    if (threadIdx.x == 0) {
+      token_sh = token;
+      tokens[blockIdx.x] = token;
+    }
+    __syncthreads();
+    if ((int)threadIdx.x < world)
+      st_word(p2p_set(peers.base[threadIdx.x], epoch, world, n) + rank * n + blockIdx.x, p2p_word(token_sh, epoch));
   } else {
     p2p_collect_cta(peers.base[rank], n, world, wait_ns, collect_out, status);
   }
-  __threadfence();
   __syncthreads();
-  if (threadIdx.x == 0) last_sh = (atomicAdd(&own->arrivals, 1u) == gridDim.x - 1u) ? 1 : 0;
-  __syncthreads();
-  if (!last_sh) return;
-  __threadfence();
-  // `published` is advanced here and nowhere else, after every CTA of the launch is done with it
-  const unsigned long long epoch = *reinterpret_cast<volatile unsigned long long*>(&own->published) + 1;
-  const int parity = (int)(epoch & 1u);
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const int32_t v = __ldcg(tokens + i);
-    for (int r = 0; r < world; ++r) p2p_data(peers.base[r], parity, world, n)[rank * n + i] = v;
-  }
-  __threadfence_system();
-  __syncthreads();
-  if ((int)threadIdx.x < world) st_release_sys(&p2p_header(peers.base[threadIdx.x])->flags[parity][rank], epoch);
   if (threadIdx.x == 0) {
-    own->arrivals = 0;
-    own->published = epoch;
+    __threadfence();
+    last_sh = (atomicAdd(&own->arrivals, 1u) == gridDim.x - 1u) ? 1 : 0;
+    if (last_sh) {
+      own->arrivals = 0;
+      own->published = epoch;
+    }
   }
 }
 
@@ -223,7 +216,7 @@ extern "C" int nvj_selftest_bounded_wait(int32_t* status, int32_t* returned, nvj
 
 extern "C" size_t nvj_p2p_gather_buffer_bytes(int world, int n) {
   if (world <= 0 || world > nvj::kP2pMaxWorld || n < 0) return 0;
-  return sizeof(nvj::P2pHeader) + sizeof(int32_t) * 2 * (size_t)world * n;
+  return sizeof(nvj::P2pHeader) + sizeof(unsigned long long) * nvj::kP2pSets * (size_t)world * n;
 }
 
 extern "C" int nvj_p2p_buffer_create(size_t bytes, void** dev_ptr, unsigned char* handle64) {

@@ -12,8 +12,10 @@
 //   y'[i + rot/2]   = bf16( y[i + rot/2] * c + y[i] * s ),   y'[j >= rot] = y[j]
 // The products and the sum are formed in fp32 and rounded once (what XLA does with its default
 // excess-precision setting); `inv_freq` comes from the caller so that it is bit-identical to
-// the framework's own table.  Text positions only (one position per token; the three rows of a
-// multimodal position id are equal for text and give the same angles).
+// the framework's own table.  Positions are one row per token (text) or three rows (temporal,
+// height, width) of a multimodal position id; with three rows frequency i takes its position from
+// the height row when i % 3 == 1 and i < 3 * section[1], from the width row when i % 3 == 2 and
+// i < 3 * section[2], else from the temporal row (the interleaved selection of layers.py:79-139).
 // One warp per (token, head): D / 32 elements per lane (D = 64, 128 or 256), sum of squares by
 // shuffle, the rotation partner rot / 2 elements away sits (rot / 2) / (D / 32) lanes away.
 // Slots and masks are those of the plain append (kv_append.cuh).
@@ -30,7 +32,8 @@ struct NormRopeParams {
   const void* q_weight;
   const void* k_weight;
   const float* inv_freq;
-  const int32_t* rope_positions;
+  const int32_t* rope_positions;  // [pos_rows][tokens]
+  int pos_rows, h_limit, w_limit;  // 1 or 3 rows; 3 * section[1], 3 * section[2]
   __nv_bfloat16* q_out;
   long long q_token_stride, q_head_stride, k_token_stride, v_token_stride;  // in elements
   int hq, hkv, d, rot, w_dtype;
@@ -99,10 +102,15 @@ __global__ void __launch_bounds__(256) qk_norm_rope_append_kernel(NormRopeParams
   for (int j = 0; j < E; ++j) other[j] = __shfl_xor_sync(kFullMask, y[j], half_lanes);
   if (lane < 2 * half_lanes) {
     const bool first = lane < half_lanes;
-    const float pos = (float)p.rope_positions[token];
+    float pos3[3];
+    pos3[0] = (float)p.rope_positions[token];
+    pos3[1] = p.pos_rows == 3 ? (float)p.rope_positions[(long long)p.a.n_tokens + token] : pos3[0];
+    pos3[2] = p.pos_rows == 3 ? (float)p.rope_positions[2LL * p.a.n_tokens + token] : pos3[0];
 #pragma unroll
     for (int j = 0; j < E; ++j) {
-      const int i = (lane & (half_lanes - 1)) * E + j;  // index into the first half
+      const int i = (lane & (half_lanes - 1)) * E + j;  // index into the first half = frequency index
+      const int m = i % 3;
+      const float pos = (m == 1 && i < p.h_limit) ? pos3[1] : ((m == 2 && i < p.w_limit) ? pos3[2] : pos3[0]);
       const float ang = __fmul_rn(pos, p.inv_freq[i]);
       const float c = __bfloat162float(__float2bfloat16_rn(cosf(ang)));
       const float s = __bfloat162float(__float2bfloat16_rn(sinf(ang)));
@@ -128,7 +136,8 @@ extern "C" int nvj_qk_norm_rope_kv_append(const void* q, int64_t q_token_stride,
                                           const void* v, int64_t v_token_stride, int act_dtype,
                                           const void* q_norm_weight, const void* k_norm_weight, int weight_dtype,
                                           float eps, const float* inv_freq, int rotary_dim,
-                                          const int32_t* rope_positions,
+                                          const int32_t* rope_positions, int position_rows,
+                                          const int32_t* mrope_section,
                                           const int32_t* slot_mapping, const int32_t* valid_mask,
                                           const int32_t* query_start_loc, int qsl_rows, int packed,
                                           int n_rows, int n_cols,
@@ -137,7 +146,8 @@ extern "C" int nvj_qk_norm_rope_kv_append(const void* q, int64_t q_token_stride,
                                           void* q_out, int32_t* status, nvj_stream_t stream) {
   using namespace nvj;
   if (n_rows < 0 || n_cols < 0 || num_slots < 0 || num_q_heads <= 0 || num_kv_heads <= 0 || head_dim <= 0 ||
-      rotary_dim < 0 || rotary_dim > head_dim)
+      rotary_dim < 0 || rotary_dim > head_dim || (position_rows != 1 && position_rows != 3) ||
+      (position_rows == 3 && !mrope_section))
     return NVJ_ERR_INVALID_ARGUMENT;
   const long long tokens = (long long)n_rows * n_cols;
   if (tokens == 0) return NVJ_OK;
@@ -166,6 +176,9 @@ extern "C" int nvj_qk_norm_rope_kv_append(const void* q, int64_t q_token_stride,
   p.v = static_cast<const __nv_bfloat16*>(v);
   p.q_weight = q_norm_weight; p.k_weight = k_norm_weight; p.w_dtype = weight_dtype;
   p.inv_freq = inv_freq; p.rope_positions = rope_positions; p.q_out = static_cast<__nv_bfloat16*>(q_out);
+  p.pos_rows = position_rows;
+  p.h_limit = position_rows == 3 ? 3 * mrope_section[1] : 0;
+  p.w_limit = position_rows == 3 ? 3 * mrope_section[2] : 0;
   p.q_token_stride = q_token_stride; p.q_head_stride = q_head_stride;
   p.k_token_stride = k_token_stride; p.v_token_stride = v_token_stride;
   p.hq = num_q_heads; p.hkv = num_kv_heads; p.d = head_dim; p.rot = rotary_dim; p.eps = eps;

@@ -158,9 +158,13 @@ class PrefixStateCache:
         self._entry[prefix_hash] = row
         return row
 
-    def _idx(self, values: List[int]) -> torch.Tensor:
-        t = torch.tensor(values, dtype=torch.int32)
-        return t.pin_memory().to(self.table.device, non_blocking=True) if self.table.device.type == "cuda" else t
+    def _idx_pair(self, first: List[int], second: List[int]):
+        """Both index lists of one copy on the device, uploaded with a single host-to-device copy."""
+        n = len(first)
+        t = torch.tensor(list(first) + list(second), dtype=torch.int32)
+        if self.table.device.type == "cuda":
+            t = t.pin_memory().to(self.table.device, non_blocking=True)
+        return t[:n], t[n:]
 
     def snapshot(self, seq_ids: Seq[int], prefix_hashes: Seq[int]) -> List[bool]:
         """pool[hash] <- table[slot(seq)] for every pair, one batched copy.  Returns, per pair, whether the state is
@@ -181,8 +185,8 @@ class PrefixStateCache:
             rows.append(row)
             stored.append(True)
         if rows:
-            _k.hybrid_copy(self.table.conv, self.table.rec, self.conv_pool, self.rec_pool,
-                           self._idx(slots), self._idx(rows), restore=False)
+            t_slots, t_rows = self._idx_pair(slots, rows)
+            _k.hybrid_copy(self.table.conv, self.table.rec, self.conv_pool, self.rec_pool, t_slots, t_rows, restore=False)
         return stored
 
     def restore(self, seq_ids: Seq[int], prefix_hashes: Seq[int]) -> None:
@@ -197,8 +201,8 @@ class PrefixStateCache:
             self._entry.move_to_end(int(h))
             rows.append(row)
         slots = [self.table.slot(int(s)) for s in seq_ids]
-        _k.hybrid_copy(self.table.conv, self.table.rec, self.conv_pool, self.rec_pool,
-                       self._idx(slots), self._idx(rows), restore=True)
+        t_slots, t_rows = self._idx_pair(slots, rows)
+        _k.hybrid_copy(self.table.conv, self.table.rec, self.conv_pool, self.rec_pool, t_slots, t_rows, restore=True)
         self.table.mark_written(seq_ids)
 
     # ---- the two engine-step hooks (llm_engine.py:432-457)

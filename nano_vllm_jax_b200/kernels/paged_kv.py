@@ -574,12 +574,14 @@ def rope_inv_freq(rope_theta: float, rotary_dim: int, device) -> torch.Tensor:
 
 def qk_norm_rope_kv_append(query, k, v, q_norm_weight, k_norm_weight, positions, slot_mapping, k_cache_layer,
                            v_cache_layer, *, eps=1e-6, rope_theta=1e7, rotary_dim=64, valid_mask=None,
-                           query_start_loc=None, packed=False):
+                           query_start_loc=None, packed=False, mrope_section=(11, 11, 10)):
     """RMSNorm(q), RMSNorm(k), partial RoPE on both, K/V rows into their slots; returns the query for attention.
 
     query `[rows, cols, Hq, D]` (may be a strided view, e.g. the first half of a `[.., Hq, 2 D]` query|gate
-    projection), k, v `[rows, cols, Hkv, D]`, positions and slot_mapping `[rows, cols]` int32; the cache layer
-    is updated in place.  Fuses nanovllm_jax/model.py:3371-3396 with the append of 3539-3550.
+    projection), k, v `[rows, cols, Hkv, D]`, slot_mapping `[rows, cols]` int32; the cache layer is updated in place.
+    positions: `[rows, cols]` int32 (text), or `[3, rows, cols]` (temporal, height, width rows of a multimodal
+    position id, nanovllm_jax/model.py:3955) combined per frequency by `mrope_section` as
+    nanovllm_jax/layers.py:79-139 does.  Fuses nanovllm_jax/model.py:3371-3396 with the append of 3539-3550.
     """
     lib = _lib.load()
     for name, t in (("query", query), ("k", k), ("v", v), ("k_cache_layer", k_cache_layer), ("v_cache_layer", v_cache_layer)):
@@ -612,9 +614,14 @@ def qk_norm_rope_kv_append(query, k, v, q_norm_weight, k_norm_weight, positions,
     if vs is None or vs[1] != d:
         v = v.contiguous(); vs = (hkv * d, d)
     slot_mapping = _i32("slot_mapping", slot_mapping)
+    pos_rows = 3 if positions.ndim == 3 else 1
+    if pos_rows == 3 and (positions.shape[0] != 3 or len(mrope_section) != 3):
+        raise ValueError("multimodal positions must have shape [3, rows, cols] and mrope_section three entries")
     pos = _i32("positions", positions).reshape(-1)
-    if slot_mapping.numel() != rows * cols or pos.numel() != rows * cols:
-        raise ValueError("positions and slot_mapping must have shape [rows, cols]")
+    if slot_mapping.numel() != rows * cols or pos.numel() != pos_rows * rows * cols:
+        raise ValueError("positions [rows, cols] (or [3, rows, cols]) and slot_mapping [rows, cols] expected")
+    import ctypes
+    sections = (ctypes.c_int32 * 3)(*[int(x) for x in mrope_section]) if pos_rows == 3 else None
     vm = None
     if valid_mask is not None:
         vm = _cuda("valid_mask", valid_mask).reshape(-1).to(torch.int32).contiguous()
@@ -631,7 +638,7 @@ def qk_norm_rope_kv_append(query, k, v, q_norm_weight, k_norm_weight, positions,
     st = _status_word(query.device)
     rc = lib.nvj_qk_norm_rope_kv_append(_ptr(query), qs[0], qs[1], _ptr(k), ks[0], _ptr(v), vs[0], _dt(query),
                                         _ptr(qw), _ptr(kw), _dt(qw), float(eps), _ptr(inv), int(rotary_dim), _ptr(pos),
-                                        _ptr(slot_mapping), _ptr(vm), _ptr(qsl), qsl_rows, 1 if packed else 0,
+                                        pos_rows, sections, _ptr(slot_mapping), _ptr(vm), _ptr(qsl), qsl_rows, 1 if packed else 0,
                                         rows, cols, _ptr(k_cache_layer), _ptr(v_cache_layer), _dt(k_cache_layer),
                                         num_slots, hq, hkv, d, _ptr(q_out), _ptr(st), _stream(query.device))
     check(rc, "nvj_qk_norm_rope_kv_append")

@@ -51,19 +51,47 @@ def main():
     assert torch.equal(got, prev_ref)
     g2.check()
     g2.close()
-    # timing, both ways, 200 steps each
+    # timing, 200 steps each: the blocking gather, the library gather, and the pieces of the split form
+    from nano_vllm_jax_b200.kernels import paged_kv as K
     tok = base.clone()
-    for fn, name in ((lambda: g.gather(tok, out=ref), "p2p"), (lambda: dist.all_gather_into_tensor(ref, tok), "nccl")):
+    x = torch.randn((n, 2048), device=dev)
+    g3 = P2PTokenGather(n)
+    tmp = torch.empty(n, dtype=torch.int32, device=dev)
+    cases = ((lambda: g.gather(tok, out=ref), "p2p blocking gather"),
+             (lambda: dist.all_gather_into_tensor(ref, tok), "nccl all-gather"),
+             (lambda: K.row_argmax(x), "row_argmax alone"),
+             (lambda: g3.publish_argmax(x, tmp, collect_out=ref), "argmax + publish + collect of the step before (one launch)"),
+             (lambda: (g3.publish_argmax(x, tmp), g3.collect(out=ref)), "argmax + publish, then collect of the same step (two launches)"))
+    side = torch.cuda.Stream(dev)
+    for fn, name in cases:
         for _ in range(20):
             fn()
         dist.barrier(); torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(200):
-            fn()
-        e1.record(); torch.cuda.synchronize()
+        if "nccl" in name:  # eager launches: the host's launch rate is part of this figure
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(200):
+                fn()
+            e1.record(); torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) / 200 * 1e3
+        else:           # 20 launches per CUDA graph, 10 replays: device time per launch
+            graph = torch.cuda.CUDAGraph()
+            side.wait_stream(torch.cuda.current_stream(dev))
+            with torch.cuda.graph(graph, stream=side):
+                for _ in range(20):
+                    fn()
+            dist.barrier(); torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(10):
+                graph.replay()
+            e1.record(); torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) / 200 * 1e3
         if rank == 0:
-            print(f"TIMING {name} {e0.elapsed_time(e1) / 200 * 1e3:.1f} us per gather of {n} int32 x {world} ranks", flush=True)
+            print(f"TIMING {name}: {us:.1f} us per step, {n} int32 x {world} ranks", flush=True)
+    g3.collect(out=ref)
+    g3.check()
+    g3.close()
     g.check()
     g.close()
     if rank == 0:

@@ -101,3 +101,33 @@ def test_unsupported_shapes_are_refused():
     with pytest.raises(NvjError):  # fp32 cache
         K.qk_norm_rope_kv_append(to_torch(c["qg"])[..., :256], to_torch(c["k"]), to_torch(c["v"]), to_torch(c["qw"]), to_torch(c["kw"]),
                                  to_torch(c["pos"]), to_torch(c["slots"]), kc[0], kc[0].clone())
+
+
+@pytest.mark.parametrize("rows,cols", [(23, 1), (1, 130)])
+def test_multimodal_three_row_positions(rows, cols):
+    """Temporal, height and width rows that differ: frequency i takes the row layers.py:79-139 gives it (sections
+    11 / 11 / 10); three equal rows reproduce the text result bit for bit."""
+    from nano_vllm_jax_b200.kernels import paged_kv as K
+    c = _case(rows + cols, rows, cols, 64, max_pos=3000)
+    rng = np.random.default_rng(99)
+    pos3 = np.stack([c["pos"], rng.integers(0, 64, size=c["pos"].shape), rng.integers(0, 64, size=c["pos"].shape)]).astype(np.int32)
+    q_view = c["qg"][..., :256]
+    ref_q, ref_k, ref_v = N.qk_norm_rope_kv_append(q_view, c["k"], c["v"], c["qw"], c["kw"], pos3, c["slots"], c["kc"], c["vc"],
+                                                   mrope_section=(11, 11, 10))
+    text_q, _, _ = N.qk_norm_rope_kv_append(q_view, c["k"], c["v"], c["qw"], c["kw"], c["pos"], c["slots"], c["kc"], c["vc"])
+    assert (_ulp_diff(ref_q, text_q) > 0).mean() > 0.05      # the rows really matter in this case
+    kc, vc = to_torch(c["kc"]), to_torch(c["vc"])
+    args = (to_torch(c["qg"])[..., :256], to_torch(c["k"]), to_torch(c["v"]), to_torch(c["qw"]), to_torch(c["kw"]))
+    q_out, _, _ = K.qk_norm_rope_kv_append(*args, to_torch(pos3), to_torch(c["slots"]), kc[0], vc[0], mrope_section=(11, 11, 10))
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(bits(to_numpy(vc)), bits(ref_v))
+    for name, got, want in (("q", to_numpy(q_out), ref_q), ("k cache", to_numpy(kc), ref_k)):
+        g, w = got.astype(np.float32), want.astype(np.float32)
+        assert (np.abs(g - w) <= 2.0 ** -7 * np.abs(w).max(axis=-1, keepdims=True)).all(), name
+        assert (_ulp_diff(got, want) > 0).mean() < 2e-3, name
+    # three equal rows == one row
+    kc1, vc1, kc3, vc3 = to_torch(c["kc"]), to_torch(c["vc"]), to_torch(c["kc"]), to_torch(c["vc"])
+    q1, _, _ = K.qk_norm_rope_kv_append(*args, to_torch(c["pos"]), to_torch(c["slots"]), kc1[0], vc1[0])
+    q3, _, _ = K.qk_norm_rope_kv_append(*args, to_torch(np.stack([c["pos"]] * 3)), to_torch(c["slots"]), kc3[0], vc3[0])
+    torch.cuda.synchronize()
+    assert torch.equal(q1, q3) and torch.equal(kc1, kc3) and torch.equal(vc1, vc3)

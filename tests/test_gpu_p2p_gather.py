@@ -108,7 +108,7 @@ def test_a_peer_that_never_publishes_runs_the_wait_out_and_the_gather_recovers()
         torch.cuda.synchronize()
         assert int(status.item()) == _lib.NVJ_DEV_TIMEOUT
         assert 1.5 <= t0.elapsed_time(t1) < 200.0           # it waited for the limit, not for the default second
-        assert int(out0.max()) == -1                         # nothing was delivered
+        assert int(out0[n:].max()) == -1                     # nothing of the silent peer was delivered
         status.zero_()
         # the peer arrives: its own wait is satisfied at once (rank 0 has published epoch 1 already)
         _lib.check(lib.nvj_p2p_allgather_i32(tok1.data_ptr(), n, 1, 2, ptrs, 1, out1.data_ptr(), status.data_ptr(), stream), "rank 1")
@@ -128,7 +128,7 @@ def test_a_peer_that_never_publishes_runs_the_wait_out_and_the_gather_recovers()
         _lib.check(lib.nvj_p2p_argmax_publish(x0.data_ptr(), n, 8, t.data_ptr(), 0, 2, ptrs2, None, status.data_ptr(), stream), "publish 0")
         _lib.check(lib.nvj_p2p_collect(bufs2[0], n, 2, got.data_ptr(), status.data_ptr(), stream), "collect 0")
         torch.cuda.synchronize()
-        assert int(status.item()) == _lib.NVJ_DEV_TIMEOUT and int(got.max()) == -1
+        assert int(status.item()) == _lib.NVJ_DEV_TIMEOUT and int(got[n:].max()) == -1
         status.zero_()
         _lib.check(lib.nvj_p2p_argmax_publish(x1.data_ptr(), n, 8, t.data_ptr(), 1, 2, ptrs2, None, status.data_ptr(), stream), "publish 1")
         _lib.check(lib.nvj_p2p_collect(bufs2[0], n, 2, got.data_ptr(), status.data_ptr(), stream), "collect 0 again")
@@ -173,3 +173,4 @@ def test_ranks_on_separate_gpus_agree_with_the_library_gather():
                         "--master-addr", "127.0.0.1", "--master-port", "29531", worker],
                        capture_output=True, text=True, timeout=300, env=env)
     assert r.returncode == 0 and "P2P_GATHER_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+    print("\n".join(line for line in r.stdout.splitlines() if line.startswith("TIMING")))

@@ -216,3 +216,26 @@ def test_copy_blocks_oracle():
     np.testing.assert_array_equal(k1[:, 5], k[:, 0])
     np.testing.assert_array_equal(v1[:, 4], v[:, 2])
     np.testing.assert_array_equal(k1[:, :4], k[:, :4])
+
+
+def test_mrope_row_selection_matches_the_interleaved_layout_of_the_reference():
+    # layers.py:86-139 with mrope_section (11, 11, 10) over 32 frequencies: the height row supplies indices
+    # 1, 4, ..., 31 (11 of them), the width row 2, 5, ..., 29 (10), the temporal row the other 11
+    from oracle import norm_rope_ref as N
+    inv = np.ones(32, np.float32)                      # unit frequencies: the result IS the selected position
+    pos = np.stack([np.full((1, 2), 100), np.full((1, 2), 200), np.full((1, 2), 300)]).astype(np.int32)
+    got = N.mrope_freqs(pos, inv, (11, 11, 10))[0, 0]
+    want = np.full(32, 100.0, np.float32)
+    want[1::3] = 200.0
+    want[2:30:3] = 300.0
+    np.testing.assert_array_equal(got, want)
+    assert (got == 100).sum() == 11 and (got == 200).sum() == 11 and (got == 300).sum() == 10
+    # equal rows are the text case, bit for bit
+    rng = np.random.default_rng(0)
+    x = rng.standard_normal((2, 5, 3, 256), dtype=np.float32).astype(N.bfloat16)
+    p = rng.integers(0, 5000, size=(2, 5)).astype(np.int32)
+    a = N.apply_rope(x, p, 256, 1e7, 0.25)
+    b = N.apply_rope(x, np.stack([p, p, p]), 256, 1e7, 0.25, mrope_section=(11, 11, 10))
+    c = N.apply_rope(x, p, 256, 1e7, 0.25, mrope_section=(11, 11, 10))
+    np.testing.assert_array_equal(a.view(np.uint16), b.view(np.uint16))
+    np.testing.assert_array_equal(a.view(np.uint16), c.view(np.uint16))
