@@ -8,8 +8,9 @@ each row's output into a token (argmax stand-in for the sampler) and, with N > 1
 ranks, all-gather the tokens.  Rank r owns its own rows, block tables and KV pool
 (request partition); nothing but the tokens crosses GPUs.
 
-Workload c2 (default; per rank): 256 rows, contexts uniform in [1024, 4096],
-400k-block bf16 pool, block tables a scattered permutation, N(0,1) values.
+Workload c2 (default; per rank): 256 rows, contexts uniform in [1024, 4096] (the same seeded
+draw on every rank), 400k-block bf16 pool, block tables a scattered permutation and N(0,1)
+values of the rank's own.
 Workload c5: 2048 rows, contexts uniform in [8192, 32768], rows dealt round-robin
 to the ranks (strong scaling), each rank's pool sized to min(150 GB, 0.9 x free
 memory) with the block tables drawn over the whole pool.
@@ -87,10 +88,12 @@ def measured_hbm_peak():
 
 
 def row_lengths(w, rank, world):
-    """Context lengths of this rank's rows (seeded)."""
-    if w["scaling"] == "weak":
-        return np.random.default_rng(w["seed"] * 1000 + rank).integers(w["lo"], w["hi"] + 1, size=w["rows"]).astype(np.int64)
+    """Context lengths of this rank's rows (seeded).  Weak scaling: every rank runs the configuration itself, i.e. the
+    SAME seeded lengths (its block tables and values are its own), so that the per-N figures compare the system and
+    not the ranks' luck in the draw.  Strong scaling: one draw for all rows, dealt round-robin."""
     ctx_all = np.random.default_rng(w["seed"]).integers(w["lo"], w["hi"] + 1, size=w["rows"])
+    if w["scaling"] == "weak":
+        return ctx_all.astype(np.int64)
     return ctx_all[rank::world].astype(np.int64)  # request id i -> rank i % world
 
 
@@ -397,7 +400,10 @@ def run_b200(args, w):
             dist.all_gather_into_tensor(gathered, K.row_argmax(out.view(rows, HQ * D)))
 
     token_gather = None
-    if world > 1 and os.environ.get("NVJ_BENCH_NCCL_GATHER", "0") != "1":
+    # NVJ_BENCH_SELF_GATHER=1: on one GPU, run the step with the NVLink gather kernel gathering from itself (a
+    # diagnostic that separates the kernel's own cost from waiting for other ranks)
+    self_gather = world == 1 and os.environ.get("NVJ_BENCH_SELF_GATHER", "0") == "1"
+    if (world > 1 and os.environ.get("NVJ_BENCH_NCCL_GATHER", "0") != "1") or self_gather:
         from nano_vllm_jax_b200.parallel import P2PTokenGather
         try:  # peer stores over NVLink inside the graph; all ranks succeed or all fall back to the NCCL gather
             token_gather = P2PTokenGather(rows)
@@ -509,20 +515,30 @@ def run_b200(args, w):
     clocks = sampler.stop() if rank == 0 else None
     K.check_device_status(dev)
 
-    # gather latency on its own (N > 1): publish + collect of one step, back to back on one stream
+    # The gather launch on its own (N > 1): token pick + publish + collect of the step before, 20 launches in a CUDA
+    # graph, so that the figure is device time per launch and not the host's launch rate.  Back to back the collect has
+    # to wait for the peers' publish of a moment ago, which it never does inside a decode step.
     gather_us = None
     if token_gather is not None:
         x = graph.out.view(rows, HQ * D) if graph_ok else torch.zeros((rows, HQ * D), device=dev)
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        g_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g_graph, stream=side):
+            for _ in range(20):
+                token_gather.publish_argmax(x, pipe_tokens, collect_out=gathered_p2p)
         for timing in (False, True):
-            dist.barrier(); torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            for _ in range(50):
-                token_gather.publish_argmax(x, pipe_tokens)
-                token_gather.collect(out=gathered_p2p)
+            for _ in range(5):
+                g_graph.replay()
             e1.record(); torch.cuda.synchronize()
             if timing:
-                gather_us = e0.elapsed_time(e1) / 50 * 1e3
+                gather_us = e0.elapsed_time(e1) / 100 * 1e3
+        token_gather.collect(out=gathered_p2p)
         token_gather.check()
 
     total_rows = rows
@@ -603,9 +619,9 @@ def run_b200(args, w):
             "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
+    if token_gather is not None:
+        token_gather.close()
     if world > 1:
-        if token_gather is not None:
-            token_gather.close()
         dist.destroy_process_group()
 
 
