@@ -125,17 +125,21 @@ def decode_cases(dev, iters):
            Timer(dev, max(3, iters // 4), flush=False).run(
                lambda: K.paged_decode_attention(q[:sub, 0], k[0], v[0], tables[:sub], t_lens[:sub], SCALE, variant=1)),
            int(lens[:sub].sum()) * TOKEN_BYTES, {"workload": "c2, first 16 rows"})
-    # speculative-verify decode: 4 query tokens per row at the last 4 positions (rows already appended)
+    # speculative-verify decode: `width` query tokens per row at the row's last positions (rows already appended)
     from nano_vllm_jax_b200 import kv_cache as kvc
+    for width in (2, 4, 5, 8):
+        qw = _randn_bf16((rows, width, HQ, D), 6, dev)
+        wpos = (t_lens[:, None] - width + torch.arange(width, device=dev, dtype=torch.int32)[None, :]).contiguous()
+        wbytes = kv_bytes + table_bytes + rows * width * (HQ * D * 2 + HQ * D * 4)
+        report("wide decode, %d query tokens per row (tensor-core streaming kernel)" % width,
+               big.run(lambda: kvc.paged_attention_decode(qw, k, v, tables, t_lens, BS, SCALE, 4, positions=wpos, out_dtype=torch.float32)),
+               wbytes, {"workload": "c2, width %d" % width})
     width = 4
     qw = _randn_bf16((rows, width, HQ, D), 6, dev)
     wpos = (t_lens[:, None] - width + torch.arange(width, device=dev, dtype=torch.int32)[None, :]).contiguous()
     wbytes = kv_bytes + table_bytes + rows * width * (HQ * D * 2 + HQ * D * 4)
-    report("wide decode, 4 query tokens per row (tensor-core streaming kernel)",
-           big.run(lambda: kvc.paged_attention_decode(qw, k, v, tables, t_lens, BS, SCALE, 4, positions=wpos, out_dtype=torch.float32)),
-           wbytes, {"workload": "c2, width 4"})
     qsl_w = torch.arange(rows + 1, dtype=torch.int32, device=dev) * width
-    report("wide decode as a packed batch of equal-width rows (tcgen05 prefill tiles; what widths above 4 take)",
+    report("wide decode as a packed batch of equal-width rows (tcgen05 prefill tiles; what widths above 8 take)",
            big.run(lambda: K.packed_paged_prefill_attention(qw.reshape(1, rows * width, HQ, D), k[0], v[0], tables, t_lens,
                                                             wpos.reshape(1, -1), qsl_w, BS, SCALE, 4, num_decode_rows=0)),
            wbytes, {"workload": "c2, width 4"})

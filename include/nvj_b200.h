@@ -247,13 +247,14 @@ int nvj_paged_decode_static_scratch(const void* q, int q_dtype,
                                     float* out, int32_t* status_out, nvj_stream_t stream);
 
 /*
- * Paged decode attention for rows that carry 2..4 query tokens (verification of speculated
+ * Paged decode attention for rows that carry 2..8 query tokens (verification of speculated
  * tokens; the reference's wide decode, nanovllm_jax/kv_cache.py:852-998 with query width T > 1,
  * reached from nanovllm_jax/backends.py:1266-1359 and nanovllm_jax/mtp/mtp_layer.py:686).
  * The rows' K/V must already be appended.  Key p of row b is visible to token t when
  * p < seq_lens[b] and (positions given) p <= positions[b, t].  The model's shape only: bf16
  * query and cache, block 16, 2 KV x 4 query heads, head_dim 256; each K/V byte is read once for
- * all of a row's tokens, the products run on the tensor cores.
+ * all of a row's tokens, the products run on the tensor cores (one 16-row tile per KV head up to width 4, two
+ * from width 5 on: the tensor work per block doubles, the HBM traffic does not).
  *
  *   q          [batch, width, 8, 256] bf16
  *   positions  [batch, width] int32, nullable (no causal limit)
@@ -261,7 +262,7 @@ int nvj_paged_decode_static_scratch(const void* q, int q_dtype,
  *   workspace  nvj_paged_decode_wide_workspace_bytes(max_batch) bytes, zeroed once
  *              (nvj_paged_decode_workspace_init) and then reused; its first word is the device
  *              status word
- * NVJ_ERR_UNSUPPORTED for width > 4 or misaligned pointers (use nvj_paged_prefill_packed with
+ * NVJ_ERR_UNSUPPORTED for width > 8 or misaligned pointers (use nvj_paged_prefill_packed with
  * rows of equal width instead).
  */
 size_t nvj_paged_decode_wide_workspace_bytes(int max_batch);

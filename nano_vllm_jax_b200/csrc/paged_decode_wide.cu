@@ -1,6 +1,6 @@
-// Paged GQA decode attention with the products on tensor-core tiles, for rows of 1..4 query tokens:
+// Paged GQA decode attention with the products on tensor-core tiles, for rows of 1..8 query tokens:
 // the decode step proper (width 1, with the optional fused append of the step's new K/V row) and
-// the verification of speculated tokens / multi-token prediction (width 2..4).  Cache shape of the
+// the verification of speculated tokens / multi-token prediction (width 2..8).  Cache shape of the
 // model's full-attention layer: bf16, 16-token blocks, 2 KV heads x 4 query heads, head_dim 256.
 //
 // The kernel is HBM-bound: every K/V byte is read from HBM exactly once.  On the CUDA cores the dot
@@ -21,6 +21,11 @@
 //     keeps the result within 2e-3 of an fp32 evaluation.
 //   * The two parities of a (kv head, dim half) merge through shared memory at the end of a row
 //     segment.
+//   * Rows of 5..8 query tokens need two 16-row tiles per KV head, and a warp has registers for one
+//     (64 of query fragments + 64 of accumulators).  The kernel is then built in its second form
+//     (kDual): the two warps of a (kv head, dim half) no longer split the blocks by parity but the
+//     ROWS: both read every staged block, one for tokens 0..3, the other for tokens 4..7, and
+//     nothing is merged between them.  K/V still cross HBM once; the tensor work per block doubles.
 // Semantics: nanovllm_jax/kv_cache.py:852-998 (key p of row b is visible to token t when
 // p < seq_lens[b] and, at width > 1 with positions given, p <= positions[b, t]); the fused append
 // follows nanovllm_jax/kernels/full_attention_triton.py:373-485 (positions are then the slots the
@@ -41,7 +46,7 @@ namespace nvj {
 // leave a copy in flight when the CTA exits (seen as a launch failure with five stages).
 constexpr int kWStages = 4;
 static_assert(kWStages % 2 == 0, "each stage must belong to one block parity");
-constexpr int kWMaxWidth = 4;
+constexpr int kWMaxWidth = 8;   // 1..4: one row tile per warp; 5..8: the dual form
 constexpr int kWPad = 136;                    // row pitch (floats) of the parity exchange buffer
 
 struct WideSmem {
@@ -199,6 +204,7 @@ __device__ __forceinline__ void w_process_block(uint32_t kt, uint32_t vt, int la
 // memory, then the even-parity warps write either the final output rows (the segment covered the
 // whole row) or this CTA's partial; the CTA that delivers a row's last partial folds them all,
 // token by token (see the width-1 kernel for the two-level scheme).
+template <bool kDual>
 __device__ __forceinline__ void w_finish_segment(const DecodeParams& p, WideSmem& sm, const Seg& s, WideState& st, int warp,
                                                  int lane, const Partition& pt) {
   const int g = lane >> 2, t = lane & 3, tid = warp * 32 + lane;
@@ -208,7 +214,7 @@ __device__ __forceinline__ void w_finish_segment(const DecodeParams& p, WideSmem
     st.l[r] += __shfl_xor_sync(kFullMask, st.l[r], 1);
     st.l[r] += __shfl_xor_sync(kFullMask, st.l[r], 2);
   }
-  if (par == 1) {
+  if (!kDual && par == 1) {
 #pragma unroll
     for (int n = 0; n < 16; ++n) {
       *reinterpret_cast<float2*>(&sm.xo[grp][g][n * 8 + 2 * t]) = make_float2(st.o[n][0], st.o[n][1]);
@@ -224,11 +230,12 @@ __device__ __forceinline__ void w_finish_segment(const DecodeParams& p, WideSmem
   const long long qbase = p.packed_rows ? (long long)p.query_start_loc[s.b] : (long long)s.b * p.width;  // first query token
   const int slot = partial_slot(blockIdx.x, s.j0 == 0);
   const int slot_rows = p.width * kHq;  // rows of one partial slot: [token][head]
-  if (par == 0) {
+  if (kDual || par == 0) {
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
-      const int row = g + 8 * r, tok = row >> 2;
-      const float m1 = sm.xm[grp][row], l1 = sm.xl[grp][row];
+      const int row = g + 8 * r, tok = (kDual ? 4 * par : 0) + (row >> 2);
+      // dual form: this warp alone holds the row's state; else the odd-parity warp's share comes from shared memory
+      const float m1 = kDual ? kNegBig : sm.xm[grp][row], l1 = kDual ? 0.f : sm.xl[grp][row];
       const float M = fmaxf(st.m[r], m1);
       const float f0 = ex2_approx(st.m[r] - M), f1 = ex2_approx(m1 - M);
       const float L = st.l[r] * f0 + l1 * f1;
@@ -240,7 +247,7 @@ __device__ __forceinline__ void w_finish_segment(const DecodeParams& p, WideSmem
       dst += dh * 128 + 2 * t;
 #pragma unroll
       for (int n = 0; n < 16; ++n) {
-        const float2 x = *reinterpret_cast<const float2*>(&sm.xo[grp][row][n * 8 + 2 * t]);
+        const float2 x = kDual ? make_float2(0.f, 0.f) : *reinterpret_cast<const float2*>(&sm.xo[grp][row][n * 8 + 2 * t]);
         *reinterpret_cast<float2*>(dst + n * 8) =
             make_float2((st.o[n][2 * r] * f0 + x.x * f1) * inv, (st.o[n][2 * r + 1] * f0 + x.y * f1) * inv);
       }
@@ -296,6 +303,7 @@ __device__ __forceinline__ void w_finish_segment(const DecodeParams& p, WideSmem
   if (tid == 0) p.counters[s.b] = 0;
 }
 
+template <bool kDual>
 __global__ void __launch_bounds__(kDecodeThreads, 1)
 decode_wide_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map, DecodeParams p) {
   extern __shared__ unsigned char w_smem_raw[];
@@ -342,7 +350,7 @@ decode_wide_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_const
   if (threadIdx.x == 0) {
     for (int s = 0; s < kWStages; ++s) {
       mbar_init(smem_u32(&sm.full_bar[s]), 1);
-      mbar_init(smem_u32(&sm.empty_bar[s]), 4);
+      mbar_init(smem_u32(&sm.empty_bar[s]), kDual ? 8 : 4);
     }
     mbar_fence_init();
   }
@@ -370,7 +378,7 @@ decode_wide_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_const
     const long long qbase = p.packed_rows ? (long long)p.query_start_loc[s.b] : (long long)s.b * p.width;
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
-      const int row = fg + 8 * r, tok = row >> 2;
+      const int row = fg + 8 * r, tok = (kDual ? 4 * par : 0) + (row >> 2);
       const bool real = tok < p.width;
       const __nv_bfloat16* qrow =
           static_cast<const __nv_bfloat16*>(p.q) + ((qbase + (real ? tok : 0)) * kHq + kvh * kG + (row & 3)) * kD;
@@ -421,7 +429,7 @@ decode_wide_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_const
         if (n0 < n_iters) fill_ring(p, sm, fs, g1, n0, n_iters - n0 < kRing / 2 ? n_iters - n0 : kRing / 2);
         named_bar_sync(1, kDecodeThreads);
       }
-      if ((it & 1) != par) continue;
+      if (!kDual && (it & 1) != par) continue;
       const int stage = it % kWStages;
       mbar_wait(smem_u32(&sm.full_bar[stage]), (uint32_t)(it / kWStages) & 1u, &sm.abort_flag, p.status);
       const int rows = sm.ring_rows[it & (kRing - 1)];
@@ -438,12 +446,13 @@ decode_wide_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_const
       __syncwarp();
       if (lane == 0) {
         mbar_arrive(smem_u32(&sm.empty_bar[stage]));
-        // the four warps of a parity take turns to refill the stage that iteration `it` just used
-        if ((warp >> 1) == ((it >> 1) & 3) && it + kWStages < n_iters) w_issue_block(p, sm, &k_map, &v_map, it + kWStages, true);
+        // the warps that read the stage take turns to refill it: the four warps of a parity, or all eight (dual form)
+        if ((kDual ? warp == (it & 7) : (warp >> 1) == ((it >> 1) & 3)) && it + kWStages < n_iters)
+          w_issue_block(p, sm, &k_map, &v_map, it + kWStages, true);
       }
       __syncwarp();
     }
-    w_finish_segment(p, sm, s, st, warp, lane, pt);
+    w_finish_segment<kDual>(p, sm, s, st, warp, lane, pt);
   }
   // Only after a timeout can copies still be in flight with nobody waiting for them: hold the
   // CTA's shared memory until they have landed.
@@ -547,10 +556,12 @@ int launch_decode_wide(const DecodeParams& p, cudaStream_t stream) {
   static PerDeviceFlags smem_opted_in;
   const int smem = (int)sizeof(WideSmem) + 1024;
   if (!once_per_device(smem_opted_in, [smem](int) {
-        return cudaFuncSetAttribute(decode_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) == cudaSuccess;
+        return cudaFuncSetAttribute(decode_wide_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) == cudaSuccess &&
+               cudaFuncSetAttribute(decode_wide_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) == cudaSuccess;
       }))
     return NVJ_ERR_LAUNCH;
-  decode_wide_kernel<<<n, kDecodeThreads, smem, stream>>>(k_map, v_map, p);
+  if (p.width > 4) decode_wide_kernel<true><<<n, kDecodeThreads, smem, stream>>>(k_map, v_map, p);
+  else decode_wide_kernel<false><<<n, kDecodeThreads, smem, stream>>>(k_map, v_map, p);
   return cudaGetLastError() == cudaSuccess ? NVJ_OK : NVJ_ERR_LAUNCH;
 }
 

@@ -1,4 +1,4 @@
-"""Decode attention for rows of 2..4 query tokens (speculative verification) on the GPU, through the C ABI,
+"""Decode attention for rows of 2..8 query tokens (speculative verification) on the GPU, through the C ABI,
 against the CPU oracle's wide decode (nanovllm_jax/kv_cache.py:852-998 restated in oracle/kv_cache_ref.py).
 
 Tolerance: the contract is max-abs 2e-2 against the oracle's fp32 mode; the kernel is also held to 2e-3.
@@ -48,7 +48,7 @@ def _oracle(c, q, tables, lens, pos):
     return R.paged_attention_decode(q, c["k_cache"], c["v_cache"], tables, lens, BS, SCALE, 4, positions=pos)
 
 
-@pytest.mark.parametrize("width", [2, 3, 4])
+@pytest.mark.parametrize("width", [2, 3, 4, 5, 6, 7, 8])
 def test_every_length_around_the_block_boundaries(width):
     lens = list(range(width, 3 * BS + 3))
     c, q, tables, lens, pos = _case(20 + width, 512, lens, width)
@@ -57,10 +57,11 @@ def test_every_length_around_the_block_boundaries(width):
     assert err <= TIGHT, err
 
 
-def test_scattered_positions_and_rows_without_keys():
+@pytest.mark.parametrize("width", [4, 7])
+def test_scattered_positions_and_rows_without_keys(width):
     # positions anywhere inside the row (not only the tail), two rows of length 0 between live ones
     lens = [700, 0, 33, 1500, 0, 16, 257]
-    c, q, tables, lens, pos = _case(31, 512, lens, 4, causal=False)
+    c, q, tables, lens, pos = _case(31, 512, lens, width, causal=False)
     out = _run(c, q, tables, lens, pos)
     ref = _oracle(c, q, tables, lens, pos)
     live = lens > 0
@@ -68,26 +69,28 @@ def test_scattered_positions_and_rows_without_keys():
     assert not out[~live].any()  # defined as zeros (the reference leaves such rows undefined)
 
 
+@pytest.mark.parametrize("width", [3, 8])
 @pytest.mark.parametrize("lens", [(20000,), (9000, 30, 9000, 700, 5), (3000, 12000, 2, 6000)])
-def test_long_rows_are_split_over_ctas_and_merged(lens):
-    c, q, tables, lens, pos = _case(9, 2600, lens, 3)
-    lens = np.maximum(lens, 3)
-    pos = np.maximum(lens[:, None] - 3 + np.arange(3)[None, :], 0).astype(np.int32)
+def test_long_rows_are_split_over_ctas_and_merged(lens, width):
+    c, q, tables, lens, pos = _case(9, 2600, lens, width)
+    lens = np.maximum(lens, width)
+    pos = np.maximum(lens[:, None] - width + np.arange(width)[None, :], 0).astype(np.int32)
     out = _run(c, q, tables, lens, pos)
     assert np.abs(out - _oracle(c, q, tables, lens, pos)).max() <= TIGHT
     again = _run(c, q, tables, lens, pos)  # counters were left at zero; the merge order is fixed
     np.testing.assert_array_equal(bits(out), bits(again))
 
 
-def test_no_positions_means_no_causal_limit_and_matches_the_packed_route():
+@pytest.mark.parametrize("width", [4, 6])
+def test_no_positions_means_no_causal_limit_and_matches_the_packed_route(width):
     from nano_vllm_jax_b200.kernels import paged_kv as K
     lens = [300, 1000, 64, 129]
-    c, q, tables, lens, pos = _case(41, 256, lens, 4)
+    c, q, tables, lens, pos = _case(41, 256, lens, width)
     out = _run(c, q, tables, lens, None)
     full = np.broadcast_to(lens[:, None] - 1, pos.shape).astype(np.int32)
     assert np.abs(out - _oracle(c, q, tables, lens, full)).max() <= TIGHT
     # the same batch as a packed batch of equal-width rows on the prefill tiles
-    qsl = torch.arange(len(lens) + 1, dtype=torch.int32, device="cuda") * 4
+    qsl = torch.arange(len(lens) + 1, dtype=torch.int32, device="cuda") * width
     packed = K.packed_paged_prefill_attention(to_torch(q).reshape(1, -1, 8, 256), to_torch(c["k_cache"][0]), to_torch(c["v_cache"][0]),
                                               to_torch(tables), to_torch(lens), to_torch(pos).reshape(1, -1), qsl, BS, SCALE, 4)
     causal = _run(c, q, tables, lens, pos)
@@ -96,10 +99,10 @@ def test_no_positions_means_no_causal_limit_and_matches_the_packed_route():
 
 def test_refusals():
     from nano_vllm_jax_b200.kernels import paged_kv as K
-    c, q, tables, lens, pos = _case(5, 64, [40, 50], 4)
-    q5 = np.concatenate([q, q[:, :1]], axis=1)
+    c, q, tables, lens, pos = _case(5, 64, [40, 50], 8)
+    q9 = np.concatenate([q, q[:, :1]], axis=1)
     with pytest.raises(ValueError):
-        K.paged_decode_attention_wide(to_torch(q5), to_torch(c["k_cache"][0]), to_torch(c["v_cache"][0]), to_torch(tables),
+        K.paged_decode_attention_wide(to_torch(q9), to_torch(c["k_cache"][0]), to_torch(c["v_cache"][0]), to_torch(tables),
                                       to_torch(lens), None, SCALE)
     with pytest.raises(ValueError):
         K.paged_decode_attention_wide(to_torch(q).float(), to_torch(c["k_cache"][0]), to_torch(c["v_cache"][0]), to_torch(tables),
