@@ -25,7 +25,10 @@
 //     (64 of query fragments + 64 of accumulators).  The kernel is then built in its second form
 //     (kDual): the two warps of a (kv head, dim half) no longer split the blocks by parity but the
 //     ROWS: both read every staged block, one for tokens 0..3, the other for tokens 4..7, and
-//     nothing is merged between them.  K/V still cross HBM once; the tensor work per block doubles.
+//     nothing is merged between them.  K/V still cross HBM once; the tensor work per block doubles
+//     and every warp now walks every block, which makes this form bound by a warp's chain of dependent
+//     tile products (width 8 takes ~1.9x the width-1 time; entering the softmax weights as one bf16
+//     term instead of two was measured: 11% faster at 4e-3 instead of 2e-3 error, not taken).
 // Semantics: nanovllm_jax/kv_cache.py:852-998 (key p of row b is visible to token t when
 // p < seq_lens[b] and, at width > 1 with positions given, p <= positions[b, t]); the fused append
 // follows nanovllm_jax/kernels/full_attention_triton.py:373-485 (positions are then the slots the
