@@ -310,6 +310,29 @@ int nvj_paged_prefill_packed(const void* q, int q_dtype,
                              void* workspace, size_t workspace_bytes, int variant,
                              nvj_stream_t stream);
 
+/*
+ * The two halves of nvj_paged_prefill_packed as separate launches, for a caller that runs them side by side on two
+ * streams: in a mixed batch (nanovllm_jax/engine/scheduler.py:956-1032) the decode rows and the prefill chunks
+ * write different rows of `out`, and neither kernel fills the machine alone.  Same arguments; the model's shape
+ * only (NVJ_ERR_UNSUPPORTED otherwise: the generic kernel serves a batch in one piece).  The caller zeroes `out`
+ * first and orders both launches behind that.
+ *   part 1   rows that hold exactly one query token, on the streaming decode kernel with at most `cta_limit` CTAs
+ *            (0 = one per SM; give the SM count minus the CTAs of part 2); `workspace` is required
+ *   part 2   every other row, on the tile kernel `variant` selects; `workspace` is ignored
+ * The reference runs a mixed batch through one packed attention call; the split has no counterpart there.
+ */
+int nvj_paged_prefill_packed_part(const void* q, int q_dtype,
+                                  const void* k_cache_layer, const void* v_cache_layer, int kv_dtype,
+                                  int64_t num_blocks, int block_size, int num_kv_heads,
+                                  int head_dim, int num_q_heads,
+                                  const int32_t* block_tables, int table_width,
+                                  const int32_t* kv_lens, const int32_t* positions,
+                                  const int32_t* query_start_loc, int rows,
+                                  int token_bucket, float scale,
+                                  float* out, int32_t* status,
+                                  void* workspace, size_t workspace_bytes, int variant,
+                                  int part, int cta_limit, nvj_stream_t stream);
+
 /* ------------------------------------------------------------------ copies */
 
 /*

@@ -54,6 +54,10 @@ SIGNATURES = {
                                          c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p,
                                          c_void_p, c_int, c_int, c_float, c_void_p, c_void_p,
                                          c_void_p, c_size_t, c_int, c_void_p]),
+    "nvj_paged_prefill_packed_part": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int64, c_int,
+                                              c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p,
+                                              c_void_p, c_int, c_int, c_float, c_void_p, c_void_p,
+                                              c_void_p, c_size_t, c_int, c_int, c_int, c_void_p]),
     "nvj_copy_blocks": (c_int, [c_void_p, c_void_p, c_int, c_int64, c_int64, c_int64, c_void_p,
                                 c_void_p, c_int, c_void_p, c_void_p]),
     "nvj_hybrid_snapshot": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int64,

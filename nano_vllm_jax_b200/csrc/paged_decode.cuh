@@ -43,6 +43,9 @@ struct DecodeParams {
   // query tokens per row of the wide kernel (2..4; 0 elsewhere): q is [batch, width, heads, dim], out
   // [batch, width, heads * dim], positions (nullable) [batch, width]
   int width;
+  // upper bound on the CTAs of the streaming kernels (0: one, or two, per SM): a caller that runs another kernel
+  // beside the decode pass leaves that kernel's SMs free
+  int cta_limit;
   float* out;
   // workspace
   int32_t* status;

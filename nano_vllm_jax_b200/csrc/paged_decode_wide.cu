@@ -550,8 +550,9 @@ static size_t wide_acc_bytes(int n, int width) { return ws_round(sizeof(float) *
 int launch_decode_wide(const DecodeParams& p, cudaStream_t stream) {
   if (p.width < 1 || p.width > kWMaxWidth || p.num_blocks < 1 || p.num_blocks * kBlk > 0x7fffffffLL || !w_encode_fn())
     return NVJ_ERR_UNSUPPORTED;
-  const int n = decode_wide_num_ctas();
+  int n = decode_wide_num_ctas();
   if (n <= 0) return NVJ_ERR_LAUNCH;
+  if (p.cta_limit > 0 && p.cta_limit < n) n = p.cta_limit;
   CUtensorMap k_map, v_map;
   if (!tensor_map_cached(&k_map, 0, p.k_cache, (uint64_t)p.num_blocks * kBlk, w_make_map) ||
       !tensor_map_cached(&v_map, 0, p.v_cache, (uint64_t)p.num_blocks * kBlk, w_make_map))

@@ -35,6 +35,51 @@ from .. import _lib
 from ..kernels import paged_kv as _k
 
 
+class CapturedStep:
+    """A step function over static device buffers, run once and then replayed from a CUDA graph.
+
+    `fn` must launch on the current stream only, allocate nothing it keeps using after the call except through
+    torch's allocator (the graph's private pool keeps such tensors alive), and never synchronise with the host.
+    `capture()` runs `fn` once for real on a side stream (kernels, workspaces and tensor maps are then warm; this
+    run is the step's first execution) and records a second run; `replay()` launches the recording.  Reading the
+    device status word back after every call (`NVJ_CHECK_STATUS=1`, what the tests do) is a host synchronisation,
+    so it is switched off while `fn` runs here; call `paged_kv.check_device_status()` afterwards instead.
+    """
+
+    def __init__(self, fn, device="cuda"):
+        self.fn = fn
+        self.device = torch.device(device)
+        self._stream = torch.cuda.Stream(self.device)
+        self._graph: Optional[torch.cuda.CUDAGraph] = None
+        self.result = None
+
+    def capture(self):
+        strict = os.environ.get("NVJ_CHECK_STATUS")
+        os.environ["NVJ_CHECK_STATUS"] = "0"
+        try:
+            self._stream.wait_stream(torch.cuda.current_stream(self.device))
+            with torch.cuda.stream(self._stream):
+                first = self.fn()
+            self._stream.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=self._stream):
+                self.result = self.fn()
+            self._graph = graph
+        finally:
+            if strict is None:
+                os.environ.pop("NVJ_CHECK_STATUS", None)
+            else:
+                os.environ["NVJ_CHECK_STATUS"] = strict
+        torch.cuda.current_stream(self.device).wait_stream(self._stream)
+        return first
+
+    def replay(self):
+        if self._graph is None:
+            raise RuntimeError("capture() has not been called")
+        self._graph.replay()
+        return self.result
+
+
 class ResidentDecodeMetadata:
     def __init__(self, rows: int, table_width: int, block_size: int, device="cuda"):
         self.device = torch.device(device)
@@ -104,8 +149,7 @@ class DecodeStepGraph:
         self.token_gather = token_gather
         self.gathered = (torch.empty(token_gather.world * meta.rows, dtype=torch.int32, device=dev)
                          if token_gather is not None else None)
-        self._graph: Optional[torch.cuda.CUDAGraph] = None
-        self._stream = torch.cuda.Stream(dev)
+        self._captured: Optional[CapturedStep] = None
         self._tokens = torch.empty(meta.rows, dtype=torch.int32, device=dev)
 
     def _step(self):
@@ -127,29 +171,14 @@ class DecodeStepGraph:
     def capture(self):
         """Run one real step from the current `query`, `new_k`, `new_v` (on a side stream: capture needs warm kernels
         and workspaces) and then capture the step for `replay()`.  Returns that first step's (out, tokens)."""
-        strict = os.environ.get("NVJ_CHECK_STATUS")
-        os.environ["NVJ_CHECK_STATUS"] = "0"  # reading the status word back is a host sync: not capturable
-        try:
-            self._stream.wait_stream(torch.cuda.current_stream(self.meta.device))
-            with torch.cuda.stream(self._stream):
-                first = self._step()
-            self._stream.synchronize()
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=self._stream):
-                self.out, self.tokens = self._step()
-            self._graph = graph
-        finally:
-            if strict is None:
-                os.environ.pop("NVJ_CHECK_STATUS", None)
-            else:
-                os.environ["NVJ_CHECK_STATUS"] = strict
-        torch.cuda.current_stream(self.meta.device).wait_stream(self._stream)
+        self._captured = CapturedStep(self._step, self.meta.device)
+        first = self._captured.capture()
+        self.out, self.tokens = self._captured.result
         return first
 
     def replay(self):
         """One decode step from the current contents of `query`, `new_k`, `new_v`; returns (out, tokens) views that
         the next replay overwrites."""
-        if self._graph is None:
+        if self._captured is None:
             raise RuntimeError("capture() has not been called")
-        self._graph.replay()
-        return self.out, self.tokens
+        return self._captured.replay()

@@ -539,19 +539,57 @@ def packed_paged_prefill_attention(query, k_cache_layer, v_cache_layer, block_ta
     if _poison():
         out.fill_(float("nan"))
     st = _status_word(q.device)
-    ws = _workspace(q.device, rows) if (num_decode_rows is None or num_decode_rows > 0) else None
-    rc = lib.nvj_paged_prefill_packed(_ptr(q), _dt(q), _ptr(k_cache_layer), _ptr(v_cache_layer),
-                                      _dt(k_cache_layer), pages, page_size, hkv, d, hq, _ptr(block_table),
-                                      block_table.shape[1], _ptr(kv_lens), _ptr(pos), _ptr(qsl), rows,
-                                      tokens, float(scale), _ptr(out), _ptr(st), _ptr(ws.buf) if ws else None, ws.nbytes if ws else 0,
-                                      int(os.environ.get("NVJ_PREFILL_VARIANT", "0")) if variant is None else int(variant),
-                                      _stream(q.device))
-    check(rc, "nvj_paged_prefill_packed")
+    variant = int(os.environ.get("NVJ_PREFILL_VARIANT", "0")) if variant is None else int(variant)
+    model_shape = (k_cache_layer.dtype == torch.bfloat16 and (page_size, hkv, d, hq) == (16, 2, 256, 8)
+                   and q.dtype in (torch.bfloat16, torch.float32))
+
+    def call(fn, ws, *extra):
+        return fn(_ptr(q), _dt(q), _ptr(k_cache_layer), _ptr(v_cache_layer), _dt(k_cache_layer), pages, page_size, hkv, d, hq,
+                  _ptr(block_table), block_table.shape[1], _ptr(kv_lens), _ptr(pos), _ptr(qsl), rows, tokens, float(scale),
+                  _ptr(out), _ptr(st), _ptr(ws.buf) if ws else None, ws.nbytes if ws else 0, variant, *extra,
+                  _stream(q.device))
+
+    # A mixed batch (decode rows + prefill chunks, counts known on the host): the two kinds of row are served by two
+    # kernels that write different rows of `out` and neither fills the machine, so they run side by side on two
+    # streams; the decode pass leaves the tile kernel's SMs free.
+    side_by_side = (model_shape and variant != 1 and num_decode_rows is not None and 0 < num_decode_rows < rows
+                    and os.environ.get("NVJ_MIXED_SERIAL", "0") != "1")
+    if side_by_side:
+        cur = torch.cuda.current_stream(q.device)
+        side = _side_stream(q.device)
+        out.zero_()
+        sms = torch.cuda.get_device_properties(q.device).multi_processor_count
+        tile_ctas = 4 * (-(-(tokens - num_decode_rows) // 64) + (rows - num_decode_rows))  # CTA pairs x 2 KV heads
+        cta_limit = max(sms // 2, sms - tile_ctas)
+        side.wait_stream(cur)
+        with torch.cuda.stream(side):
+            ws = _workspace(q.device, rows)  # the side stream's own workspace
+            rc1 = call(lib.nvj_paged_prefill_packed_part, ws, 1, cta_limit)
+        rc2 = call(lib.nvj_paged_prefill_packed_part, None, 2, 0)
+        cur.wait_stream(side)
+        check(rc1, "nvj_paged_prefill_packed_part (decode rows)")
+        check(rc2, "nvj_paged_prefill_packed_part (tiles)")
+    else:
+        ws = _workspace(q.device, rows) if (num_decode_rows is None or num_decode_rows > 0) else None
+        check(call(lib.nvj_paged_prefill_packed, ws), "nvj_paged_prefill_packed")
     if _strict():
         _check_word(st, "nvj_paged_prefill_packed")
         if ws is not None:
             _check_word(ws.status_tensor(), "nvj_paged_prefill_packed (decode rows)", ws)
     return out.reshape(1, tokens, hq * d)
+
+
+_side_streams: dict[int, "torch.cuda.Stream"] = {}
+
+
+def _side_stream(device: torch.device) -> "torch.cuda.Stream":
+    """One extra stream per device for work that runs beside the current stream (forked and joined inside a call)."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    s = _side_streams.get(idx)
+    if s is None:
+        s = torch.cuda.Stream(device)
+        _side_streams[idx] = s
+    return s
 
 
 # --------------------------------------------------------------------------- norm + rope + append
