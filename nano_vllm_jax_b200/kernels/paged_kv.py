@@ -550,10 +550,17 @@ def packed_paged_prefill_attention(query, k_cache_layer, v_cache_layer, block_ta
                   _stream(q.device))
 
     # A mixed batch (decode rows + prefill chunks, counts known on the host): the two kinds of row are served by two
-    # kernels that write different rows of `out` and neither fills the machine, so they run side by side on two
-    # streams; the decode pass leaves the tile kernel's SMs free.
-    side_by_side = (model_shape and variant != 1 and num_decode_rows is not None and 0 < num_decode_rows < rows
-                    and os.environ.get("NVJ_MIXED_SERIAL", "0") != "1")
+    # kernels that write different rows of `out` and neither fills the machine, so they can run side by side on two
+    # streams, the decode pass leaving the tile kernel's SMs free.  That pays when the launches come from a CUDA graph
+    # (one 6-layer step: 369 -> 272 us); launched eagerly the extra stream bookkeeping costs the host more than the
+    # overlap saves, so the fork is taken only while the current stream is being captured (NVJ_MIXED_SIDE_BY_SIDE=1
+    # forces it, =0 forbids it).
+    mixed = model_shape and variant != 1 and num_decode_rows is not None and 0 < num_decode_rows < rows
+    mode = os.environ.get("NVJ_MIXED_SIDE_BY_SIDE", "auto")
+    side_by_side = mixed and (mode == "1" or (mode != "0" and torch.cuda.is_current_stream_capturing()))
+    if mixed and not side_by_side:
+        with torch.cuda.stream(_side_stream(q.device)):
+            _workspace(q.device, rows)  # exists before any capture: a capture must not allocate it
     if side_by_side:
         cur = torch.cuda.current_stream(q.device)
         side = _side_stream(q.device)

@@ -155,6 +155,28 @@ def test_mixed_batch_decode_rows_travel_the_packed_route():
     assert np.abs(to_numpy(out) - ref).max() <= PREFILL_TC
 
 
+@pytest.mark.parametrize("mode", ["0", "1"])
+def test_mixed_batch_with_host_counts_serial_and_side_by_side(mode, monkeypatch):
+    # The scheduler's host-side query lengths tell how many rows hold one token; the decode rows and the prefill
+    # chunks can then run as two launches on two streams (forced here; taken by itself only under graph capture).
+    # 20 decode rows with long contexts (split over CTAs and merged) + 2 chunks, padded bucket.
+    from nano_vllm_jax_b200 import kv_cache as kv
+    monkeypatch.setenv("NVJ_MIXED_SIDE_BY_SIDE", mode)
+    rng = np.random.default_rng(77)
+    cached = [int(x) for x in rng.integers(100, 3000, size=20)] + [256, 0]
+    chunk = [1] * 20 + [200, 129]
+    c = _prefill_case(7, 4500, [0] * 22, cached=cached, chunk=chunk, bucket=384)
+    ref = R.paged_attention_prefill_packed(c["q"], c["k"], c["v"], c["tables"], c["kv_lens"], c["pos"], c["rid"],
+                                           c["qsl"], BS, SCALE, 4)
+    for _ in range(2):  # twice: counters and the side stream's workspace are left clean
+        out = kv.paged_attention_prefill_packed(to_torch(c["q"]), to_torch(c["k"]), to_torch(c["v"]), to_torch(c["tables"]),
+                                                to_torch(c["kv_lens"]), to_torch(c["pos"]), to_torch(c["rid"]),
+                                                to_torch(c["qsl"]), BS, SCALE, 4, out_dtype=torch.float32, num_decode_rows=20)
+        torch.cuda.synchronize()
+        assert np.abs(to_numpy(out) - ref).max() <= PREFILL_TC
+        assert not to_numpy(out)[0, sum(chunk):].any()
+
+
 def test_copy_blocks_bit_exact_all_layers():
     from nano_vllm_jax_b200.kernels import paged_kv as K
     rng = np.random.default_rng(3)
