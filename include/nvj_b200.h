@@ -371,6 +371,23 @@ int nvj_hybrid_restore(void* conv_table, const void* conv_pool, int64_t conv_row
                        const int32_t* table_slots, const int32_t* pool_slots, int n,
                        int32_t* status, nvj_stream_t stream);
 
+/*
+ * The same two copies with the slot lists in HOST memory (n <= NVJ_HYBRID_HOST_SLOTS pairs, else NVJ_ERR_TOO_LARGE):
+ * the indices travel in the kernel's parameters, so a restore of one sequence on a prefix hit is a single launch with
+ * no host-to-device copy in front of it.  The arrays are read before the call returns.
+ */
+#define NVJ_HYBRID_HOST_SLOTS 24
+int nvj_hybrid_snapshot_host_slots(const void* conv_table, void* conv_pool, int64_t conv_row_bytes,
+                                   const void* rec_table, void* rec_pool, int64_t rec_row_bytes,
+                                   int64_t table_rows, int64_t pool_rows,
+                                   const int32_t* table_slots, const int32_t* pool_slots, int n,
+                                   int32_t* status, nvj_stream_t stream);
+int nvj_hybrid_restore_host_slots(void* conv_table, const void* conv_pool, int64_t conv_row_bytes,
+                                  void* rec_table, const void* rec_pool, int64_t rec_row_bytes,
+                                  int64_t table_rows, int64_t pool_rows,
+                                  const int32_t* table_slots, const int32_t* pool_slots, int n,
+                                  int32_t* status, nvj_stream_t stream);
+
 /* ---------------------------------------------------- resident decode metadata */
 
 /*

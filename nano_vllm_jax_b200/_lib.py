@@ -64,6 +64,10 @@ SIGNATURES = {
                                     c_int64, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
     "nvj_hybrid_restore": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int64,
                                    c_int64, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
+    "nvj_hybrid_snapshot_host_slots": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int64,
+                                               c_int64, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
+    "nvj_hybrid_restore_host_slots": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int64,
+                                              c_int64, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
     "nvj_advance_decode_metadata": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
     "nvj_p2p_gather_buffer_bytes": (c_size_t, [c_int, c_int]),
     "nvj_p2p_buffer_create": (c_int, [c_size_t, c_void_p, c_void_p]),

@@ -45,6 +45,19 @@ __device__ __forceinline__ void copy_span1(const char* src, char* dst, long long
     dst[c] = src[c];
 }
 
+// The (source, destination) row indices of a copy: two device arrays, or, for a handful of pairs that the host knows
+// (the usual case: one restore per prefix hit), the values themselves, carried in the kernel's parameters so that no
+// host-to-device copy has to run in front of the launch.
+constexpr int kInlinePairs = 24;
+struct SlotLists {
+  const int32_t* src;
+  const int32_t* dst;
+  int32_t inline_src[kInlinePairs];
+  int32_t inline_dst[kInlinePairs];
+  __device__ __forceinline__ long long source(int i) const { return src ? src[i] : inline_src[i]; }
+  __device__ __forceinline__ long long destination(int i) const { return dst ? dst[i] : inline_dst[i]; }
+};
+
 // One table of rows that are copied by index: dst_base[dst_idx[i]] <- src_base[src_idx[i]].
 struct RowTable {
   const char* src_base;
@@ -56,10 +69,10 @@ struct RowTable {
 
 // Both tables of a hybrid state (recurrent and conv) in one launch; grid.y = pair, grid.x = a.blocks + b.blocks.
 __global__ void __launch_bounds__(kCopyThreads)
-copy_rows_kernel(RowTable a, RowTable b, long long src_rows, const int32_t* src_idx, long long dst_rows,
-                 const int32_t* dst_idx, int32_t* status) {
+copy_rows_kernel(RowTable a, RowTable b, long long src_rows, long long dst_rows, const __grid_constant__ SlotLists slots,
+                 int32_t* status) {
   const int i = blockIdx.y;
-  const long long s = src_idx[i], d = dst_idx[i];
+  const long long s = slots.source(i), d = slots.destination(i);
   if (s < 0 || s >= src_rows || d < 0 || d >= dst_rows) {
     if (threadIdx.x == 0 && blockIdx.x == 0 && status) atomicOr(status, NVJ_DEV_BAD_BLOCK_ID);
     return;
@@ -99,8 +112,8 @@ template <int N>
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory"); }
 
 __global__ void __launch_bounds__(32)
-copy_rows_bulk_kernel(RowTable a, RowTable b, long long src_rows, const int32_t* src_idx, long long dst_rows,
-                      const int32_t* dst_idx, int n_pairs, int32_t* status) {
+copy_rows_bulk_kernel(RowTable a, RowTable b, long long src_rows, long long dst_rows, const __grid_constant__ SlotLists slots,
+                      int n_pairs, int32_t* status) {
   extern __shared__ unsigned char bulk_smem_raw[];
   BulkSmem& sm = *reinterpret_cast<BulkSmem*>((reinterpret_cast<uintptr_t>(bulk_smem_raw) + 127) & ~(uintptr_t)127);
   if (threadIdx.x != 0) return;  // one thread drives the copy engine; the warp exists only to own the shared memory
@@ -114,7 +127,7 @@ copy_rows_bulk_kernel(RowTable a, RowTable b, long long src_rows, const int32_t*
   auto locate = [&](long long c, const char*& src, char*& dst) -> uint32_t {
     const int pair = (int)(c / per_pair);
     long long r = c - (long long)pair * per_pair;
-    const long long si = src_idx[pair], di = dst_idx[pair];
+    const long long si = slots.source(pair), di = slots.destination(pair);
     if (si < 0 || si >= src_rows || di < 0 || di >= dst_rows) {
       if (status) atomicOr(status, NVJ_DEV_BAD_BLOCK_ID);
       return 0;
@@ -292,13 +305,21 @@ extern "C" int nvj_copy_blocks(void* k_cache, void* v_cache, int num_layers, int
 static int hybrid_copy(const void* conv_src, void* conv_dst, int64_t conv_row_bytes,
                        const void* rec_src, void* rec_dst, int64_t rec_row_bytes,
                        int64_t src_rows, int64_t dst_rows, const int32_t* src_slots,
-                       const int32_t* dst_slots, int n, int32_t* status, nvj_stream_t stream) {
+                       const int32_t* dst_slots, int n, bool slots_on_host, int32_t* status, nvj_stream_t stream) {
   using namespace nvj;
   if (n < 0 || conv_row_bytes < 0 || rec_row_bytes < 0 || src_rows < 0 || dst_rows < 0)
     return NVJ_ERR_INVALID_ARGUMENT;
   if (n == 0) return NVJ_OK;
   if (!src_slots || !dst_slots) return NVJ_ERR_INVALID_ARGUMENT;
   if (n > 65535) return NVJ_ERR_UNSUPPORTED;
+  SlotLists slots{};
+  if (slots_on_host) {
+    if (n > kInlinePairs) return NVJ_ERR_TOO_LARGE;
+    for (int i = 0; i < n; ++i) { slots.inline_src[i] = src_slots[i]; slots.inline_dst[i] = dst_slots[i]; }
+  } else {
+    slots.src = src_slots;
+    slots.dst = dst_slots;
+  }
   if ((conv_src == nullptr) != (conv_dst == nullptr) || (rec_src == nullptr) != (rec_dst == nullptr))
     return NVJ_ERR_INVALID_ARGUMENT;
   const RowTable rec = row_table(rec_src, rec_dst, rec_row_bytes, n);
@@ -312,12 +333,11 @@ static int hybrid_copy(const void* conv_src, void* conv_dst, int64_t conv_row_by
     const long long cap = (long long)(sms > 0 ? sms : 148) * 3;  // three CTAs of 64 KiB shared memory per SM
     const int ctas = (int)(chunks < cap ? chunks : cap);
     copy_rows_bulk_kernel<<<ctas, 32, sizeof(BulkSmem) + 128, static_cast<cudaStream_t>(stream)>>>(
-        rec, conv, src_rows, src_slots, dst_rows, dst_slots, n, status);
+        rec, conv, src_rows, dst_rows, slots, n, status);
     return cudaGetLastError() == cudaSuccess ? NVJ_OK : NVJ_ERR_LAUNCH;
   }
   dim3 grid(rec.blocks + conv.blocks, n, 1);
-  copy_rows_kernel<<<grid, kCopyThreads, 0, static_cast<cudaStream_t>(stream)>>>(rec, conv, src_rows, src_slots, dst_rows,
-                                                                                 dst_slots, status);
+  copy_rows_kernel<<<grid, kCopyThreads, 0, static_cast<cudaStream_t>(stream)>>>(rec, conv, src_rows, dst_rows, slots, status);
   return cudaGetLastError() == cudaSuccess ? NVJ_OK : NVJ_ERR_LAUNCH;
 }
 
@@ -327,7 +347,16 @@ extern "C" int nvj_hybrid_snapshot(const void* conv_table, void* conv_pool, int6
                                    const int32_t* table_slots, const int32_t* pool_slots, int n,
                                    int32_t* status, nvj_stream_t stream) {
   return hybrid_copy(conv_table, conv_pool, conv_row_bytes, rec_table, rec_pool, rec_row_bytes,
-                     table_rows, pool_rows, table_slots, pool_slots, n, status, stream);
+                     table_rows, pool_rows, table_slots, pool_slots, n, false, status, stream);
+}
+
+extern "C" int nvj_hybrid_snapshot_host_slots(const void* conv_table, void* conv_pool, int64_t conv_row_bytes,
+                                              const void* rec_table, void* rec_pool, int64_t rec_row_bytes,
+                                              int64_t table_rows, int64_t pool_rows,
+                                              const int32_t* table_slots, const int32_t* pool_slots, int n,
+                                              int32_t* status, nvj_stream_t stream) {
+  return hybrid_copy(conv_table, conv_pool, conv_row_bytes, rec_table, rec_pool, rec_row_bytes,
+                     table_rows, pool_rows, table_slots, pool_slots, n, true, status, stream);
 }
 
 extern "C" int nvj_hybrid_restore(void* conv_table, const void* conv_pool, int64_t conv_row_bytes,
@@ -336,7 +365,16 @@ extern "C" int nvj_hybrid_restore(void* conv_table, const void* conv_pool, int64
                                   const int32_t* table_slots, const int32_t* pool_slots, int n,
                                   int32_t* status, nvj_stream_t stream) {
   return hybrid_copy(conv_pool, conv_table, conv_row_bytes, rec_pool, rec_table, rec_row_bytes,
-                     pool_rows, table_rows, pool_slots, table_slots, n, status, stream);
+                     pool_rows, table_rows, pool_slots, table_slots, n, false, status, stream);
+}
+
+extern "C" int nvj_hybrid_restore_host_slots(void* conv_table, const void* conv_pool, int64_t conv_row_bytes,
+                                             void* rec_table, const void* rec_pool, int64_t rec_row_bytes,
+                                             int64_t table_rows, int64_t pool_rows,
+                                             const int32_t* table_slots, const int32_t* pool_slots, int n,
+                                             int32_t* status, nvj_stream_t stream) {
+  return hybrid_copy(conv_pool, conv_table, conv_row_bytes, rec_pool, rec_table, rec_row_bytes,
+                     pool_rows, table_rows, pool_slots, table_slots, n, true, status, stream);
 }
 
 extern "C" int nvj_advance_decode_metadata(int32_t* seq_lens, int32_t* positions, int batch,

@@ -18,8 +18,8 @@
 //
 // (2) the split form for a pipelined decode step, where the wait must not sit between two steps:
 //     nvj_p2p_argmax_publish   token pick of the step fused with the publish: every CTA takes a row's argmax and
-//                              stores the word into every peer's set.  One more CTA of the same launch can collect
-//                              the step before (below).  The publish waits for nobody.
+//                              stores the word into every peer's set.  The same CTAs can collect the step before
+//                              (below), one word per thread.  The publish waits for nobody.
 //     nvj_p2p_collect          waits (bounded) for the oldest published epoch that has not been collected yet and
 //                              copies its tokens out; does nothing when there is none.
 //     A step k + 1 runs  append + decode,  then one launch that collects step k and publishes step k + 1: step k's
@@ -47,8 +47,9 @@ constexpr int kP2pSets = 3;
 struct P2pHeader {
   unsigned long long published;  // last epoch this rank published (device-kept epochs)
   unsigned long long consumed;   // last epoch this rank collected
-  unsigned int arrivals;         // CTAs of the running publish kernel that are done
-  unsigned int pad[3];
+  unsigned int arrivals;         // CTAs of the running publish / collect kernel that are done
+  unsigned int failed;           // a wait of the running kernel ran out
+  unsigned int pad[2];
 };
 static_assert(sizeof(P2pHeader) % 16 == 0, "the data sets start 16-byte aligned");
 
@@ -72,31 +73,26 @@ __device__ __forceinline__ unsigned long long ld_word(const unsigned long long* 
   return v;
 }
 
-// All threads of a CTA: wait (bounded) until the world * n words of `set` carry `epoch`, writing each token to `out` as
-// it arrives.  Returns false in every thread (and flags the status word) when the limit ran out.
-__device__ __forceinline__ bool p2p_gather_words(const unsigned long long* set, unsigned long long epoch, int count,
-                                                 unsigned long long wait_ns, int32_t* out, int32_t* status, int* failed_sh) {
-  if (threadIdx.x == 0) *failed_sh = 0;
-  __syncthreads();
+// One thread waits (bounded) until `word` carries `epoch` and returns the token; `*ok` is cleared when the limit
+// ran out (or another thread of the CTA has given up already: `failed_sh`).  `first` is the value of a load issued
+// earlier, so that callers can put other work between the load and the check.
+__device__ __forceinline__ int32_t p2p_await_word(const unsigned long long* word, unsigned long long first, unsigned long long epoch,
+                                                  unsigned long long wait_ns, volatile int* failed_sh, bool* ok) {
   const unsigned long long want = epoch & 0xffffffffull;
-  const unsigned long long t0 = global_timer_ns();
-  for (int i = threadIdx.x; i < count; i += blockDim.x) {
+  unsigned long long w = first;
+  if ((w >> 32) != want) {
+    const unsigned long long t0 = global_timer_ns();
     for (uint32_t spins = 0;; ++spins) {
-      const unsigned long long w = ld_word(set + i);
-      if ((w >> 32) == want) {
-        out[i] = (int32_t)(uint32_t)w;
-        break;
-      }
-      if ((spins & 63u) == 63u && (*reinterpret_cast<volatile int*>(failed_sh) || global_timer_ns() - t0 > wait_ns)) {
+      w = ld_word(word);
+      if ((w >> 32) == want) break;
+      if ((spins & 63u) == 63u && (*failed_sh || global_timer_ns() - t0 > wait_ns)) {
         *failed_sh = 1;
-        break;
+        *ok = false;
+        return 0;
       }
     }
   }
-  __syncthreads();
-  const bool ok = *failed_sh == 0;
-  if (!ok && threadIdx.x == 0 && status) atomicOr(status, NVJ_DEV_TIMEOUT);
-  return ok;
+  return (int32_t)(uint32_t)w;
 }
 
 __global__ void __launch_bounds__(256) p2p_allgather_kernel(P2pPeers peers, const int32_t* local, int n, int rank, int world,
@@ -106,6 +102,7 @@ __global__ void __launch_bounds__(256) p2p_allgather_kernel(P2pPeers peers, cons
   __shared__ int failed;
   P2pHeader* own = p2p_header(peers.base[rank]);
   if (threadIdx.x == 0) {
+    failed = 0;
     if (epoch == 0) {  // epoch kept on the device: the same launch can then be replayed from a CUDA graph
       epoch = own->published + 1;
       own->published = epoch;
@@ -119,59 +116,117 @@ __global__ void __launch_bounds__(256) p2p_allgather_kernel(P2pPeers peers, cons
     const unsigned long long w = p2p_word(local[i], epoch);
     for (int r = 0; r < world; ++r) st_word(p2p_set(peers.base[r], epoch, world, n) + rank * n + i, w);
   }
-  p2p_gather_words(p2p_set(peers.base[rank], epoch, world, n), epoch, world * n, wait_ns, out, status, &failed);
+  // eight independent loads per thread in flight, then the checks: the words arrive together, so after the first
+  // wait the others cost no round trip each
+  const unsigned long long* set = p2p_set(peers.base[rank], epoch, world, n);
+  const int count = world * n;
+  bool ok = true;
+  for (int base = threadIdx.x; base < count; base += 8 * blockDim.x) {
+    unsigned long long w[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int i = base + u * blockDim.x;
+      w[u] = i < count ? ld_word(set + i) : 0ull;
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int i = base + u * blockDim.x;
+      if (i < count && ok) {
+        const int32_t token = p2p_await_word(set + i, w[u], epoch, wait_ns, &failed, &ok);
+        if (ok) out[i] = token;
+      }
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && failed && status) atomicOr(status, NVJ_DEV_TIMEOUT);
 }
 
-// Waits (bounded) for the oldest published epoch this rank has not collected and copies its tokens out.
-// Called by all threads of one CTA.  Returns without doing anything when there is no such epoch; on a timeout the
-// status word is flagged, nothing is consumed, and a later call tries the same epoch again.
-__device__ __forceinline__ void p2p_collect_cta(char* own_base, int n, int world, unsigned long long wait_ns, int32_t* out,
-                                                int32_t* status) {
-  __shared__ int failed;
-  P2pHeader* own = p2p_header(own_base);
-  const unsigned long long epoch = *reinterpret_cast<volatile unsigned long long*>(&own->consumed) + 1;
-  if (epoch > *reinterpret_cast<volatile unsigned long long*>(&own->published)) return;
-  if (!p2p_gather_words(p2p_set(own_base, epoch, world, n), epoch, world * n, wait_ns, out, status, &failed)) return;
-  if (threadIdx.x == 0) own->consumed = epoch;
-}
-
-// Token pick fused with the publish (and, optionally, with the collect of the step before).  CTA r < n takes the
-// argmax of row r (first maximum wins, as row_argmax_kernel), stores the token locally and sends its word to every
-// peer; CTA n, present when collect_out is given, collects the previous epoch.  The CTA that finishes last advances
-// this rank's epoch counter (a local store: nothing here waits for the links).
+// Token pick fused with the publish (and, optionally, with the collect of the step before).  CTA r takes the argmax
+// of row r (first maximum wins, as row_argmax_kernel), stores the token locally and sends its word to every peer
+// (thread t to peer t).  With collect_out the same threads first fetch row r's tokens of the oldest epoch that has
+// not been collected, one word per thread, loaded before the argmax and checked after it.  The CTA that finishes last
+// advances this rank's epoch counters (local stores: nothing here waits for the links unless a peer is a step late).
 __global__ void __launch_bounds__(kArgmaxThreads) p2p_argmax_publish_kernel(P2pPeers peers, const float* x, int row_len, int n, int rank,
                                                                             int world, int32_t* tokens, int32_t* collect_out,
                                                                             unsigned long long wait_ns, int32_t* status) {
   P2pHeader* own = p2p_header(peers.base[rank]);
-  // `published` is advanced by the last CTA only, after every CTA of the launch has read it
-  const unsigned long long epoch = *reinterpret_cast<volatile unsigned long long*>(&own->published) + 1;
-  __shared__ int token_sh, last_sh;
-  if ((int)blockIdx.x < n) {
-    const int token = row_argmax_cta(x + (long long)blockIdx.x * row_len, row_len);
-    if (threadIdx.x == 0) {
-      token_sh = token;
-      tokens[blockIdx.x] = token;
+  // the counters are advanced by the last CTA only, after every CTA of the launch has read them
+  const unsigned long long published = *reinterpret_cast<volatile unsigned long long*>(&own->published);
+  const unsigned long long consumed = *reinterpret_cast<volatile unsigned long long*>(&own->consumed);
+  const unsigned long long epoch = published + 1, wanted = consumed + 1;
+  const bool collecting = collect_out != nullptr && wanted <= published;
+  __shared__ int token_sh, failed_sh;
+  const int r = blockIdx.x;
+  const unsigned long long* word = nullptr;
+  unsigned long long first = 0;
+  if (threadIdx.x == 0) failed_sh = 0;
+  if (collecting && (int)threadIdx.x < world) {
+    word = p2p_set(peers.base[rank], wanted, world, n) + threadIdx.x * n + r;
+    first = ld_word(word);
+  }
+  const int token = row_argmax_cta(x + (long long)r * row_len, row_len);
+  if (threadIdx.x == 0) {
+    token_sh = token;
+    tokens[r] = token;
+  }
+  __syncthreads();
+  if ((int)threadIdx.x < world) {
+    st_word(p2p_set(peers.base[threadIdx.x], epoch, world, n) + rank * n + r, p2p_word(token_sh, epoch));
+    if (collecting) {
+      bool ok = true;
+      const int32_t got = p2p_await_word(word, first, wanted, wait_ns, &failed_sh, &ok);
+      if (ok) collect_out[threadIdx.x * n + r] = got;
     }
-    __syncthreads();
-    if ((int)threadIdx.x < world)
-      st_word(p2p_set(peers.base[threadIdx.x], epoch, world, n) + rank * n + blockIdx.x, p2p_word(token_sh, epoch));
-  } else {
-    p2p_collect_cta(peers.base[rank], n, world, wait_ns, collect_out, status);
   }
   __syncthreads();
   if (threadIdx.x == 0) {
+    if (failed_sh) {
+      atomicOr(&own->failed, 1u);
+      if (status) atomicOr(status, NVJ_DEV_TIMEOUT);
+    }
     __threadfence();
-    last_sh = (atomicAdd(&own->arrivals, 1u) == gridDim.x - 1u) ? 1 : 0;
-    if (last_sh) {
+    if (atomicAdd(&own->arrivals, 1u) == gridDim.x - 1u) {
+      __threadfence();
+      const unsigned int failed = *reinterpret_cast<volatile unsigned int*>(&own->failed);
       own->arrivals = 0;
+      own->failed = 0;
       own->published = epoch;
+      if (collecting && !failed) own->consumed = wanted;  // after a timeout the same epoch is collected again
     }
   }
 }
 
+// The collect alone: one word per thread; the CTA that finishes last advances `consumed` unless a wait ran out.
 __global__ void __launch_bounds__(kArgmaxThreads) p2p_collect_kernel(char* own_base, int n, int world, unsigned long long wait_ns,
                                                                      int32_t* out, int32_t* status) {
-  p2p_collect_cta(own_base, n, world, wait_ns, out, status);
+  P2pHeader* own = p2p_header(own_base);
+  const unsigned long long epoch = *reinterpret_cast<volatile unsigned long long*>(&own->consumed) + 1;
+  if (epoch > *reinterpret_cast<volatile unsigned long long*>(&own->published)) return;  // nothing to collect
+  __shared__ int failed_sh;
+  if (threadIdx.x == 0) failed_sh = 0;
+  __syncthreads();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < world * n) {
+    const unsigned long long* word = p2p_set(own_base, epoch, world, n) + i;
+    bool ok = true;
+    const int32_t got = p2p_await_word(word, ld_word(word), epoch, wait_ns, &failed_sh, &ok);
+    if (ok) out[i] = got;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (failed_sh) {
+      atomicOr(&own->failed, 1u);
+      if (status) atomicOr(status, NVJ_DEV_TIMEOUT);
+    }
+    __threadfence();
+    if (atomicAdd(&own->arrivals, 1u) == gridDim.x - 1u) {
+      __threadfence();
+      const unsigned int failed = *reinterpret_cast<volatile unsigned int*>(&own->failed);
+      own->arrivals = 0;
+      own->failed = 0;
+      if (!failed) own->consumed = epoch;
+    }
+  }
 }
 
 static std::atomic<unsigned long long> g_wait_limit_ns{kWaitLimitNs};
@@ -274,7 +329,7 @@ extern "C" int nvj_p2p_argmax_publish(const float* x, int rows, int row_len, int
   if (!p2p_args_ok(rank, world, peer_buffers, peers)) return NVJ_ERR_INVALID_ARGUMENT;
   if (rows == 0) return NVJ_OK;
   if (!x || !tokens) return NVJ_ERR_INVALID_ARGUMENT;
-  p2p_argmax_publish_kernel<<<rows + (collect_out ? 1 : 0), kArgmaxThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+  p2p_argmax_publish_kernel<<<rows, kArgmaxThreads, 0, static_cast<cudaStream_t>(stream)>>>(
       peers, x, row_len, rows, rank, world, tokens, collect_out, wait_limit_ns(), status);
   return cudaGetLastError() == cudaSuccess ? NVJ_OK : NVJ_ERR_LAUNCH;
 }
@@ -284,7 +339,8 @@ extern "C" int nvj_p2p_collect(void* own_buffer, int n, int world, int32_t* out,
   if (world <= 0 || world > kP2pMaxWorld || n < 0 || !own_buffer) return NVJ_ERR_INVALID_ARGUMENT;
   if (n == 0) return NVJ_OK;
   if (!out) return NVJ_ERR_INVALID_ARGUMENT;
-  p2p_collect_kernel<<<1, kArgmaxThreads, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<char*>(own_buffer), n, world,
-                                                                                 wait_limit_ns(), out, status);
+  const int ctas = (world * n + kArgmaxThreads - 1) / kArgmaxThreads;
+  p2p_collect_kernel<<<ctas, kArgmaxThreads, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<char*>(own_buffer), n, world,
+                                                                                    wait_limit_ns(), out, status);
   return cudaGetLastError() == cudaSuccess ? NVJ_OK : NVJ_ERR_LAUNCH;
 }

@@ -159,8 +159,11 @@ class PrefixStateCache:
         return row
 
     def _idx_pair(self, first: List[int], second: List[int]):
-        """Both index lists of one copy on the device, uploaded with a single host-to-device copy."""
+        """The two index lists of one copy: as they are when few enough to ride in the kernel's parameters, else on
+        the device, uploaded with a single host-to-device copy."""
         n = len(first)
+        if self.table.device.type == "cuda" and n <= _k.HYBRID_HOST_SLOTS:
+            return list(first), list(second)
         t = torch.tensor(list(first) + list(second), dtype=torch.int32)
         if self.table.device.type == "cuda":
             t = t.pin_memory().to(self.table.device, non_blocking=True)

@@ -719,8 +719,15 @@ def _row_bytes(t):
     return 0 if t is None else t[0].numel() * t.element_size()
 
 
+HYBRID_HOST_SLOTS = 24
+
+
 def hybrid_copy(conv_table, rec_table, conv_pool, rec_pool, table_slots, pool_slots, *, restore: bool):
-    """Snapshot (table -> pool) or restore (pool -> table) GDN state rows, in place."""
+    """Snapshot (table -> pool) or restore (pool -> table) GDN state rows, in place.
+
+    `table_slots` / `pool_slots`: int32 CUDA tensors, or plain Python sequences of at most `HYBRID_HOST_SLOTS`
+    ints, which ride in the kernel's parameters (no index upload in front of the launch).
+    """
     lib = _lib.load()
     for name, t in (("conv_table", conv_table), ("rec_table", rec_table), ("conv_pool", conv_pool), ("rec_pool", rec_pool)):
         if t is not None and not (t.is_cuda and t.is_contiguous()):
@@ -731,12 +738,22 @@ def hybrid_copy(conv_table, rec_table, conv_pool, rec_pool, table_slots, pool_sl
         return
     if _row_bytes(conv_table) != _row_bytes(conv_pool) or _row_bytes(rec_table) != _row_bytes(rec_pool):
         raise ValueError("table and pool rows must have the same size")
-    table_slots, pool_slots = _i32("table_slots", table_slots), _i32("pool_slots", pool_slots)
     st = _status_word(ref_t.device)
-    fn = lib.nvj_hybrid_restore if restore else lib.nvj_hybrid_snapshot
-    rc = fn(_ptr(conv_table), _ptr(conv_pool), _row_bytes(conv_table), _ptr(rec_table), _ptr(rec_pool),
-            _row_bytes(rec_table), ref_t.shape[0], ref_p.shape[0], _ptr(table_slots), _ptr(pool_slots),
-            table_slots.numel(), _ptr(st), _stream(ref_t.device))
+    if not isinstance(table_slots, torch.Tensor):
+        import ctypes
+        n = len(table_slots)
+        if n != len(pool_slots) or n > HYBRID_HOST_SLOTS:
+            raise ValueError(f"host slot lists must have equal length of at most {HYBRID_HOST_SLOTS}")
+        t_arr, p_arr = (ctypes.c_int32 * n)(*[int(x) for x in table_slots]), (ctypes.c_int32 * n)(*[int(x) for x in pool_slots])
+        fn = lib.nvj_hybrid_restore_host_slots if restore else lib.nvj_hybrid_snapshot_host_slots
+        rc = fn(_ptr(conv_table), _ptr(conv_pool), _row_bytes(conv_table), _ptr(rec_table), _ptr(rec_pool),
+                _row_bytes(rec_table), ref_t.shape[0], ref_p.shape[0], t_arr, p_arr, n, _ptr(st), _stream(ref_t.device))
+    else:
+        table_slots, pool_slots = _i32("table_slots", table_slots), _i32("pool_slots", pool_slots)
+        fn = lib.nvj_hybrid_restore if restore else lib.nvj_hybrid_snapshot
+        rc = fn(_ptr(conv_table), _ptr(conv_pool), _row_bytes(conv_table), _ptr(rec_table), _ptr(rec_pool),
+                _row_bytes(rec_table), ref_t.shape[0], ref_p.shape[0], _ptr(table_slots), _ptr(pool_slots),
+                table_slots.numel(), _ptr(st), _stream(ref_t.device))
     check(rc, "nvj_hybrid_restore" if restore else "nvj_hybrid_snapshot")
     if _strict():
         _check_word(st, "hybrid state copy")
