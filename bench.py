@@ -462,9 +462,10 @@ def run_b200(args, w):
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms.item()), step_ms, block_ms
 
-    # The same step replayed from a CUDA graph over device-resident metadata: advance (positions, seq_lens) -> fused
-    # append + decode -> token argmax, one graph launch per step.  With N > 1 the argmax publishes the tokens to every
-    # rank over NVLink and a second branch of the graph collects the step before while the attention runs.
+    # The same step replayed from a CUDA graph over device-resident metadata: fused append + decode (pre-append form:
+    # the row's token goes to position seq_lens[b]) -> token argmax that also advances the lengths, one graph launch
+    # of two kernels per step.  With N > 1 the argmax launch also publishes the tokens to every rank over NVLink and
+    # collects the step before.
     from nano_vllm_jax_b200.engine.resident_decode import DecodeStepGraph, ResidentDecodeMetadata
     meta = ResidentDecodeMetadata(rows, tables.shape[1], BS, device=dev)
     graph = DecodeStepGraph(meta, k_cache, v_cache, 0, SCALE, HQ // HKV, token_gather=token_gather)
@@ -487,7 +488,7 @@ def run_b200(args, w):
         sampler.start()
     ms_eager, _, _ = timed(device_step, blocks=reps)
     timed_events = kernel_events[W_steps:]  # the launches of the timed blocks (warm-up launches come first)
-    step_mode = "CUDA graph replay over device-resident metadata (advance -> append+decode -> argmax)"
+    step_mode = "CUDA graph replay over device-resident metadata (append+decode -> argmax+advance)"
     graph_ok = True
     try:
         ms_dev, dev_step_ms, dev_block_ms = timed(graph_step, blocks=reps)
@@ -600,9 +601,9 @@ def run_b200(args, w):
                             "from pinned host memory and its whole result back; compute stage "
                             + ("replayed from a CUDA graph per slot" if pipe_capture else "launched eagerly"),
                     "serial_value": total_rows / (ms_e2e_serial / K_steps * 1e-3), "serial_ms_per_step": ms_e2e_serial / K_steps},
-            # per step of the timed pass: metadata advance, fused append+decode, token argmax (N > 1: the same launch
-            # also collects and publishes)
-            "gpu_launches": 3 * K_steps,
+            # per step of the timed pass: fused append+decode, token argmax with the metadata advance (N > 1: the same
+            # launch also collects and publishes)
+            "gpu_launches": 2 * K_steps,
             "step_mode": step_mode,
             "eager_value": total_rows / (ms_eager / K_steps * 1e-3), "eager_ms_per_step": ms_eager / K_steps,
             "roofline": {"bound": "hbm", "kernel": "decode_wide_kernel at width 1 (fused append + paged GQA decode, TMA-staged, tensor-core tiles)",

@@ -204,6 +204,10 @@ int nvj_paged_decode(const void* q, int q_dtype,
  * head_dim] in the cache dtype.  Rows with seq_lens[b] <= 0 are inactive: no
  * write, zero output.  Cache contents equal nvj_kv_append followed by
  * nvj_paged_decode bit for bit.
+ * positions == NULL is the pre-append form for device-resident metadata: seq_lens[b] then is the row's length BEFORE
+ * this step's token, the new row goes to position seq_lens[b] and seq_lens[b] + 1 keys are attended; nothing is
+ * written to seq_lens (nvj_row_argmax_advance / nvj_p2p_argmax_publish advance it at the end of the step).  A row
+ * whose block table has no room left is flagged NVJ_DEV_BAD_LENGTH / NVJ_DEV_BAD_BLOCK_ID as in the other form.
  */
 int nvj_paged_decode_fused_append(const void* q, int q_dtype,
                                   const void* new_k, const void* new_v,
@@ -430,6 +434,9 @@ int nvj_advance_decode_metadata(int32_t* seq_lens, int32_t* positions, int batch
  *                                 waits for nobody.  rows must equal the n the buffers were sized for.  With
  *                                 `collect_out` (nullable) the same launch first collects the step before, as
  *                                 nvj_p2p_collect does: the usual form of a step, whose gathered tokens then lag by one.
+ *                                 With `seq_lens` (nullable; `positions` nullable) it also advances the rows' resident
+ *                                 decode metadata, as nvj_row_argmax_advance does, except that a row without room
+ *                                 is only left alone, not flagged (the pre-append decode pass has flagged it).
  *   nvj_p2p_collect               waits (up to the wait limit) for the oldest published epoch not collected yet and
  *                                 writes out[r * n + i]; returns at once when there is none.  After the last step one
  *                                 call fetches the last tokens.  On a timeout NVJ_DEV_TIMEOUT is flagged in *status,
@@ -445,7 +452,8 @@ int nvj_p2p_buffer_destroy(void* dev_ptr);
 int nvj_p2p_allgather_i32(const int32_t* local, int n, int rank, int world, void* const* peer_buffers,
                           uint32_t epoch, int32_t* out, int32_t* status, nvj_stream_t stream);
 int nvj_p2p_argmax_publish(const float* x, int rows, int row_len, int32_t* tokens, int rank, int world,
-                           void* const* peer_buffers, int32_t* collect_out, int32_t* status, nvj_stream_t stream);
+                           void* const* peer_buffers, int32_t* collect_out, int32_t* seq_lens, int32_t* positions,
+                           int table_width, int block_size, int32_t* status, nvj_stream_t stream);
 int nvj_p2p_collect(void* own_buffer, int n, int world, int32_t* out, int32_t* status, nvj_stream_t stream);
 
 /* ------------------------------------------------------------- bounded waits */
@@ -472,6 +480,15 @@ int nvj_selftest_bounded_wait(int32_t* status, int32_t* returned, nvj_stream_t s
  */
 int nvj_row_argmax(const float* x, int rows, int row_len, int32_t* tokens,
                    nvj_stream_t stream);
+
+/*
+ * The same token pick, and in the same launch the advance of the rows' resident decode metadata that
+ * nvj_advance_decode_metadata would make (positions nullable): the tail of a decode step whose attention ran in
+ * the pre-append form of nvj_paged_decode_fused_append, so that the step is two launches instead of three.
+ */
+int nvj_row_argmax_advance(const float* x, int rows, int row_len, int32_t* tokens, int32_t* seq_lens,
+                           int32_t* positions, int table_width, int block_size, int32_t* status,
+                           nvj_stream_t stream);
 
 #ifdef __cplusplus
 }

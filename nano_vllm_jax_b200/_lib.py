@@ -75,12 +75,14 @@ SIGNATURES = {
     "nvj_p2p_buffer_close": (c_int, [c_void_p]),
     "nvj_p2p_buffer_destroy": (c_int, [c_void_p]),
     "nvj_p2p_allgather_i32": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_uint32, c_void_p, c_void_p, c_void_p]),
-    "nvj_p2p_argmax_publish": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "nvj_p2p_argmax_publish": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                       c_int, c_int, c_void_p, c_void_p]),
     "nvj_p2p_collect": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "nvj_set_wait_limit_ns": (None, [c_uint64]),
     "nvj_get_wait_limit_ns": (c_uint64, []),
     "nvj_selftest_bounded_wait": (c_int, [c_void_p, c_void_p, c_void_p]),
     "nvj_row_argmax": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p]),
+    "nvj_row_argmax_advance": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),
 }
 
 _lock = threading.Lock()

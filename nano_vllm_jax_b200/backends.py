@@ -73,6 +73,7 @@ class B200Backend:
     def __init__(self, config=None, device: str | torch.device = "cuda"):
         self.config = config
         self.device = torch.device(device)
+        self._decode_qsl: dict = {}  # (rows, device) -> arange(rows + 1) of a decode batch
         for field in ("full_attention_kv_append_impl", "full_attention_decode_impl", "full_attention_prefill_impl"):
             if config is not None and getattr(config, field, None) not in (None, "", "reference", B200_IMPL):
                 normalize_full_attention_impl(getattr(config, field))
@@ -110,14 +111,22 @@ class B200Backend:
                 raise ValueError("positions and block_tables batch dimensions must match")
             if positions.shape[0] != seq_lens.shape[0]:
                 raise ValueError("positions and seq_lens batch dimensions must match")
-            slot_mapping = kvc.compute_slot_mapping(positions, block_tables, block_size, is_prefill)
+            if is_prefill:
+                slot_mapping = kvc.compute_slot_mapping(positions, block_tables, block_size, is_prefill)
+            else:  # decode: made when first read (the fused append + decode kernel never reads it)
+                slot_mapping = lambda: kvc.compute_slot_mapping(positions, block_tables, block_size, is_prefill)  # noqa: E731
         batch, query_len = positions.shape
         if query_start_loc is None:
             if is_prefill:
                 query_start_loc = torch.cat([torch.zeros(1, dtype=torch.int32, device=seq_lens.device),
                                              torch.cumsum(seq_lens.to(torch.int32), 0).to(torch.int32)])
-            else:  # one query token per row
-                query_start_loc = torch.arange(seq_lens.shape[0] + 1, dtype=torch.int32, device=seq_lens.device)
+            else:  # one query token per row: a constant per batch size, built once
+                key = (int(seq_lens.shape[0]), seq_lens.device)
+                query_start_loc = self._decode_qsl.get(key)
+                if query_start_loc is None:
+                    query_start_loc = torch.arange(key[0] + 1, dtype=torch.int32, device=seq_lens.device)
+                    if not (seq_lens.is_cuda and torch.cuda.is_current_stream_capturing()):
+                        self._decode_qsl[key] = query_start_loc
         return AttentionMetadata(
             slot_mapping=slot_mapping, block_tables=block_tables, seq_lens=seq_lens,
             query_start_loc=query_start_loc,

@@ -201,11 +201,16 @@ copy_blocks_kernel(char* k_cache, char* v_cache, long long num_blocks, long long
   else copy_span1(base + s * block_bytes, base + d * block_bytes, block_bytes, blockIdx.x, gridDim.x);
 }
 
-// One CTA per row.
+// One CTA per row.  With seq_lens the row's resident decode metadata is advanced in the same launch, as
+// advance_decode_metadata_kernel would (the tail of a decode step whose attention ran in pre-append form).
 __global__ void __launch_bounds__(kArgmaxThreads)
-row_argmax_kernel(const float* x, int row_len, int32_t* tokens) {
+row_argmax_kernel(const float* x, int row_len, int32_t* tokens, int32_t* seq_lens, int32_t* positions, long long capacity,
+                  int32_t* status) {
   const int token = row_argmax_cta(x + (long long)blockIdx.x * row_len, row_len);
-  if (threadIdx.x == 0) tokens[blockIdx.x] = token;
+  if (threadIdx.x == 0) {
+    tokens[blockIdx.x] = token;
+    if (seq_lens) advance_row(seq_lens, positions, blockIdx.x, capacity, status);
+  }
 }
 
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -257,14 +262,7 @@ __global__ void advance_decode_metadata_kernel(int32_t* seq_lens, int32_t* posit
                                                int32_t* status) {
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
   if (b >= batch) return;
-  const int len = seq_lens[b];
-  if (len <= 0) return;
-  if ((long long)len + 1 > capacity) {
-    if (status) atomicOr(status, NVJ_DEV_BAD_LENGTH);
-    return;
-  }
-  positions[b] = len;
-  seq_lens[b] = len + 1;
+  advance_row(seq_lens, positions, b, capacity, status);
 }
 
 }  // namespace nvj
@@ -395,6 +393,18 @@ extern "C" int nvj_row_argmax(const float* x, int rows, int row_len, int32_t* to
   if (rows < 0 || row_len <= 0) return NVJ_ERR_INVALID_ARGUMENT;
   if (rows == 0) return NVJ_OK;
   if (!x || !tokens) return NVJ_ERR_INVALID_ARGUMENT;
-  row_argmax_kernel<<<rows, kArgmaxThreads, 0, static_cast<cudaStream_t>(stream)>>>(x, row_len, tokens);
+  row_argmax_kernel<<<rows, kArgmaxThreads, 0, static_cast<cudaStream_t>(stream)>>>(x, row_len, tokens, nullptr, nullptr, 0, nullptr);
+  return cudaGetLastError() == cudaSuccess ? NVJ_OK : NVJ_ERR_LAUNCH;
+}
+
+extern "C" int nvj_row_argmax_advance(const float* x, int rows, int row_len, int32_t* tokens, int32_t* seq_lens,
+                                      int32_t* positions, int table_width, int block_size, int32_t* status,
+                                      nvj_stream_t stream) {
+  using namespace nvj;
+  if (rows < 0 || row_len <= 0 || table_width < 0 || block_size <= 0) return NVJ_ERR_INVALID_ARGUMENT;
+  if (rows == 0) return NVJ_OK;
+  if (!x || !tokens || !seq_lens) return NVJ_ERR_INVALID_ARGUMENT;
+  row_argmax_kernel<<<rows, kArgmaxThreads, 0, static_cast<cudaStream_t>(stream)>>>(x, row_len, tokens, seq_lens, positions,
+                                                                                   (long long)table_width * block_size, status);
   return cudaGetLastError() == cudaSuccess ? NVJ_OK : NVJ_ERR_LAUNCH;
 }

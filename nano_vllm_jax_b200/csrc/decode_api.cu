@@ -28,7 +28,8 @@ static int run_decode(DecodeParams& p, void* workspace, size_t workspace_bytes, 
   if (p.batch == 0) return NVJ_OK;
   if (!p.q || !p.k_cache || !p.v_cache || !p.block_tables || !p.seq_lens || !p.out)
     return NVJ_ERR_INVALID_ARGUMENT;
-  if (p.new_k && (!p.new_v || !p.positions)) return NVJ_ERR_INVALID_ARGUMENT;
+  if (p.new_k && !p.new_v) return NVJ_ERR_INVALID_ARGUMENT;
+  p.pre_append = (p.new_k && !p.positions) ? 1 : 0;
   const int num_ctas = decode_num_ctas();
   if (num_ctas <= 0) return NVJ_ERR_LAUNCH;
   const int rc = carve_workspace(p, workspace, workspace_bytes, num_ctas);
@@ -47,7 +48,7 @@ static int run_decode(DecodeParams& p, void* workspace, size_t workspace_bytes, 
   if (variant == 2 || (variant == 0 && fast_ok)) return launch_decode_pipelined(p, num_ctas, stream);
   if (p.new_k) {
     if (p.kv_indptr) return NVJ_ERR_UNSUPPORTED;
-    const int a = append_decode_rows(p.new_k, p.new_v, p.positions, p.seq_lens,
+    const int a = append_decode_rows(p.new_k, p.new_v, p.pre_append ? p.seq_lens : p.positions, p.seq_lens,
                                      const_cast<char*>(p.k_cache), const_cast<char*>(p.v_cache),
                                      p.kv_dtype, p.num_blocks, p.block_size,
                                      p.num_kv_heads * p.head_dim, p.block_tables, p.table_width,
@@ -114,7 +115,7 @@ extern "C" int nvj_paged_decode_fused_append(const void* q, int q_dtype, const v
                                              const int32_t* seq_lens, int batch, float scale,
                                              float* out, void* workspace, size_t workspace_bytes,
                                              int variant, nvj_stream_t stream) {
-  if (batch > 0 && (!new_k || !new_v || !positions)) return NVJ_ERR_INVALID_ARGUMENT;
+  if (batch > 0 && (!new_k || !new_v)) return NVJ_ERR_INVALID_ARGUMENT;
   nvj::DecodeParams p{};
   p.q = q;
   p.k_cache = static_cast<const char*>(k_cache_layer);

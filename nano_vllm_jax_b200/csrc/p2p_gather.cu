@@ -148,6 +148,7 @@ __global__ void __launch_bounds__(256) p2p_allgather_kernel(P2pPeers peers, cons
 // advances this rank's epoch counters (local stores: nothing here waits for the links unless a peer is a step late).
 __global__ void __launch_bounds__(kArgmaxThreads) p2p_argmax_publish_kernel(P2pPeers peers, const float* x, int row_len, int n, int rank,
                                                                             int world, int32_t* tokens, int32_t* collect_out,
+                                                                            int32_t* seq_lens, int32_t* positions, long long capacity,
                                                                             unsigned long long wait_ns, int32_t* status) {
   P2pHeader* own = p2p_header(peers.base[rank]);
   // the counters are advanced by the last CTA only, after every CTA of the launch has read them
@@ -168,6 +169,9 @@ __global__ void __launch_bounds__(kArgmaxThreads) p2p_argmax_publish_kernel(P2pP
   if (threadIdx.x == 0) {
     token_sh = token;
     tokens[r] = token;
+    // the step's resident metadata, for the next step; a row without room was flagged by the decode pass already
+    // (this launch's status word reports waits that ran out, nothing else)
+    if (seq_lens) advance_row(seq_lens, positions, r, capacity, nullptr);
   }
   __syncthreads();
   if ((int)threadIdx.x < world) {
@@ -322,15 +326,17 @@ extern "C" int nvj_p2p_allgather_i32(const int32_t* local, int n, int rank, int 
 }
 
 extern "C" int nvj_p2p_argmax_publish(const float* x, int rows, int row_len, int32_t* tokens, int rank, int world,
-                                      void* const* peer_buffers, int32_t* collect_out, int32_t* status, nvj_stream_t stream) {
+                                      void* const* peer_buffers, int32_t* collect_out, int32_t* seq_lens, int32_t* positions,
+                                      int table_width, int block_size, int32_t* status, nvj_stream_t stream) {
   using namespace nvj;
-  if (rows < 0 || row_len <= 0) return NVJ_ERR_INVALID_ARGUMENT;
+  if (rows < 0 || row_len <= 0 || (seq_lens && (table_width < 0 || block_size <= 0))) return NVJ_ERR_INVALID_ARGUMENT;
   P2pPeers peers{};
   if (!p2p_args_ok(rank, world, peer_buffers, peers)) return NVJ_ERR_INVALID_ARGUMENT;
   if (rows == 0) return NVJ_OK;
   if (!x || !tokens) return NVJ_ERR_INVALID_ARGUMENT;
   p2p_argmax_publish_kernel<<<rows, kArgmaxThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      peers, x, row_len, rows, rank, world, tokens, collect_out, wait_limit_ns(), status);
+      peers, x, row_len, rows, rank, world, tokens, collect_out, seq_lens, positions, (long long)table_width * block_size,
+      wait_limit_ns(), status);
   return cudaGetLastError() == cudaSuccess ? NVJ_OK : NVJ_ERR_LAUNCH;
 }
 

@@ -378,7 +378,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_pipelined_kernel(Dec
     // has landed: no fence is needed and nothing waits for the store.
     int patch_j = -1, patch_t = 0;
     if (p.new_k) {
-      const int pos = p.positions[s.b];
+      const int pos = p.pre_append ? p.seq_lens[s.b] : p.positions[s.b];
       const int jt = pos >> 4;
       const int jw = jt < s.nb - 1 ? jt : s.nb - 1;
       if (pos >= 0 && jw >= s.j0 && jw < s.j1 && (warp >> 1) == ((pos & 15) >> 2)) {

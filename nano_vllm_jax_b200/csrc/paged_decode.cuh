@@ -29,6 +29,9 @@ struct DecodeParams {
   const void* new_k;
   const void* new_v;
   const int32_t* positions;
+  // fused append without positions: seq_lens holds every row's length BEFORE this step's token; the new row goes to
+  // position seq_lens[b] and seq_lens[b] + 1 keys are attended (rows with seq_lens[b] <= 0 stay inactive)
+  int pre_append;
   // packed prefill through the generic kernel (nullable): query i belongs to the
   // table row r with query_start_loc[r] <= i < query_start_loc[r + 1] and attends
   // keys p <= query_positions[i]
@@ -68,6 +71,7 @@ struct DecodeParams {
 // Keys row b attends: seq_lens[b], clipped to what its page list can hold.
 __device__ __forceinline__ int decode_row_len(const DecodeParams& p, int b) {
   int len = p.seq_lens[b];
+  if (p.pre_append && len > 0) ++len;
   if (p.packed_rows) {
     const int i = p.query_start_loc[b];
     if (p.query_start_loc[b + 1] - i != 1) return 0;

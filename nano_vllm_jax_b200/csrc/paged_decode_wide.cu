@@ -405,7 +405,7 @@ decode_wide_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_const
     // and nothing waits for the store.
     int patch_j = -1, patch_t = 0;
     if (p.new_k) {
-      const int pos = p.positions[s.b];
+      const int pos = p.pre_append ? p.seq_lens[s.b] : p.positions[s.b];
       const int jt = pos >> 4;
       const int jw = jt < s.nb - 1 ? jt : s.nb - 1;
       if (pos >= 0 && jw >= s.j0 && jw < s.j1) {

@@ -8,6 +8,19 @@ namespace nvj {
 
 constexpr int kArgmaxThreads = 128;
 
+// One decode step of a row's resident metadata: an active row (length > 0) grows by the token it has just appended;
+// its position is the old length.  A row that would outgrow its block table is flagged and left alone.
+__device__ __forceinline__ void advance_row(int32_t* seq_lens, int32_t* positions, int b, long long capacity, int32_t* status) {
+  const int len = seq_lens[b];
+  if (len <= 0) return;
+  if ((long long)len + 1 > capacity) {
+    if (status) atomicOr(status, NVJ_DEV_BAD_LENGTH);
+    return;
+  }
+  if (positions) positions[b] = len;
+  seq_lens[b] = len + 1;
+}
+
 // Argmax of `row_len` floats by one CTA of kArgmaxThreads threads: the first maximum wins, NaNs are never
 // selected unless the whole row is NaN (then index 0).  The result is valid in thread 0.
 __device__ __forceinline__ int row_argmax_cta(const float* row, int row_len) {

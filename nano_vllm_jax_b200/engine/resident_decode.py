@@ -11,9 +11,12 @@ costs no host-to-device traffic for metadata.  Here the same arrays are torch CU
                            `set_block()` pushes a newly allocated block id from the host
                            (the only per-step host work, and only when a row crosses a block
                            boundary), `load()` (re)installs a batch.
-  DecodeStepGraph          captures  advance -> fused append + paged decode -> token pick
-                           once and replays it: one graph launch per step, the kernels run
-                           back to back, and nothing is allocated or copied per step.  On
+  DecodeStepGraph          captures  fused append + paged decode -> token pick + advance
+                           once and replays it: one graph launch per step, two kernels back to
+                           back, and nothing is allocated or copied per step.  The decode pass
+                           runs in its pre-append form (a row's token goes to position
+                           seq_lens[b], seq_lens[b] + 1 keys are attended) and the token pick
+                           advances the lengths for the next step in the same launch.  On
                            several GPUs the token pick also publishes the tokens to every
                            peer over NVLink and, in the same launch, collects the PREVIOUS
                            step's tokens, which have had a whole step to arrive: the wait for
@@ -126,7 +129,7 @@ class ResidentDecodeMetadata:
 
 
 class DecodeStepGraph:
-    """advance -> append + decode -> argmax of one layer, captured once, replayed per step."""
+    """append + decode -> argmax + metadata advance of one layer, captured once, replayed per step."""
 
     def __init__(self, meta: ResidentDecodeMetadata, k_cache: torch.Tensor, v_cache: torch.Tensor, layer_id: int,
                  scale: float, num_key_value_groups: int, query_dtype=torch.bfloat16, token_gather=None):
@@ -153,14 +156,16 @@ class DecodeStepGraph:
         self._tokens = torch.empty(meta.rows, dtype=torch.int32, device=dev)
 
     def _step(self):
-        self.meta.advance()
+        m = self.meta
         out, _, _ = _k.paged_decode_attention_with_kv_append(self.query, self.new_k, self.new_v, self.k_cache, self.v_cache,
-                                                             self.meta.block_tables, self.meta.seq_lens, self.meta.positions,
-                                                             self.layer_id, self.meta.block_size, self.scale, self.groups)
+                                                             m.block_tables, m.seq_lens, None, self.layer_id, m.block_size,
+                                                             self.scale, self.groups)
+        advance = (m.seq_lens, m.positions, m.table_width, m.block_size)
         if self.token_gather is None:
-            return out, _k.row_argmax(out.view(self.meta.rows, -1))
-        # one launch: collect the step before, pick this step's tokens, publish them
-        return out, self.token_gather.publish_argmax(out.view(self.meta.rows, -1), self._tokens, collect_out=self.gathered)
+            return out, _k.row_argmax(out.view(m.rows, -1), self._tokens, advance=advance)
+        # one launch: collect the step before, pick this step's tokens, publish them, advance the lengths
+        return out, self.token_gather.publish_argmax(out.view(m.rows, -1), self._tokens, collect_out=self.gathered,
+                                                     advance=advance)
 
     def flush(self) -> Optional[torch.Tensor]:
         """Collect the tokens of the last replayed step into `gathered` (several GPUs only)."""

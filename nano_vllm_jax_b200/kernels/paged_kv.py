@@ -475,7 +475,11 @@ def paged_decode_attention_gqa_nhd(q, k_cache, v_cache, kv_indptr, kv_indices, k
 def paged_decode_attention_with_kv_append(query, new_k, new_v, k_cache, v_cache, block_table, seq_lens,
                                           positions, layer_id, block_size, scale,
                                           num_key_value_groups, *, variant=0):
-    """Fused decode step on the 5-D caches: returns (out `[B, 1, Hq*D]` fp32, k_cache, v_cache)."""
+    """Fused decode step on the 5-D caches: returns (out `[B, 1, Hq*D]` fp32, k_cache, v_cache).
+
+    `positions=None` is the pre-append form for device-resident metadata: `seq_lens` then holds the rows' lengths
+    before this step's token (the token goes to position `seq_lens[b]`, `seq_lens[b] + 1` keys are attended) and is
+    not written; `row_argmax(..., advance=...)` or the token gather's publish advances it at the end of the step."""
     if query.ndim != 4 or query.shape[1] != 1 or new_k.shape[1] != 1 or new_v.shape[1] != 1:
         raise ValueError("fused decode attention supports only width-1 decode")
     if k_cache.ndim != 5 or v_cache.ndim != 5:
@@ -494,7 +498,7 @@ def paged_decode_attention_with_kv_append(query, new_k, new_v, k_cache, v_cache,
     q3 = query[:, 0]
     if q3.dtype not in (torch.float32, dt):
         q3 = q3.to(dt)
-    pos = _i32("positions", positions.reshape(batch).to(torch.int32))
+    pos = None if positions is None else _i32("positions", positions.reshape(batch).to(torch.int32))
     out = _decode_call(q3, k_cache[layer_id], v_cache[layer_id], block_table, block_table.shape[1],
                        None, None, seq_lens, scale, variant, nk, nv, pos)
     return out.reshape(batch, 1, hq * d), k_cache, v_cache
@@ -759,13 +763,40 @@ def hybrid_copy(conv_table, rec_table, conv_pool, rec_pool, table_slots, pool_sl
         _check_word(st, "hybrid state copy")
 
 
-def row_argmax(x: torch.Tensor) -> torch.Tensor:
-    """int32 argmax of each row of a float32 `[rows, n]` tensor (first maximum wins)."""
+def _advance_args(advance, rows):
+    """(seq_lens, positions or None, table_width, block_size) of a step's resident metadata, checked."""
+    seq_lens, positions, table_width, block_size = advance
+    seq_lens = _i32("seq_lens", seq_lens)
+    if seq_lens.shape != (rows,) or not seq_lens.is_contiguous():
+        raise ValueError("advance: seq_lens must be a contiguous int32 [rows] tensor")
+    if positions is not None:
+        positions = _i32("positions", positions)
+        if positions.numel() != rows or not positions.is_contiguous():
+            raise ValueError("advance: positions must be a contiguous int32 tensor of one entry per row")
+    return seq_lens, positions, int(table_width), int(block_size)
+
+
+def row_argmax(x: torch.Tensor, out: torch.Tensor | None = None, advance=None) -> torch.Tensor:
+    """int32 argmax of each row of a float32 `[rows, n]` tensor (first maximum wins).
+
+    `advance=(seq_lens, positions, table_width, block_size)` also advances the rows' resident decode metadata in the
+    same launch, as `advance_decode_metadata` would (positions may be None): the tail of a pre-append decode step."""
     lib = _lib.load()
     _cuda("x", x)
     if x.dtype != torch.float32 or x.ndim != 2:
         raise ValueError("row_argmax expects a float32 [rows, n] tensor")
     x = x.contiguous()
-    out = torch.empty(x.shape[0], dtype=torch.int32, device=x.device)
-    check(lib.nvj_row_argmax(_ptr(x), x.shape[0], x.shape[1], _ptr(out), _stream(x.device)), "nvj_row_argmax")
+    if out is None:
+        out = torch.empty(x.shape[0], dtype=torch.int32, device=x.device)
+    elif out.dtype != torch.int32 or out.shape != (x.shape[0],) or not out.is_contiguous() or out.device != x.device:
+        raise ValueError("row_argmax: out must be a contiguous int32 [rows] tensor on x's device")
+    if advance is None:
+        check(lib.nvj_row_argmax(_ptr(x), x.shape[0], x.shape[1], _ptr(out), _stream(x.device)), "nvj_row_argmax")
+        return out
+    seq_lens, positions, table_width, block_size = _advance_args(advance, x.shape[0])
+    st = _status_word(x.device)
+    check(lib.nvj_row_argmax_advance(_ptr(x), x.shape[0], x.shape[1], _ptr(out), _ptr(seq_lens), _ptr(positions),
+                                     table_width, block_size, _ptr(st), _stream(x.device)), "nvj_row_argmax_advance")
+    if _strict():
+        _check_word(st, "nvj_row_argmax_advance")
     return out

@@ -48,7 +48,12 @@ class KVCacheStorage:
 
 @dataclass
 class AttentionMetadata:
-    """Per-step paged/ragged attention metadata (kv_cache.py:51-64)."""
+    """Per-step paged/ragged attention metadata (kv_cache.py:51-64).
+
+    `slot_mapping` may be given as a zero-argument callable; it is then computed when first read.  A width-1 decode
+    step that goes through the fused append + attention kernel never reads it (the kernel resolves the slots from the
+    block table itself), so the step is spared a launch.
+    """
 
     slot_mapping: torch.Tensor
     block_tables: torch.Tensor
@@ -62,6 +67,21 @@ class AttentionMetadata:
     max_query_len: Optional[int] = None
     # not in the reference: the caller's own count of 1-token rows in a packed batch (None = not told)
     single_token_rows: Optional[int] = None
+
+
+def _read_slot_mapping(self):
+    value = self.__dict__.get("slot_mapping")
+    if value is not None and not isinstance(value, torch.Tensor) and callable(value):
+        value = value()
+        self.__dict__["slot_mapping"] = value
+    return value
+
+
+def _store_slot_mapping(self, value):
+    self.__dict__["slot_mapping"] = value
+
+
+AttentionMetadata.slot_mapping = property(_read_slot_mapping, _store_slot_mapping)
 
 
 @dataclass

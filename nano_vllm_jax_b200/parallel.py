@@ -155,11 +155,13 @@ class P2PTokenGather:
         return out
 
     def publish_argmax(self, x: torch.Tensor, tokens: Optional[torch.Tensor] = None,
-                       collect_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                       collect_out: Optional[torch.Tensor] = None, advance=None) -> torch.Tensor:
         """tokens[r] = argmax of row r of the float32 `[n, row_len]` tensor, and the same tokens stored into every peer's
         buffer and published as this rank's next epoch.  The publish waits for nobody.  With `collect_out` (`[world * n]`
         int32) the same launch first collects the step before into it, as `collect` would: one launch per step, and the
-        gathered tokens lag the step by one.  Returns the local tokens."""
+        gathered tokens lag the step by one.  `advance=(seq_lens, positions or None, table_width, block_size)` also
+        advances the rows' resident decode metadata in that launch (see `paged_kv.row_argmax`).  Returns the local
+        tokens."""
         if x.dtype != torch.float32 or x.ndim != 2 or x.shape[0] != self.n or not x.is_cuda or not x.is_contiguous():
             raise ValueError("x must be a contiguous CUDA float32 tensor [n, row_len]")
         if tokens is None:
@@ -167,8 +169,15 @@ class P2PTokenGather:
         if collect_out is not None and (collect_out.dtype != torch.int32 or collect_out.numel() != self.world * self.n
                                         or not collect_out.is_cuda or not collect_out.is_contiguous()):
             raise ValueError("collect_out must be a contiguous CUDA int32 tensor of world * n elements")
+        seq_lens = positions = None
+        table_width, block_size = 0, 1
+        if advance is not None:
+            from .kernels.paged_kv import _advance_args
+            seq_lens, positions, table_width, block_size = _advance_args(advance, self.n)
         rc = self._lib.nvj_p2p_argmax_publish(x.data_ptr(), self.n, int(x.shape[1]), tokens.data_ptr(), self.rank, self.world,
                                               self._ptr_array, None if collect_out is None else collect_out.data_ptr(),
+                                              None if seq_lens is None else seq_lens.data_ptr(),
+                                              None if positions is None else positions.data_ptr(), table_width, block_size,
                                               self._status.data_ptr(), torch.cuda.current_stream(self.device).cuda_stream)
         self._check(rc, "nvj_p2p_argmax_publish")
         return tokens

@@ -85,3 +85,59 @@ def test_graph_replayed_steps_equal_eager_steps():
         assert not to_numpy(got[s][0])[~active].any()
     np.testing.assert_array_equal(bits(to_numpy(k_g)), bits(ok))
     np.testing.assert_array_equal(bits(to_numpy(v_g)), bits(ov))
+
+
+@pytest.mark.parametrize("variant,dtype", [(3, "bf16"), (2, "bf16"), (1, "bf16"), (1, "f32")])
+def test_pre_append_form_equals_the_form_with_positions(variant, dtype):
+    """positions=None: the token goes to position seq_lens[b] and seq_lens[b] + 1 keys are attended, bit for bit what
+    the call with (positions = old length, seq_lens = old length + 1) does; inactive rows stay inactive."""
+    from nano_vllm_jax_b200.kernels import paged_kv as K
+    rows = 24
+    c = decode_case(77, 2048, rows, 40, 600, empty_rows=(5,))
+    td = torch.float32 if dtype == "f32" else torch.bfloat16
+    after = c["seq_lens"].astype(np.int32)
+    before = np.where(after > 0, after - 1, 0).astype(np.int32)
+    rng = np.random.default_rng(3)
+    q = to_torch(rng.standard_normal((rows, 1, 8, 256), dtype=np.float32)).to(td)
+    nk = to_torch(rng.standard_normal((rows, 1, 2, 256), dtype=np.float32)).to(td)
+    nv = to_torch(rng.standard_normal((rows, 1, 2, 256), dtype=np.float32)).to(td)
+    tables = to_torch(c["tables"])
+    k_a, v_a = to_torch(c["k_cache"]).to(td), to_torch(c["v_cache"]).to(td)
+    k_b, v_b = k_a.clone(), v_a.clone()
+    ref, _, _ = K.paged_decode_attention_with_kv_append(q, nk, nv, k_a, v_a, tables, torch.from_numpy(after).cuda(),
+                                                        torch.from_numpy(before).cuda().view(rows, 1), 0, BS, SCALE, 4,
+                                                        variant=variant)
+    got, _, _ = K.paged_decode_attention_with_kv_append(q, nk, nv, k_b, v_b, tables, torch.from_numpy(before).cuda(),
+                                                        None, 0, BS, SCALE, 4, variant=variant)
+    torch.cuda.synchronize()
+    assert torch.equal(got, ref)
+    assert torch.equal(k_a.view(torch.uint8), k_b.view(torch.uint8)) and torch.equal(v_a.view(torch.uint8), v_b.view(torch.uint8))
+    assert not got[5].any()
+
+
+def test_pre_append_form_flags_a_row_without_room():
+    from nano_vllm_jax_b200.kernels import paged_kv as K
+    k = torch.zeros((1, 8, BS, 2, 256), dtype=torch.bfloat16, device="cuda")
+    v = torch.zeros_like(k)
+    q = torch.ones((2, 1, 8, 256), dtype=torch.bfloat16, device="cuda")
+    n = torch.ones((2, 1, 2, 256), dtype=torch.bfloat16, device="cuda")
+    tables = torch.tensor([[1, 2], [3, 4]], dtype=torch.int32, device="cuda")
+    lens = torch.tensor([2 * BS, 5], dtype=torch.int32, device="cuda")  # row 0 is full: no place for a 33rd token
+    with pytest.raises(K.DeviceStatusError):
+        K.paged_decode_attention_with_kv_append(q, n, n, k, v, tables, lens, None, 0, BS, SCALE, 4)
+    assert not k[0, 1:3].any() and k[0, 3, 5].any()  # the full row wrote nothing, the other row appended at 5
+
+
+def test_token_pick_with_advance_is_pick_plus_advance():
+    from nano_vllm_jax_b200.engine.resident_decode import ResidentDecodeMetadata
+    from nano_vllm_jax_b200.kernels import paged_kv as K
+    x = torch.randn((6, 2048), device="cuda")
+    meta = ResidentDecodeMetadata(rows=6, table_width=2, block_size=16)
+    meta.load(np.zeros((5, 2), np.int32), np.array([0, 1, 15, 16, 31], np.int32))
+    tok = K.row_argmax(x, advance=(meta.seq_lens, meta.positions, 2, 16))
+    assert torch.equal(tok, x.argmax(dim=1).to(torch.int32))
+    assert meta.seq_lens.tolist() == [0, 2, 16, 17, 32, 0]
+    assert meta.positions.view(-1).tolist() == [0, 1, 15, 16, 31, 0]
+    with pytest.raises(K.DeviceStatusError):  # row 4 is full now
+        K.row_argmax(x, advance=(meta.seq_lens, None, 2, 16))
+    assert meta.seq_lens.tolist() == [0, 3, 17, 18, 32, 0]
