@@ -125,12 +125,12 @@ def test_a_peer_that_never_publishes_runs_the_wait_out_and_the_gather_recovers()
         x1 = torch.zeros((n, 8), device="cuda"); x1[:, 5] = 1.0
         t = torch.empty(n, dtype=torch.int32, device="cuda")
         got = torch.full((2 * n,), -1, dtype=torch.int32, device="cuda")
-        _lib.check(lib.nvj_p2p_argmax_publish(x0.data_ptr(), n, 8, t.data_ptr(), 0, 2, ptrs2, None, status.data_ptr(), stream), "publish 0")
+        _lib.check(lib.nvj_p2p_argmax_publish(x0.data_ptr(), n, 8, t.data_ptr(), 0, 2, ptrs2, None, None, None, 0, 1, status.data_ptr(), stream), "publish 0")
         _lib.check(lib.nvj_p2p_collect(bufs2[0], n, 2, got.data_ptr(), status.data_ptr(), stream), "collect 0")
         torch.cuda.synchronize()
         assert int(status.item()) == _lib.NVJ_DEV_TIMEOUT and int(got[n:].max()) == -1
         status.zero_()
-        _lib.check(lib.nvj_p2p_argmax_publish(x1.data_ptr(), n, 8, t.data_ptr(), 1, 2, ptrs2, None, status.data_ptr(), stream), "publish 1")
+        _lib.check(lib.nvj_p2p_argmax_publish(x1.data_ptr(), n, 8, t.data_ptr(), 1, 2, ptrs2, None, None, None, 0, 1, status.data_ptr(), stream), "publish 1")
         _lib.check(lib.nvj_p2p_collect(bufs2[0], n, 2, got.data_ptr(), status.data_ptr(), stream), "collect 0 again")
         torch.cuda.synchronize()
         assert int(status.item()) == 0
