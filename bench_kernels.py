@@ -393,15 +393,72 @@ def hybrid_cases(dev, iters):
     K.check_device_status(dev)
 
 
+def _use_phase_timing_library():
+    """Build the library once more with -DNVJ_PHASE_TIMING (under the package's build/ folder, beside the normal one)
+    and make it the one this process loads: the streaming decode kernel then stamps the global timer at its phase
+    boundaries and `nvj_debug_phase_ns` copies the stamps out."""
+    from pathlib import Path
+
+    from nano_vllm_jax_b200 import build as B
+    B.NVCC_FLAGS = B.NVCC_FLAGS + ["-DNVJ_PHASE_TIMING"]
+    B.OBJ_DIR = B.PKG_DIR / "build" / "phase"
+    B.OBJ_DIR.mkdir(parents=True, exist_ok=True)
+    B.LIB_PATH = Path(B.OBJ_DIR) / "libnvj_b200_phase.so"
+    B.build()
+
+
+def decode_phase_cases(dev, iters):
+    """Where the time of a SHORT decode batch goes: per case, the kernel's phase boundaries relative to the first
+    CTA's entry (min / median / max over the CTAs of the last launch), next to the CUDA-event time of the call."""
+    import ctypes
+
+    from nano_vllm_jax_b200 import _lib
+    lib = _lib.load()
+    lib.nvj_debug_phase_ns.argtypes = [ctypes.c_void_p]
+    lib.nvj_debug_phase_ns.restype = ctypes.c_int
+    pool = 40_000
+    k = _randn_bf16((1, pool, BS, HKV, D), 1, dev)
+    v = _randn_bf16((1, pool, BS, HKV, D), 2, dev)
+    timer = Timer(dev, iters)
+    names = ["entry", "lengths scanned", "start located, barriers up", "block ids staged, first copies issued",
+             "first block landed", "last block done", "segment finished (folds included)", "partial counted in"]
+    for rows, ctx in ((1, 32768), (16, 4096), (32, 1500), (8, 1040)):
+        nb = -(-ctx // BS)
+        tables = torch.randperm(pool, device=dev)[: rows * nb].to(torch.int32).view(rows, nb).contiguous()
+        lens = torch.full((rows,), ctx, dtype=torch.int32, device=dev)
+        q = _randn_bf16((rows, HQ, D), 3, dev)
+        us = timer.run(lambda: K.paged_decode_attention(q, k[0], v[0], tables, lens, SCALE, variant=3))
+        host = np.zeros((256, 8), np.uint64)
+        if lib.nvj_debug_phase_ns(host.ctypes.data) != 0:
+            raise RuntimeError("nvj_debug_phase_ns failed")
+        t0 = host[:, 0].astype(np.int64)
+        live = t0 >= t0.max() - 200_000  # CTAs of the last launch
+        rel = (host[live].astype(np.int64) - t0[live].min()) / 1e3
+        phases = {}
+        for i, name in enumerate(names):
+            col = rel[:, i]
+            col = col[col >= 0]  # a CTA that left early keeps an older launch's stamp
+            if len(col):
+                phases[name] = {"min": round(float(col.min()), 2), "median": round(float(np.median(col)), 2),
+                                "max": round(float(col.max()), 2), "ctas": int(len(col))}
+        report("paged_decode, %d rows x %d tokens: phases in us after the first CTA's entry" % (rows, ctx), us,
+               rows * ctx * TOKEN_BYTES, {"workload": "short batch", "ctas": int(live.sum()), "phases": phases})
+    K.check_device_status(dev)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--iters", type=int, default=20)
-    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "hybrid", "mixed", "front", "comparator"])
+    ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "hybrid", "mixed", "front", "comparator", "phases"])
     ap.add_argument("--small", action="store_true",
                     help="prefill cases on a 1-layer, 4096-block cache (128 MiB): the size to run under a profiler")
     args = ap.parse_args()
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
+    if args.only == "phases":  # its own library build: not part of "all"
+        _use_phase_timing_library()
+        decode_phase_cases(dev, args.iters)
+        return
     if args.only in ("all", "decode"):
         decode_cases(dev, args.iters)
     if args.only in ("all", "prefill"):

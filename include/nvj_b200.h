@@ -241,7 +241,7 @@ int nvj_paged_decode_fused_append(const void* q, int q_dtype,
  *                serialised by the caller.
  */
 #define NVJ_STATIC_SCRATCH_MAX_BATCH 4096
-#define NVJ_STATIC_SCRATCH_BYTES 5630976
+#define NVJ_STATIC_SCRATCH_BYTES 5713664
 int nvj_paged_decode_static_scratch(const void* q, int q_dtype,
                                     const void* k_cache_layer, const void* v_cache_layer,
                                     int kv_dtype, int64_t num_blocks, int block_size,

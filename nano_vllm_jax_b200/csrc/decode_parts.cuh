@@ -138,13 +138,25 @@ __device__ __forceinline__ int partial_slot(int cta, bool begins_row) { return 2
 // round trips.  A slot holds slot_rows rows of (kD accumulators, (max, sum)); the fold covers the kHq rows
 // from row_off on, so a kernel with several query tokens per row folds each token's heads in turn.
 // dst: kFinal, first of the kHq output rows; otherwise the destination slot.  All 256 threads call it;
-// `red` is shared-memory scratch of 384 floats.
-template <bool kFinal>
+// `red` is shared-memory scratch of 384 floats.  kBatch parts' accumulators are in flight at a time (4 * kBatch
+// registers): 8 in the kernel that runs two CTAs per SM, 16 where a thread has 255 registers.
+template <bool kFinal, int kBatch = 8>
 __device__ __forceinline__ void fold_parts(const DecodeParams& p, float* red, int tid, long long base, int first,
                                            int row_first, int n, long long dst, int slot_rows = kHq, int row_off = 0) {
   float* m_sh = red + 64;         // [8 heads]
   float* w_sh = red + 128;        // [32 parts][8 heads]
   const int warp = tid >> 5, lane = tid & 31;
+  // the first batch of accumulators is requested before the (max, sum) round trip, not after it
+  float4 x[kBatch][2];
+#pragma unroll
+  for (int k = 0; k < kBatch; ++k) {
+    const bool ok = k < n;
+    const int c = first + (ok ? k : 0);
+    const long long sl = base + 2 * c + (c == row_first ? 1 : 0);
+    const float4* src = reinterpret_cast<const float4*>(p.part_acc + (sl * slot_rows + row_off + warp) * kD + lane * 8);
+    x[k][0] = ok ? __ldcg(src) : make_float4(0.f, 0.f, 0.f, 0.f);
+    x[k][1] = ok ? __ldcg(src + 1) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
   {
     const int i = tid >> 3, h = tid & 7;
     const bool ok = i < n;
@@ -177,10 +189,10 @@ __device__ __forceinline__ void fold_parts(const DecodeParams& p, float* red, in
 #pragma unroll
   for (int k = 0; k < 8; ++k) acc[k] = 0.f;
 #pragma unroll 1
-  for (int i0 = 0; i0 < n; i0 += 8) {
-    float4 x[8][2];
+  for (int i0 = 0; i0 < n; i0 += kBatch) {
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
+    for (int k = 0; k < kBatch; ++k) {
+      if (i0 == 0) break;  // loaded above
       const bool ok = i0 + k < n;
       const int c = first + (ok ? i0 + k : 0);
       const long long sl = base + 2 * c + (c == row_first ? 1 : 0);
@@ -189,7 +201,7 @@ __device__ __forceinline__ void fold_parts(const DecodeParams& p, float* red, in
       x[k][1] = ok ? __ldcg(src + 1) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
+    for (int k = 0; k < kBatch; ++k) {
       const float wgt = i0 + k < n ? w_sh[(i0 + k) * 8 + h] : 0.f;
       acc[0] = fmaf(x[k][0].x, wgt, acc[0]); acc[1] = fmaf(x[k][0].y, wgt, acc[1]);
       acc[2] = fmaf(x[k][0].z, wgt, acc[2]); acc[3] = fmaf(x[k][0].w, wgt, acc[3]);

@@ -109,7 +109,9 @@ __host__ __device__ inline size_t ws_round(size_t x) { return (x + kWsAlign - 1)
 // one group of kMergeGroup consecutive CTA ids fold their partials into one group partial, and
 // the group that finishes last folds the group partials.  kGroupCounters arrival counters
 // (two per group) follow the per-row counters; a launch never has more CTAs than they cover.
-constexpr int kMergeGroup = 16;
+// 13: the tensor-core kernel keeps 13 parts' accumulators in flight while it folds (what its registers hold without
+// spilling), so on 148 SMs both levels (13 parts, then 12 groups) are one batch of loads each.
+constexpr int kMergeGroup = 13;
 constexpr int kTreeMergeMin = 32;
 constexpr int kGroupCounters = 64;
 __host__ __device__ inline int ws_groups(int num_ctas) { return (num_ctas + kMergeGroup - 1) / kMergeGroup; }

@@ -43,6 +43,15 @@
 
 namespace nvj {
 
+// Development aid, compiled in only with -DNVJ_PHASE_TIMING: thread 0 of every CTA stamps the global timer at the
+// kernel's phase boundaries, and nvj_debug_phase_ns copies the stamps out.
+#ifdef NVJ_PHASE_TIMING
+__device__ unsigned long long g_phase_ns[256][8];
+#define NVJ_PHASE(i) do { if (threadIdx.x == 0) g_phase_ns[blockIdx.x][i] = global_timer_ns(); } while (0)
+#else
+#define NVJ_PHASE(i) do { } while (0)
+#endif
+
 // An even number, so that a stage always holds blocks of the same parity and is read by the same four warps: a
 // parity wait can only tell two consecutive phases of an mbarrier apart, and a warp that waited for every other
 // phase of a stage's barrier could take an unfinished phase for the one after it, release the stage early and
@@ -276,18 +285,19 @@ __device__ __forceinline__ void w_finish_segment(const DecodeParams& p, WideSmem
   named_bar_sync(1, kDecodeThreads);
   if (tid == 0) sm.is_last = (atomicAdd(counter, 1) == last - first) ? 1 : 0;
   named_bar_sync(1, kDecodeThreads);
+  NVJ_PHASE(7);
   if (!sm.is_last) return;
   __threadfence();
   if (!tree) {
     for (int tok = 0; tok < p.width; ++tok) {
-      fold_parts<true>(p, sm.red, tid, 0, c_lo, c_lo, c_hi - c_lo + 1, (qbase + tok) * kHq, slot_rows, tok * kHq);
+      fold_parts<true, 13>(p, sm.red, tid, 0, c_lo, c_lo, c_hi - c_lo + 1, (qbase + tok) * kHq, slot_rows, tok * kHq);
       named_bar_sync(1, kDecodeThreads);
     }
     if (tid == 0) *counter = 0;
     return;
   }
   for (int tok = 0; tok < p.width; ++tok) {
-    fold_parts<false>(p, sm.red, tid, 0, first, c_lo, last - first + 1, 2LL * grid + 2 * cg + (cg == g_lo ? 1 : 0), slot_rows,
+    fold_parts<false, 13>(p, sm.red, tid, 0, first, c_lo, last - first + 1, 2LL * grid + 2 * cg + (cg == g_lo ? 1 : 0), slot_rows,
                       tok * kHq);
     named_bar_sync(1, kDecodeThreads);
   }
@@ -299,7 +309,7 @@ __device__ __forceinline__ void w_finish_segment(const DecodeParams& p, WideSmem
   if (!sm.is_last) return;
   __threadfence();
   for (int tok = 0; tok < p.width; ++tok) {
-    fold_parts<true>(p, sm.red, tid, 2LL * grid, g_lo, g_lo, g_hi - g_lo + 1, (qbase + tok) * kHq, slot_rows,
+    fold_parts<true, 13>(p, sm.red, tid, 2LL * grid, g_lo, g_lo, g_hi - g_lo + 1, (qbase + tok) * kHq, slot_rows,
                      tok * kHq);
     named_bar_sync(1, kDecodeThreads);
   }
@@ -314,12 +324,27 @@ decode_wide_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_const
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int grid = gridDim.x;
 
+  NVJ_PHASE(0);
+  // The kernel opens with three dependent trips to memory (lengths -> block ids -> K/V blocks).  While the first is
+  // under way, pull what the others will need towards the SM: the tensor maps, and this CTA's share of the block
+  // tables into the L2 (all CTAs together cover the tables, so the second trip ends in the L2 for everyone).
+  if (threadIdx.x == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&k_map)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&v_map)) : "memory");
+  }
+  if (!p.kv_indptr) {
+    const long long lines = ((long long)p.batch * p.table_width * (long long)sizeof(int32_t) + 127) / 128;
+    const long long line = (long long)blockIdx.x * kDecodeThreads + threadIdx.x;
+    if (line < lines) asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(p.block_tables) + line * 128));
+  }
+  if (threadIdx.x == 0) { sm.start_b = p.batch; sm.start_j = 0; sm.abort_flag = 0; sm.is_last = 0; }  // the scan below has the barrier
   // ---- pass 1: total number of blocks; zero the output of inactive rows
-  int mine = 0;
+  int mine = 0, first_n = 0;
   for (int base = 0; base < p.batch; base += kDecodeThreads) {
     const int b = base + threadIdx.x;
     int len = 0;
     if (b < p.batch) len = decode_row_len(p, b);
+    if (base == 0) first_n = (len + kBlk - 1) / kBlk;
     mine += (len + kBlk - 1) / kBlk;
     const unsigned idle = __ballot_sync(kFullMask, !p.packed_rows && b < p.batch && len <= 0 && (b % grid) == (int)blockIdx.x);
     for (unsigned m = idle; m; m &= m - 1) {
@@ -329,7 +354,7 @@ decode_wide_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_const
     }
   }
   int total = 0;
-  cta_inclusive_scan(mine, sm.scan, total);
+  const int incl = cta_inclusive_scan(mine, sm.scan, total);
   if (total == 0) return;
   const Partition pt = make_partition(total, grid);
   if ((int)blockIdx.x >= pt.n) return;
@@ -337,10 +362,15 @@ decode_wide_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_const
   const long long g1 = pt.start(blockIdx.x + 1);
   if (g0 == g1) return;
   const int n_iters = (int)(g1 - g0);
+  NVJ_PHASE(1);
 
   // ---- pass 2: locate (row, block) of g0
-  if (threadIdx.x == 0) { sm.start_b = p.batch; sm.start_j = 0; sm.abort_flag = 0; sm.is_last = 0; }
   long long carry = 0;
+  if (p.batch <= kDecodeThreads) {  // one row per thread: the scan of pass 1 has the answer already
+    const long long excl = incl - first_n;
+    if (first_n > 0 && excl <= g0 && g0 < excl + first_n) { sm.start_b = threadIdx.x; sm.start_j = (int)(g0 - excl); }
+    carry = g0 + 1;  // skips the loop below
+  }
   for (int base = 0; base < p.batch && carry <= g0; base += kDecodeThreads) {
     const int b = base + threadIdx.x;
     int n = 0;
@@ -358,6 +388,7 @@ decode_wide_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_const
     mbar_fence_init();
   }
   __syncthreads();
+  NVJ_PHASE(2);
 
   FillState fs;
   fs.b = sm.start_b; fs.jn = sm.start_j; fs.g = g0; fs.j = 0; fs.nsegs = 0; fs.has = false;
@@ -366,6 +397,7 @@ decode_wide_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_const
   if (threadIdx.x == 0) {
     for (int n = 0; n < kWStages && n < n_iters; ++n) w_issue_block(p, sm, &k_map, &v_map, n, false);
   }
+  NVJ_PHASE(3);
 
   int b = sm.start_b, j = sm.start_j;
   long long g = g0;
@@ -436,6 +468,7 @@ decode_wide_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_const
       const int stage = it % kWStages;
       mbar_wait(smem_u32(&sm.full_bar[stage]), (uint32_t)(it / kWStages) & 1u, &sm.abort_flag, p.status);
       const int rows = sm.ring_rows[it & (kRing - 1)];
+      if (it == 0) NVJ_PHASE(4);
       if (jb == patch_j) {  // lane l carries 16-byte piece l of the KV head's 512-byte row; the source is cache-hot
         const long long src = (long long)s.b * kTokenBytes + kvh * kRowBytes + lane * 16;
         const uint32_t off = kvh * 8192 + (lane >> 3) * 2048 + patch_t * 128 + (((lane & 7) ^ (patch_t & 7)) << 4);
@@ -455,7 +488,9 @@ decode_wide_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_const
       }
       __syncwarp();
     }
+    NVJ_PHASE(5);
     w_finish_segment<kDual>(p, sm, s, st, warp, lane, pt);
+    NVJ_PHASE(6);
   }
   // Only after a timeout can copies still be in flight with nobody waiting for them: hold the
   // CTA's shared memory until they have landed.
@@ -570,6 +605,12 @@ int launch_decode_wide(const DecodeParams& p, cudaStream_t stream) {
 }
 
 }  // namespace nvj
+
+#ifdef NVJ_PHASE_TIMING
+extern "C" int nvj_debug_phase_ns(unsigned long long* host_out) {  // [256][8]
+  return cudaMemcpyFromSymbol(host_out, nvj::g_phase_ns, sizeof(nvj::g_phase_ns)) == cudaSuccess ? 0 : 1;
+}
+#endif
 
 extern "C" size_t nvj_paged_decode_wide_workspace_bytes(int max_batch) {
   using namespace nvj;
