@@ -444,6 +444,38 @@ def decode_phase_cases(dev, iters):
         report("paged_decode, %d rows x %d tokens: phases in us after the first CTA's entry" % (rows, ctx), us,
                rows * ctx * TOKEN_BYTES, {"workload": "short batch", "ctas": int(live.sum()), "phases": phases})
     K.check_device_status(dev)
+    del k, v
+
+    # the CTA-pair prefill kernel on a 512-token chunk behind a 512-token prefix: per CTA, phases and key tiles
+    lib.nvj_debug_prefill_phase_ns.argtypes = [ctypes.c_void_p]
+    lib.nvj_debug_prefill_phase_ns.restype = ctypes.c_int
+    pool, chunk, prefix = 4096, 512, 512
+    k = _randn_bf16((1, pool, BS, HKV, D), 11, dev)
+    v = _randn_bf16((1, pool, BS, HKV, D), 12, dev)
+    tab = torch.randperm(pool, device=dev)[: (prefix + chunk) // BS].to(torch.int32).view(1, -1).contiguous()
+    pos = (prefix + torch.arange(chunk, dtype=torch.int32, device=dev))[None].contiguous()
+    qsl = torch.tensor([0, chunk], dtype=torch.int32, device=dev)
+    kvl = torch.tensor([prefix + chunk], dtype=torch.int32, device=dev)
+    q = _randn_bf16((1, chunk, HQ, D), 13, dev)
+    us = timer.run(lambda: K.packed_paged_prefill_attention(q, k[0], v[0], tab, kvl, pos, qsl, BS, SCALE, 4, variant=4,
+                                                            num_decode_rows=0))
+    host = np.zeros((512, 8), np.uint64)
+    if lib.nvj_debug_prefill_phase_ns(host.ctypes.data) != 0:
+        raise RuntimeError("nvj_debug_prefill_phase_ns failed")
+    t0 = host[:, 0].astype(np.int64)
+    live = (t0 >= t0.max() - 200_000) & (host[:, 7] > 0)  # CTAs of the last launch that had key tiles
+    rel = (host[live, :7].astype(np.int64) - t0[t0 >= t0.max() - 200_000].min()) / 1e3
+    names = ["entry", "set up (tensor memory, barriers, cluster barrier)", "query rows staged", "first scores ready",
+             "last tile's weights written", "output written", "pair released"]
+    per_cta = [{"tiles": int(host[i, 7]), **{names[j]: round(float((int(host[i, j]) - int(t0[t0 >= t0.max() - 200_000].min())) / 1e3), 2)
+                                               for j in range(7)}} for i in np.nonzero(live)[0]]
+    per_cta.sort(key=lambda d: d["tiles"])
+    flops = 4 * HQ * D * int(sum(prefix + i + 1 for i in range(chunk)))
+    report("packed prefill, tcgen05 CTA pairs, %d-token chunk behind a %d-token prefix: phases in us after the first CTA's entry"
+           % (chunk, prefix), us, (prefix + chunk) * TOKEN_BYTES + chunk * HQ * D * 6,
+           {"workload": "c3 chunk", "TFLOP/s": round(flops / us / 1e6, 2), "ctas": int(live.sum()),
+            "fewest_tiles": per_cta[0], "most_tiles": per_cta[-1], "kernel_end": round(float(rel[:, 6].max()), 2)})
+    K.check_device_status(dev)
 
 
 def main():

@@ -21,6 +21,8 @@
 // the final cluster barrier and free their tensor memory.
 // Semantics: nanovllm_jax/kv_cache.py:831-849, nanovllm_jax/kernels/full_attention_triton.py:51-145.
 
+#include <cstddef>
+
 #include "paged_decode.cuh"
 #include "umma.cuh"
 
@@ -38,6 +40,17 @@ constexpr uint32_t kU2TileBytes = kU2Keys * kRowBytes;  // a whole K (or V) tile
 constexpr uint32_t kU2LeaderMask = 0xFEFFFFFFu;         // clears the CTA-rank bit of a shared::cluster address
 constexpr float kU2Log2e = 1.4426950408889634f;
 constexpr float kU2RescaleGap = 8.f;
+
+// Development aid, compiled in only with -DNVJ_PHASE_TIMING: the first softmax thread of every CTA stamps the global
+// timer at the kernel's phase boundaries (slot 7: the number of key tiles), nvj_debug_prefill_phase_ns copies them out.
+#ifdef NVJ_PHASE_TIMING
+__device__ unsigned long long g_u2_phase_ns[512][8];
+#define NVJ_U2_PHASE(i) do { if (threadIdx.x == 64) g_u2_phase_ns[(blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x & 511][i] = global_timer_ns(); } while (0)
+#define NVJ_U2_NOTE(i, v) do { if (threadIdx.x == 64) g_u2_phase_ns[(blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x & 511][i] = (v); } while (0)
+#else
+#define NVJ_U2_PHASE(i) do { } while (0)
+#define NVJ_U2_NOTE(i, v) do { } while (0)
+#endif
 
 struct Umma2Params {
   const void* q;
@@ -61,6 +74,9 @@ struct Umma2Smem {
   alignas(8) unsigned long long q_full, k_full[kU2Stages], v_full[kU2Stages], k_empty[kU2Stages], v_empty[kU2Stages],
       s_full[2], p_full, pv_done, x_full;
   float xchg[2][2][kU2Rows];
+  // this CTA's query rows on their way into tensor memory: [token][head of the group][32 pieces of 16 B], the pieces
+  // of token t stored at (piece ^ (t & 7)) so that both the row-wise fill and the token-wise read are conflict-free
+  alignas(16) char qstage[kU2Tokens * kG * kD * 2];
   uint32_t tmem_base;
   int row, tok0, ntok, pair_last_tok, idle_index, abort_flag;
 };
@@ -226,7 +242,46 @@ __device__ __forceinline__ void u2_softmax_warps(Umma2Smem& sm, const Umma2Param
   const int quarter = warp & 3, half = (warp - 2) >> 2;
   const int r = quarter * 32 + lane, token = lane, hl = quarter;
   const uint32_t my_tmem = tmem + ((uint32_t)(quarter * 32) << 16);
-  {  // this row's half of Q (128 dims) -> 64 TMEM columns, two bf16 per column
+  if (p.q_dtype == NVJ_BF16) {
+    // The tile's query rows, 2 KiB per token (the group's four heads lie side by side), come in as whole 512-byte
+    // rows per warp instruction, all sixteen loads of a thread in flight at once, and go through shared memory:
+    // a thread that fetched its own row directly would touch 32 lines per instruction and wait for memory four
+    // times in a row (4.4 us of a 30 us kernel on a 512-token chunk).
+    const int sw = (warp - 2) & 7;  // 0..7: four tokens each
+    uint4 u[4][4];
+#pragma unroll
+    for (int a = 0; a < 4; ++a) {
+      const int tk = sw * 4 + a;
+      const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.q) +
+                                                        ((long long)(tok0 + tk) * kHq + kvh * kG) * kD) + lane;
+#pragma unroll
+      for (int h = 0; h < 4; ++h) u[a][h] = tk < ntok ? ld_nc_u4(src + h * 32) : make_uint4(0u, 0u, 0u, 0u);
+    }
+#pragma unroll
+    for (int a = 0; a < 4; ++a) {
+      const int tk = sw * 4 + a;
+#pragma unroll
+      for (int h = 0; h < 4; ++h)
+        *reinterpret_cast<uint4*>(sm.qstage + tk * 2048 + h * 512 + ((lane ^ (tk & 7)) << 4)) = u[a][h];
+    }
+    named_bar_sync(1, kU2SoftmaxThreads);
+    // this row's half of Q (128 dims) -> 64 TMEM columns, two bf16 per column
+    const char* mine = sm.qstage + token * 2048 + hl * 512;
+#pragma unroll 1
+    for (int part = 0; part < 4; ++part) {
+      uint32_t w[16];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint4 x = *reinterpret_cast<const uint4*>(mine + (((half * 16 + part * 4 + i) ^ (token & 7)) << 4));
+        w[4 * i] = x.x; w[4 * i + 1] = x.y; w[4 * i + 2] = x.z; w[4 * i + 3] = x.w;
+      }
+      tmem_st16(my_tmem + kU2ColQ + half * 64 + part * 16, w);
+    }
+    tmem_st_wait();
+    tc_fence_before_sync();
+    mbar_arrive_leader(smem_u32(&sm.q_full));
+    NVJ_U2_PHASE(2);
+  } else {  // fp32 queries: every thread converts its own row
     const long long qrow = ((long long)(tok0 + token) * kHq + kvh * kG + hl) * kD + half * (kD / 2);
 #pragma unroll 1
     for (int part = 0; part < 4; ++part) {
@@ -234,13 +289,6 @@ __device__ __forceinline__ void u2_softmax_warps(Umma2Smem& sm, const Umma2Param
       if (token >= ntok) {
 #pragma unroll
         for (int i = 0; i < 16; ++i) w[i] = 0u;
-      } else if (p.q_dtype == NVJ_BF16) {
-        const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.q) + qrow + part * 32);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const uint4 u = ld_nc_u4(src + i);
-          w[4 * i] = u.x; w[4 * i + 1] = u.y; w[4 * i + 2] = u.z; w[4 * i + 3] = u.w;
-        }
       } else {
         const float4* src = reinterpret_cast<const float4*>(static_cast<const float*>(p.q) + qrow + part * 32);
 #pragma unroll
@@ -256,6 +304,7 @@ __device__ __forceinline__ void u2_softmax_warps(Umma2Smem& sm, const Umma2Param
     tmem_st_wait();
     tc_fence_before_sync();
     mbar_arrive_leader(smem_u32(&sm.q_full));
+    NVJ_U2_PHASE(2);
   }
   const int my_pos = token < ntok ? p.positions[tok0 + token] : -1;
   const int last_key = my_pos < kv_len - 1 ? my_pos : kv_len - 1;
@@ -266,6 +315,7 @@ __device__ __forceinline__ void u2_softmax_warps(Umma2Smem& sm, const Umma2Param
     const int b = t & 1;
     const uint32_t s_tmem = my_tmem + kU2ColS + b * kU2Keys;
     if (!um_wait(&sm.s_full[b], (t >> 1) & 1, &sm.abort_flag, p.status)) return;
+    if (t == 0) NVJ_U2_PHASE(3);
     tc_fence_after_sync();
     float s[32];
     tmem_ld32(s_tmem + half * 32, s);
@@ -320,6 +370,7 @@ __device__ __forceinline__ void u2_softmax_warps(Umma2Smem& sm, const Umma2Param
     mbar_arrive_leader(smem_u32(&sm.p_full));
   }
   // ---- epilogue
+  NVJ_U2_PHASE(4);
   sm.xchg[n_tiles & 1][half][r] = l_row;
   mbar_arrive(smem_u32(&sm.x_full));
   if (!um_wait(&sm.x_full, n_tiles & 1, &sm.abort_flag, p.status)) return;
@@ -327,17 +378,40 @@ __device__ __forceinline__ void u2_softmax_warps(Umma2Smem& sm, const Umma2Param
   if (!um_wait(&sm.pv_done, (n_tiles - 1) & 1, &sm.abort_flag, p.status)) return;
   tc_fence_after_sync();
   const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
-  float* dst = p.out + ((long long)(tok0 + token) * kHq + kvh * kG + hl) * kD + half * (kD / 2);
+  // The K and V stages (128 KiB, contiguous) are free now: every copy has landed and every product has retired.  The
+  // normalised rows are laid down there, [row][256 floats] with the 16-byte pieces of row r stored at (piece ^ (r & 7))
+  // inside their group of eight, and leave as whole 512-byte runs per warp instruction.  (Stored straight from the
+  // registers, a warp instruction touched 32 lines: 5.4 us of a 30 us kernel on a 512-token chunk.)
+  float* stage = reinterpret_cast<float*>(&sm.k[0][0][0]);
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the stages were last written by bulk copies
+  static_assert(sizeof(sm.k) + sizeof(sm.v) >= (size_t)kU2Rows * kD * sizeof(float) && offsetof(Umma2Smem, v) == sizeof(sm.k),
+                "the output tile is staged across the K and V stages");
 #pragma unroll 1
   for (int cc = 0; cc < kD / 64; ++cc) {
     float o[32];
     tmem_ld32(my_tmem + kU2ColO + half * (kD / 2) + cc * 32, o);
-    if (token < ntok) {
+    const int c0 = (half * (kD / 2) + cc * 32) >> 2;  // first 16-byte piece of these 32 floats within the row
 #pragma unroll
-      for (int i = 0; i < 32; i += 4)
-        *reinterpret_cast<float4*>(dst + cc * 32 + i) = make_float4(o[i] * inv, o[i + 1] * inv, o[i + 2] * inv, o[i + 3] * inv);
+    for (int i = 0; i < 8; ++i)
+      *reinterpret_cast<float4*>(stage + r * kD + ((c0 + (i ^ (r & 7))) << 2)) =
+          make_float4(o[4 * i] * inv, o[4 * i + 1] * inv, o[4 * i + 2] * inv, o[4 * i + 3] * inv);
+  }
+  named_bar_sync(1, kU2SoftmaxThreads);
+  {
+    const int sw = (warp - 2) & 7;
+#pragma unroll 4
+    for (int a = 0; a < kU2Rows / 8; ++a) {
+      const int rr = sw * (kU2Rows / 8) + a, tk = rr & 31, hd = rr >> 5;
+      if (tk >= ntok) continue;
+      float* dst = p.out + ((long long)(tok0 + tk) * kHq + kvh * kG + hd) * kD;
+#pragma unroll
+      for (int h2 = 0; h2 < 2; ++h2) {
+        const int c = h2 * 32 + lane;
+        reinterpret_cast<float4*>(dst)[c] = *reinterpret_cast<const float4*>(stage + rr * kD + (((c & ~7) | ((c ^ rr) & 7)) << 2));
+      }
     }
   }
+  NVJ_U2_PHASE(5);
 }
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kU2Threads, 1)
@@ -348,6 +422,8 @@ prefill_umma2_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_con
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kvh = blockIdx.y;
   const int rank = (int)cluster_ctarank();  // == blockIdx.x & 1
+  NVJ_U2_PHASE(0);
+  NVJ_U2_NOTE(7, 0ull);
 
   // ---- which (table row, pair of 32-token tiles) this cluster serves; both CTAs compute the same
   if (threadIdx.x == 0) {
@@ -432,6 +508,8 @@ prefill_umma2_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_con
   cluster_sync_all();  // the peer's barriers exist before anything is sent to them
   tc_fence_after_sync();
   const uint32_t tmem = sm.tmem_base;
+  NVJ_U2_PHASE(1);
+  NVJ_U2_NOTE(7, (unsigned long long)n_tiles);
 
   if (warp == 0) u2_producer(&k_map, &v_map, p, sm, row, kvh, kv_len, n_tiles, rank, lane);
   else if (warp == 1) { if (rank == 0) u2_mma_warp(sm, p, tmem, n_tiles); }
@@ -444,6 +522,7 @@ prefill_umma2_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_con
     while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
   }
   cluster_sync_all();  // CTA 0's MMAs read this CTA's shared and tensor memory until its last commit
+  NVJ_U2_PHASE(6);
   if (warp == 1) tmem2_dealloc(tmem, kU2TmemCols);
 }
 
@@ -506,3 +585,9 @@ int launch_prefill_umma2(const void* q, int q_dtype, const char* k_cache, const 
 }
 
 }  // namespace nvj
+
+#ifdef NVJ_PHASE_TIMING
+extern "C" int nvj_debug_prefill_phase_ns(unsigned long long* host_out) {  // [512][8]
+  return cudaMemcpyFromSymbol(host_out, nvj::g_u2_phase_ns, sizeof(nvj::g_u2_phase_ns)) == cudaSuccess ? 0 : 1;
+}
+#endif
