@@ -195,6 +195,24 @@ def prefill_and_copy_cases(dev, iters, small=False):
                                                              variant=variant, num_decode_rows=0))
         report("packed prefill attention, %s (%d tokens, %d rows)" % (name, total, len(rows)), us, nbytes,
                {"workload": "c3 chunk", "TFLOP/s": round(flops / us / 1e6, 2), "flops": flops})
+    # one 512-token chunk behind a long cached prefix: few query tiles, long key ranges (what the key-range splits are for)
+    for prefix in (512, 1536, 3584):
+        if (prefix + chunk) // BS > pool:
+            continue
+        c_tab = torch.from_numpy(rng.permutation(pool)[:(prefix + chunk) // BS].astype(np.int32).reshape(1, -1)).to(dev)
+        c_pos = (prefix + torch.arange(chunk, dtype=torch.int32, device=dev))[None].contiguous()
+        c_qsl = torch.tensor([0, chunk], dtype=torch.int32, device=dev)
+        c_len = torch.tensor([prefix + chunk], dtype=torch.int32, device=dev)
+        c_flops = 4 * HQ * D * sum(prefix + i + 1 for i in range(chunk))
+        c_bytes = (prefix + chunk) * TOKEN_BYTES + chunk * (HQ * D * 2 + HQ * D * 4)
+        for splits in ("1", "0"):
+            os.environ["NVJ_PREFILL_KEY_SPLITS"] = splits
+            us = tm.run(lambda: K.packed_paged_prefill_attention(q, k[0], v[0], c_tab, c_len, c_pos, c_qsl, BS, SCALE, 4,
+                                                                 variant=4, num_decode_rows=0))
+            report("packed prefill attention, tcgen05 CTA pairs, key ranges %s (512-token chunk behind %d cached tokens)"
+                   % ("split" if splits == "1" else "unsplit", prefix), us, c_bytes,
+                   {"workload": "chunk behind a prefix", "TFLOP/s": round(c_flops / us / 1e6, 2), "flops": c_flops})
+        os.environ.pop("NVJ_PREFILL_KEY_SPLITS", None)
     # long prompts in a single chunk, nothing cached
     for n_long in (4096, 16384):
         if n_long // BS > pool:

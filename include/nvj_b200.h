@@ -291,7 +291,13 @@ int nvj_paged_decode_wide(const void* q, const void* k_cache_layer, const void* 
  *   workspace  nullable decode workspace (nvj_paged_decode_workspace_bytes(rows)); when given,
  *              rows that hold exactly one query token (the decode rows of a mixed batch,
  *              nanovllm_jax/engine/scheduler.py:956-1032) are served by the streaming decode
- *              kernel instead of a query tile
+ *              kernel instead of a query tile.  A workspace of nvj_paged_prefill_workspace_bytes(rows)
+ *              bytes also lets the CTA-pair tile kernel (variants 0, 4, 5) split every tile's key
+ *              range over several CTA pairs when the batch is too short to fill the GPU (a
+ *              512-token chunk is 16 pairs on 74 pair slots): the splits park their un-normalised
+ *              rows between the workspace's header and the decode partials, and the pair that
+ *              arrives last folds them.  Like the decode workspace it must start zeroed and is left
+ *              zeroed where that matters.
  *   variant    0 = automatic; 1 = generic CUDA-core kernel (any shape or dtype); for the model's
  *              shape (bf16 cache, block 16, 2 KV x 4 query heads, head_dim 256): 2 = mma.sync
  *              tiles of 16 tokens, 3 = tcgen05 tiles of 32 tokens with accumulators in tensor
@@ -302,6 +308,7 @@ int nvj_paged_decode_wide(const void* q, const void* k_cache_layer, const void* 
  *              prompts, max-abs error ~3e-3 instead of < 2e-3 against an fp32 softmax.
  *              NVJ_ERR_UNSUPPORTED when 2-5 is asked for another shape.
  */
+size_t nvj_paged_prefill_workspace_bytes(int max_rows);
 int nvj_paged_prefill_packed(const void* q, int q_dtype,
                              const void* k_cache_layer, const void* v_cache_layer, int kv_dtype,
                              int64_t num_blocks, int block_size, int num_kv_heads,
@@ -322,7 +329,10 @@ int nvj_paged_prefill_packed(const void* q, int q_dtype,
  * first and orders both launches behind that.
  *   part 1   rows that hold exactly one query token, on the streaming decode kernel with at most `cta_limit` CTAs
  *            (0 = one per SM; give the SM count minus the CTAs of part 2); `workspace` is required
- *   part 2   every other row, on the tile kernel `variant` selects; `workspace` is ignored
+ *   part 2   every other row, on the tile kernel `variant` selects; `workspace` (nullable, NOT the buffer part 1 is
+ *            using at the same time) only gives the key-range splits of a short batch their room
+ *   part 3   all rows on the tile kernel, which then zeroes what it does not write itself (no zeroed `out` needed):
+ *            a batch without decode rows that still wants the key-range splits
  * The reference runs a mixed batch through one packed attention call; the split has no counterpart there.
  */
 int nvj_paged_prefill_packed_part(const void* q, int q_dtype,

@@ -19,7 +19,8 @@ int launch_prefill_umma2(const void* q, int q_dtype, const char* k_cache, const 
                          long long num_blocks, const int32_t* block_tables, int table_width,
                          const int32_t* kv_lens, const int32_t* positions, const int32_t* query_start_loc,
                          int rows, int token_bucket, float scale, float* out, int32_t* status,
-                         int skip_single, int split_p, cudaStream_t stream);
+                         int skip_single, int split_p, int32_t* split_counters, float* split_area, size_t split_bytes,
+                         cudaStream_t stream);
 int launch_prefill_umma(const void* q, int q_dtype, const char* k_cache, const char* v_cache,
                         long long num_blocks, const int32_t* block_tables, int table_width,
                         const int32_t* kv_lens, const int32_t* positions, const int32_t* query_start_loc,
@@ -106,9 +107,24 @@ static int run_tiles(const PackedArgs& a, int skip_single, cudaStream_t s) {
   const char* vc = static_cast<const char*>(a.v_cache_layer);
   const int variant = a.variant;
   if (variant == 0 || variant == 4 || variant == 5) {
+    // A workspace with room between the header and the decode partials (what run_single_token_rows carves from the
+    // same buffer) lets a short batch split every tile's key range over several CTA pairs.
+    int32_t* split_counters = nullptr;
+    float* split_area = nullptr;
+    size_t split_bytes = 0;
+    const int num_ctas = decode_num_ctas();
+    if (a.workspace && num_ctas > 0 && (reinterpret_cast<uintptr_t>(a.workspace) & 15u) == 0) {
+      const size_t end = a.workspace_bytes / kWsAlign * kWsAlign;
+      const size_t tail = ws_ml_bytes(num_ctas) + ws_acc_bytes(num_ctas), head = ws_header_bytes(a.rows);
+      if (end > head + tail) {
+        split_bytes = (end - head - tail) / kWsAlign * kWsAlign;
+        split_area = reinterpret_cast<float*>(static_cast<char*>(a.workspace) + end - tail - split_bytes);
+        split_counters = ws_split_counters(a.workspace);
+      }
+    }
     const int rc = launch_prefill_umma2(a.q, a.q_dtype, kc, vc, a.num_blocks, a.block_tables, a.table_width, a.kv_lens, a.positions,
                                         a.query_start_loc, a.rows, a.token_bucket, a.scale, a.out, a.status, skip_single,
-                                        variant == 5 ? 0 : 1, s);
+                                        variant == 5 ? 0 : 1, split_counters, split_area, split_bytes, s);
     if (rc != NVJ_ERR_UNSUPPORTED || variant != 0) return rc;
   }
   if (variant == 0 || variant == 3) {
@@ -146,6 +162,14 @@ static int run_generic(const PackedArgs& a, cudaStream_t s) {
 }
 
 }  // namespace nvj
+
+extern "C" size_t nvj_paged_prefill_workspace_bytes(int max_rows) {
+  using namespace nvj;
+  if (max_rows < 0) return 0;
+  const int n = decode_num_ctas();
+  if (n <= 0) return 0;
+  return ws_header_bytes(max_rows) + prefill_split_bytes() + ws_ml_bytes(n) + ws_acc_bytes(n);
+}
 
 extern "C" int nvj_paged_prefill_packed(const void* q, int q_dtype, const void* k_cache_layer,
                                         const void* v_cache_layer, int kv_dtype,
@@ -192,11 +216,12 @@ extern "C" int nvj_paged_prefill_packed_part(const void* q, int q_dtype, const v
   const PackedArgs a{q, q_dtype, k_cache_layer, v_cache_layer, kv_dtype, num_blocks, block_size, num_kv_heads, head_dim,
                      num_q_heads, block_tables, table_width, kv_lens, positions, query_start_loc, rows, token_bucket,
                      scale, out, status, workspace, workspace_bytes, variant};
-  if ((part != 1 && part != 2) || cta_limit < 0) return NVJ_ERR_INVALID_ARGUMENT;
+  if (part < 1 || part > 3 || cta_limit < 0) return NVJ_ERR_INVALID_ARGUMENT;
   bool tile_ok = false;
   const int rc = check_packed(a, &tile_ok);
   if (rc != NVJ_OK || token_bucket == 0) return rc;
   if (!tile_ok || variant == 1) return NVJ_ERR_UNSUPPORTED;  // the generic kernel serves a batch in one piece
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  return part == 1 ? run_single_token_rows(a, cta_limit, s) : run_tiles(a, 1, s);
+  if (part == 1) return run_single_token_rows(a, cta_limit, s);
+  return run_tiles(a, part == 2 ? 1 : 0, s);
 }

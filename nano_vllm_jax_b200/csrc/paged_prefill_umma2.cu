@@ -19,6 +19,10 @@
 // A cluster barrier after set-up and one before the tensor memory is freed fence the pair.
 // Every mbarrier wait is bounded; a timeout flags NVJ_DEV_TIMEOUT and both CTAs still reach
 // the final cluster barrier and free their tensor memory.
+// Short batches (a 512-token chunk is 16 CTA pairs on 74 pair slots) split every tile's key range over up to
+// kU2MaxSplits pairs (blockIdx.z): each split writes its un-normalised rows and their (max, sum) to a workspace,
+// counts itself in per CTA tile, and the CTA that arrives last folds the splits into the output.  Nothing waits
+// for another CTA.
 // Semantics: nanovllm_jax/kv_cache.py:831-849, nanovllm_jax/kernels/full_attention_triton.py:51-145.
 
 #include <cstddef>
@@ -40,6 +44,14 @@ constexpr uint32_t kU2TileBytes = kU2Keys * kRowBytes;  // a whole K (or V) tile
 constexpr uint32_t kU2LeaderMask = 0xFEFFFFFFu;         // clears the CTA-rank bit of a shared::cluster address
 constexpr float kU2Log2e = 1.4426950408889634f;
 constexpr float kU2RescaleGap = 8.f;
+constexpr int kU2MaxSplits = 4;
+// What a split costs is fixed: its rows go out to the workspace, and the pair that arrives last fetches the other
+// splits' rows from the L2, about five round trips of ~2 us on this two-die part whatever their number.  A key tile
+// costs a pair ~1 us.  So only key ranges of kU2SplitFrom tiles or more are split, into pieces of at least
+// kU2MinSplitTiles tiles (512-token chunk behind a 512-token prefix, 16 tiles: 32.8 us unsplit, 30.8 us in four
+// pieces; behind 1536 tokens the range is twice as long and the split pays properly).
+constexpr int kU2SplitFrom = 16;
+constexpr int kU2MinSplitTiles = 4;
 
 // Development aid, compiled in only with -DNVJ_PHASE_TIMING: the first softmax thread of every CTA stamps the global
 // timer at the kernel's phase boundaries (slot 7: the number of key tiles), nvj_debug_prefill_phase_ns copies them out.
@@ -65,6 +77,12 @@ struct Umma2Params {
   int zero_fill;  // 1: the kernel itself zeroes what no tile writes (padding tokens, rows without keys)
   int split_p;  // 1: P enters P V as two bf16 terms (hi + lo), 0: as one (the weights are then bf16-rounded)
   float scale;
+  // key-range splits (gridDim.z > 1): un-normalised rows [split][token][head][kD], their (max, sum)
+  // [split][token][head][2], one arrival counter per (CTA tile, KV head), zero between launches; pair slots of the device
+  float* part_o;
+  float* part_ml;
+  int32_t* split_counters;
+  int pair_slots;
 };
 
 struct Umma2Smem {
@@ -77,8 +95,9 @@ struct Umma2Smem {
   // this CTA's query rows on their way into tensor memory: [token][head of the group][32 pieces of 16 B], the pieces
   // of token t stored at (piece ^ (t & 7)) so that both the row-wise fill and the token-wise read are conflict-free
   alignas(16) char qstage[kU2Tokens * kG * kD * 2];
+  float own_ml[2][kU2Rows];  // this split's (max, sum) per row, for the fold
   uint32_t tmem_base;
-  int row, tok0, ntok, pair_last_tok, idle_index, abort_flag;
+  int row, tok0, ntok, pair_last_tok, idle_index, abort_flag, total_pairs, is_last;
 };
 
 // ---- cta_group::2 wrappers ---------------------------------------------------------------------
@@ -131,7 +150,8 @@ __device__ __forceinline__ constexpr uint32_t umma2_idesc(int n, bool b_mn_major
 
 // ---- warp 0 of both CTAs: TMA loads of this CTA's halves ------------------------------------
 __device__ __forceinline__ void u2_producer(const CUtensorMap* k_map, const CUtensorMap* v_map, const Umma2Params& p,
-                                            Umma2Smem& sm, int row, int kvh, int kv_len, int n_tiles, int rank, int lane) {
+                                            Umma2Smem& sm, int row, int kvh, int kv_len, int tile0, int n_tiles, int rank,
+                                            int lane, int first_ids) {
   const int need_blocks = (kv_len + kBlk - 1) / kBlk;
   const int oob = (int)(p.num_blocks * kBlk);  // a box that starts here is filled with zeros
   int ids = -1;
@@ -139,10 +159,10 @@ __device__ __forceinline__ void u2_producer(const CUtensorMap* k_map, const CUte
     const int s = t % kU2Stages;
     const uint32_t reuse_parity = ((t / kU2Stages) - 1) & 1;
     if ((t & 7) == 0) {  // block ids of the next 8 tiles, one per lane
-      const int bi = t * 4 + lane;
+      const int bi = (tile0 + t) * 4 + lane;
       ids = -1;
       if (bi < need_blocks && bi < p.table_width) {
-        ids = p.block_tables[(long long)row * p.table_width + bi];
+        ids = t == 0 ? first_ids : p.block_tables[(long long)row * p.table_width + bi];  // the first eight tiles' came early
         if (ids < 0 || ids >= p.num_blocks) {
           if (rank == 0) atomicOr(p.status, NVJ_DEV_BAD_BLOCK_ID);
           ids = -1;
@@ -236,27 +256,102 @@ __device__ __forceinline__ void u2_mma_warp(Umma2Smem& sm, const Umma2Params& p,
   }
 }
 
+// The walk over the key tiles for one softmax thread (row r, column half): scores out of tensor memory, mask, running
+// max shared with the other half, weights back into tensor memory.  False when a wait ran out (the caller still
+// joins its barriers).
+__device__ __forceinline__ bool u2_softmax_tiles(Umma2Smem& sm, const Umma2Params& p, uint32_t my_tmem, int tok0, int ntok,
+                                                 int kv_len, int tile0, int n_tiles, int half, int r, int token, float& m_row,
+                                                 float& l_row) {
+  const int my_pos = token < ntok ? p.positions[tok0 + token] : -1;
+  const int last_key = my_pos < kv_len - 1 ? my_pos : kv_len - 1;
+  const float scale_log2 = p.scale * kU2Log2e;
+  for (int t = 0; t < n_tiles; ++t) {
+    const int b = t & 1;
+    const uint32_t s_tmem = my_tmem + kU2ColS + b * kU2Keys;
+    if (!um_wait(&sm.s_full[b], (t >> 1) & 1, &sm.abort_flag, p.status)) return false;
+    if (t == 0) NVJ_U2_PHASE(3);
+    tc_fence_after_sync();
+    float s[32];
+    tmem_ld32(s_tmem + half * 32, s);
+    const int lim = last_key - (tile0 + t) * kU2Keys - half * 32;
+    float hmax = -INFINITY;
+    if (lim >= 31) {
+#pragma unroll
+      for (int i = 0; i < 32; i += 2) hmax = fmaxf(hmax, fmaxf(s[i], s[i + 1]));
+    } else {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) { s[i] = i <= lim ? s[i] : -INFINITY; hmax = fmaxf(hmax, s[i]); }
+    }
+    sm.xchg[b][half][r] = hmax;
+    mbar_arrive(smem_u32(&sm.x_full));
+    if (!um_wait(&sm.x_full, t & 1, &sm.abort_flag, p.status)) return false;
+    const float tmax = fmaxf(hmax, sm.xchg[b][half ^ 1][r]) * scale_log2;  // scale > 0
+    if (t == 0) {
+      m_row = tmax;
+    } else if (__any_sync(0xffffffffu, tmax > m_row + kU2RescaleGap)) {
+      if (!um_wait(&sm.pv_done, (t - 1) & 1, &sm.abort_flag, p.status)) return false;
+      tc_fence_after_sync();
+      const float m_new = fmaxf(m_row, tmax);
+      const float f = m_new == -INFINITY ? 1.f : ex2_approx(m_row - m_new);
+      m_row = m_new;
+      l_row *= f;
+#pragma unroll 1
+      for (int cc = 0; cc < kD / 64; ++cc) {
+        float o[32];
+        tmem_ld32(my_tmem + kU2ColO + half * (kD / 2) + cc * 32, o);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o[i] *= f;
+        tmem_st32(my_tmem + kU2ColO + half * (kD / 2) + cc * 32, o);
+      }
+    }
+    const float neg_m = m_row == -INFINITY ? 0.f : -m_row;
+    uint32_t hi[16], lo[16];
+#pragma unroll
+    for (int e = 0; e < 16; ++e) {
+      const float p0 = ex2_approx(fmaf(s[2 * e], scale_log2, neg_m)), p1 = ex2_approx(fmaf(s[2 * e + 1], scale_log2, neg_m));
+      l_row += p0 + p1;
+      const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+      const __nv_bfloat162 g = __floats2bfloat162_rn(p0 - __low2float(h), p1 - __high2float(h));
+      hi[e] = *reinterpret_cast<const uint32_t*>(&h);
+      lo[e] = *reinterpret_cast<const uint32_t*>(&g);
+    }
+    // every phase of pv_done is observed in turn (parity waits tell only two phases apart)
+    if (t >= 1 && !um_wait(&sm.pv_done, (t - 1) & 1, &sm.abort_flag, p.status)) return false;
+    tmem_st16(s_tmem + half * 16, hi);
+    if (p.split_p) tmem_st16(s_tmem + 32 + half * 16, lo);
+    tmem_st_wait();
+    tc_fence_before_sync();
+    mbar_arrive_leader(smem_u32(&sm.p_full));
+  }
+  return true;
+}
+
+// The tile's query rows, 2 KiB per token (the group's four heads lie side by side), as whole 512-byte rows per warp
+// instruction, all sixteen loads of a thread in flight at once: softmax warp sw takes tokens 4 sw .. 4 sw + 3.
+__device__ __forceinline__ void u2_request_q(const Umma2Params& p, int tok0, int ntok, int kvh, int warp, int lane, uint4 (&u)[4][4]) {
+  const int sw = (warp - 2) & 7;
+#pragma unroll
+  for (int a = 0; a < 4; ++a) {
+    const int tk = sw * 4 + a;
+    const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.q) +
+                                                      ((long long)(tok0 + tk) * kHq + kvh * kG) * kD) + lane;
+#pragma unroll
+    for (int h = 0; h < 4; ++h) u[a][h] = tk < ntok ? ld_nc_u4(src + h * 32) : make_uint4(0u, 0u, 0u, 0u);
+  }
+}
+
 // ---- warps 2-9 of both CTAs: Q staging, softmax, epilogue for this CTA's 128 rows -------------
 __device__ __forceinline__ void u2_softmax_warps(Umma2Smem& sm, const Umma2Params& p, uint32_t tmem, int tok0, int ntok,
-                                                 int kvh, int kv_len, int n_tiles, int warp, int lane) {
+                                                 int kvh, int kv_len, int tile0, int n_tiles, int splits, int warp, int lane,
+                                                 const uint4 (&u)[4][4]) {
   const int quarter = warp & 3, half = (warp - 2) >> 2;
   const int r = quarter * 32 + lane, token = lane, hl = quarter;
   const uint32_t my_tmem = tmem + ((uint32_t)(quarter * 32) << 16);
   if (p.q_dtype == NVJ_BF16) {
-    // The tile's query rows, 2 KiB per token (the group's four heads lie side by side), come in as whole 512-byte
-    // rows per warp instruction, all sixteen loads of a thread in flight at once, and go through shared memory:
-    // a thread that fetched its own row directly would touch 32 lines per instruction and wait for memory four
-    // times in a row (4.4 us of a 30 us kernel on a 512-token chunk).
+    // The tile's query rows (`u`, requested by u2_request_q before the pair was set up) go through shared memory: a
+    // thread that fetched its own row directly would touch 32 lines per instruction and wait for memory four times
+    // in a row (4.4 us of a 30 us kernel on a 512-token chunk).
     const int sw = (warp - 2) & 7;  // 0..7: four tokens each
-    uint4 u[4][4];
-#pragma unroll
-    for (int a = 0; a < 4; ++a) {
-      const int tk = sw * 4 + a;
-      const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.q) +
-                                                        ((long long)(tok0 + tk) * kHq + kvh * kG) * kD) + lane;
-#pragma unroll
-      for (int h = 0; h < 4; ++h) u[a][h] = tk < ntok ? ld_nc_u4(src + h * 32) : make_uint4(0u, 0u, 0u, 0u);
-    }
 #pragma unroll
     for (int a = 0; a < 4; ++a) {
       const int tk = sw * 4 + a;
@@ -306,78 +401,23 @@ __device__ __forceinline__ void u2_softmax_warps(Umma2Smem& sm, const Umma2Param
     mbar_arrive_leader(smem_u32(&sm.q_full));
     NVJ_U2_PHASE(2);
   }
-  const int my_pos = token < ntok ? p.positions[tok0 + token] : -1;
-  const int last_key = my_pos < kv_len - 1 ? my_pos : kv_len - 1;
-  const float scale_log2 = p.scale * kU2Log2e;
   float m_row = -INFINITY, l_row = 0.f;
-
-  for (int t = 0; t < n_tiles; ++t) {
-    const int b = t & 1;
-    const uint32_t s_tmem = my_tmem + kU2ColS + b * kU2Keys;
-    if (!um_wait(&sm.s_full[b], (t >> 1) & 1, &sm.abort_flag, p.status)) return;
-    if (t == 0) NVJ_U2_PHASE(3);
-    tc_fence_after_sync();
-    float s[32];
-    tmem_ld32(s_tmem + half * 32, s);
-    const int lim = last_key - t * kU2Keys - half * 32;
-    float hmax = -INFINITY;
-    if (lim >= 31) {
-#pragma unroll
-      for (int i = 0; i < 32; i += 2) hmax = fmaxf(hmax, fmaxf(s[i], s[i + 1]));
-    } else {
-#pragma unroll
-      for (int i = 0; i < 32; ++i) { s[i] = i <= lim ? s[i] : -INFINITY; hmax = fmaxf(hmax, s[i]); }
-    }
-    sm.xchg[b][half][r] = hmax;
-    mbar_arrive(smem_u32(&sm.x_full));
-    if (!um_wait(&sm.x_full, t & 1, &sm.abort_flag, p.status)) return;
-    const float tmax = fmaxf(hmax, sm.xchg[b][half ^ 1][r]) * scale_log2;  // scale > 0
-    if (t == 0) {
-      m_row = tmax;
-    } else if (__any_sync(0xffffffffu, tmax > m_row + kU2RescaleGap)) {
-      if (!um_wait(&sm.pv_done, (t - 1) & 1, &sm.abort_flag, p.status)) return;
-      tc_fence_after_sync();
-      const float m_new = fmaxf(m_row, tmax);
-      const float f = m_new == -INFINITY ? 1.f : ex2_approx(m_row - m_new);
-      m_row = m_new;
-      l_row *= f;
-#pragma unroll 1
-      for (int cc = 0; cc < kD / 64; ++cc) {
-        float o[32];
-        tmem_ld32(my_tmem + kU2ColO + half * (kD / 2) + cc * 32, o);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[i] *= f;
-        tmem_st32(my_tmem + kU2ColO + half * (kD / 2) + cc * 32, o);
-      }
-    }
-    const float neg_m = m_row == -INFINITY ? 0.f : -m_row;
-    uint32_t hi[16], lo[16];
-#pragma unroll
-    for (int e = 0; e < 16; ++e) {
-      const float p0 = ex2_approx(fmaf(s[2 * e], scale_log2, neg_m)), p1 = ex2_approx(fmaf(s[2 * e + 1], scale_log2, neg_m));
-      l_row += p0 + p1;
-      const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-      const __nv_bfloat162 g = __floats2bfloat162_rn(p0 - __low2float(h), p1 - __high2float(h));
-      hi[e] = *reinterpret_cast<const uint32_t*>(&h);
-      lo[e] = *reinterpret_cast<const uint32_t*>(&g);
-    }
-    // every phase of pv_done is observed in turn (parity waits tell only two phases apart)
-    if (t >= 1 && !um_wait(&sm.pv_done, (t - 1) & 1, &sm.abort_flag, p.status)) return;
-    tmem_st16(s_tmem + half * 16, hi);
-    if (p.split_p) tmem_st16(s_tmem + 32 + half * 16, lo);
-    tmem_st_wait();
-    tc_fence_before_sync();
-    mbar_arrive_leader(smem_u32(&sm.p_full));
-  }
-  // ---- epilogue
+  bool alive = u2_softmax_tiles(sm, p, my_tmem, tok0, ntok, kv_len, tile0, n_tiles, half, r, token, m_row, l_row);
+  // ---- epilogue.  From here on the softmax threads meet at CTA-wide named barriers, so a thread whose wait ran out
+  // does not leave: it skips the work and everybody returns together once the barrier has made the flag visible.
   NVJ_U2_PHASE(4);
-  sm.xchg[n_tiles & 1][half][r] = l_row;
-  mbar_arrive(smem_u32(&sm.x_full));
-  if (!um_wait(&sm.x_full, n_tiles & 1, &sm.abort_flag, p.status)) return;
-  l_row += sm.xchg[n_tiles & 1][half ^ 1][r];
-  if (!um_wait(&sm.pv_done, (n_tiles - 1) & 1, &sm.abort_flag, p.status)) return;
+  if (alive) {
+    sm.xchg[n_tiles & 1][half][r] = l_row;
+    mbar_arrive(smem_u32(&sm.x_full));
+    alive = um_wait(&sm.x_full, n_tiles & 1, &sm.abort_flag, p.status);
+  }
+  if (alive) {
+    l_row += sm.xchg[n_tiles & 1][half ^ 1][r];
+    alive = um_wait(&sm.pv_done, (n_tiles - 1) & 1, &sm.abort_flag, p.status);
+  }
   tc_fence_after_sync();
-  const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
+  const float inv = splits > 1 ? 1.f : (l_row > 0.f ? 1.f / l_row : 0.f);  // a split leaves its rows un-normalised
+  if (splits > 1 && half == 0) { sm.own_ml[0][r] = m_row; sm.own_ml[1][r] = l_row; }
   // The K and V stages (128 KiB, contiguous) are free now: every copy has landed and every product has retired.  The
   // normalised rows are laid down there, [row][256 floats] with the 16-byte pieces of row r stored at (piece ^ (r & 7))
   // inside their group of eight, and leave as whole 512-byte runs per warp instruction.  (Stored straight from the
@@ -387,7 +427,7 @@ __device__ __forceinline__ void u2_softmax_warps(Umma2Smem& sm, const Umma2Param
   static_assert(sizeof(sm.k) + sizeof(sm.v) >= (size_t)kU2Rows * kD * sizeof(float) && offsetof(Umma2Smem, v) == sizeof(sm.k),
                 "the output tile is staged across the K and V stages");
 #pragma unroll 1
-  for (int cc = 0; cc < kD / 64; ++cc) {
+  for (int cc = 0; cc < kD / 64 && alive; ++cc) {
     float o[32];
     tmem_ld32(my_tmem + kU2ColO + half * (kD / 2) + cc * 32, o);
     const int c0 = (half * (kD / 2) + cc * 32) >> 2;  // first 16-byte piece of these 32 floats within the row
@@ -397,21 +437,99 @@ __device__ __forceinline__ void u2_softmax_warps(Umma2Smem& sm, const Umma2Param
           make_float4(o[4 * i] * inv, o[4 * i + 1] * inv, o[4 * i + 2] * inv, o[4 * i + 3] * inv);
   }
   named_bar_sync(1, kU2SoftmaxThreads);
+  if (*reinterpret_cast<volatile int*>(&sm.abort_flag)) return;  // somebody gave up: the same answer in every thread
+  const int sw = (warp - 2) & 7;
+  const long long split_rows = (long long)p.token_bucket * kHq;  // rows of one split's partial area
   {
-    const int sw = (warp - 2) & 7;
+    float* base = splits > 1 ? p.part_o + (long long)blockIdx.z * split_rows * kD : p.out;
 #pragma unroll 4
     for (int a = 0; a < kU2Rows / 8; ++a) {
       const int rr = sw * (kU2Rows / 8) + a, tk = rr & 31, hd = rr >> 5;
       if (tk >= ntok) continue;
-      float* dst = p.out + ((long long)(tok0 + tk) * kHq + kvh * kG + hd) * kD;
+      const long long g = (long long)(tok0 + tk) * kHq + kvh * kG + hd;
 #pragma unroll
       for (int h2 = 0; h2 < 2; ++h2) {
         const int c = h2 * 32 + lane;
-        reinterpret_cast<float4*>(dst)[c] = *reinterpret_cast<const float4*>(stage + rr * kD + (((c & ~7) | ((c ^ rr) & 7)) << 2));
+        reinterpret_cast<float4*>(base + g * kD)[c] = *reinterpret_cast<const float4*>(stage + rr * kD + (((c & ~7) | ((c ^ rr) & 7)) << 2));
       }
+      if (splits > 1 && lane == 0)
+        *reinterpret_cast<float2*>(p.part_ml + ((long long)blockIdx.z * split_rows + g) * 2) = make_float2(sm.own_ml[0][rr], sm.own_ml[1][rr]);
     }
   }
   NVJ_U2_PHASE(5);
+  if (splits == 1) return;
+  // ---- count this split in; the CTA that delivers a tile's last split folds them (its own rows are still staged)
+  int32_t* counter = p.split_counters + blockIdx.x * kHkv + kvh;
+  __threadfence();
+  named_bar_sync(1, kU2SoftmaxThreads);
+  if (warp == 2 && lane == 0) sm.is_last = (atomicAdd(counter, 1) == splits - 1) ? 1 : 0;
+  named_bar_sync(1, kU2SoftmaxThreads);
+  if (!sm.is_last) return;
+  __threadfence();
+  if (warp == 2 && lane == 0) *counter = 0;
+  // Pass 1: the weights.  Lane (row a or a + 8 of this warp's sixteen, split) reads that split's (max, sum); groups of
+  // four lanes reduce them; every split's weight, already divided by the row's total, is left in shared memory (the
+  // exchange buffer of the softmax is free by now).
+  static_assert(kU2MaxSplits == 4 && sizeof(sm.xchg) >= 8 * 16 * kU2MaxSplits * sizeof(float), "fold weights live in xchg");
+  float* fw = &sm.xchg[0][0][0] + sw * 16 * kU2MaxSplits;
+  const int own = (int)blockIdx.z;
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int a = (lane >> 2) + 8 * h, s2 = lane & 3;
+    const int rr = sw * 16 + a, tk = rr & 31, hd = rr >> 5;
+    const long long g = (long long)(tok0 + tk) * kHq + kvh * kG + hd;
+    float2 e = make_float2(-INFINITY, 0.f);
+    if (tk < ntok && s2 < splits)
+      e = s2 == own ? make_float2(sm.own_ml[0][rr], sm.own_ml[1][rr])
+                    : __ldcg(reinterpret_cast<const float2*>(p.part_ml + ((long long)s2 * split_rows + g) * 2));
+    float big = fmaxf(e.x, __shfl_xor_sync(0xffffffffu, e.x, 1));
+    big = fmaxf(big, __shfl_xor_sync(0xffffffffu, big, 2));
+    const float w = e.x == -INFINITY ? 0.f : ex2_approx(e.x - big);
+    float total = w * e.y;
+    total += __shfl_xor_sync(0xffffffffu, total, 1);
+    total += __shfl_xor_sync(0xffffffffu, total, 2);
+    fw[a * kU2MaxSplits + s2] = total > 0.f ? w / total : 0.f;
+  }
+  __syncwarp();
+  // Pass 2: four rows at a time, the other splits' pieces of all four requested before any is used (the fold is bound
+  // by the round trips to the L2, not by their volume).
+#pragma unroll 1
+  for (int a0 = 0; a0 < 16; a0 += 4) {
+    float4 x[4][kU2MaxSplits - 1][2];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int rr = sw * 16 + a0 + i, tk = rr & 31, hd = rr >> 5;
+      const long long g = (long long)(tok0 + tk) * kHq + kvh * kG + hd;
+#pragma unroll
+      for (int jx = 0; jx < kU2MaxSplits - 1; ++jx) {
+        const int s2 = jx + (jx >= own ? 1 : 0);
+        const bool ok = tk < ntok && s2 < splits;
+        const float4* src = reinterpret_cast<const float4*>(p.part_o + ((long long)s2 * split_rows + g) * kD);
+        x[i][jx][0] = ok ? __ldcg(src + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
+        x[i][jx][1] = ok ? __ldcg(src + 32 + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int rr = sw * 16 + a0 + i, tk = rr & 31, hd = rr >> 5;
+      if (tk >= ntok) continue;
+      const long long g = (long long)(tok0 + tk) * kHq + kvh * kG + hd;
+      const float w_own = fw[(a0 + i) * kU2MaxSplits + own];
+#pragma unroll
+      for (int h2 = 0; h2 < 2; ++h2) {
+        const int c = h2 * 32 + lane;
+        const float4 mine = *reinterpret_cast<const float4*>(stage + rr * kD + (((c & ~7) | ((c ^ rr) & 7)) << 2));
+        float4 acc = make_float4(mine.x * w_own, mine.y * w_own, mine.z * w_own, mine.w * w_own);
+#pragma unroll
+        for (int jx = 0; jx < kU2MaxSplits - 1; ++jx) {
+          const float ws = fw[(a0 + i) * kU2MaxSplits + jx + (jx >= own ? 1 : 0)];  // 0 for a split that does not exist
+          acc.x = fmaf(x[i][jx][h2].x, ws, acc.x); acc.y = fmaf(x[i][jx][h2].y, ws, acc.y);
+          acc.z = fmaf(x[i][jx][h2].z, ws, acc.z); acc.w = fmaf(x[i][jx][h2].w, ws, acc.w);
+        }
+        reinterpret_cast<float4*>(p.out + g * kD)[c] = acc;
+      }
+    }
+  }
 }
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kU2Threads, 1)
@@ -424,35 +542,41 @@ prefill_umma2_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_con
   const int rank = (int)cluster_ctarank();  // == blockIdx.x & 1
   NVJ_U2_PHASE(0);
   NVJ_U2_NOTE(7, 0ull);
+  if (blockIdx.z > 0) {  // the extra splits leave at once when no row's key range is long enough to be split
+    int any = 0;
+    for (int rr = threadIdx.x; rr < p.rows; rr += kU2Threads) any |= p.kv_lens[rr] > (kU2SplitFrom - 1) * kU2Keys ? 1 : 0;
+    if (!__syncthreads_or(any)) return;
+  }
 
   // ---- which (table row, pair of 32-token tiles) this cluster serves; both CTAs compute the same
   if (threadIdx.x == 0) {
     // heaviest pairs (the last tokens of a row see the most keys) get the lowest cluster indices
-    int idx = (gridDim.x >> 1) - 1 - (blockIdx.x >> 1), row = -1, tok0 = 0, ntok = 0, last = 0;
+    int idx = (gridDim.x >> 1) - 1 - (blockIdx.x >> 1), row = -1, tok0 = 0, ntok = 0, last = 0, total = 0;
     for (int r = 0; r < p.rows; ++r) {
       const int lo = p.query_start_loc[r];
       int hi = p.query_start_loc[r + 1];
       hi = hi < p.token_bucket ? hi : p.token_bucket;
       int pairs = hi > lo ? (hi - lo + 2 * kU2Tokens - 1) / (2 * kU2Tokens) : 0;
       if (p.skip_single && p.query_start_loc[r + 1] - lo == 1) pairs = 0;
-      if (idx < pairs) {
+      total += pairs;
+      if (row < 0 && idx < pairs) {
         row = r;
         tok0 = lo + (2 * idx + rank) * kU2Tokens;
         ntok = hi - tok0 < kU2Tokens ? hi - tok0 : kU2Tokens;
         if (ntok < 0) ntok = 0;
         const int pair_end = lo + (2 * idx + 2) * kU2Tokens;
         last = (pair_end < hi ? pair_end : hi) - 1;
-        break;
+        if (gridDim.z == 1) break;  // only the key-range splits need the batch's number of pairs
       }
-      idx -= pairs;
+      if (row < 0) idx -= pairs;
     }
-    sm.row = row; sm.tok0 = tok0; sm.ntok = ntok; sm.pair_last_tok = last; sm.abort_flag = 0;
+    sm.row = row; sm.tok0 = tok0; sm.ntok = ntok; sm.pair_last_tok = last; sm.abort_flag = 0; sm.total_pairs = total;
     sm.idle_index = row < 0 ? idx : -1;  // clusters beyond the last pair: 0, 1, ...
   }
   __syncthreads();
   const int row = sm.row, tok0 = sm.tok0, ntok = sm.ntok;
   if (row < 0) {  // the whole cluster leaves: nothing has been allocated or shared yet
-    if (p.zero_fill && sm.idle_index == 0) {
+    if (p.zero_fill && sm.idle_index == 0 && blockIdx.z == 0) {
       // the first idle cluster (there is always one) zeroes the padding tokens, a quarter per CTA of the cluster pair x KV head
       int real = p.query_start_loc[p.rows];
       real = real < p.token_bucket ? real : p.token_bucket;
@@ -478,13 +602,37 @@ prefill_umma2_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_con
   const int key_end = kv_len < max_pos + 1 ? kv_len : max_pos + 1;
   const int n_tiles = key_end > 0 ? (key_end + kU2Keys - 1) / kU2Keys : 0;
   if (n_tiles == 0) {  // same decision in both CTAs; a row without keys produces zeros
-    if (p.zero_fill) {
+    if (p.zero_fill && blockIdx.z == 0) {
       for (int i = threadIdx.x; i < ntok * kG * (kD / 4); i += kU2Threads) {
         const int t = i / (kG * (kD / 4)), rest = i - t * (kG * (kD / 4));
         reinterpret_cast<float4*>(p.out + ((long long)(tok0 + t) * kHq + kvh * kG) * kD)[rest] = make_float4(0.f, 0.f, 0.f, 0.f);
       }
     }
     return;
+  }
+
+  // Key-range splits of this pair: as many as leave every split kU2MinSplitTiles tiles and as the batch's pairs
+  // leave pair slots for; the splits beyond that leave at once (both CTAs decide alike).
+  int splits = 1, tile0 = 0, my_tiles = n_tiles;
+  if (gridDim.z > 1) {
+    const int room = p.pair_slots / (sm.total_pairs * kHkv > 0 ? sm.total_pairs * kHkv : 1);
+    splits = n_tiles >= kU2SplitFrom ? n_tiles / kU2MinSplitTiles : 1;
+    splits = splits < room ? splits : room;
+    splits = splits < (int)gridDim.z ? splits : (int)gridDim.z;
+    splits = splits > 1 ? splits : 1;
+    if ((int)blockIdx.z >= splits) return;
+    tile0 = (int)blockIdx.z * n_tiles / splits;
+    my_tiles = ((int)blockIdx.z + 1) * n_tiles / splits - tile0;
+  }
+
+  // the query rows, and the block ids of the producer's first eight tiles, are asked for now and arrive while the
+  // pair is being set up
+  uint4 qv[4][4];
+  if (warp >= 2 && p.q_dtype == NVJ_BF16) u2_request_q(p, tok0, ntok, kvh, warp, lane, qv);
+  int first_ids = -1;
+  if (warp == 0) {
+    const int bi = tile0 * 4 + lane;
+    if (bi < (kv_len + kBlk - 1) / kBlk && bi < p.table_width) first_ids = p.block_tables[(long long)row * p.table_width + bi];
   }
 
   if (warp == 1) tmem2_alloc(smem_u32(&sm.tmem_base), kU2TmemCols);
@@ -509,11 +657,11 @@ prefill_umma2_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_con
   tc_fence_after_sync();
   const uint32_t tmem = sm.tmem_base;
   NVJ_U2_PHASE(1);
-  NVJ_U2_NOTE(7, (unsigned long long)n_tiles);
+  NVJ_U2_NOTE(7, (unsigned long long)my_tiles);
 
-  if (warp == 0) u2_producer(&k_map, &v_map, p, sm, row, kvh, kv_len, n_tiles, rank, lane);
-  else if (warp == 1) { if (rank == 0) u2_mma_warp(sm, p, tmem, n_tiles); }
-  else u2_softmax_warps(sm, p, tmem, tok0, ntok, kvh, kv_len, n_tiles, warp, lane);
+  if (warp == 0) u2_producer(&k_map, &v_map, p, sm, row, kvh, kv_len, tile0, my_tiles, rank, lane, first_ids);
+  else if (warp == 1) { if (rank == 0) u2_mma_warp(sm, p, tmem, my_tiles); }
+  else u2_softmax_warps(sm, p, tmem, tok0, ntok, kvh, kv_len, tile0, my_tiles, splits, warp, lane, qv);
 
   tc_fence_before_sync();
   __syncthreads();
@@ -542,6 +690,28 @@ static U2EncodeTiledFn u2_encode_fn() {
   return fn;
 }
 
+static int u2_pair_slots() {  // CTA pairs that run at once: half the SMs of the current device
+  static PerDeviceFlags slots;
+  const int dev = current_device();
+  if (dev < 0) return 0;
+  int n = slots.v[dev].load(std::memory_order_acquire);
+  if (n == 0) {
+    int sms = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    n = sms / 2;
+    slots.v[dev].store(n, std::memory_order_release);
+  }
+  return n;
+}
+
+// Room for the un-normalised rows and (max, sum) pairs of the splits of the largest batch that is split at all:
+// splits x tokens never exceeds the pair slots x 64 tokens (plus one pair per split of rounding).
+size_t prefill_split_bytes() {
+  const int slots = u2_pair_slots();
+  const size_t tokens = (size_t)(slots > 0 ? slots : 74) * 2 * kU2Tokens / kHkv + (size_t)kU2MaxSplits * 2 * kU2Tokens;
+  return ws_round(sizeof(float) * tokens * kHq * (kD + 2));
+}
+
 static bool u2_make_map(CUtensorMap* map, const void* base, uint64_t outer) {
   const cuuint64_t dims[3] = {(cuuint64_t)kD, (cuuint64_t)kHkv, outer};
   const cuuint64_t strides[2] = {(cuuint64_t)kRowBytes, (cuuint64_t)kRowBytes * kHkv};
@@ -557,7 +727,8 @@ int launch_prefill_umma2(const void* q, int q_dtype, const char* k_cache, const 
                          long long num_blocks, const int32_t* block_tables, int table_width,
                          const int32_t* kv_lens, const int32_t* positions, const int32_t* query_start_loc,
                          int rows, int token_bucket, float scale, float* out, int32_t* status,
-                         int skip_single, int split_p, cudaStream_t stream) {
+                         int skip_single, int split_p, int32_t* split_counters, float* split_area, size_t split_bytes,
+                         cudaStream_t stream) {
   static PerDeviceFlags opted_in;
   constexpr int kSmemBytes = (int)sizeof(Umma2Smem) + 1024;
   static_assert(kSmemBytes <= 232448, "tiles exceed the shared memory of one CTA");
@@ -579,7 +750,27 @@ int launch_prefill_umma2(const void* q, int q_dtype, const char* k_cache, const 
   p.out = out; p.status = status; p.num_blocks = num_blocks; p.rows = rows; p.token_bucket = token_bucket;
   p.table_width = table_width; p.skip_single = skip_single; p.scale = scale; p.split_p = split_p;
   const int pairs = (token_bucket + 2 * kU2Tokens - 1) / (2 * kU2Tokens) + rows;
-  dim3 grid(2 * pairs, kHkv, 1);
+  // Key-range splits: only while the batch's token bucket leaves pair slots free, as many as the lent area holds and
+  // the counters cover; the kernel settles the number per pair from what the batch really holds.
+  int splits = 1;
+  const int slots = u2_pair_slots();
+  if (split_counters && split_area && slots > 0 && 2 * pairs * kHkv <= kSplitCounters) {
+    const int least = (token_bucket + 2 * kU2Tokens - 1) / (2 * kU2Tokens) * kHkv;
+    splits = slots / least < kU2MaxSplits ? slots / least : kU2MaxSplits;
+    const size_t per_split = sizeof(float) * (size_t)token_bucket * kHq * (kD + 2);
+    const size_t room = split_bytes < prefill_split_bytes() ? split_bytes : prefill_split_bytes();
+    while (splits > 1 && ws_round(per_split * splits) > room) --splits;
+    if (splits < 1) splits = 1;
+    // The partials end where the lent area ends: its low end borders arrival counters of calls with more rows.
+    split_area = reinterpret_cast<float*>(reinterpret_cast<char*>(split_area) + split_bytes - ws_round(per_split * splits));
+  }
+  if (splits > 1) {
+    p.part_o = split_area;
+    p.part_ml = split_area + (size_t)splits * token_bucket * kHq * kD;
+    p.split_counters = split_counters;
+    p.pair_slots = slots;
+  }
+  dim3 grid(2 * pairs, kHkv, splits);
   prefill_umma2_kernel<<<grid, kU2Threads, kSmemBytes, stream>>>(k_map, v_map, p);
   return cudaGetLastError() == cudaSuccess ? NVJ_OK : NVJ_ERR_LAUNCH;
 }

@@ -89,7 +89,8 @@ class _Workspace:
         lib = _lib.load()
         with torch.cuda.device(device):  # one buffer serves the width-1 and the wide kernel (never in flight together)
             nbytes = max(int(lib.nvj_paged_decode_workspace_bytes(int(max_batch))),
-                         int(lib.nvj_paged_decode_wide_workspace_bytes(int(max_batch))))
+                         int(lib.nvj_paged_decode_wide_workspace_bytes(int(max_batch))),
+                         int(lib.nvj_paged_prefill_workspace_bytes(int(max_batch))))
         if nbytes <= 0:
             raise NvjError("nvj_paged_decode_workspace_bytes failed (no CUDA device?)")
         self.max_batch = int(max_batch)
@@ -576,10 +577,16 @@ def packed_paged_prefill_attention(query, k_cache_layer, v_cache_layer, block_ta
         with torch.cuda.stream(side):
             ws = _workspace(q.device, rows)  # the side stream's own workspace
             rc1 = call(lib.nvj_paged_prefill_packed_part, ws, 1, cta_limit)
+        # no workspace for the tiles: key-range splits would ask for the SMs the decode pass is running on
         rc2 = call(lib.nvj_paged_prefill_packed_part, None, 2, 0)
         cur.wait_stream(side)
         check(rc1, "nvj_paged_prefill_packed_part (decode rows)")
         check(rc2, "nvj_paged_prefill_packed_part (tiles)")
+    elif model_shape and variant != 1 and num_decode_rows == 0 and os.environ.get("NVJ_PREFILL_KEY_SPLITS", "1") != "0":
+        # no decode rows: the tile kernel alone (it zero-fills what it does not write), with the workspace lent for
+        # the key-range splits of a short batch
+        ws = _workspace(q.device, rows)
+        check(call(lib.nvj_paged_prefill_packed_part, ws, 3, 0), "nvj_paged_prefill_packed_part (tiles, all rows)")
     else:
         ws = _workspace(q.device, rows) if (num_decode_rows is None or num_decode_rows > 0) else None
         check(call(lib.nvj_paged_prefill_packed, ws), "nvj_paged_prefill_packed")

@@ -279,3 +279,46 @@ def test_row_argmax_first_maximum_wins():
         want = torch.argmax(y, dim=1)
         assert int(t[2]) == n - 1 and int(t[4]) == 0
         assert torch.equal(t[[0, 1, 3]].long(), want[[0, 1, 3]])
+
+
+def test_short_chunk_with_key_range_splits_matches_the_unsplit_kernels_and_the_oracle():
+    """A 512-token chunk behind a 512-token prefix, plus a ragged second row: too few CTA pairs to fill the GPU, so the
+    pair kernel splits every tile's key range (the wrapper lends it the workspace); the single-CTA tile kernel never
+    splits.  Both must agree with the oracle, and the split counters must be back at zero for the next call."""
+    import numpy as np
+    import torch
+    from helpers import BS, SCALE, to_numpy, to_torch
+    from nano_vllm_jax_b200.kernels import paged_kv as K
+    from oracle import kv_cache_ref as R
+    rng = np.random.default_rng(21)
+    pool = 512
+    lens = np.array([1024, 300], np.int32)           # kv lengths after the chunk
+    take = np.array([512, 44], np.int32)             # chunk tokens per row
+    k = rng.standard_normal((1, pool, BS, 2, 256), dtype=np.float32)
+    v = rng.standard_normal((1, pool, BS, 2, 256), dtype=np.float32)
+    perm = rng.permutation(pool).astype(np.int32)
+    tables = np.zeros((2, 64), np.int32)
+    tables[0, :64] = perm[:64]
+    tables[1, :19] = perm[64:83]
+    bucket = 576
+    qsl = np.array([0, 512, 556], np.int32)
+    pos = np.zeros((1, bucket), np.int32)
+    pos[0, :512] = np.arange(512, 1024)
+    pos[0, 512:556] = np.arange(256, 300)
+    q = rng.standard_normal((1, bucket, 8, 256), dtype=np.float32)
+    tk, tv = to_torch(k).to(torch.bfloat16), to_torch(v).to(torch.bfloat16)
+    tq = to_torch(q).to(torch.bfloat16)
+    args = (tk[0], tv[0], to_torch(tables), to_torch(lens), to_torch(pos), to_torch(qsl), BS, SCALE, 4)
+    outs = {}
+    for variant in (4, 3, 4):  # the split path twice: the second call finds the counters as the first left them
+        outs[variant] = to_numpy(K.packed_paged_prefill_attention(tq, *args, variant=variant, num_decode_rows=0)).reshape(bucket, 8, 256)
+    torch.cuda.synchronize()
+    rid = np.zeros((1, bucket), np.int32)
+    rid[0, 512:556] = 1
+    ref = R.paged_attention_prefill_packed(to_numpy(tq), to_numpy(tk), to_numpy(tv), tables, lens, pos, rid, qsl, BS, SCALE, 4, 0)
+    ref = np.asarray(ref, np.float32).reshape(bucket, 8, 256)
+    for variant, out in outs.items():
+        err = np.abs(out[:556] - ref[:556]).max()
+        assert err <= 2e-3, f"variant {variant}: max-abs {err}"
+        assert not out[556:].any()
+    assert np.abs(outs[4] - outs[3]).max() <= 2e-3
