@@ -131,8 +131,12 @@ def decode_cases(dev, iters):
         qw = _randn_bf16((rows, width, HQ, D), 6, dev)
         wpos = (t_lens[:, None] - width + torch.arange(width, device=dev, dtype=torch.int32)[None, :]).contiguous()
         wbytes = kv_bytes + table_bytes + rows * width * (HQ * D * 2 + HQ * D * 4)
-        report("wide decode, %d query tokens per row (tensor-core streaming kernel)" % width,
+        report("wide decode, %d query tokens per row (automatic: mma.sync tiles up to width 4, tcgen05 beyond)" % width,
                big.run(lambda: kvc.paged_attention_decode(qw, k, v, tables, t_lens, BS, SCALE, 4, positions=wpos, out_dtype=torch.float32)),
+               wbytes, {"workload": "c2, width %d" % width})
+        other, name = (1, "mma.sync tiles, two row tiles per warp pair") if width > 4 else (2, "tcgen05, query rows in a 128-row tile")
+        report("wide decode, %d query tokens per row (%s)" % (width, name),
+               big.run(lambda: K.paged_decode_attention_wide(qw, k[0], v[0], tables, t_lens, wpos, SCALE, form=other)),
                wbytes, {"workload": "c2, width %d" % width})
     width = 4
     qw = _randn_bf16((rows, width, HQ, D), 6, dev)

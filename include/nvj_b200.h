@@ -270,6 +270,18 @@ int nvj_paged_decode_static_scratch(const void* q, int q_dtype,
  * rows of equal width instead).
  */
 size_t nvj_paged_decode_wide_workspace_bytes(int max_batch);
+/*
+ * nvj_paged_decode_wide_form: the same call with the kernel chosen by the caller.  form 0 = automatic (what
+ * nvj_paged_decode_wide does: widths 1-4 on mma.sync tiles, 16 query rows per warp; widths 5-8 on tcgen05, the 4 x width
+ * query rows of a KV head in a 128-row tile with scores and output in tensor memory, a row cut over several CTA pairs
+ * folded by a second small launch), 1 = mma.sync tiles (widths 5-8: two row tiles per warp pair, ~1.9x the width-1
+ * time), 2 = tcgen05 at any width 1-8 (NVJ_ERR_UNSUPPORTED without a tensor-map encoder or for scale <= 0).
+ */
+int nvj_paged_decode_wide_form(const void* q, const void* k_cache_layer, const void* v_cache_layer,
+                               int64_t num_blocks, const int32_t* block_tables, int table_width,
+                               const int32_t* seq_lens, const int32_t* positions, int batch, int width,
+                               float scale, float* out, void* workspace, size_t workspace_bytes,
+                               int form, nvj_stream_t stream);
 int nvj_paged_decode_wide(const void* q, const void* k_cache_layer, const void* v_cache_layer,
                           int64_t num_blocks, const int32_t* block_tables, int table_width,
                           const int32_t* seq_lens, const int32_t* positions, int batch, int width,

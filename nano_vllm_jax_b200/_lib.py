@@ -39,6 +39,8 @@ SIGNATURES = {
     "nvj_paged_decode_wide_workspace_bytes": (c_size_t, [c_int]),
     "nvj_paged_decode_wide": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int, c_void_p, c_void_p,
                                       c_int, c_int, c_float, c_void_p, c_void_p, c_size_t, c_void_p]),
+    "nvj_paged_decode_wide_form": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_int, c_void_p, c_void_p,
+                                           c_int, c_int, c_float, c_void_p, c_void_p, c_size_t, c_int, c_void_p]),
     "nvj_paged_decode": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int64, c_int, c_int,
                                  c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                  c_float, c_void_p, c_void_p, c_size_t, c_int, c_void_p]),

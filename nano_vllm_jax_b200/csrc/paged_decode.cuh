@@ -49,6 +49,9 @@ struct DecodeParams {
   // upper bound on the CTAs of the streaming kernels (0: one, or two, per SM): a caller that runs another kernel
   // beside the decode pass leaves that kernel's SMs free
   int cta_limit;
+  // which wide kernel serves rows of several query tokens: 0 = automatic (mma.sync tiles up to width 4, tcgen05 beyond),
+  // 1 = mma.sync tiles, 2 = tcgen05
+  int wide_form;
   float* out;
   // workspace
   int32_t* status;
@@ -163,7 +166,8 @@ int decode_num_ctas();  // 2 per SM of the current device
 int launch_decode_generic(const DecodeParams& p, cudaStream_t stream);
 int launch_decode_pipelined(const DecodeParams& p, int num_ctas, cudaStream_t stream);
 int decode_wide_num_ctas();  // 1 per SM of the current device
-int launch_decode_wide(const DecodeParams& p, cudaStream_t stream);  // tensor-core streaming kernel, width 1..4
+int launch_decode_wide(const DecodeParams& p, cudaStream_t stream);  // tensor-core streaming kernels, width 1..8
+int launch_decode_umma(const DecodeParams& p, cudaStream_t stream);  // the tcgen05 form, rows already appended
 int append_decode_rows(const void* new_k, const void* new_v, const int32_t* positions,
                        const int32_t* seq_lens, void* k_cache, void* v_cache, int kv_dtype,
                        long long num_blocks, int block_size, int row_elems,

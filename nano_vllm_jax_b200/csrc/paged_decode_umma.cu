@@ -1,0 +1,510 @@
+// Paged GQA decode attention for rows of several query tokens (speculative verification, widths up to 8) on the
+// 5th-generation tensor cores: tcgen05.mma with the scores and the output accumulators in tensor memory.
+//
+// Why a second wide kernel.  decode_wide_kernel (mma.sync) holds one 16-row tile of query rows per warp; rows of
+// 5..8 tokens are two tiles per KV head, every warp then walks every block, and the kernel takes 1.9x its width-1
+// time: 512 mma.sync per block and SM are more than the legacy tensor path issues in the HBM time of a block.  Here
+// the 4 x width <= 32 query rows of one KV head sit in lanes 0..31 of a 128-row UMMA tile (the other lanes compute
+// on whatever they hold and are never read): per block and KV head 16 MMAs of N = 16 for the scores and two of
+// N = 256 for the weighted sum, ~1500 tensor cycles per 64 keys against ~3000 cycles of HBM time.
+//
+// Work split.  The blocks of all rows form one sequence cut into equal ranges as in the other decode kernels
+// (decode_parts.cuh), but a range belongs to a PAIR of CTAs, one per KV head: CTA 2c + h streams head h's half of
+// every block of range c (8 KiB of K and 8 KiB of V per block, one TMA box each), so every K/V byte still crosses
+// HBM once.  One CTA per SM (192 KiB of shared memory: twelve blocks in flight; 512 TMEM columns).
+//   warp 0   softmax and epilogue: lane r = query row r = token * 4 + head of the group.  Per row segment it stages
+//            the query rows into tensor memory, per tile of up to four blocks (64 keys) reads the scores
+//            (tcgen05.ld), masks (key < length, key <= the token's position), keeps the running maximum lazily (O in
+//            tensor memory is rescaled only when a tile exceeds it by 2^8) and writes the weights back over the
+//            scores as two bf16 terms (hi + lo); at the end of the segment it reads O and stores the row (whole row
+//            in this range) or the un-normalised partial with its (max, sum).
+//   warp 1   producer: block ids straight from the block table (32 at a time), TMA boxes into the ring.
+//   warp 2   MMA issue: S(t) = Q K(t)^T block by block into one of two score buffers, O += P(t) V(t) once the
+//            weights are written; S(t + 2) follows P V (t).  tcgen05.commit releases ring stages and signals the
+//            softmax warp.
+// A row cut over several ranges is folded afterwards by decode_umma_merge_kernel (one CTA per row, stream order
+// instead of counters and fences): the merge costs a second small launch, which rows of this width can afford.
+// Every wait is bounded; on a timeout the kernel flags NVJ_DEV_TIMEOUT, stops issuing, lets copies in flight land
+// and still frees its tensor memory.  A block id outside the pool is flagged and its box is fetched from beyond the
+// tensor (zeros), so nothing foreign is read; the row's result is then meaningless but finite.
+// Semantics: nanovllm_jax/kv_cache.py:852-998 with query width > 1 (key p of row b is visible to token t when
+// p < seq_lens[b] and, with positions given, p <= positions[b, t]).
+
+#include <cuda.h>
+
+#include "decode_parts.cuh"
+#include "umma.cuh"
+
+namespace nvj {
+
+constexpr int kUdStages = 12;     // cache blocks (K and V of one KV head, 16 KiB) in flight
+constexpr int kUdTileBlocks = 4;  // blocks per softmax step: 64 keys
+constexpr int kUdTmemCols = 512;
+constexpr int kUdColQ = 0;        // query rows as the A operand: 256 bf16 per row = 128 columns
+constexpr int kUdColS = 128;      // two score buffers of 64 columns; the weights (hi: 32 columns, lo: 32) overwrite theirs
+constexpr int kUdColO = 256;      // output accumulator: columns [256, 512)
+constexpr int kUdHalfBlock = kBlk * kD * 2;  // K (or V) of one KV head of one block: 8 KiB
+constexpr float kUdRescaleGap = 8.f;
+constexpr int kUdMaxWidth = 8;
+
+struct UdSmem {
+  alignas(1024) char kv[kUdStages][2][kUdHalfBlock];  // [stage][K|V][64-d chunk][16 tokens][128 B], swizzled
+  alignas(8) unsigned long long full_bar[kUdStages], empty_bar[kUdStages], q_full, s_full[2], p_full, pv_done;
+  float red[384];
+  int scan[16];
+  int start_b, start_j, abort_flag;
+  uint32_t tmem_base;
+};
+
+// One KV head's half of a block: the box {64 dims, 16 tokens, 4 chunks, 1 head} of the 4-D view of a cache layer.
+__device__ __forceinline__ void ud_tma_half_block(uint32_t dst, const CUtensorMap* map, int token, int kvh, uint32_t bar) {
+  uint64_t policy;  // every block is read once
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3, %4, %5}], [%6], %7;"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(0), "r"(token), "r"(0), "r"(kvh), "r"(bar), "l"(policy)
+      : "memory");
+}
+
+// ---- warp 1: TMA loads --------------------------------------------------------------------------
+__device__ __forceinline__ void ud_producer(const CUtensorMap* k_map, const CUtensorMap* v_map, const DecodeParams& p,
+                                            UdSmem& sm, int kvh, int b, int j, long long g, long long g1, int lane) {
+  const int oob = (int)(p.num_blocks * kBlk);  // a box that starts here is filled with zeros
+  Seg s;
+  int it = 0;
+  while (next_seg(p, b, j, g, g1, s)) {
+    const long long tbase = decode_table_base(p, s.b);
+    for (int jb = s.j0; jb < s.j1; jb += 32) {
+      const int n = s.j1 - jb < 32 ? s.j1 - jb : 32;
+      int id = -1;
+      if (lane < n) {
+        id = p.block_tables[tbase + jb + lane];
+        if (id < 0 || id >= p.num_blocks) {
+          atomicOr(p.status, NVJ_DEV_BAD_BLOCK_ID);
+          id = -1;
+        }
+      }
+      for (int i = 0; i < n; ++i, ++it) {
+        const int blk = __shfl_sync(kFullMask, id, i);
+        const int stage = it % kUdStages;
+        if (it >= kUdStages && !um_wait(&sm.empty_bar[stage], (uint32_t)((it / kUdStages) - 1) & 1u, &sm.abort_flag, p.status)) return;
+        if (lane == 0) {
+          const uint32_t fb = smem_u32(&sm.full_bar[stage]);
+          const int token = blk >= 0 ? blk * kBlk : oob;
+          mbar_arrive_expect_tx(fb, 2u * kUdHalfBlock);
+          ud_tma_half_block(smem_u32(sm.kv[stage][0]), k_map, token, kvh, fb);
+          ud_tma_half_block(smem_u32(sm.kv[stage][1]), v_map, token, kvh, fb);
+        }
+        __syncwarp();
+      }
+    }
+  }
+}
+
+// ---- warp 2: MMA issue --------------------------------------------------------------------------
+// Scores of the blocks [first, first + count) of the CTA's block sequence into score buffer `buf`, 16 columns per block.
+__device__ __forceinline__ bool ud_issue_s(UdSmem& sm, const DecodeParams& p, uint32_t tmem, uint64_t desc0, int first, int count,
+                                           int buf) {
+  for (int i = 0; i < count; ++i) {
+    const int it = first + i, stage = it % kUdStages;
+    if (!um_wait(&sm.full_bar[stage], (uint32_t)(it / kUdStages) & 1u, &sm.abort_flag, p.status)) return false;
+    tc_fence_after_sync();
+    if (um_elect_one()) {
+      constexpr uint32_t idesc = umma_idesc(kBlk, false);
+      const uint64_t k_desc = desc0 + (uint64_t)((stage * 2 * kUdHalfBlock) >> 4);
+      const uint32_t d = tmem + kUdColS + buf * 64 + i * kBlk;
+#pragma unroll
+      for (int ks = 0; ks < 16; ++ks)  // 16 dims per MMA: 8 columns of Q; K chunk ks / 4, 32 bytes into its swizzled rows
+        umma_bf16_ts(d, tmem + kUdColQ + ks * 8, k_desc + (uint64_t)(((ks >> 2) * (kBlk * 128) + (ks & 3) * 32) >> 4), idesc,
+                     ks > 0 ? 1u : 0u);
+    }
+    __syncwarp();
+  }
+  if (um_elect_one()) umma_commit(smem_u32(&sm.s_full[buf]));
+  __syncwarp();
+  return true;
+}
+
+__device__ __forceinline__ void ud_mma_warp(UdSmem& sm, const DecodeParams& p, uint32_t tmem, int b, int j, long long g,
+                                            long long g1) {
+  const uint64_t desc0 = umma_desc(smem_u32(&sm.kv[0][0][0]), 16, 1024);             // K: keys are rows, dims contracted
+  const uint64_t v_desc0 = umma_desc(smem_u32(&sm.kv[0][1][0]), kBlk * 128, 1024);   // V: 64-d chunks 2 KiB apart, keys contracted
+  Seg s;
+  int it0 = 0;      // index of the segment's first block in the CTA's block sequence
+  uint32_t gt = 0;  // tiles issued so far, over all segments: picks the score buffer and the barrier phases
+  uint32_t seg = 0;
+  while (next_seg(p, b, j, g, g1, s)) {
+    const int nblk = s.j1 - s.j0, nt = (nblk + kUdTileBlocks - 1) / kUdTileBlocks;
+    if (!um_wait(&sm.q_full, seg & 1u, &sm.abort_flag, p.status)) return;
+    for (int t = 0; t < 2 && t < nt; ++t) {
+      const int cnt = nblk - t * kUdTileBlocks < kUdTileBlocks ? nblk - t * kUdTileBlocks : kUdTileBlocks;
+      if (!ud_issue_s(sm, p, tmem, desc0, it0 + t * kUdTileBlocks, cnt, (int)((gt + t) & 1u))) return;
+    }
+    for (int t = 0; t < nt; ++t, ++gt) {
+      const int cnt = nblk - t * kUdTileBlocks < kUdTileBlocks ? nblk - t * kUdTileBlocks : kUdTileBlocks;
+      if (!um_wait(&sm.p_full, gt & 1u, &sm.abort_flag, p.status)) return;
+      tc_fence_after_sync();
+      if (um_elect_one()) {
+        constexpr uint32_t idesc = umma_idesc(kD, true);
+        const uint32_t pa = tmem + kUdColS + (gt & 1u) * 64;
+        for (int i = 0; i < cnt; ++i) {  // 16 keys per MMA: 8 columns of P, the block's two 8-key groups of V
+          const int stage = (it0 + t * kUdTileBlocks + i) % kUdStages;
+          const uint64_t dv = v_desc0 + (uint64_t)((stage * 2 * kUdHalfBlock) >> 4);
+          umma_bf16_ts(tmem + kUdColO, pa + i * 8, dv, idesc, (t > 0 || i > 0) ? 1u : 0u);
+          umma_bf16_ts(tmem + kUdColO, pa + 32 + i * 8, dv, idesc, 1u);
+        }
+        for (int i = 0; i < cnt; ++i) umma_commit(smem_u32(&sm.empty_bar[(it0 + t * kUdTileBlocks + i) % kUdStages]));
+        umma_commit(smem_u32(&sm.pv_done));
+      }
+      __syncwarp();
+      // S(t + 2) overwrites the columns P V (t) reads P(t) from, and every phase of pv_done is observed in turn
+      if (!um_wait(&sm.pv_done, gt & 1u, &sm.abort_flag, p.status)) return;
+      if (t + 2 < nt) {
+        const int c2 = nblk - (t + 2) * kUdTileBlocks < kUdTileBlocks ? nblk - (t + 2) * kUdTileBlocks : kUdTileBlocks;
+        if (!ud_issue_s(sm, p, tmem, desc0, it0 + (t + 2) * kUdTileBlocks, c2, (int)(gt & 1u))) return;
+      }
+    }
+    it0 += nblk;
+    ++seg;
+  }
+}
+
+// ---- warp 0: query staging, softmax, epilogue ----------------------------------------------------
+__device__ __forceinline__ void ud_softmax_warp(UdSmem& sm, const DecodeParams& p, uint32_t tmem, int kvh, int b, int j,
+                                                long long g, long long g1, int range, int lane) {
+  const int tok = lane >> 2, head = lane & 3;
+  const bool real = tok < p.width;
+  const float scale_log2 = p.scale * kLog2e;
+  const int slot_rows = p.width * kHq;
+  Seg s;
+  uint32_t gt = 0;
+  while (next_seg(p, b, j, g, g1, s)) {
+    const long long qbase = (long long)s.b * p.width;
+    {  // this row's 256 dims -> 128 TMEM columns, two bf16 per column
+      const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.q) +
+                                                        ((qbase + (real ? tok : 0)) * kHq + kvh * kG + head) * kD);
+#pragma unroll 1
+      for (int part = 0; part < 8; ++part) {  // 32 dims = 16 columns at a time
+        uint32_t w[16];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const uint4 u = real ? ld_nc_u4(src + part * 4 + i) : make_uint4(0u, 0u, 0u, 0u);
+          w[4 * i] = u.x; w[4 * i + 1] = u.y; w[4 * i + 2] = u.z; w[4 * i + 3] = u.w;
+        }
+        tmem_st16(tmem + kUdColQ + part * 16, w);
+      }
+      tmem_st_wait();
+      tc_fence_before_sync();
+      mbar_arrive(smem_u32(&sm.q_full));
+    }
+    const int my_pos = real ? (p.positions ? p.positions[qbase + tok] : 0x7fffffff) : -1;
+    const int last_key = my_pos < s.len - 1 ? my_pos : s.len - 1;  // last key this row may see
+    float m_row = -INFINITY, l_row = 0.f;                           // m_row in units of log2(e) * scale
+    const int nblk = s.j1 - s.j0, nt = (nblk + kUdTileBlocks - 1) / kUdTileBlocks;
+    for (int t = 0; t < nt; ++t, ++gt) {
+      const uint32_t s_tmem = tmem + kUdColS + (gt & 1u) * 64;
+      if (!um_wait(&sm.s_full[gt & 1u], (gt >> 1) & 1u, &sm.abort_flag, p.status)) return;
+      tc_fence_after_sync();
+      float sc[64];
+      {
+        float a[32];
+        tmem_ld32(s_tmem, a);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) sc[i] = a[i];
+        tmem_ld32(s_tmem + 32, a);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) sc[32 + i] = a[i];
+      }
+      const int cnt = nblk - t * kUdTileBlocks < kUdTileBlocks ? nblk - t * kUdTileBlocks : kUdTileBlocks;
+      int lim = last_key - (s.j0 + t * kUdTileBlocks) * kBlk;  // columns [0, lim] are visible
+      lim = lim < cnt * kBlk - 1 ? lim : cnt * kBlk - 1;       // columns of blocks the tile does not have hold old scores
+      float tmax = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 64; ++i) {
+        sc[i] = i <= lim ? sc[i] : -INFINITY;
+        tmax = fmaxf(tmax, sc[i]);
+      }
+      tmax *= scale_log2;  // scale > 0
+      if (t == 0) {
+        m_row = tmax;
+      } else if (__any_sync(kFullMask, tmax > m_row + kUdRescaleGap)) {
+        // rare: raise the maxima and rescale O, once the last P V has landed
+        if (!um_wait(&sm.pv_done, (gt - 1) & 1u, &sm.abort_flag, p.status)) return;
+        tc_fence_after_sync();
+        const float m_new = fmaxf(m_row, tmax);
+        const float f = m_new == -INFINITY ? 1.f : ex2_approx(m_row - m_new);
+        m_row = m_new;
+        l_row *= f;
+#pragma unroll 1
+        for (int cc = 0; cc < kD / 32; ++cc) {
+          float o[32];
+          tmem_ld32(tmem + kUdColO + cc * 32, o);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] *= f;
+          tmem_st32(tmem + kUdColO + cc * 32, o);
+        }
+      }
+      const float neg_m = m_row == -INFINITY ? 0.f : -m_row;
+      uint32_t hi[32], lo[32];
+#pragma unroll
+      for (int e = 0; e < 32; ++e) {
+        const float p0 = ex2_approx(fmaf(sc[2 * e], scale_log2, neg_m)), p1 = ex2_approx(fmaf(sc[2 * e + 1], scale_log2, neg_m));
+        l_row += p0 + p1;
+        const __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+        const __nv_bfloat162 r2 = __floats2bfloat162_rn(p0 - __low2float(h), p1 - __high2float(h));
+        hi[e] = *reinterpret_cast<const uint32_t*>(&h);
+        lo[e] = *reinterpret_cast<const uint32_t*>(&r2);
+      }
+      // every phase of pv_done is observed in turn (a parity wait tells only two consecutive phases apart)
+      if (gt >= 1 && !um_wait(&sm.pv_done, (gt - 1) & 1u, &sm.abort_flag, p.status)) return;
+      {  // P(t) as the A operand of P V: keys 2j, 2j + 1 in column j; hi in columns [0, 32), lo in [32, 64)
+        uint32_t w[16];
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) w[i] = q4 < 2 ? hi[(q4 & 1) * 16 + i] : lo[(q4 & 1) * 16 + i];
+          tmem_st16(s_tmem + q4 * 16, w);
+        }
+      }
+      tmem_st_wait();
+      tc_fence_before_sync();
+      mbar_arrive(smem_u32(&sm.p_full));
+    }
+    // ---- end of the segment: O -> the output row (the whole row lies in this range) or this range's partial
+    if (!um_wait(&sm.pv_done, (gt - 1) & 1u, &sm.abort_flag, p.status)) return;
+    tc_fence_after_sync();
+    const bool whole_row = (s.j0 == 0 && s.j1 == s.nb);
+    const float inv = whole_row ? (l_row > 0.f ? 1.f / l_row : 0.f) : 1.f;
+    const int slot = partial_slot(range, s.j0 == 0);
+    const int row_in_slot = tok * kHq + kvh * kG + head;
+    float* dst = whole_row ? p.out + ((qbase + tok) * kHq + kvh * kG + head) * kD
+                           : p.part_acc + ((long long)slot * slot_rows + row_in_slot) * kD;
+#pragma unroll 1
+    for (int cc = 0; cc < kD / 32; ++cc) {
+      float o[32];
+      tmem_ld32(tmem + kUdColO + cc * 32, o);
+      if (real) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 4)
+          *reinterpret_cast<float4*>(dst + cc * 32 + i) = make_float4(o[i] * inv, o[i + 1] * inv, o[i + 2] * inv, o[i + 3] * inv);
+      }
+    }
+    if (real && !whole_row)
+      *reinterpret_cast<float2*>(p.part_ml + ((long long)slot * slot_rows + row_in_slot) * 2) =
+          make_float2(m_row == -INFINITY ? kNegBig : m_row, l_row);
+    tc_fence_before_sync();  // the next segment's query rows and first P V overwrite what was just read
+  }
+}
+
+__global__ void __launch_bounds__(kDecodeThreads, 1)
+decode_umma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map, DecodeParams p) {
+  extern __shared__ unsigned char ud_smem_raw[];
+  UdSmem& sm = *reinterpret_cast<UdSmem*>((reinterpret_cast<uintptr_t>(ud_smem_raw) + 1023) & ~(uintptr_t)1023);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kvh = blockIdx.x & 1, range = blockIdx.x >> 1, ranges = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&k_map)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&v_map)) : "memory");
+    sm.start_b = p.batch; sm.start_j = 0; sm.abort_flag = 0;
+  }
+  // ---- pass 1: total number of blocks; zero the output of inactive rows
+  int mine = 0;
+  for (int base = 0; base < p.batch; base += kDecodeThreads) {
+    const int b = base + threadIdx.x;
+    int len = 0;
+    if (b < p.batch) len = decode_row_len(p, b);
+    mine += (len + kBlk - 1) / kBlk;
+    const unsigned idle = __ballot_sync(kFullMask, b < p.batch && len <= 0 && (b % (int)gridDim.x) == (int)blockIdx.x);
+    for (unsigned m = idle; m; m &= m - 1) {
+      const int bb = base + (warp << 5) + (__ffs(m) - 1);
+      float4* o = reinterpret_cast<float4*>(p.out + (long long)bb * p.width * kHq * kD);
+      for (int i = lane; i < p.width * kHq * kD / 4; i += 32) o[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  }
+  int total = 0;
+  cta_inclusive_scan(mine, sm.scan, total);
+  if (total == 0) return;
+  const Partition pt = make_partition(total, ranges);
+  if (range >= pt.n) return;
+  const long long g0 = pt.start(range);
+  const long long g1 = pt.start(range + 1);
+  if (g0 == g1) return;
+
+  // ---- pass 2: locate (row, block) of g0
+  long long carry = 0;
+  for (int base = 0; base < p.batch && carry <= g0; base += kDecodeThreads) {
+    const int b = base + threadIdx.x;
+    int n = 0;
+    if (b < p.batch) n = (decode_row_len(p, b) + kBlk - 1) / kBlk;
+    int chunk_total = 0;
+    const long long excl = carry + cta_inclusive_scan(n, sm.scan, chunk_total) - n;
+    if (n > 0 && excl <= g0 && g0 < excl + n) { sm.start_b = b; sm.start_j = (int)(g0 - excl); }
+    carry += chunk_total;
+  }
+  if (warp == 2) tmem_alloc(smem_u32(&sm.tmem_base), kUdTmemCols);
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kUdStages; ++i) {
+      mbar_init(smem_u32(&sm.full_bar[i]), 1);
+      mbar_init(smem_u32(&sm.empty_bar[i]), 1);
+    }
+    mbar_init(smem_u32(&sm.q_full), 32);
+    mbar_init(smem_u32(&sm.s_full[0]), 1);
+    mbar_init(smem_u32(&sm.s_full[1]), 1);
+    mbar_init(smem_u32(&sm.p_full), 32);
+    mbar_init(smem_u32(&sm.pv_done), 1);
+    mbar_fence_init();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = sm.tmem_base;
+  const int b0 = sm.start_b, j0 = sm.start_j;
+
+  if (warp == 0) ud_softmax_warp(sm, p, tmem, kvh, b0, j0, g0, g1, range, lane);
+  else if (warp == 1) ud_producer(&k_map, &v_map, p, sm, kvh, b0, j0, g0, g1, lane);
+  else if (warp == 2) ud_mma_warp(sm, p, tmem, b0, j0, g0, g1);
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (sm.abort_flag) {  // give copies and MMAs in flight time to land before the CTA's memory is released
+    const unsigned long long t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 2) tmem_dealloc(tmem, kUdTmemCols);
+}
+
+// One CTA per row: a row whose blocks were cut over several ranges is folded from the ranges' partials.  Runs behind
+// decode_umma_kernel in stream order, so it needs neither counters nor fences.
+__global__ void __launch_bounds__(kDecodeThreads)
+decode_umma_merge_kernel(DecodeParams p, int ranges) {
+  __shared__ float red[384];
+  __shared__ long long sums[2][kDecodeThreads / 32];
+  const int b = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  // blocks in front of row b and in all rows
+  long long before = 0, all = 0;
+  for (int r = tid; r < p.batch; r += kDecodeThreads) {
+    const int n = (decode_row_len(p, r) + kBlk - 1) / kBlk;
+    all += n;
+    if (r < b) before += n;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    before += __shfl_xor_sync(kFullMask, before, o);
+    all += __shfl_xor_sync(kFullMask, all, o);
+  }
+  if (lane == 0) { sums[0][warp] = before; sums[1][warp] = all; }
+  __syncthreads();
+  before = 0; all = 0;
+#pragma unroll
+  for (int w = 0; w < kDecodeThreads / 32; ++w) { before += sums[0][w]; all += sums[1][w]; }
+  const int nb = (decode_row_len(p, b) + kBlk - 1) / kBlk;
+  if (nb == 0 || all == 0) return;
+  const Partition pt = make_partition(all, ranges);
+  const int c_lo = pt.cta_of(before), c_hi = pt.cta_of(before + nb - 1);
+  if (c_lo == c_hi) return;  // the range's CTAs wrote the row themselves
+  const int slot_rows = p.width * kHq;
+  const long long qbase = (long long)b * p.width;
+  int first = c_lo, n = c_hi - c_lo + 1;
+  if (n <= 32) {
+    for (int tok = 0; tok < p.width; ++tok) {
+      fold_parts<true>(p, red, tid, 0, first, c_lo, n, (qbase + tok) * kHq, slot_rows, tok * kHq);
+      named_bar_sync(1, kDecodeThreads);
+    }
+    return;
+  }
+  // more than 32 parts (a few very long rows): a plain running fold, thread = (head, 8 dims), four parts in flight
+  const int h = warp, d0 = lane * 8;
+  for (int tok = 0; tok < p.width; ++tok) {
+    float M = kNegBig, L = 0.f, acc[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+    for (int i0 = 0; i0 < n; i0 += 4) {
+      float2 e[4];
+      float4 x[4][2];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const bool ok = i0 + k < n;
+        const int c = c_lo + (ok ? i0 + k : 0);
+        const long long row = ((long long)(2 * c + (c == c_lo ? 1 : 0)) * slot_rows + tok * kHq + h);
+        e[k] = ok ? __ldcg(reinterpret_cast<const float2*>(p.part_ml + row * 2)) : make_float2(kNegBig, 0.f);
+        const float4* src = reinterpret_cast<const float4*>(p.part_acc + row * kD + d0);
+        x[k][0] = ok ? __ldcg(src) : make_float4(0.f, 0.f, 0.f, 0.f);
+        x[k][1] = ok ? __ldcg(src + 1) : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const float Mn = fmaxf(M, e[k].x);
+        const float fo = ex2_approx(M - Mn), fn = ex2_approx(e[k].x - Mn);
+        M = Mn;
+        L = L * fo + e[k].y * fn;
+        acc[0] = acc[0] * fo + x[k][0].x * fn; acc[1] = acc[1] * fo + x[k][0].y * fn;
+        acc[2] = acc[2] * fo + x[k][0].z * fn; acc[3] = acc[3] * fo + x[k][0].w * fn;
+        acc[4] = acc[4] * fo + x[k][1].x * fn; acc[5] = acc[5] * fo + x[k][1].y * fn;
+        acc[6] = acc[6] * fo + x[k][1].z * fn; acc[7] = acc[7] * fo + x[k][1].w * fn;
+      }
+    }
+    const float inv = L > 0.f ? 1.f / L : 0.f;
+    float4* o = reinterpret_cast<float4*>(p.out + ((qbase + tok) * kHq + h) * kD + d0);
+    o[0] = make_float4(acc[0] * inv, acc[1] * inv, acc[2] * inv, acc[3] * inv);
+    o[1] = make_float4(acc[4] * inv, acc[5] * inv, acc[6] * inv, acc[7] * inv);
+  }
+}
+
+typedef CUresult (*UdEncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static UdEncodeTiledFn ud_encode_fn() {
+  static UdEncodeTiledFn fn = [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult res;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &res) != cudaSuccess ||
+        res != cudaDriverEntryPointSuccess)
+      ptr = nullptr;
+    return reinterpret_cast<UdEncodeTiledFn>(ptr);
+  }();
+  return fn;
+}
+
+// A cache layer [token, kv head, 256] bf16 seen as {64 dims, token, 64-dim chunk, kv head}: one box of {64, 16, 4, 1}
+// is one KV head's half of a block and lands as [chunk][16 tokens][128 B] with the 128-byte swizzle in every panel.
+static bool ud_make_map(CUtensorMap* map, const void* base, uint64_t tokens) {
+  const cuuint64_t dims[4] = {64, tokens, 4, (cuuint64_t)kHkv};
+  const cuuint64_t strides[3] = {(cuuint64_t)kTokenBytes, 128, (cuuint64_t)kRowBytes};
+  const cuuint32_t box[4] = {64, (cuuint32_t)kBlk, 4, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  return ud_encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// p as launch_decode_wide takes it (width 1..8, carved workspace whose partial area holds ws_slots(decode_wide_num_ctas())
+// slots of width * kHq rows).  NVJ_ERR_UNSUPPORTED: no tensor-map encoder, a scale that is not positive (row maxima are
+// taken before scaling), the packed or the appending form.
+int launch_decode_umma(const DecodeParams& p, cudaStream_t stream) {
+  if (p.width < 1 || p.width > kUdMaxWidth || p.num_blocks < 1 || (p.num_blocks + 1) * kBlk > 0x7fffffffLL || !ud_encode_fn() ||
+      !(p.scale > 0.f) || p.packed_rows || p.new_k || p.kv_indptr)
+    return NVJ_ERR_UNSUPPORTED;
+  const int ctas = decode_wide_num_ctas();
+  if (ctas < 2) return NVJ_ERR_LAUNCH;
+  const int ranges = ctas / 2;
+  CUtensorMap k_map, v_map;
+  if (!tensor_map_cached(&k_map, 3, p.k_cache, (uint64_t)p.num_blocks * kBlk, ud_make_map) ||
+      !tensor_map_cached(&v_map, 3, p.v_cache, (uint64_t)p.num_blocks * kBlk, ud_make_map))
+    return NVJ_ERR_UNSUPPORTED;
+  static PerDeviceFlags smem_opted_in;
+  constexpr int kSmemBytes = (int)sizeof(UdSmem) + 1024;
+  static_assert(kSmemBytes <= 232448, "the block ring exceeds the shared memory of one CTA");
+  if (!once_per_device(smem_opted_in, [](int) {
+        return cudaFuncSetAttribute(decode_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) == cudaSuccess;
+      }))
+    return NVJ_ERR_LAUNCH;
+  decode_umma_kernel<<<2 * ranges, kDecodeThreads, kSmemBytes, stream>>>(k_map, v_map, p);
+  if (cudaGetLastError() != cudaSuccess) return NVJ_ERR_LAUNCH;
+  decode_umma_merge_kernel<<<p.batch, kDecodeThreads, 0, stream>>>(p, ranges);
+  return cudaGetLastError() == cudaSuccess ? NVJ_OK : NVJ_ERR_LAUNCH;
+}
+
+}  // namespace nvj

@@ -590,6 +590,11 @@ int launch_decode_wide(const DecodeParams& p, cudaStream_t stream) {
     return NVJ_ERR_UNSUPPORTED;
   int n = decode_wide_num_ctas();
   if (n <= 0) return NVJ_ERR_LAUNCH;
+  // rows of 5..8 query tokens: the tcgen05 form (two 16-row tiles per warp pair make the mma.sync form compute-bound)
+  if (p.wide_form == 2 || (p.wide_form == 0 && p.width > 4)) {
+    const int rc = launch_decode_umma(p, stream);
+    if (rc != NVJ_ERR_UNSUPPORTED || p.wide_form == 2) return rc;
+  }
   if (p.cta_limit > 0 && p.cta_limit < n) n = p.cta_limit;
   CUtensorMap k_map, v_map;
   if (!tensor_map_cached(&k_map, 0, p.k_cache, (uint64_t)p.num_blocks * kBlk, w_make_map) ||
@@ -627,8 +632,16 @@ extern "C" int nvj_paged_decode_wide(const void* q, const void* k_cache_layer, c
                                      const int32_t* block_tables, int table_width, const int32_t* seq_lens,
                                      const int32_t* positions, int batch, int width, float scale, float* out,
                                      void* workspace, size_t workspace_bytes, nvj_stream_t stream) {
+  return nvj_paged_decode_wide_form(q, k_cache_layer, v_cache_layer, num_blocks, block_tables, table_width, seq_lens, positions,
+                                    batch, width, scale, out, workspace, workspace_bytes, 0, stream);
+}
+
+extern "C" int nvj_paged_decode_wide_form(const void* q, const void* k_cache_layer, const void* v_cache_layer, int64_t num_blocks,
+                                          const int32_t* block_tables, int table_width, const int32_t* seq_lens,
+                                          const int32_t* positions, int batch, int width, float scale, float* out,
+                                          void* workspace, size_t workspace_bytes, int form, nvj_stream_t stream) {
   using namespace nvj;
-  if (batch < 0 || table_width < 0 || num_blocks < 0 || width < 1) return NVJ_ERR_INVALID_ARGUMENT;
+  if (batch < 0 || table_width < 0 || num_blocks < 0 || width < 1 || form < 0 || form > 2) return NVJ_ERR_INVALID_ARGUMENT;
   if (width > kWMaxWidth) return NVJ_ERR_UNSUPPORTED;
   if (batch == 0) return NVJ_OK;
   if (!q || !k_cache_layer || !v_cache_layer || !block_tables || !seq_lens || !out) return NVJ_ERR_INVALID_ARGUMENT;
@@ -649,6 +662,7 @@ extern "C" int nvj_paged_decode_wide(const void* q, const void* k_cache_layer, c
   p.seq_lens = seq_lens;
   p.positions = positions;
   p.width = width;
+  p.wide_form = form;
   p.out = out;
   p.num_blocks = num_blocks;
   p.table_width = table_width;

@@ -368,11 +368,12 @@ def wide_decode_supported(q, k_layer) -> bool:
             and k_layer.dtype == torch.bfloat16 and tuple(q.shape[2:]) == (8, 256) and tuple(k_layer.shape[1:]) == (16, 2, 256))
 
 
-def paged_decode_attention_wide(q, k_layer, v_layer, block_table, seq_lens, positions, scale):
+def paged_decode_attention_wide(q, k_layer, v_layer, block_table, seq_lens, positions, scale, *, form=0):
     """Decode attention for rows of 2..8 query tokens: q `[B, T, 8, 256]` bf16 -> `[B, T, 8 * 256]` fp32.
 
     Token t of row b sees keys p < seq_lens[b] with p <= positions[b, t] (the reference's wide decode,
     nanovllm_jax/kv_cache.py:852-998); K and V of a row are read once for all of its tokens.
+    `form`: 0 automatic (mma.sync tiles up to 4 tokens per row, tcgen05 beyond), 1 mma.sync tiles, 2 tcgen05.
     """
     if not wide_decode_supported(q, k_layer):
         raise ValueError("paged_decode_attention_wide: 2..8 bf16 query tokens per row over the bf16 cache [NB, 16, 2, 256]")
@@ -384,10 +385,11 @@ def paged_decode_attention_wide(q, k_layer, v_layer, block_table, seq_lens, posi
     pos = None if positions is None else positions.to(torch.int32).reshape(batch, width).contiguous()
     out = torch.empty((batch, width, 8 * 256), dtype=torch.float32, device=q.device)
     ws = _workspace(q.device, batch)
-    _lib.check(lib.nvj_paged_decode_wide(q.data_ptr(), k_layer.data_ptr(), v_layer.data_ptr(), int(k_layer.shape[0]),
-                                         tables.data_ptr(), int(tables.shape[1]), lens.data_ptr(),
-                                         0 if pos is None else pos.data_ptr(), batch, width, float(scale), out.data_ptr(),
-                                         ws.buf.data_ptr(), ws.nbytes, _stream(q.device)), "nvj_paged_decode_wide")
+    _lib.check(lib.nvj_paged_decode_wide_form(q.data_ptr(), k_layer.data_ptr(), v_layer.data_ptr(), int(k_layer.shape[0]),
+                                              tables.data_ptr(), int(tables.shape[1]), lens.data_ptr(),
+                                              0 if pos is None else pos.data_ptr(), batch, width, float(scale), out.data_ptr(),
+                                              ws.buf.data_ptr(), ws.nbytes, int(form), _stream(q.device)),
+               "nvj_paged_decode_wide_form")
     if _strict():
         _check_word(ws.status_tensor(), "paged decode (wide)", ws)
     return out

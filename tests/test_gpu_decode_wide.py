@@ -36,10 +36,13 @@ def _case(seed, num_blocks, lens, width, causal=True):
     return c, q, tables, lens, pos
 
 
-def _run(c, q, tables, lens, pos):
+FORMS = pytest.mark.parametrize("form", [1, 2], ids=["mma_sync", "tcgen05"])
+
+
+def _run(c, q, tables, lens, pos, form=0):
     from nano_vllm_jax_b200.kernels import paged_kv as K
     out = K.paged_decode_attention_wide(to_torch(q), to_torch(c["k_cache"][0]), to_torch(c["v_cache"][0]), to_torch(tables),
-                                        to_torch(lens), None if pos is None else to_torch(pos), SCALE)
+                                        to_torch(lens), None if pos is None else to_torch(pos), SCALE, form=form)
     torch.cuda.synchronize()
     return to_numpy(out)
 
@@ -48,52 +51,56 @@ def _oracle(c, q, tables, lens, pos):
     return R.paged_attention_decode(q, c["k_cache"], c["v_cache"], tables, lens, BS, SCALE, 4, positions=pos)
 
 
+@FORMS
 @pytest.mark.parametrize("width", [2, 3, 4, 5, 6, 7, 8])
-def test_every_length_around_the_block_boundaries(width):
-    lens = list(range(width, 3 * BS + 3))
+def test_every_length_around_the_block_boundaries(width, form):
+    lens = list(range(width, 3 * BS + 3)) + [5 * BS - 1, 5 * BS, 5 * BS + 1, 8 * BS + 7]  # beyond one 64-key tile too
     c, q, tables, lens, pos = _case(20 + width, 512, lens, width)
-    out = _run(c, q, tables, lens, pos)
+    out = _run(c, q, tables, lens, pos, form)
     err = np.abs(out - _oracle(c, q, tables, lens, pos)).max()
     assert err <= TIGHT, err
 
 
+@FORMS
 @pytest.mark.parametrize("width", [4, 7])
-def test_scattered_positions_and_rows_without_keys(width):
+def test_scattered_positions_and_rows_without_keys(width, form):
     # positions anywhere inside the row (not only the tail), two rows of length 0 between live ones
     lens = [700, 0, 33, 1500, 0, 16, 257]
     c, q, tables, lens, pos = _case(31, 512, lens, width, causal=False)
-    out = _run(c, q, tables, lens, pos)
+    out = _run(c, q, tables, lens, pos, form)
     ref = _oracle(c, q, tables, lens, pos)
     live = lens > 0
     assert np.abs(out[live] - ref[live]).max() <= TIGHT
     assert not out[~live].any()  # defined as zeros (the reference leaves such rows undefined)
 
 
+@FORMS
 @pytest.mark.parametrize("width", [3, 8])
 @pytest.mark.parametrize("lens", [(20000,), (9000, 30, 9000, 700, 5), (3000, 12000, 2, 6000)])
-def test_long_rows_are_split_over_ctas_and_merged(lens, width):
+def test_long_rows_are_split_over_ctas_and_merged(lens, width, form):
     c, q, tables, lens, pos = _case(9, 2600, lens, width)
     lens = np.maximum(lens, width)
     pos = np.maximum(lens[:, None] - width + np.arange(width)[None, :], 0).astype(np.int32)
-    out = _run(c, q, tables, lens, pos)
+    out = _run(c, q, tables, lens, pos, form)
     assert np.abs(out - _oracle(c, q, tables, lens, pos)).max() <= TIGHT
-    again = _run(c, q, tables, lens, pos)  # counters were left at zero; the merge order is fixed
+    again = _run(c, q, tables, lens, pos, form)  # counters were left at zero; the merge order is fixed
     np.testing.assert_array_equal(bits(out), bits(again))
 
 
+@FORMS
 @pytest.mark.parametrize("width", [4, 6])
-def test_no_positions_means_no_causal_limit_and_matches_the_packed_route(width):
+def test_no_positions_means_no_causal_limit_and_matches_the_packed_route(width, form):
     from nano_vllm_jax_b200.kernels import paged_kv as K
     lens = [300, 1000, 64, 129]
     c, q, tables, lens, pos = _case(41, 256, lens, width)
-    out = _run(c, q, tables, lens, None)
+    out = _run(c, q, tables, lens, None, form)
     full = np.broadcast_to(lens[:, None] - 1, pos.shape).astype(np.int32)
     assert np.abs(out - _oracle(c, q, tables, lens, full)).max() <= TIGHT
     # the same batch as a packed batch of equal-width rows on the prefill tiles
     qsl = torch.arange(len(lens) + 1, dtype=torch.int32, device="cuda") * width
     packed = K.packed_paged_prefill_attention(to_torch(q).reshape(1, -1, 8, 256), to_torch(c["k_cache"][0]), to_torch(c["v_cache"][0]),
                                               to_torch(tables), to_torch(lens), to_torch(pos).reshape(1, -1), qsl, BS, SCALE, 4)
-    causal = _run(c, q, tables, lens, pos)
+    causal = _run(c, q, tables, lens, pos, form)
     assert np.abs(to_numpy(packed).reshape(causal.shape) - causal).max() <= TIGHT
 
 
@@ -107,3 +114,18 @@ def test_refusals():
     with pytest.raises(ValueError):
         K.paged_decode_attention_wide(to_torch(q).float(), to_torch(c["k_cache"][0]), to_torch(c["v_cache"][0]), to_torch(tables),
                                       to_torch(lens), None, SCALE)
+
+
+@pytest.mark.parametrize("width", [5, 8])
+def test_the_two_forms_agree_on_a_batch_of_many_rows(width):
+    """What the automatic choice takes at these widths (tcgen05) against the mma.sync form, 96 rows of 600..2500 tokens:
+    most rows lie inside one CTA pair's range, some are cut over two and folded by the merge launch."""
+    rng = np.random.default_rng(77)
+    lens = rng.integers(600, 2501, size=96)
+    c, q, tables, lens, pos = _case(13, 96 * 160, lens, width)
+    auto = _run(c, q, tables, lens, pos, 0)
+    mma = _run(c, q, tables, lens, pos, 1)
+    assert np.abs(auto - mma).max() <= TIGHT
+    rows = [0, 17, 95]
+    ref = _oracle({"k_cache": c["k_cache"], "v_cache": c["v_cache"]}, q[rows], tables[rows], lens[rows], pos[rows])
+    assert np.abs(auto[rows] - ref).max() <= TIGHT
