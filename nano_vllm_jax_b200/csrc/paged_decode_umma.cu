@@ -5,13 +5,18 @@
 // 5..8 tokens are two tiles per KV head, every warp then walks every block, and the kernel takes 1.9x its width-1
 // time: 512 mma.sync per block and SM are more than the legacy tensor path issues in the HBM time of a block.  Here
 // the 4 x width <= 32 query rows of one KV head sit in lanes 0..31 of a 128-row UMMA tile (the other lanes compute
-// on whatever they hold and are never read): per block and KV head 16 MMAs of N = 16 for the scores and two of
-// N = 256 for the weighted sum, ~1500 tensor cycles per 64 keys against ~3000 cycles of HBM time.
+// on whatever they hold and are never read): per tile of 64 keys and KV head 16 MMAs of N = 64 for the scores and
+// eight of N = 256 for the weighted sum, ~1500 tensor cycles against ~3000 cycles of HBM time.  (Scores block by
+// block, 64 MMAs of N = 16 per tile, were measured first: 345 us on C2 shapes, the small MMAs cost more to issue
+// than they compute.)
 //
 // Work split.  The blocks of all rows form one sequence cut into equal ranges as in the other decode kernels
 // (decode_parts.cuh), but a range belongs to a PAIR of CTAs, one per KV head: CTA 2c + h streams head h's half of
-// every block of range c (8 KiB of K and 8 KiB of V per block, one TMA box each), so every K/V byte still crosses
-// HBM once.  One CTA per SM (192 KiB of shared memory: twelve blocks in flight; 512 TMEM columns).
+// every block of range c, so every K/V byte still crosses HBM once.  Keys are walked in tiles of up to four blocks
+// that never straddle a row; a tile's K lands as [64-d chunk][64 keys][128 B] (one 2 KiB TMA box per block and
+// chunk, so that the whole tile is one N = 64 operand), its V block by block as [chunk][16 keys][128 B] (one 8 KiB
+// box per block: P V contracts 16 keys per MMA anyway).  One CTA per SM (192 KiB of shared memory: three tiles in
+// flight; 512 TMEM columns).
 //   warp 0   softmax and epilogue: lane r = query row r = token * 4 + head of the group.  Per row segment it stages
 //            the query rows into tensor memory, per tile of up to four blocks (64 keys) reads the scores
 //            (tcgen05.ld), masks (key < length, key <= the token's position), keeps the running maximum lazily (O in
@@ -19,9 +24,8 @@
 //            scores as two bf16 terms (hi + lo); at the end of the segment it reads O and stores the row (whole row
 //            in this range) or the un-normalised partial with its (max, sum).
 //   warp 1   producer: block ids straight from the block table (32 at a time), TMA boxes into the ring.
-//   warp 2   MMA issue: S(t) = Q K(t)^T block by block into one of two score buffers, O += P(t) V(t) once the
-//            weights are written; S(t + 2) follows P V (t).  tcgen05.commit releases ring stages and signals the
-//            softmax warp.
+//   warp 2   MMA issue: S(t) = Q K(t)^T into one of two score buffers, O += P(t) V(t) once the weights are
+//            written; S(t + 2) follows P V (t).  tcgen05.commit releases ring stages and signals the softmax warp.
 // A row cut over several ranges is folded afterwards by decode_umma_merge_kernel (one CTA per row, stream order
 // instead of counters and fences): the merge costs a second small launch, which rows of this width can afford.
 // Every wait is bounded; on a timeout the kernel flags NVJ_DEV_TIMEOUT, stops issuing, lets copies in flight land
@@ -37,8 +41,8 @@
 
 namespace nvj {
 
-constexpr int kUdStages = 12;     // cache blocks (K and V of one KV head, 16 KiB) in flight
-constexpr int kUdTileBlocks = 4;  // blocks per softmax step: 64 keys
+constexpr int kUdStages = 3;      // tiles (K and V of one KV head for up to 64 keys: 64 KiB) in flight
+constexpr int kUdTileBlocks = 4;  // blocks per tile: 64 keys
 constexpr int kUdTmemCols = 512;
 constexpr int kUdColQ = 0;        // query rows as the A operand: 256 bf16 per row = 128 columns
 constexpr int kUdColS = 128;      // two score buffers of 64 columns; the weights (hi: 32 columns, lo: 32) overwrite theirs
@@ -48,7 +52,8 @@ constexpr float kUdRescaleGap = 8.f;
 constexpr int kUdMaxWidth = 8;
 
 struct UdSmem {
-  alignas(1024) char kv[kUdStages][2][kUdHalfBlock];  // [stage][K|V][64-d chunk][16 tokens][128 B], swizzled
+  alignas(1024) char k[kUdStages][4][kUdTileBlocks * kBlk * 128];  // [stage][64-d chunk][64 keys][128 B], swizzled
+  alignas(1024) char v[kUdStages][kUdTileBlocks][kUdHalfBlock];    // [stage][block][64-d chunk][16 keys][128 B], swizzled
   alignas(8) unsigned long long full_bar[kUdStages], empty_bar[kUdStages], q_full, s_full[2], p_full, pv_done;
   float red[384];
   int scan[16];
@@ -56,13 +61,13 @@ struct UdSmem {
   uint32_t tmem_base;
 };
 
-// One KV head's half of a block: the box {64 dims, 16 tokens, 4 chunks, 1 head} of the 4-D view of a cache layer.
-__device__ __forceinline__ void ud_tma_half_block(uint32_t dst, const CUtensorMap* map, int token, int kvh, uint32_t bar) {
-  uint64_t policy;  // every block is read once
-  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+// One box of the 4-D view {64 dims, token, 64-dim chunk, kv head} of a cache layer: with the V map all four chunks of
+// one KV head's half of a block (8 KiB), with the K map one chunk of it (2 KiB).
+__device__ __forceinline__ void ud_tma_box(uint32_t dst, const CUtensorMap* map, int token, int chunk, int kvh, uint32_t bar,
+                                           uint64_t policy) {
   asm volatile(
       "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3, %4, %5}], [%6], %7;"
-      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(0), "r"(token), "r"(0), "r"(kvh), "r"(bar), "l"(policy)
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(0), "r"(token), "r"(chunk), "r"(kvh), "r"(bar), "l"(policy)
       : "memory");
 }
 
@@ -70,11 +75,13 @@ __device__ __forceinline__ void ud_tma_half_block(uint32_t dst, const CUtensorMa
 __device__ __forceinline__ void ud_producer(const CUtensorMap* k_map, const CUtensorMap* v_map, const DecodeParams& p,
                                             UdSmem& sm, int kvh, int b, int j, long long g, long long g1, int lane) {
   const int oob = (int)(p.num_blocks * kBlk);  // a box that starts here is filled with zeros
+  uint64_t policy;  // every block is read once: do not let it displace what the L2 is good for
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
   Seg s;
-  int it = 0;
+  uint32_t gt = 0;  // tiles so far, over all segments
   while (next_seg(p, b, j, g, g1, s)) {
     const long long tbase = decode_table_base(p, s.b);
-    for (int jb = s.j0; jb < s.j1; jb += 32) {
+    for (int jb = s.j0; jb < s.j1; jb += 32) {  // 32 block ids = 8 tiles at a time
       const int n = s.j1 - jb < 32 ? s.j1 - jb : 32;
       int id = -1;
       if (lane < n) {
@@ -84,16 +91,18 @@ __device__ __forceinline__ void ud_producer(const CUtensorMap* k_map, const CUte
           id = -1;
         }
       }
-      for (int i = 0; i < n; ++i, ++it) {
-        const int blk = __shfl_sync(kFullMask, id, i);
-        const int stage = it % kUdStages;
-        if (it >= kUdStages && !um_wait(&sm.empty_bar[stage], (uint32_t)((it / kUdStages) - 1) & 1u, &sm.abort_flag, p.status)) return;
-        if (lane == 0) {
-          const uint32_t fb = smem_u32(&sm.full_bar[stage]);
+      for (int i0 = 0; i0 < n; i0 += kUdTileBlocks, ++gt) {
+        const int cnt = n - i0 < kUdTileBlocks ? n - i0 : kUdTileBlocks;
+        const int stage = (int)(gt % kUdStages);
+        if (gt >= kUdStages && !um_wait(&sm.empty_bar[stage], ((gt / kUdStages) - 1) & 1u, &sm.abort_flag, p.status)) return;
+        const uint32_t fb = smem_u32(&sm.full_bar[stage]);
+        if (lane == 0) mbar_arrive_expect_tx(fb, (uint32_t)cnt * 2u * kUdHalfBlock);
+        __syncwarp();
+        for (int i = 0; i < cnt; ++i) {
+          const int blk = __shfl_sync(kFullMask, id, i0 + i);
           const int token = blk >= 0 ? blk * kBlk : oob;
-          mbar_arrive_expect_tx(fb, 2u * kUdHalfBlock);
-          ud_tma_half_block(smem_u32(sm.kv[stage][0]), k_map, token, kvh, fb);
-          ud_tma_half_block(smem_u32(sm.kv[stage][1]), v_map, token, kvh, fb);
+          if (lane < 4) ud_tma_box(smem_u32(&sm.k[stage][lane][0]) + i * (kBlk * 128), k_map, token, lane, kvh, fb, policy);
+          else if (lane == 4) ud_tma_box(smem_u32(&sm.v[stage][i][0]), v_map, token, 0, kvh, fb, policy);
         }
         __syncwarp();
       }
@@ -102,69 +111,59 @@ __device__ __forceinline__ void ud_producer(const CUtensorMap* k_map, const CUte
 }
 
 // ---- warp 2: MMA issue --------------------------------------------------------------------------
-// Scores of the blocks [first, first + count) of the CTA's block sequence into score buffer `buf`, 16 columns per block.
-__device__ __forceinline__ bool ud_issue_s(UdSmem& sm, const DecodeParams& p, uint32_t tmem, uint64_t desc0, int first, int count,
-                                           int buf) {
-  for (int i = 0; i < count; ++i) {
-    const int it = first + i, stage = it % kUdStages;
-    if (!um_wait(&sm.full_bar[stage], (uint32_t)(it / kUdStages) & 1u, &sm.abort_flag, p.status)) return false;
-    tc_fence_after_sync();
-    if (um_elect_one()) {
-      constexpr uint32_t idesc = umma_idesc(kBlk, false);
-      const uint64_t k_desc = desc0 + (uint64_t)((stage * 2 * kUdHalfBlock) >> 4);
-      const uint32_t d = tmem + kUdColS + buf * 64 + i * kBlk;
+// Scores of tile `gt` (stage gt % kUdStages) into score buffer gt & 1: columns of blocks the tile does not have are
+// computed from whatever the stage holds there and masked by the softmax warp.
+__device__ __forceinline__ bool ud_issue_s(UdSmem& sm, const DecodeParams& p, uint32_t tmem, uint64_t k_desc0, uint32_t gt) {
+  const int stage = (int)(gt % kUdStages);
+  if (!um_wait(&sm.full_bar[stage], (gt / kUdStages) & 1u, &sm.abort_flag, p.status)) return false;
+  tc_fence_after_sync();
+  if (um_elect_one()) {
+    constexpr uint32_t idesc = umma_idesc(kUdTileBlocks * kBlk, false);
+    const uint64_t k_desc = k_desc0 + (uint64_t)((stage * 4 * kUdTileBlocks * kBlk * 128) >> 4);
+    const uint32_t d = tmem + kUdColS + (gt & 1u) * 64;
 #pragma unroll
-      for (int ks = 0; ks < 16; ++ks)  // 16 dims per MMA: 8 columns of Q; K chunk ks / 4, 32 bytes into its swizzled rows
-        umma_bf16_ts(d, tmem + kUdColQ + ks * 8, k_desc + (uint64_t)(((ks >> 2) * (kBlk * 128) + (ks & 3) * 32) >> 4), idesc,
-                     ks > 0 ? 1u : 0u);
-    }
-    __syncwarp();
+    for (int ks = 0; ks < 16; ++ks)  // 16 dims per MMA: 8 columns of Q; K chunk ks / 4, 32 bytes into its swizzled rows
+      umma_bf16_ts(d, tmem + kUdColQ + ks * 8, k_desc + (uint64_t)(((ks >> 2) * (kUdTileBlocks * kBlk * 128) + (ks & 3) * 32) >> 4),
+                   idesc, ks > 0 ? 1u : 0u);
+    umma_commit(smem_u32(&sm.s_full[gt & 1u]));
   }
-  if (um_elect_one()) umma_commit(smem_u32(&sm.s_full[buf]));
   __syncwarp();
   return true;
 }
 
 __device__ __forceinline__ void ud_mma_warp(UdSmem& sm, const DecodeParams& p, uint32_t tmem, int b, int j, long long g,
                                             long long g1) {
-  const uint64_t desc0 = umma_desc(smem_u32(&sm.kv[0][0][0]), 16, 1024);             // K: keys are rows, dims contracted
-  const uint64_t v_desc0 = umma_desc(smem_u32(&sm.kv[0][1][0]), kBlk * 128, 1024);   // V: 64-d chunks 2 KiB apart, keys contracted
+  const uint64_t k_desc0 = umma_desc(smem_u32(&sm.k[0][0][0]), 16, 1024);          // K: keys are rows, dims contracted
+  const uint64_t v_desc0 = umma_desc(smem_u32(&sm.v[0][0][0]), kBlk * 128, 1024);  // V: 64-d chunks 2 KiB apart, keys contracted
   Seg s;
-  int it0 = 0;      // index of the segment's first block in the CTA's block sequence
-  uint32_t gt = 0;  // tiles issued so far, over all segments: picks the score buffer and the barrier phases
+  uint32_t gt = 0;  // tiles so far, over all segments: picks the stage, the score buffer and the barrier phases
   uint32_t seg = 0;
   while (next_seg(p, b, j, g, g1, s)) {
     const int nblk = s.j1 - s.j0, nt = (nblk + kUdTileBlocks - 1) / kUdTileBlocks;
     if (!um_wait(&sm.q_full, seg & 1u, &sm.abort_flag, p.status)) return;
-    for (int t = 0; t < 2 && t < nt; ++t) {
-      const int cnt = nblk - t * kUdTileBlocks < kUdTileBlocks ? nblk - t * kUdTileBlocks : kUdTileBlocks;
-      if (!ud_issue_s(sm, p, tmem, desc0, it0 + t * kUdTileBlocks, cnt, (int)((gt + t) & 1u))) return;
-    }
+    for (int t = 0; t < 2 && t < nt; ++t)
+      if (!ud_issue_s(sm, p, tmem, k_desc0, gt + t)) return;
     for (int t = 0; t < nt; ++t, ++gt) {
       const int cnt = nblk - t * kUdTileBlocks < kUdTileBlocks ? nblk - t * kUdTileBlocks : kUdTileBlocks;
+      const int stage = (int)(gt % kUdStages);
       if (!um_wait(&sm.p_full, gt & 1u, &sm.abort_flag, p.status)) return;
       tc_fence_after_sync();
       if (um_elect_one()) {
         constexpr uint32_t idesc = umma_idesc(kD, true);
         const uint32_t pa = tmem + kUdColS + (gt & 1u) * 64;
         for (int i = 0; i < cnt; ++i) {  // 16 keys per MMA: 8 columns of P, the block's two 8-key groups of V
-          const int stage = (it0 + t * kUdTileBlocks + i) % kUdStages;
-          const uint64_t dv = v_desc0 + (uint64_t)((stage * 2 * kUdHalfBlock) >> 4);
+          const uint64_t dv = v_desc0 + (uint64_t)(((stage * kUdTileBlocks + i) * kUdHalfBlock) >> 4);
           umma_bf16_ts(tmem + kUdColO, pa + i * 8, dv, idesc, (t > 0 || i > 0) ? 1u : 0u);
           umma_bf16_ts(tmem + kUdColO, pa + 32 + i * 8, dv, idesc, 1u);
         }
-        for (int i = 0; i < cnt; ++i) umma_commit(smem_u32(&sm.empty_bar[(it0 + t * kUdTileBlocks + i) % kUdStages]));
+        umma_commit(smem_u32(&sm.empty_bar[stage]));
         umma_commit(smem_u32(&sm.pv_done));
       }
       __syncwarp();
       // S(t + 2) overwrites the columns P V (t) reads P(t) from, and every phase of pv_done is observed in turn
       if (!um_wait(&sm.pv_done, gt & 1u, &sm.abort_flag, p.status)) return;
-      if (t + 2 < nt) {
-        const int c2 = nblk - (t + 2) * kUdTileBlocks < kUdTileBlocks ? nblk - (t + 2) * kUdTileBlocks : kUdTileBlocks;
-        if (!ud_issue_s(sm, p, tmem, desc0, it0 + (t + 2) * kUdTileBlocks, c2, (int)(gt & 1u))) return;
-      }
+      if (t + 2 < nt && !ud_issue_s(sm, p, tmem, k_desc0, gt + 2)) return;
     }
-    it0 += nblk;
     ++seg;
   }
 }
@@ -469,11 +468,13 @@ static UdEncodeTiledFn ud_encode_fn() {
 }
 
 // A cache layer [token, kv head, 256] bf16 seen as {64 dims, token, 64-dim chunk, kv head}: one box of {64, 16, 4, 1}
-// is one KV head's half of a block and lands as [chunk][16 tokens][128 B] with the 128-byte swizzle in every panel.
+// is one KV head's half of a block and lands as [chunk][16 tokens][128 B] with the 128-byte swizzle in every panel;
+// a box of {64, 16, 1, 1} is one such panel.
+template <int kChunks>
 static bool ud_make_map(CUtensorMap* map, const void* base, uint64_t tokens) {
   const cuuint64_t dims[4] = {64, tokens, 4, (cuuint64_t)kHkv};
   const cuuint64_t strides[3] = {(cuuint64_t)kTokenBytes, 128, (cuuint64_t)kRowBytes};
-  const cuuint32_t box[4] = {64, (cuuint32_t)kBlk, 4, 1};
+  const cuuint32_t box[4] = {64, (cuuint32_t)kBlk, kChunks, 1};
   const cuuint32_t estr[4] = {1, 1, 1, 1};
   return ud_encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -491,12 +492,12 @@ int launch_decode_umma(const DecodeParams& p, cudaStream_t stream) {
   if (ctas < 2) return NVJ_ERR_LAUNCH;
   const int ranges = ctas / 2;
   CUtensorMap k_map, v_map;
-  if (!tensor_map_cached(&k_map, 3, p.k_cache, (uint64_t)p.num_blocks * kBlk, ud_make_map) ||
-      !tensor_map_cached(&v_map, 3, p.v_cache, (uint64_t)p.num_blocks * kBlk, ud_make_map))
+  if (!tensor_map_cached(&k_map, 4, p.k_cache, (uint64_t)p.num_blocks * kBlk, ud_make_map<1>) ||
+      !tensor_map_cached(&v_map, 3, p.v_cache, (uint64_t)p.num_blocks * kBlk, ud_make_map<4>))
     return NVJ_ERR_UNSUPPORTED;
   static PerDeviceFlags smem_opted_in;
   constexpr int kSmemBytes = (int)sizeof(UdSmem) + 1024;
-  static_assert(kSmemBytes <= 232448, "the block ring exceeds the shared memory of one CTA");
+  static_assert(kSmemBytes <= 232448, "the tile ring exceeds the shared memory of one CTA");
   if (!once_per_device(smem_opted_in, [](int) {
         return cudaFuncSetAttribute(decode_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) == cudaSuccess;
       }))
