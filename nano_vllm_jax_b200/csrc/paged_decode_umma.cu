@@ -54,7 +54,7 @@ constexpr int kUdMaxWidth = 8;
 struct UdSmem {
   alignas(1024) char k[kUdStages][4][kUdTileBlocks * kBlk * 128];  // [stage][64-d chunk][64 keys][128 B], swizzled
   alignas(1024) char v[kUdStages][kUdTileBlocks][kUdHalfBlock];    // [stage][block][64-d chunk][16 keys][128 B], swizzled
-  alignas(8) unsigned long long full_bar[kUdStages], empty_bar[kUdStages], q_full, s_full[2], p_full, pv_done;
+  alignas(8) unsigned long long full_bar[kUdStages], empty_bar[kUdStages], q_full, s_full[2], p_full, pv_done, o_free;
   float red[384];
   int scan[16];
   int start_b, start_j, abort_flag;
@@ -147,6 +147,8 @@ __device__ __forceinline__ void ud_mma_warp(UdSmem& sm, const DecodeParams& p, u
       const int cnt = nblk - t * kUdTileBlocks < kUdTileBlocks ? nblk - t * kUdTileBlocks : kUdTileBlocks;
       const int stage = (int)(gt % kUdStages);
       if (!um_wait(&sm.p_full, gt & 1u, &sm.abort_flag, p.status)) return;
+      // the first P V of a segment overwrites O: the segment before must have been read out
+      if (t == 0 && seg > 0 && !um_wait(&sm.o_free, (seg - 1) & 1u, &sm.abort_flag, p.status)) return;
       tc_fence_after_sync();
       if (um_elect_one()) {
         constexpr uint32_t idesc = umma_idesc(kD, true);
@@ -168,6 +170,34 @@ __device__ __forceinline__ void ud_mma_warp(UdSmem& sm, const DecodeParams& p, u
   }
 }
 
+// Query rows of one table row into tensor memory: lane = row (token * 4 + head), 256 dims -> 128 columns, two bf16 per
+// column; sixteen 16-byte loads in flight at a time (one at a time, the eight round trips to memory cost a segment
+// more than its epilogue).  Arrives on q_full.
+__device__ __forceinline__ void ud_stage_q(UdSmem& sm, const DecodeParams& p, uint32_t tmem, int kvh, int row_b, int lane) {
+  const int tok = lane >> 2, head = lane & 3;
+  const bool real = tok < p.width;
+  const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.q) +
+                                                    (((long long)row_b * p.width + (real ? tok : 0)) * kHq + kvh * kG + head) * kD);
+#pragma unroll 1
+  for (int half = 0; half < 2; ++half) {
+    uint4 u[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) u[i] = real ? ld_nc_u4(src + half * 16 + i) : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+    for (int part = 0; part < 4; ++part) {  // 32 dims = 16 columns at a time
+      uint32_t w[16];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        w[4 * i] = u[part * 4 + i].x; w[4 * i + 1] = u[part * 4 + i].y; w[4 * i + 2] = u[part * 4 + i].z; w[4 * i + 3] = u[part * 4 + i].w;
+      }
+      tmem_st16(tmem + kUdColQ + half * 64 + part * 16, w);
+    }
+  }
+  tmem_st_wait();
+  tc_fence_before_sync();
+  mbar_arrive(smem_u32(&sm.q_full));
+}
+
 // ---- warp 0: query staging, softmax, epilogue ----------------------------------------------------
 __device__ __forceinline__ void ud_softmax_warp(UdSmem& sm, const DecodeParams& p, uint32_t tmem, int kvh, int b, int j,
                                                 long long g, long long g1, int range, int lane) {
@@ -175,27 +205,13 @@ __device__ __forceinline__ void ud_softmax_warp(UdSmem& sm, const DecodeParams& 
   const bool real = tok < p.width;
   const float scale_log2 = p.scale * kLog2e;
   const int slot_rows = p.width * kHq;
-  Seg s;
+  Seg s, nxt;
   uint32_t gt = 0;
-  while (next_seg(p, b, j, g, g1, s)) {
+  bool have = next_seg(p, b, j, g, g1, s);
+  if (have) ud_stage_q(sm, p, tmem, kvh, s.b, lane);
+  while (have) {
     const long long qbase = (long long)s.b * p.width;
-    {  // this row's 256 dims -> 128 TMEM columns, two bf16 per column
-      const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.q) +
-                                                        ((qbase + (real ? tok : 0)) * kHq + kvh * kG + head) * kD);
-#pragma unroll 1
-      for (int part = 0; part < 8; ++part) {  // 32 dims = 16 columns at a time
-        uint32_t w[16];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const uint4 u = real ? ld_nc_u4(src + part * 4 + i) : make_uint4(0u, 0u, 0u, 0u);
-          w[4 * i] = u.x; w[4 * i + 1] = u.y; w[4 * i + 2] = u.z; w[4 * i + 3] = u.w;
-        }
-        tmem_st16(tmem + kUdColQ + part * 16, w);
-      }
-      tmem_st_wait();
-      tc_fence_before_sync();
-      mbar_arrive(smem_u32(&sm.q_full));
-    }
+    bool have_next = false;
     const int my_pos = real ? (p.positions ? p.positions[qbase + tok] : 0x7fffffff) : -1;
     const int last_key = my_pos < s.len - 1 ? my_pos : s.len - 1;  // last key this row may see
     float m_row = -INFINITY, l_row = 0.f;                           // m_row in units of log2(e) * scale
@@ -268,6 +284,13 @@ __device__ __forceinline__ void ud_softmax_warp(UdSmem& sm, const DecodeParams& 
       tmem_st_wait();
       tc_fence_before_sync();
       mbar_arrive(smem_u32(&sm.p_full));
+      if (t == nt - 1) {
+        // The segment's last scores have been read, so all of its S products have retired and the query columns are
+        // free: the next row's queries go in now, and its first scores are computed while this segment's output is
+        // still being read out below (the MMA warp holds the next P V back until o_free).
+        have_next = next_seg(p, b, j, g, g1, nxt);
+        if (have_next) ud_stage_q(sm, p, tmem, kvh, nxt.b, lane);
+      }
     }
     // ---- end of the segment: O -> the output row (the whole row lies in this range) or this range's partial
     if (!um_wait(&sm.pv_done, (gt - 1) & 1u, &sm.abort_flag, p.status)) return;
@@ -291,7 +314,10 @@ __device__ __forceinline__ void ud_softmax_warp(UdSmem& sm, const DecodeParams& 
     if (real && !whole_row)
       *reinterpret_cast<float2*>(p.part_ml + ((long long)slot * slot_rows + row_in_slot) * 2) =
           make_float2(m_row == -INFINITY ? kNegBig : m_row, l_row);
-    tc_fence_before_sync();  // the next segment's query rows and first P V overwrite what was just read
+    tc_fence_before_sync();  // the next segment's first P V overwrites what was just read
+    if (have_next) mbar_arrive(smem_u32(&sm.o_free));
+    s = nxt;
+    have = have_next;
   }
 }
 
@@ -352,6 +378,7 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_const
     mbar_init(smem_u32(&sm.s_full[1]), 1);
     mbar_init(smem_u32(&sm.p_full), 32);
     mbar_init(smem_u32(&sm.pv_done), 1);
+    mbar_init(smem_u32(&sm.o_free), 32);
     mbar_fence_init();
   }
   tc_fence_before_sync();
