@@ -87,9 +87,9 @@ def tables_for(lens, pool, rng):
     return t
 
 
-def decode_cases(dev, iters):
+def decode_cases(dev, iters, small=False):
     rng = np.random.default_rng(2)
-    rows, pool = 256, 400_000
+    rows, pool = (64, 40_000) if small else (256, 400_000)  # small: what a profiler capture may hold (2.6 GB of cache)
     ctx = rng.integers(1024, 4097, size=rows)
     lens = (ctx + 1).astype(np.int32)
     tables = torch.from_numpy(tables_for(lens, pool, rng)).to(dev)
@@ -505,7 +505,7 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill", "hybrid", "mixed", "front", "comparator", "phases"])
     ap.add_argument("--small", action="store_true",
-                    help="prefill cases on a 1-layer, 4096-block cache (128 MiB): the size to run under a profiler")
+                    help="prefill cases on a 1-layer, 4096-block cache (128 MiB), decode cases on 64 rows over a 40 000-block cache (2.6 GB): the sizes to run under a profiler")
     args = ap.parse_args()
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
@@ -514,7 +514,7 @@ def main():
         decode_phase_cases(dev, args.iters)
         return
     if args.only in ("all", "decode"):
-        decode_cases(dev, args.iters)
+        decode_cases(dev, args.iters, small=args.small)
     if args.only in ("all", "prefill"):
         prefill_and_copy_cases(dev, args.iters, small=args.small)
     if args.only in ("all", "hybrid"):
