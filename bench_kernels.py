@@ -127,13 +127,15 @@ def decode_cases(dev, iters, small=False):
            int(lens[:sub].sum()) * TOKEN_BYTES, {"workload": "c2, first 16 rows"})
     # speculative-verify decode: `width` query tokens per row at the row's last positions (rows already appended)
     from nano_vllm_jax_b200 import kv_cache as kvc
-    for width in (2, 4, 5, 8):
+    for width in (2, 4, 5, 8, 9, 16):
         qw = _randn_bf16((rows, width, HQ, D), 6, dev)
         wpos = (t_lens[:, None] - width + torch.arange(width, device=dev, dtype=torch.int32)[None, :]).contiguous()
         wbytes = kv_bytes + table_bytes + rows * width * (HQ * D * 2 + HQ * D * 4)
         report("wide decode, %d query tokens per row (automatic: mma.sync tiles up to width 4, tcgen05 beyond)" % width,
                big.run(lambda: kvc.paged_attention_decode(qw, k, v, tables, t_lens, BS, SCALE, 4, positions=wpos, out_dtype=torch.float32)),
                wbytes, {"workload": "c2, width %d" % width})
+        if width > 8:  # the mma.sync form ends at 8
+            continue
         other, name = (1, "mma.sync tiles, two row tiles per warp pair") if width > 4 else (2, "tcgen05, query rows in a 128-row tile")
         report("wide decode, %d query tokens per row (%s)" % (width, name),
                big.run(lambda: K.paged_decode_attention_wide(qw, k[0], v[0], tables, t_lens, wpos, SCALE, form=other)),

@@ -266,8 +266,9 @@ int nvj_paged_decode_static_scratch(const void* q, int q_dtype,
  *   workspace  nvj_paged_decode_wide_workspace_bytes(max_batch) bytes, zeroed once
  *              (nvj_paged_decode_workspace_init) and then reused; its first word is the device
  *              status word
- * NVJ_ERR_UNSUPPORTED for width > 8 or misaligned pointers (use nvj_paged_prefill_packed with
- * rows of equal width instead).
+ * NVJ_ERR_UNSUPPORTED for width > 16 or misaligned pointers (use nvj_paged_prefill_packed with
+ * rows of equal width instead); widths 9-16 (the reference verifies up to 9 tokens per row) exist on the tcgen05
+ * form only.
  */
 size_t nvj_paged_decode_wide_workspace_bytes(int max_batch);
 /*
@@ -275,7 +276,8 @@ size_t nvj_paged_decode_wide_workspace_bytes(int max_batch);
  * nvj_paged_decode_wide does: widths 1-4 on mma.sync tiles, 16 query rows per warp; widths 5-8 on tcgen05, the 4 x width
  * query rows of a KV head in a 128-row tile with scores and output in tensor memory, a row cut over several CTA pairs
  * folded by a second small launch), 1 = mma.sync tiles (widths 5-8: two row tiles per warp pair, ~1.9x the width-1
- * time), 2 = tcgen05 at any width 1-8 (NVJ_ERR_UNSUPPORTED without a tensor-map encoder or for scale <= 0).
+ * time; NVJ_ERR_UNSUPPORTED beyond 8), 2 = tcgen05 at any width 1-16 (NVJ_ERR_UNSUPPORTED without a tensor-map
+ * encoder or for scale <= 0).
  */
 int nvj_paged_decode_wide_form(const void* q, const void* k_cache_layer, const void* v_cache_layer,
                                int64_t num_blocks, const int32_t* block_tables, int table_width,

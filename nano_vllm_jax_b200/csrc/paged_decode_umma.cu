@@ -1,12 +1,12 @@
-// Paged GQA decode attention for rows of several query tokens (speculative verification, widths up to 8) on the
+// Paged GQA decode attention for rows of several query tokens (speculative verification, widths up to 16) on the
 // 5th-generation tensor cores: tcgen05.mma with the scores and the output accumulators in tensor memory.
 //
 // Why a second wide kernel.  decode_wide_kernel (mma.sync) holds one 16-row tile of query rows per warp; rows of
 // 5..8 tokens are two tiles per KV head, every warp then walks every block, and the kernel takes 1.9x its width-1
 // time: 512 mma.sync per block and SM are more than the legacy tensor path issues in the HBM time of a block.  Here
-// the 4 x width <= 32 query rows of one KV head sit in lanes 0..31 of a 128-row UMMA tile (the other lanes compute
-// on whatever they hold and are never read): per tile of 64 keys and KV head 16 MMAs of N = 64 for the scores and
-// eight of N = 256 for the weighted sum, ~1500 tensor cycles against ~3000 cycles of HBM time.  (Scores block by
+// the 4 x width <= 64 query rows of one KV head sit in lanes 0..63 of a 128-row UMMA tile (the other lanes compute
+// on whatever they hold and are never read; up to 8 tokens per row only lanes 0..31 are used): per tile of 64 keys
+// and KV head 16 MMAs of N = 64 for the scores and eight of N = 256 for the weighted sum, ~1500 tensor cycles against ~3000 cycles of HBM time.  (Scores block by
 // block, 64 MMAs of N = 16 per tile, were measured first: 345 us on C2 shapes, the small MMAs cost more to issue
 // than they compute.)
 //
@@ -17,13 +17,14 @@
 // chunk, so that the whole tile is one N = 64 operand), its V block by block as [chunk][16 keys][128 B] (one 8 KiB
 // box per block: P V contracts 16 keys per MMA anyway).  One CTA per SM (192 KiB of shared memory: three tiles in
 // flight; 512 TMEM columns).
-//   warp 0   softmax and epilogue: lane r = query row r = token * 4 + head of the group.  Per row segment it stages
+//   warp 0   (and warp 1 for rows of more than 8 tokens: a warp may only touch the 32 TMEM lanes of its quarter)
+//            softmax and epilogue: lane r = query row r = token * 4 + head of the group.  Per row segment it stages
 //            the query rows into tensor memory, per tile of up to four blocks (64 keys) reads the scores
 //            (tcgen05.ld), masks (key < length, key <= the token's position), keeps the running maximum lazily (O in
 //            tensor memory is rescaled only when a tile exceeds it by 2^8) and writes the weights back over the
 //            scores as two bf16 terms (hi + lo); at the end of the segment it reads O and stores the row (whole row
 //            in this range) or the un-normalised partial with its (max, sum).
-//   warp 1   producer: block ids straight from the block table (32 at a time), TMA boxes into the ring.
+//   warp 3   producer: block ids straight from the block table (32 at a time), TMA boxes into the ring.
 //   warp 2   MMA issue: S(t) = Q K(t)^T into one of two score buffers, O += P(t) V(t) once the weights are
 //            written; S(t + 2) follows P V (t).  tcgen05.commit releases ring stages and signals the softmax warp.
 // A row cut over several ranges is folded afterwards by decode_umma_merge_kernel (one CTA per row, stream order
@@ -49,7 +50,7 @@ constexpr int kUdColS = 128;      // two score buffers of 64 columns; the weight
 constexpr int kUdColO = 256;      // output accumulator: columns [256, 512)
 constexpr int kUdHalfBlock = kBlk * kD * 2;  // K (or V) of one KV head of one block: 8 KiB
 constexpr float kUdRescaleGap = 8.f;
-constexpr int kUdMaxWidth = 8;
+constexpr int kUdMaxWidth = 16;  // 64 query rows per KV head: two softmax warps
 
 struct UdSmem {
   alignas(1024) char k[kUdStages][4][kUdTileBlocks * kBlk * 128];  // [stage][64-d chunk][64 keys][128 B], swizzled
@@ -71,7 +72,7 @@ __device__ __forceinline__ void ud_tma_box(uint32_t dst, const CUtensorMap* map,
       : "memory");
 }
 
-// ---- warp 1: TMA loads --------------------------------------------------------------------------
+// ---- warp 3: TMA loads --------------------------------------------------------------------------
 __device__ __forceinline__ void ud_producer(const CUtensorMap* k_map, const CUtensorMap* v_map, const DecodeParams& p,
                                             UdSmem& sm, int kvh, int b, int j, long long g, long long g1, int lane) {
   const int oob = (int)(p.num_blocks * kBlk);  // a box that starts here is filled with zeros
@@ -172,9 +173,9 @@ __device__ __forceinline__ void ud_mma_warp(UdSmem& sm, const DecodeParams& p, u
 
 // Query rows of one table row into tensor memory: lane = row (token * 4 + head), 256 dims -> 128 columns, two bf16 per
 // column; sixteen 16-byte loads in flight at a time (one at a time, the eight round trips to memory cost a segment
-// more than its epilogue).  Arrives on q_full.
-__device__ __forceinline__ void ud_stage_q(UdSmem& sm, const DecodeParams& p, uint32_t tmem, int kvh, int row_b, int lane) {
-  const int tok = lane >> 2, head = lane & 3;
+// more than its epilogue).  `tmem` addresses this warp's lanes; `row` = 32 * warp + lane.  Arrives on q_full.
+__device__ __forceinline__ void ud_stage_q(UdSmem& sm, const DecodeParams& p, uint32_t tmem, int kvh, int row_b, int row) {
+  const int tok = row >> 2, head = row & 3;
   const bool real = tok < p.width;
   const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.q) +
                                                     (((long long)row_b * p.width + (real ? tok : 0)) * kHq + kvh * kG + head) * kD);
@@ -198,17 +199,17 @@ __device__ __forceinline__ void ud_stage_q(UdSmem& sm, const DecodeParams& p, ui
   mbar_arrive(smem_u32(&sm.q_full));
 }
 
-// ---- warp 0: query staging, softmax, epilogue ----------------------------------------------------
+// ---- warps 0 and 1: query staging, softmax, epilogue ----------------------------------------------------
 __device__ __forceinline__ void ud_softmax_warp(UdSmem& sm, const DecodeParams& p, uint32_t tmem, int kvh, int b, int j,
-                                                long long g, long long g1, int range, int lane) {
-  const int tok = lane >> 2, head = lane & 3;
+                                                long long g, long long g1, int range, int row) {
+  const int tok = row >> 2, head = row & 3;
   const bool real = tok < p.width;
   const float scale_log2 = p.scale * kLog2e;
   const int slot_rows = p.width * kHq;
   Seg s, nxt;
   uint32_t gt = 0;
   bool have = next_seg(p, b, j, g, g1, s);
-  if (have) ud_stage_q(sm, p, tmem, kvh, s.b, lane);
+  if (have) ud_stage_q(sm, p, tmem, kvh, s.b, row);
   while (have) {
     const long long qbase = (long long)s.b * p.width;
     bool have_next = false;
@@ -289,7 +290,7 @@ __device__ __forceinline__ void ud_softmax_warp(UdSmem& sm, const DecodeParams& 
         // free: the next row's queries go in now, and its first scores are computed while this segment's output is
         // still being read out below (the MMA warp holds the next P V back until o_free).
         have_next = next_seg(p, b, j, g, g1, nxt);
-        if (have_next) ud_stage_q(sm, p, tmem, kvh, nxt.b, lane);
+        if (have_next) ud_stage_q(sm, p, tmem, kvh, nxt.b, row);
       }
     }
     // ---- end of the segment: O -> the output row (the whole row lies in this range) or this range's partial
@@ -373,12 +374,13 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_const
       mbar_init(smem_u32(&sm.full_bar[i]), 1);
       mbar_init(smem_u32(&sm.empty_bar[i]), 1);
     }
-    mbar_init(smem_u32(&sm.q_full), 32);
+    const uint32_t softmax_threads = p.width > 8 ? 64u : 32u;
+    mbar_init(smem_u32(&sm.q_full), softmax_threads);
     mbar_init(smem_u32(&sm.s_full[0]), 1);
     mbar_init(smem_u32(&sm.s_full[1]), 1);
-    mbar_init(smem_u32(&sm.p_full), 32);
+    mbar_init(smem_u32(&sm.p_full), softmax_threads);
     mbar_init(smem_u32(&sm.pv_done), 1);
-    mbar_init(smem_u32(&sm.o_free), 32);
+    mbar_init(smem_u32(&sm.o_free), softmax_threads);
     mbar_fence_init();
   }
   tc_fence_before_sync();
@@ -387,9 +389,10 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_const
   const uint32_t tmem = sm.tmem_base;
   const int b0 = sm.start_b, j0 = sm.start_j;
 
-  if (warp == 0) ud_softmax_warp(sm, p, tmem, kvh, b0, j0, g0, g1, range, lane);
-  else if (warp == 1) ud_producer(&k_map, &v_map, p, sm, kvh, b0, j0, g0, g1, lane);
+  if (warp == 0 || (warp == 1 && p.width > 8))  // this warp's quarter of the TMEM lanes: rows 32 * warp ..
+    ud_softmax_warp(sm, p, tmem + ((uint32_t)(warp * 32) << 16), kvh, b0, j0, g0, g1, range, warp * 32 + lane);
   else if (warp == 2) ud_mma_warp(sm, p, tmem, b0, j0, g0, g1);
+  else if (warp == 3) ud_producer(&k_map, &v_map, p, sm, kvh, b0, j0, g0, g1, lane);
 
   tc_fence_before_sync();
   __syncthreads();

@@ -59,6 +59,7 @@ __device__ unsigned long long g_phase_ns[256][8];
 constexpr int kWStages = 4;
 static_assert(kWStages % 2 == 0, "each stage must belong to one block parity");
 constexpr int kWMaxWidth = 8;   // 1..4: one row tile per warp; 5..8: the dual form
+constexpr int kWideMaxWidth = 16;  // what nvj_paged_decode_wide takes; beyond kWMaxWidth on the tcgen05 form only
 constexpr int kWPad = 136;                    // row pitch (floats) of the parity exchange buffer
 
 struct WideSmem {
@@ -586,15 +587,17 @@ static size_t wide_acc_bytes(int n, int width) { return ws_round(sizeof(float) *
 // p carries everything but the tensor maps: pointers, shapes, width (1..4) and the carved workspace, whose
 // partial area holds ws_slots(decode_wide_num_ctas()) slots of width * kHq rows.
 int launch_decode_wide(const DecodeParams& p, cudaStream_t stream) {
-  if (p.width < 1 || p.width > kWMaxWidth || p.num_blocks < 1 || p.num_blocks * kBlk > 0x7fffffffLL || !w_encode_fn())
+  if (p.width < 1 || p.width > kWideMaxWidth || p.num_blocks < 1 || p.num_blocks * kBlk > 0x7fffffffLL || !w_encode_fn())
     return NVJ_ERR_UNSUPPORTED;
   int n = decode_wide_num_ctas();
   if (n <= 0) return NVJ_ERR_LAUNCH;
-  // rows of 5..8 query tokens: the tcgen05 form (two 16-row tiles per warp pair make the mma.sync form compute-bound)
+  // rows of 5 and more query tokens: the tcgen05 form (two 16-row tiles per warp pair make the mma.sync form
+  // compute-bound, and it ends at 8 tokens)
   if (p.wide_form == 2 || (p.wide_form == 0 && p.width > 4)) {
     const int rc = launch_decode_umma(p, stream);
     if (rc != NVJ_ERR_UNSUPPORTED || p.wide_form == 2) return rc;
   }
+  if (p.width > kWMaxWidth) return NVJ_ERR_UNSUPPORTED;
   if (p.cta_limit > 0 && p.cta_limit < n) n = p.cta_limit;
   CUtensorMap k_map, v_map;
   if (!tensor_map_cached(&k_map, 0, p.k_cache, (uint64_t)p.num_blocks * kBlk, w_make_map) ||
@@ -642,7 +645,7 @@ extern "C" int nvj_paged_decode_wide_form(const void* q, const void* k_cache_lay
                                           void* workspace, size_t workspace_bytes, int form, nvj_stream_t stream) {
   using namespace nvj;
   if (batch < 0 || table_width < 0 || num_blocks < 0 || width < 1 || form < 0 || form > 2) return NVJ_ERR_INVALID_ARGUMENT;
-  if (width > kWMaxWidth) return NVJ_ERR_UNSUPPORTED;
+  if (width > kWideMaxWidth || (form == 1 && width > kWMaxWidth)) return NVJ_ERR_UNSUPPORTED;
   if (batch == 0) return NVJ_OK;
   if (!q || !k_cache_layer || !v_cache_layer || !block_tables || !seq_lens || !out) return NVJ_ERR_INVALID_ARGUMENT;
   const uintptr_t al = reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_cache_layer) |
@@ -653,7 +656,10 @@ extern "C" int nvj_paged_decode_wide_form(const void* q, const void* k_cache_lay
   if (n <= 0) return NVJ_ERR_LAUNCH;
   DecodeParams p{};
   p.batch = batch;
-  const int carved = carve_decode_workspace(p, workspace, workspace_bytes, wide_ml_bytes(n, width), wide_acc_bytes(n, width));
+  // rows of more than 8 tokens run on the tcgen05 form only, which parks two partials per pair of CTAs: n slots
+  const size_t ml_bytes = width > kWMaxWidth ? ws_round(sizeof(float) * n * width * kHq * 2) : wide_ml_bytes(n, width);
+  const size_t acc_bytes = width > kWMaxWidth ? ws_round(sizeof(float) * n * width * kHq * kD) : wide_acc_bytes(n, width);
+  const int carved = carve_decode_workspace(p, workspace, workspace_bytes, ml_bytes, acc_bytes);
   if (carved != NVJ_OK) return carved;
   p.q = q;
   p.k_cache = static_cast<const char*>(k_cache_layer);

@@ -359,24 +359,25 @@ def _decode_call(q3, k_layer, v_layer, block_tables, table_width, kv_indptr, kv_
     return out
 
 
-WIDE_DECODE_MAX_WIDTH = 8
+WIDE_DECODE_MAX_WIDTH = 16
 
 
 def wide_decode_supported(q, k_layer) -> bool:
-    """Whether `paged_decode_attention_wide` takes this batch: 2..8 query tokens per row, the model's shape, bf16."""
+    """Whether `paged_decode_attention_wide` takes this batch: 2..16 query tokens per row, the model's shape, bf16."""
     return (q.ndim == 4 and 2 <= q.shape[1] <= WIDE_DECODE_MAX_WIDTH and q.dtype == torch.bfloat16
             and k_layer.dtype == torch.bfloat16 and tuple(q.shape[2:]) == (8, 256) and tuple(k_layer.shape[1:]) == (16, 2, 256))
 
 
 def paged_decode_attention_wide(q, k_layer, v_layer, block_table, seq_lens, positions, scale, *, form=0):
-    """Decode attention for rows of 2..8 query tokens: q `[B, T, 8, 256]` bf16 -> `[B, T, 8 * 256]` fp32.
+    """Decode attention for rows of 2..16 query tokens: q `[B, T, 8, 256]` bf16 -> `[B, T, 8 * 256]` fp32.
 
     Token t of row b sees keys p < seq_lens[b] with p <= positions[b, t] (the reference's wide decode,
     nanovllm_jax/kv_cache.py:852-998); K and V of a row are read once for all of its tokens.
-    `form`: 0 automatic (mma.sync tiles up to 4 tokens per row, tcgen05 beyond), 1 mma.sync tiles, 2 tcgen05.
+    `form`: 0 automatic (mma.sync tiles up to 4 tokens per row, tcgen05 beyond), 1 mma.sync tiles (up to 8 tokens),
+    2 tcgen05.
     """
     if not wide_decode_supported(q, k_layer):
-        raise ValueError("paged_decode_attention_wide: 2..8 bf16 query tokens per row over the bf16 cache [NB, 16, 2, 256]")
+        raise ValueError("paged_decode_attention_wide: 2..16 bf16 query tokens per row over the bf16 cache [NB, 16, 2, 256]")
     lib = _lib.load()
     batch, width = int(q.shape[0]), int(q.shape[1])
     q = q.contiguous()

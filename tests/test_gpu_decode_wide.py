@@ -106,8 +106,8 @@ def test_no_positions_means_no_causal_limit_and_matches_the_packed_route(width, 
 
 def test_refusals():
     from nano_vllm_jax_b200.kernels import paged_kv as K
-    c, q, tables, lens, pos = _case(5, 64, [40, 50], 8)
-    q9 = np.concatenate([q, q[:, :1]], axis=1)
+    c, q, tables, lens, pos = _case(5, 64, [40, 50], 16)
+    q9 = np.concatenate([q, q[:, :1]], axis=1)  # 17 tokens per row
     with pytest.raises(ValueError):
         K.paged_decode_attention_wide(to_torch(q9), to_torch(c["k_cache"][0]), to_torch(c["v_cache"][0]), to_torch(tables),
                                       to_torch(lens), None, SCALE)
@@ -129,3 +129,16 @@ def test_the_two_forms_agree_on_a_batch_of_many_rows(width):
     rows = [0, 17, 95]
     ref = _oracle({"k_cache": c["k_cache"], "v_cache": c["v_cache"]}, q[rows], tables[rows], lens[rows], pos[rows])
     assert np.abs(auto[rows] - ref).max() <= TIGHT
+
+
+@pytest.mark.parametrize("width", [9, 12, 16])
+def test_rows_of_nine_to_sixteen_tokens_take_the_tcgen05_form(width):
+    """The reference verifies up to 9 tokens per row (kv_cache.py:972-977); the second half of the query rows sits in
+    the next 32 TMEM lanes and has a softmax warp of its own."""
+    lens = list(range(width, 2 * BS + 2)) + [5 * BS, 5 * BS + 1, 700, 2600, 9000]
+    c, q, tables, lens, pos = _case(50 + width, 1024, lens, width)
+    out = _run(c, q, tables, lens, pos, 0)
+    assert np.abs(out - _oracle(c, q, tables, lens, pos)).max() <= TIGHT
+    from nano_vllm_jax_b200._lib import NvjError
+    with pytest.raises(NvjError):  # the mma.sync form ends at 8
+        _run(c, q, tables, lens, pos, 1)
