@@ -440,21 +440,34 @@ def decode_phase_cases(dev, iters):
     lib = _lib.load()
     lib.nvj_debug_phase_ns.argtypes = [ctypes.c_void_p]
     lib.nvj_debug_phase_ns.restype = ctypes.c_int
-    pool = 40_000
+    pool = 48_000
     k = _randn_bf16((1, pool, BS, HKV, D), 1, dev)
     v = _randn_bf16((1, pool, BS, HKV, D), 2, dev)
     timer = Timer(dev, iters)
     names = ["entry", "lengths scanned", "start located, barriers up", "block ids staged, first copies issued",
              "first block landed", "last block done", "segment finished (folds included)", "partial counted in"]
-    for rows, ctx in ((1, 32768), (16, 4096), (32, 1500), (8, 1040)):
-        nb = -(-ctx // BS)
-        tables = torch.randperm(pool, device=dev)[: rows * nb].to(torch.int32).view(rows, nb).contiguous()
-        lens = torch.full((rows,), ctx, dtype=torch.int32, device=dev)
+    rng = np.random.default_rng(2)
+    c2_lens = (rng.integers(1024, 4097, size=256) + 1).astype(np.int32)  # the benchmark's batch, for comparison
+    for rows, ctx in ((1, 32768), (16, 4096), (32, 1500), (8, 1040), (256, 0)):
+        if ctx:
+            nb = -(-ctx // BS)
+            tables = torch.randperm(pool, device=dev)[: rows * nb].to(torch.int32).view(rows, nb).contiguous()
+            lens = torch.full((rows,), ctx, dtype=torch.int32, device=dev)
+        else:  # 256 rows of U[1024, 4096] tokens over the same pool (blocks drawn without replacement)
+            tables = torch.from_numpy(tables_for(c2_lens, pool, rng)).to(dev)
+            lens = torch.from_numpy(c2_lens).to(dev)
         q = _randn_bf16((rows, HQ, D), 3, dev)
         us = timer.run(lambda: K.paged_decode_attention(q, k[0], v[0], tables, lens, SCALE, variant=3))
-        host = np.zeros((256, 8), np.uint64)
+        host = np.zeros((256, 12), np.uint64)
         if lib.nvj_debug_phase_ns(host.ctypes.data) != 0:
             raise RuntimeError("nvj_debug_phase_ns failed")
+        if os.environ.get("NVJ_PHASE_DUMP"):  # per CTA: index, SM, blocks, first block landed, last block done (us)
+            base_ns = int(host[:, 0].max()) - 400_000
+            t_first = int(host[host[:, 0] >= base_ns][:, 0].min())
+            np.savetxt(os.environ["NVJ_PHASE_DUMP"] + "_%dx%d.txt" % (rows, ctx),
+                       np.array([[i, int(host[i, 8]), int(host[i, 9]), (int(host[i, 4]) - t_first) / 1e3, (int(host[i, 5]) - t_first) / 1e3,
+                                  int(host[i, 10]) / 1e3, int(host[i, 11])]
+                                 for i in range(256) if host[i, 0] >= base_ns]), fmt="%.2f")
         t0 = host[:, 0].astype(np.int64)
         live = t0 >= t0.max() - 200_000  # CTAs of the last launch
         rel = (host[live].astype(np.int64) - t0[live].min()) / 1e3
@@ -465,8 +478,8 @@ def decode_phase_cases(dev, iters):
             if len(col):
                 phases[name] = {"min": round(float(col.min()), 2), "median": round(float(np.median(col)), 2),
                                 "max": round(float(col.max()), 2), "ctas": int(len(col))}
-        report("paged_decode, %d rows x %d tokens: phases in us after the first CTA's entry" % (rows, ctx), us,
-               rows * ctx * TOKEN_BYTES, {"workload": "short batch", "ctas": int(live.sum()), "phases": phases})
+        report("paged_decode, %d rows x %s tokens: phases in us after the first CTA's entry" % (rows, ctx or "U[1024, 4096]"), us,
+               int(lens.sum().item()) * TOKEN_BYTES, {"workload": "short batch" if ctx else "c2 lengths", "ctas": int(live.sum()), "phases": phases})
     K.check_device_status(dev)
     del k, v
 

@@ -70,6 +70,9 @@ struct FillState {
 // number of attended tokens in the block (0 for a block id outside the pool).
 // All kDecodeThreads threads call this with identical arguments; the caller
 // separates it from the readers of the ring with CTA barriers.
+// (A thread waits for memory once per row segment here, and CTAs whose range holds three rows instead of two issue
+// their first K/V copies later than the others.  Asynchronous 4-byte copies of the ids with a second walk that checks
+// them were measured: the late CTAs gained 1.8 us, the others lost 0.8, the kernel's time did not change.)
 template <class Smem>
 __device__ __forceinline__ void fill_ring(const DecodeParams& p, Smem& sm, FillState& f,
                                           long long g1, int n0, int count) {

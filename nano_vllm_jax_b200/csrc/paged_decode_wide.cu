@@ -46,10 +46,12 @@ namespace nvj {
 // Development aid, compiled in only with -DNVJ_PHASE_TIMING: thread 0 of every CTA stamps the global timer at the
 // kernel's phase boundaries, and nvj_debug_phase_ns copies the stamps out.
 #ifdef NVJ_PHASE_TIMING
-__device__ unsigned long long g_phase_ns[256][8];
+__device__ unsigned long long g_phase_ns[256][12];  // slots 0-7: stamps; 8: the SM the CTA ran on; 9: its number of blocks; 10: ns spent finishing segments; 11: folds it did
 #define NVJ_PHASE(i) do { if (threadIdx.x == 0) g_phase_ns[blockIdx.x][i] = global_timer_ns(); } while (0)
+#define NVJ_PHASE_NOTE(i, v) do { if (threadIdx.x == 0) g_phase_ns[blockIdx.x][i] = (v); } while (0)
 #else
 #define NVJ_PHASE(i) do { } while (0)
+#define NVJ_PHASE_NOTE(i, v) do { } while (0)
 #endif
 
 // An even number, so that a stage always holds blocks of the same parity and is read by the same four warps: a
@@ -367,6 +369,16 @@ decode_wide_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_const
   if (g0 == g1) return;
   const int n_iters = (int)(g1 - g0);
   NVJ_PHASE(1);
+#ifdef NVJ_PHASE_TIMING
+  {
+    unsigned smid;
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+    NVJ_PHASE_NOTE(8, (unsigned long long)smid);
+    NVJ_PHASE_NOTE(9, (unsigned long long)n_iters);
+    NVJ_PHASE_NOTE(10, 0ull);
+    NVJ_PHASE_NOTE(11, 0ull);
+  }
+#endif
 
   // ---- pass 2: locate (row, block) of g0
   long long carry = 0;
@@ -493,7 +505,16 @@ decode_wide_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_const
       __syncwarp();
     }
     NVJ_PHASE(5);
+#ifdef NVJ_PHASE_TIMING
+    const unsigned long long fin0 = global_timer_ns();
+#endif
     w_finish_segment<kDual>(p, sm, s, st, warp, lane, pt);
+#ifdef NVJ_PHASE_TIMING
+    if (threadIdx.x == 0) {
+      g_phase_ns[blockIdx.x][10] += global_timer_ns() - fin0;
+      g_phase_ns[blockIdx.x][11] += (unsigned long long)sm.is_last;
+    }
+#endif
     NVJ_PHASE(6);
   }
   // Only after a timeout can copies still be in flight with nobody waiting for them: hold the
