@@ -96,6 +96,65 @@ class HybridStateTable:
         return HybridLayerState(None if self.conv is None else self.conv[s:s + 1],
                                 None if self.rec is None else self.rec[s:s + 1])
 
+    # ---- a step's batch (model_runner.py:4181-4305)
+    def batch_slot_ids(self, seq_ids: Seq[int]) -> List[int]:
+        """Slots of a scheduled batch, assigning (and zeroing) new ones; -1 for padding rows (seq id < 0).  A forward
+        pass that indexes the table by these ids needs no gather (model_runner.py:4307-4330)."""
+        return [self.slot(int(i)) if int(i) >= 0 else -1 for i in seq_ids]
+
+    def _pairs(self, slots: Seq[int], rows: Seq[int]):
+        if self.device.type == "cuda" and len(slots) <= _k.HYBRID_HOST_SLOTS:
+            return list(slots), list(rows)
+        t = torch.tensor(list(slots) + list(rows), dtype=torch.int32)
+        if self.device.type == "cuda":
+            t = t.pin_memory().to(self.device, non_blocking=True)
+        return t[:len(slots)], t[len(slots):]
+
+    def gather_batch(self, seq_ids: Seq[int], out: Optional[HybridLayerState] = None) -> HybridLayerState:
+        """The batch's state rows as one `[B, ...]` pair, row r = the slot of seq_ids[r] (`_batch_hybrid_state`): zeros
+        for padding rows and for sequences seen for the first time.  When the batch is the whole table in slot order
+        the table itself is returned, as the reference does; otherwise one index-list copy launch into `out`
+        (allocated when not given)."""
+        slots = self.batch_slot_ids(seq_ids)
+        n = len(slots)
+        if n == self.max_slots and slots == list(range(n)):
+            return HybridLayerState(self.conv, self.rec)
+        if out is None:
+            out = HybridLayerState(None if self.conv is None else torch.empty((n, *self.conv.shape[1:]), dtype=self.conv.dtype, device=self.device),
+                                   None if self.rec is None else torch.empty((n, *self.rec.shape[1:]), dtype=self.rec.dtype, device=self.device))
+        live = [(s, r) for r, s in enumerate(slots) if s >= 0]
+        for r, s in enumerate(slots):
+            if s < 0:
+                for t in (out.conv_state, out.recurrent_state):
+                    if t is not None:
+                        t[r].zero_()
+        if live:
+            t_slots, t_rows = self._pairs([s for s, _ in live], [r for _, r in live])
+            _k.hybrid_copy(self.conv, self.rec, out.conv_state, out.recurrent_state, t_slots, t_rows, restore=False)
+        return out
+
+    def store_batch(self, seq_ids: Seq[int], state: Optional[HybridLayerState], query_lens: Optional[Seq[int]] = None,
+                    is_prefill: bool = True) -> None:
+        """table[slot(seq_ids[r])] <- state[r] for the rows that ran (`_store_batch_hybrid_state`): padding rows, and in
+        a decode batch rows whose query length is 0, are left alone.  Nothing to do when `state` is the table."""
+        if state is None or (state.conv_state is self.conv and state.recurrent_state is self.rec):
+            if state is not None:
+                self.mark_written([int(i) for i in seq_ids if int(i) >= 0])
+            return
+        rows, slots, ids = [], [], []
+        for r, i in enumerate(seq_ids):
+            i = int(i)
+            if i < 0 or (not is_prefill and query_lens is not None and int(query_lens[r]) <= 0):
+                continue
+            rows.append(r)
+            slots.append(self.slot(i))
+            ids.append(i)
+        if not rows:
+            return
+        t_slots, t_rows = self._pairs(slots, rows)
+        _k.hybrid_copy(self.conv, self.rec, state.conv_state, state.recurrent_state, t_slots, t_rows, restore=True)
+        self.mark_written(ids)
+
 
 class PrefixStateCache:
     """Pool of state snapshots keyed by prefix hash (scheduler.py:67-69, 239-279)."""

@@ -322,3 +322,45 @@ def test_short_chunk_with_key_range_splits_matches_the_unsplit_kernels_and_the_o
         assert err <= 2e-3, f"variant {variant}: max-abs {err}"
         assert not out[556:].any()
     assert np.abs(outs[4] - outs[3]).max() <= 2e-3
+
+
+def test_hybrid_state_batch_gather_and_store_match_indexing():
+    """`gather_batch` / `store_batch` (the reference's `_batch_hybrid_state` / `_store_batch_hybrid_state`) against
+    plain indexing: row order, zeros for padding rows and first-time sequences, rows of a decode batch that did not run
+    left alone, the whole table in slot order handed out without a copy."""
+    import torch
+    from nano_vllm_jax_b200.engine.prefix_state import HybridStateTable
+    from nano_vllm_jax_b200.kv_cache import HybridLayerState
+    tab = HybridStateTable((3, 64, 4), (3, 4, 16, 16), max_slots=6)
+    for sid in (10, 11, 12, 13):
+        tab.slot(sid)
+    for sid in (10, 11, 12, 13):  # only rows of assigned slots may hold data: free slots are known to be zero
+        s = tab.slot(sid)
+        tab.conv[s].copy_(torch.randn(tab.conv.shape[1:], device="cuda").to(tab.conv.dtype))
+        tab.rec[s].copy_(torch.randn(tab.rec.shape[1:], device="cuda"))
+    tab.mark_written([10, 11, 12, 13])
+    conv0, rec0 = tab.conv.clone(), tab.rec.clone()
+    ids = [12, -1, 10, 99, 13]  # a padding row and a sequence never seen before (gets a zeroed slot)
+    got = tab.gather_batch(ids)
+    slots = [tab.slot(12), -1, tab.slot(10), tab.slot(99), tab.slot(13)]
+    for r, s in enumerate(slots):
+        if s < 0 or ids[r] == 99:
+            assert not got.conv_state[r].any() and not got.recurrent_state[r].any()
+        else:
+            assert torch.equal(got.conv_state[r], conv0[s]) and torch.equal(got.recurrent_state[r], rec0[s])
+    # a decode batch: the row with query length 0 and the padding row keep their table rows
+    new = HybridLayerState(torch.randn_like(got.conv_state), torch.randn_like(got.recurrent_state))
+    before = (tab.conv.clone(), tab.rec.clone())
+    tab.store_batch(ids, new, query_lens=[1, 0, 0, 1, 1], is_prefill=False)
+    torch.cuda.synchronize()
+    for r, s in enumerate(slots):
+        if s < 0:
+            continue
+        ran = [1, 0, 0, 1, 1][r] > 0
+        want_c, want_r = (new.conv_state[r], new.recurrent_state[r]) if ran else (before[0][s], before[1][s])
+        assert torch.equal(tab.conv[s], want_c) and torch.equal(tab.rec[s], want_r)
+    # the whole table in slot order: no copy
+    full = HybridStateTable((3, 64, 4), (3, 4, 16, 16), max_slots=3)
+    whole = full.gather_batch([0, 1, 2])
+    assert whole.conv_state is full.conv and whole.recurrent_state is full.rec
+    full.store_batch([0, 1, 2], whole)
