@@ -309,9 +309,8 @@ int nvj_paged_decode_wide(const void* q, const void* k_cache_layer, const void* 
  *              bytes also lets the CTA-pair tile kernel (variants 0, 4, 5) split every tile's key
  *              range over several CTA pairs when the batch is too short to fill the GPU (a
  *              512-token chunk is 16 pairs on 74 pair slots): the splits park their un-normalised
- *              rows between the workspace's header and the decode partials, and the pair that
- *              arrives last folds them.  Like the decode workspace it must start zeroed and is left
- *              zeroed where that matters.
+ *              rows between the workspace's header and the decode partials, and a second small
+ *              launch behind the tile kernel folds them (batches without single-token rows only).
  *   variant    0 = automatic; 1 = generic CUDA-core kernel (any shape or dtype); for the model's
  *              shape (bf16 cache, block 16, 2 KV x 4 query heads, head_dim 256): 2 = mma.sync
  *              tiles of 16 tokens, 3 = tcgen05 tiles of 32 tokens with accumulators in tensor

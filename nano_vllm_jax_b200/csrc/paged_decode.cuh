@@ -117,15 +117,11 @@ __host__ __device__ inline size_t ws_round(size_t x) { return (x + kWsAlign - 1)
 constexpr int kMergeGroup = 13;
 constexpr int kTreeMergeMin = 32;
 constexpr int kGroupCounters = 64;
-// Arrival counters of the prefill tile kernel's key-range splits (one per CTA tile and KV head), after the group counters.
-constexpr int kSplitCounters = 512;
 __host__ __device__ inline int ws_groups(int num_ctas) { return (num_ctas + kMergeGroup - 1) / kMergeGroup; }
 // Partial slots: two per CTA, then two per group.
 __host__ __device__ inline size_t ws_slots(int num_ctas) { return 2ull * num_ctas + 2ull * ws_groups(num_ctas); }
-// Header = status word (64 B) + the group counters + the split counters + one int32 counter per row.
-inline size_t ws_header_bytes(int max_batch) {
-  return ws_round(64 + sizeof(int32_t) * ((size_t)max_batch + kGroupCounters + kSplitCounters));
-}
+// Header = status word (64 B) + the group counters + one int32 counter per row.
+inline size_t ws_header_bytes(int max_batch) { return ws_round(64 + sizeof(int32_t) * ((size_t)max_batch + kGroupCounters)); }
 inline size_t ws_ml_bytes(int num_ctas) { return ws_round(sizeof(float) * ws_slots(num_ctas) * kHq * 2); }
 inline size_t ws_acc_bytes(int num_ctas) { return ws_round(sizeof(float) * ws_slots(num_ctas) * kHq * kD); }
 
@@ -134,8 +130,7 @@ inline size_t ws_acc_bytes(int num_ctas) { return ws_round(sizeof(float) * ws_sl
 // writes may land where a later call keeps state that must start at zero:
 //   [0, 64)              status word
 //   [64, 320)            group arrival counters
-//   [320, 2368)          arrival counters of the prefill kernel's key-range splits
-//   [2368, 2368 + 4 rows)  row arrival counters
+//   [320, 320 + 4 rows)  row arrival counters
 //   ... unused, or the partial outputs of the prefill kernel's key-range splits, which end where the next part begins ...
 //   the last ml_bytes + acc_bytes of the buffer: partial (max, sum) pairs and accumulators
 // The counters are zero before the first use and every launch leaves them zero again; the partials are always
@@ -150,15 +145,12 @@ inline int carve_decode_workspace(DecodeParams& p, void* workspace, size_t bytes
   char* w = static_cast<char*>(workspace);
   p.status = reinterpret_cast<int32_t*>(w);
   p.group_counters = reinterpret_cast<int32_t*>(w + 64);
-  p.counters = reinterpret_cast<int32_t*>(w + 64 + sizeof(int32_t) * (kGroupCounters + kSplitCounters));
+  p.counters = reinterpret_cast<int32_t*>(w + 64 + sizeof(int32_t) * kGroupCounters);
   p.part_acc = reinterpret_cast<float*>(w + end - acc_bytes);
   p.part_ml = reinterpret_cast<float*>(w + end - acc_bytes - ml_bytes);
   return NVJ_OK;
 }
 
-inline int32_t* ws_split_counters(void* workspace) {
-  return reinterpret_cast<int32_t*>(static_cast<char*>(workspace) + 64 + sizeof(int32_t) * kGroupCounters);
-}
 // Bytes that the prefill kernel's key-range splits may need for their partial outputs on the current device.
 size_t prefill_split_bytes();
 

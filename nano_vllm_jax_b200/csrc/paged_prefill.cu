@@ -19,8 +19,7 @@ int launch_prefill_umma2(const void* q, int q_dtype, const char* k_cache, const 
                          long long num_blocks, const int32_t* block_tables, int table_width,
                          const int32_t* kv_lens, const int32_t* positions, const int32_t* query_start_loc,
                          int rows, int token_bucket, float scale, float* out, int32_t* status,
-                         int skip_single, int split_p, int32_t* split_counters, float* split_area, size_t split_bytes,
-                         cudaStream_t stream);
+                         int skip_single, int split_p, float* split_area, size_t split_bytes, cudaStream_t stream);
 int launch_prefill_umma(const void* q, int q_dtype, const char* k_cache, const char* v_cache,
                         long long num_blocks, const int32_t* block_tables, int table_width,
                         const int32_t* kv_lens, const int32_t* positions, const int32_t* query_start_loc,
@@ -109,22 +108,22 @@ static int run_tiles(const PackedArgs& a, int skip_single, cudaStream_t s) {
   if (variant == 0 || variant == 4 || variant == 5) {
     // A workspace with room between the header and the decode partials (what run_single_token_rows carves from the
     // same buffer) lets a short batch split every tile's key range over several CTA pairs.
-    int32_t* split_counters = nullptr;
     float* split_area = nullptr;
     size_t split_bytes = 0;
     const int num_ctas = decode_num_ctas();
-    if (a.workspace && num_ctas > 0 && (reinterpret_cast<uintptr_t>(a.workspace) & 15u) == 0) {
+    // (not in a mixed batch, whose decode rows have just been served from the same workspace: there the extra merge
+    // launch costs a host-bound step more than the split saves)
+    if (!skip_single && a.workspace && num_ctas > 0 && (reinterpret_cast<uintptr_t>(a.workspace) & 15u) == 0) {
       const size_t end = a.workspace_bytes / kWsAlign * kWsAlign;
       const size_t tail = ws_ml_bytes(num_ctas) + ws_acc_bytes(num_ctas), head = ws_header_bytes(a.rows);
       if (end > head + tail) {
         split_bytes = (end - head - tail) / kWsAlign * kWsAlign;
         split_area = reinterpret_cast<float*>(static_cast<char*>(a.workspace) + end - tail - split_bytes);
-        split_counters = ws_split_counters(a.workspace);
       }
     }
     const int rc = launch_prefill_umma2(a.q, a.q_dtype, kc, vc, a.num_blocks, a.block_tables, a.table_width, a.kv_lens, a.positions,
                                         a.query_start_loc, a.rows, a.token_bucket, a.scale, a.out, a.status, skip_single,
-                                        variant == 5 ? 0 : 1, split_counters, split_area, split_bytes, s);
+                                        variant == 5 ? 0 : 1, split_area, split_bytes, s);
     if (rc != NVJ_ERR_UNSUPPORTED || variant != 0) return rc;
   }
   if (variant == 0 || variant == 3) {

@@ -20,9 +20,10 @@
 // Every mbarrier wait is bounded; a timeout flags NVJ_DEV_TIMEOUT and both CTAs still reach
 // the final cluster barrier and free their tensor memory.
 // Short batches (a 512-token chunk is 16 CTA pairs on 74 pair slots) split every tile's key range over up to
-// kU2MaxSplits pairs (blockIdx.z): each split writes its un-normalised rows and their (max, sum) to a workspace,
-// counts itself in per CTA tile, and the CTA that arrives last folds the splits into the output.  Nothing waits
-// for another CTA.
+// kU2MaxSplits pairs (blockIdx.z): each split writes its un-normalised rows and their (max, sum) to a workspace and
+// is done; prefill_umma2_merge_kernel, launched behind this kernel, folds the splits of every tile into the output
+// with the whole GPU (a first build let the pair that arrived last fold its tile alone: ~10 us of round trips to
+// the L2 on two SMs, so that only key ranges of 16 tiles or more were worth splitting).
 // Semantics: nanovllm_jax/kv_cache.py:831-849, nanovllm_jax/kernels/full_attention_triton.py:51-145.
 
 #include <cstddef>
@@ -45,13 +46,13 @@ constexpr uint32_t kU2LeaderMask = 0xFEFFFFFFu;         // clears the CTA-rank b
 constexpr float kU2Log2e = 1.4426950408889634f;
 constexpr float kU2RescaleGap = 8.f;
 constexpr int kU2MaxSplits = 4;
-// What a split costs is fixed: its rows go out to the workspace, and the pair that arrives last fetches the other
-// splits' rows from the L2, about five round trips of ~2 us on this two-die part whatever their number.  A key tile
-// costs a pair ~1 us.  So only key ranges of kU2SplitFrom tiles or more are split, into pieces of at least
-// kU2MinSplitTiles tiles (512-token chunk behind a 512-token prefix, 16 tiles: 32.8 us unsplit, 30.8 us in four
-// pieces; behind 1536 tokens the range is twice as long and the split pays properly).
-constexpr int kU2SplitFrom = 16;
-constexpr int kU2MinSplitTiles = 4;
+// What a split costs: its rows go out to the workspace (~1 us) and the merge launch behind the kernel (~5 us for the
+// batch, whatever the number of splits).  A key tile costs a pair ~1 us.  Key ranges of kU2SplitFrom tiles or more
+// are split into pieces of at least kU2MinSplitTiles tiles.
+constexpr int kU2SplitFrom = 8;
+constexpr int kU2MinSplitTiles = 3;
+constexpr int kU2MergeThreads = 256;
+constexpr int kU2MergeParts = 8;  // CTAs of the merge launch per CTA tile: 4 of its 32 tokens each
 
 // Development aid, compiled in only with -DNVJ_PHASE_TIMING: the first softmax thread of every CTA stamps the global
 // timer at the kernel's phase boundaries (slot 7: the number of key tiles), nvj_debug_prefill_phase_ns copies them out.
@@ -78,10 +79,10 @@ struct Umma2Params {
   int split_p;  // 1: P enters P V as two bf16 terms (hi + lo), 0: as one (the weights are then bf16-rounded)
   float scale;
   // key-range splits (gridDim.z > 1): un-normalised rows [split][token][head][kD], their (max, sum)
-  // [split][token][head][2], one arrival counter per (CTA tile, KV head), zero between launches; pair slots of the device
+  // [split][token][head][2]; pair slots of the device
   float* part_o;
   float* part_ml;
-  int32_t* split_counters;
+  int4* tile_info;  // per (CTA of the x grid, KV head): {first token, tokens, splits, 0}, written by split 0 for the merge launch
   int pair_slots;
 };
 
@@ -97,7 +98,7 @@ struct Umma2Smem {
   alignas(16) char qstage[kU2Tokens * kG * kD * 2];
   float own_ml[2][kU2Rows];  // this split's (max, sum) per row, for the fold
   uint32_t tmem_base;
-  int row, tok0, ntok, pair_last_tok, idle_index, abort_flag, total_pairs, is_last;
+  int row, tok0, ntok, pair_last_tok, idle_index, abort_flag, total_pairs;
 };
 
 // ---- cta_group::2 wrappers ---------------------------------------------------------------------
@@ -456,80 +457,64 @@ __device__ __forceinline__ void u2_softmax_warps(Umma2Smem& sm, const Umma2Param
         *reinterpret_cast<float2*>(p.part_ml + ((long long)blockIdx.z * split_rows + g) * 2) = make_float2(sm.own_ml[0][rr], sm.own_ml[1][rr]);
     }
   }
-  NVJ_U2_PHASE(5);
-  if (splits == 1) return;
-  // ---- count this split in; the CTA that delivers a tile's last split folds them (its own rows are still staged)
-  int32_t* counter = p.split_counters + blockIdx.x * kHkv + kvh;
-  __threadfence();
-  named_bar_sync(1, kU2SoftmaxThreads);
-  if (warp == 2 && lane == 0) sm.is_last = (atomicAdd(counter, 1) == splits - 1) ? 1 : 0;
-  named_bar_sync(1, kU2SoftmaxThreads);
-  if (!sm.is_last) return;
-  __threadfence();
-  if (warp == 2 && lane == 0) *counter = 0;
-  // Pass 1: the weights.  Lane (row a or a + 8 of this warp's sixteen, split) reads that split's (max, sum); groups of
-  // four lanes reduce them; every split's weight, already divided by the row's total, is left in shared memory (the
-  // exchange buffer of the softmax is free by now).
-  static_assert(kU2MaxSplits == 4 && sizeof(sm.xchg) >= 8 * 16 * kU2MaxSplits * sizeof(float), "fold weights live in xchg");
-  float* fw = &sm.xchg[0][0][0] + sw * 16 * kU2MaxSplits;
-  const int own = (int)blockIdx.z;
-#pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    const int a = (lane >> 2) + 8 * h, s2 = lane & 3;
-    const int rr = sw * 16 + a, tk = rr & 31, hd = rr >> 5;
-    const long long g = (long long)(tok0 + tk) * kHq + kvh * kG + hd;
-    float2 e = make_float2(-INFINITY, 0.f);
-    if (tk < ntok && s2 < splits)
-      e = s2 == own ? make_float2(sm.own_ml[0][rr], sm.own_ml[1][rr])
-                    : __ldcg(reinterpret_cast<const float2*>(p.part_ml + ((long long)s2 * split_rows + g) * 2));
-    float big = fmaxf(e.x, __shfl_xor_sync(0xffffffffu, e.x, 1));
-    big = fmaxf(big, __shfl_xor_sync(0xffffffffu, big, 2));
-    const float w = e.x == -INFINITY ? 0.f : ex2_approx(e.x - big);
-    float total = w * e.y;
-    total += __shfl_xor_sync(0xffffffffu, total, 1);
-    total += __shfl_xor_sync(0xffffffffu, total, 2);
-    fw[a * kU2MaxSplits + s2] = total > 0.f ? w / total : 0.f;
-  }
-  __syncwarp();
-  // Pass 2: four rows at a time, the other splits' pieces of all four requested before any is used (the fold is bound
-  // by the round trips to the L2, not by their volume).
-#pragma unroll 1
-  for (int a0 = 0; a0 < 16; a0 += 4) {
-    float4 x[4][kU2MaxSplits - 1][2];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int rr = sw * 16 + a0 + i, tk = rr & 31, hd = rr >> 5;
-      const long long g = (long long)(tok0 + tk) * kHq + kvh * kG + hd;
-#pragma unroll
-      for (int jx = 0; jx < kU2MaxSplits - 1; ++jx) {
-        const int s2 = jx + (jx >= own ? 1 : 0);
-        const bool ok = tk < ntok && s2 < splits;
-        const float4* src = reinterpret_cast<const float4*>(p.part_o + ((long long)s2 * split_rows + g) * kD);
-        x[i][jx][0] = ok ? __ldcg(src + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
-        x[i][jx][1] = ok ? __ldcg(src + 32 + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
-      }
+  NVJ_U2_PHASE(5);  // a split is done here: the merge launch folds the splits
+}
+
+// Which (table row, 32-token tile) the CTA with cluster index `cluster` of `clusters` and rank `rank` serves: the
+// heaviest pairs (the last tokens of a row see the most keys) get the lowest cluster indices.  One thread runs this.
+// row < 0: no tile (`idle` then numbers the clusters beyond the last pair 0, 1, ...).  `total` (the batch's number
+// of pairs) is complete only when `need_total`.
+struct U2Tile {
+  int row, tok0, ntok, pair_last_tok, idle, total;
+};
+__device__ __forceinline__ U2Tile u2_find_tile(const Umma2Params& p, int cluster, int clusters, int rank, bool need_total) {
+  U2Tile t{-1, 0, 0, 0, -1, 0};
+  int idx = clusters - 1 - cluster;
+  for (int r = 0; r < p.rows; ++r) {
+    const int lo = p.query_start_loc[r];
+    int hi = p.query_start_loc[r + 1];
+    hi = hi < p.token_bucket ? hi : p.token_bucket;
+    int pairs = hi > lo ? (hi - lo + 2 * kU2Tokens - 1) / (2 * kU2Tokens) : 0;
+    if (p.skip_single && p.query_start_loc[r + 1] - lo == 1) pairs = 0;
+    t.total += pairs;
+    if (t.row < 0 && idx < pairs) {
+      t.row = r;
+      t.tok0 = lo + (2 * idx + rank) * kU2Tokens;
+      t.ntok = hi - t.tok0 < kU2Tokens ? hi - t.tok0 : kU2Tokens;
+      if (t.ntok < 0) t.ntok = 0;
+      const int pair_end = lo + (2 * idx + 2) * kU2Tokens;
+      t.pair_last_tok = (pair_end < hi ? pair_end : hi) - 1;
+      if (!need_total) break;
     }
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int rr = sw * 16 + a0 + i, tk = rr & 31, hd = rr >> 5;
-      if (tk >= ntok) continue;
-      const long long g = (long long)(tok0 + tk) * kHq + kvh * kG + hd;
-      const float w_own = fw[(a0 + i) * kU2MaxSplits + own];
-#pragma unroll
-      for (int h2 = 0; h2 < 2; ++h2) {
-        const int c = h2 * 32 + lane;
-        const float4 mine = *reinterpret_cast<const float4*>(stage + rr * kD + (((c & ~7) | ((c ^ rr) & 7)) << 2));
-        float4 acc = make_float4(mine.x * w_own, mine.y * w_own, mine.z * w_own, mine.w * w_own);
-#pragma unroll
-        for (int jx = 0; jx < kU2MaxSplits - 1; ++jx) {
-          const float ws = fw[(a0 + i) * kU2MaxSplits + jx + (jx >= own ? 1 : 0)];  // 0 for a split that does not exist
-          acc.x = fmaf(x[i][jx][h2].x, ws, acc.x); acc.y = fmaf(x[i][jx][h2].y, ws, acc.y);
-          acc.z = fmaf(x[i][jx][h2].z, ws, acc.z); acc.w = fmaf(x[i][jx][h2].w, ws, acc.w);
-        }
-        reinterpret_cast<float4*>(p.out + g * kD)[c] = acc;
-      }
-    }
+    if (t.row < 0) idx -= pairs;
   }
+  if (t.row < 0) t.idle = idx;
+  return t;
+}
+// Key tiles of the pair (warp-collective; the same in every warp of both CTAs): the token of the pair that sees the most
+// keys bounds the key range (positions need not grow along the tiles).  `kv_len` comes back clipped to the table.
+__device__ __forceinline__ int u2_key_tiles(const Umma2Params& p, int row, int tok0, int rank, int pair_last_tok, int lane,
+                                            int& kv_len, bool flag) {
+  kv_len = p.kv_lens[row];
+  if (kv_len > p.table_width * kBlk) {
+    if (flag) atomicOr(p.status, NVJ_DEV_BAD_LENGTH);
+    kv_len = p.table_width * kBlk;
+  }
+  const int pair_tok0 = tok0 - rank * kU2Tokens, pair_n = pair_last_tok - pair_tok0 + 1;
+  int seen = lane < pair_n ? p.positions[pair_tok0 + lane] : -1;
+  if (lane + 32 < pair_n) seen = max(seen, p.positions[pair_tok0 + lane + 32]);
+  const int max_pos = __reduce_max_sync(0xffffffffu, seen);
+  const int key_end = kv_len < max_pos + 1 ? kv_len : max_pos + 1;
+  return key_end > 0 ? (key_end + kU2Keys - 1) / kU2Keys : 0;
+}
+// Key-range splits of a pair: as many as leave every split kU2MinSplitTiles tiles, as the batch's pairs leave pair
+// slots for, and as the launch has.
+__device__ __forceinline__ int u2_split_count(const Umma2Params& p, int n_tiles, int total_pairs, int launched) {
+  const int room = p.pair_slots / (total_pairs * kHkv > 0 ? total_pairs * kHkv : 1);
+  int splits = n_tiles >= kU2SplitFrom ? n_tiles / kU2MinSplitTiles : 1;
+  splits = splits < room ? splits : room;
+  splits = splits < launched ? splits : launched;
+  return splits > 1 ? splits : 1;
 }
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kU2Threads, 1)
@@ -550,32 +535,15 @@ prefill_umma2_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_con
 
   // ---- which (table row, pair of 32-token tiles) this cluster serves; both CTAs compute the same
   if (threadIdx.x == 0) {
-    // heaviest pairs (the last tokens of a row see the most keys) get the lowest cluster indices
-    int idx = (gridDim.x >> 1) - 1 - (blockIdx.x >> 1), row = -1, tok0 = 0, ntok = 0, last = 0, total = 0;
-    for (int r = 0; r < p.rows; ++r) {
-      const int lo = p.query_start_loc[r];
-      int hi = p.query_start_loc[r + 1];
-      hi = hi < p.token_bucket ? hi : p.token_bucket;
-      int pairs = hi > lo ? (hi - lo + 2 * kU2Tokens - 1) / (2 * kU2Tokens) : 0;
-      if (p.skip_single && p.query_start_loc[r + 1] - lo == 1) pairs = 0;
-      total += pairs;
-      if (row < 0 && idx < pairs) {
-        row = r;
-        tok0 = lo + (2 * idx + rank) * kU2Tokens;
-        ntok = hi - tok0 < kU2Tokens ? hi - tok0 : kU2Tokens;
-        if (ntok < 0) ntok = 0;
-        const int pair_end = lo + (2 * idx + 2) * kU2Tokens;
-        last = (pair_end < hi ? pair_end : hi) - 1;
-        if (gridDim.z == 1) break;  // only the key-range splits need the batch's number of pairs
-      }
-      if (row < 0) idx -= pairs;
-    }
-    sm.row = row; sm.tok0 = tok0; sm.ntok = ntok; sm.pair_last_tok = last; sm.abort_flag = 0; sm.total_pairs = total;
-    sm.idle_index = row < 0 ? idx : -1;  // clusters beyond the last pair: 0, 1, ...
+    const U2Tile t = u2_find_tile(p, blockIdx.x >> 1, gridDim.x >> 1, rank, gridDim.z > 1);
+    sm.row = t.row; sm.tok0 = t.tok0; sm.ntok = t.ntok; sm.pair_last_tok = t.pair_last_tok; sm.abort_flag = 0;
+    sm.total_pairs = t.total; sm.idle_index = t.idle;
   }
   __syncthreads();
   const int row = sm.row, tok0 = sm.tok0, ntok = sm.ntok;
+  int4* info = gridDim.z > 1 && blockIdx.z == 0 && threadIdx.x == 0 ? p.tile_info + blockIdx.x * kHkv + kvh : nullptr;
   if (row < 0) {  // the whole cluster leaves: nothing has been allocated or shared yet
+    if (info) *info = make_int4(0, 0, 0, 0);
     if (p.zero_fill && sm.idle_index == 0 && blockIdx.z == 0) {
       // the first idle cluster (there is always one) zeroes the padding tokens, a quarter per CTA of the cluster pair x KV head
       int real = p.query_start_loc[p.rows];
@@ -589,19 +557,10 @@ prefill_umma2_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_con
     return;
   }
 
-  int kv_len = p.kv_lens[row];
-  if (kv_len > p.table_width * kBlk) {
-    if (threadIdx.x == 0 && rank == 0) atomicOr(p.status, NVJ_DEV_BAD_LENGTH);
-    kv_len = p.table_width * kBlk;
-  }
-  // the token of the pair that sees the most keys bounds the key range (positions need not grow along the tiles)
-  const int pair_tok0 = tok0 - rank * kU2Tokens, pair_n = sm.pair_last_tok - pair_tok0 + 1;
-  int seen = lane < pair_n ? p.positions[pair_tok0 + lane] : -1;
-  if (lane + 32 < pair_n) seen = max(seen, p.positions[pair_tok0 + lane + 32]);
-  const int max_pos = __reduce_max_sync(0xffffffffu, seen);
-  const int key_end = kv_len < max_pos + 1 ? kv_len : max_pos + 1;
-  const int n_tiles = key_end > 0 ? (key_end + kU2Keys - 1) / kU2Keys : 0;
+  int kv_len;
+  const int n_tiles = u2_key_tiles(p, row, tok0, rank, sm.pair_last_tok, lane, kv_len, threadIdx.x == 0 && rank == 0);
   if (n_tiles == 0) {  // same decision in both CTAs; a row without keys produces zeros
+    if (info) *info = make_int4(tok0, ntok, 0, 0);
     if (p.zero_fill && blockIdx.z == 0) {
       for (int i = threadIdx.x; i < ntok * kG * (kD / 4); i += kU2Threads) {
         const int t = i / (kG * (kD / 4)), rest = i - t * (kG * (kD / 4));
@@ -615,11 +574,8 @@ prefill_umma2_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_con
   // leave pair slots for; the splits beyond that leave at once (both CTAs decide alike).
   int splits = 1, tile0 = 0, my_tiles = n_tiles;
   if (gridDim.z > 1) {
-    const int room = p.pair_slots / (sm.total_pairs * kHkv > 0 ? sm.total_pairs * kHkv : 1);
-    splits = n_tiles >= kU2SplitFrom ? n_tiles / kU2MinSplitTiles : 1;
-    splits = splits < room ? splits : room;
-    splits = splits < (int)gridDim.z ? splits : (int)gridDim.z;
-    splits = splits > 1 ? splits : 1;
+    splits = u2_split_count(p, n_tiles, sm.total_pairs, (int)gridDim.z);
+    if (info) *info = make_int4(tok0, ntok, splits, 0);
     if ((int)blockIdx.z >= splits) return;
     tile0 = (int)blockIdx.z * n_tiles / splits;
     my_tiles = ((int)blockIdx.z + 1) * n_tiles / splits - tile0;
@@ -674,6 +630,63 @@ prefill_umma2_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_con
   if (warp == 1) tmem2_dealloc(tmem, kU2TmemCols);
 }
 
+// Behind prefill_umma2_kernel in stream order (no counters, no fences): folds the key-range splits of every tile into the
+// output.  Grid = the tile kernel's (x, y) with kU2MergeParts CTAs per CTA tile (4 of its 32 tokens each).  Split 0 of
+// every tile left {first token, tokens, splits} in the workspace, so a CTA is two trips to memory: that record, then
+// every split's (max, sum) and both 16-byte pieces per lane of its rows, all requested before anything is used.  (A
+// build that found its tile and its splits again from the batch's metadata took 8.8 us: five trips.)
+// Warp w folds token 4 part + w / 2, heads 2 (w & 1) and 2 (w & 1) + 1 of the group.
+__global__ void __launch_bounds__(kU2MergeThreads)
+prefill_umma2_merge_kernel(const Umma2Params p) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kvh = blockIdx.y, part = blockIdx.z;
+  const int4 info = __ldcg(p.tile_info + blockIdx.x * kHkv + kvh);
+  const int tok0 = info.x, ntok = info.y, splits = info.z;
+  if (splits <= 1) return;
+  const int tk = part * (kU2Tokens / kU2MergeParts) + (warp >> 1);
+  if (tk >= ntok) return;
+  const long long split_rows = (long long)p.token_bucket * kHq;
+  float2 e[2];
+  float4 x[2][kU2MaxSplits][2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const long long g = (long long)(tok0 + tk) * kHq + kvh * kG + (warp & 1) * 2 + h;
+    e[h] = make_float2(-INFINITY, 0.f);  // lane s2 < splits: that split's (max, sum) of the row
+    if (lane < splits) e[h] = __ldcg(reinterpret_cast<const float2*>(p.part_ml + ((long long)lane * split_rows + g) * 2));
+#pragma unroll
+    for (int s2 = 0; s2 < kU2MaxSplits; ++s2) {
+      const float4* src = reinterpret_cast<const float4*>(p.part_o + ((long long)s2 * split_rows + g) * kD);
+      x[h][s2][0] = s2 < splits ? __ldcg(src + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
+      x[h][s2][1] = s2 < splits ? __ldcg(src + 32 + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+  }
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const long long g = (long long)(tok0 + tk) * kHq + kvh * kG + (warp & 1) * 2 + h;
+    float big = e[h].x;
+#pragma unroll
+    for (int o = 1; o < kU2MaxSplits; o <<= 1) big = fmaxf(big, __shfl_xor_sync(0xffffffffu, big, o));
+    float w = e[h].x == -INFINITY ? 0.f : ex2_approx(e[h].x - big);
+    float total = w * e[h].y;
+#pragma unroll
+    for (int o = 1; o < kU2MaxSplits; o <<= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
+    w = total > 0.f ? w / total : 0.f;  // lanes 0 .. kU2MaxSplits - 1 hold their split's normalised weight
+    float4 acc[2] = {make_float4(0.f, 0.f, 0.f, 0.f), make_float4(0.f, 0.f, 0.f, 0.f)};
+#pragma unroll
+    for (int s2 = 0; s2 < kU2MaxSplits; ++s2) {
+      const float ws = __shfl_sync(0xffffffffu, w, s2);
+#pragma unroll
+      for (int h2 = 0; h2 < 2; ++h2) {
+        acc[h2].x = fmaf(x[h][s2][h2].x, ws, acc[h2].x); acc[h2].y = fmaf(x[h][s2][h2].y, ws, acc[h2].y);
+        acc[h2].z = fmaf(x[h][s2][h2].z, ws, acc[h2].z); acc[h2].w = fmaf(x[h][s2][h2].w, ws, acc[h2].w);
+      }
+    }
+    float4* dst = reinterpret_cast<float4*>(p.out + g * kD);
+    dst[lane] = acc[0];
+    dst[32 + lane] = acc[1];
+  }
+}
+
 typedef CUresult (*U2EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                     const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                     CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -709,7 +722,7 @@ static int u2_pair_slots() {  // CTA pairs that run at once: half the SMs of the
 size_t prefill_split_bytes() {
   const int slots = u2_pair_slots();
   const size_t tokens = (size_t)(slots > 0 ? slots : 74) * 2 * kU2Tokens / kHkv + (size_t)kU2MaxSplits * 2 * kU2Tokens;
-  return ws_round(sizeof(float) * tokens * kHq * (kD + 2));
+  return ws_round(sizeof(float) * tokens * kHq * (kD + 2)) + ws_round(sizeof(int4) * 2 * (tokens / (2 * kU2Tokens) + 4096) * kHkv);
 }
 
 static bool u2_make_map(CUtensorMap* map, const void* base, uint64_t outer) {
@@ -727,8 +740,7 @@ int launch_prefill_umma2(const void* q, int q_dtype, const char* k_cache, const 
                          long long num_blocks, const int32_t* block_tables, int table_width,
                          const int32_t* kv_lens, const int32_t* positions, const int32_t* query_start_loc,
                          int rows, int token_bucket, float scale, float* out, int32_t* status,
-                         int skip_single, int split_p, int32_t* split_counters, float* split_area, size_t split_bytes,
-                         cudaStream_t stream) {
+                         int skip_single, int split_p, float* split_area, size_t split_bytes, cudaStream_t stream) {
   static PerDeviceFlags opted_in;
   constexpr int kSmemBytes = (int)sizeof(Umma2Smem) + 1024;
   static_assert(kSmemBytes <= 232448, "tiles exceed the shared memory of one CTA");
@@ -754,24 +766,27 @@ int launch_prefill_umma2(const void* q, int q_dtype, const char* k_cache, const 
   // the counters cover; the kernel settles the number per pair from what the batch really holds.
   int splits = 1;
   const int slots = u2_pair_slots();
-  if (split_counters && split_area && slots > 0 && 2 * pairs * kHkv <= kSplitCounters) {
+  if (split_area && slots > 0) {
     const int least = (token_bucket + 2 * kU2Tokens - 1) / (2 * kU2Tokens) * kHkv;
     splits = slots / least < kU2MaxSplits ? slots / least : kU2MaxSplits;
     const size_t per_split = sizeof(float) * (size_t)token_bucket * kHq * (kD + 2);
+    const size_t info_bytes = ws_round(sizeof(int4) * 2 * (size_t)pairs * kHkv);
     const size_t room = split_bytes < prefill_split_bytes() ? split_bytes : prefill_split_bytes();
-    while (splits > 1 && ws_round(per_split * splits) > room) --splits;
+    while (splits > 1 && ws_round(per_split * splits) + info_bytes > room) --splits;
     if (splits < 1) splits = 1;
     // The partials end where the lent area ends: its low end borders arrival counters of calls with more rows.
-    split_area = reinterpret_cast<float*>(reinterpret_cast<char*>(split_area) + split_bytes - ws_round(per_split * splits));
+    split_area = reinterpret_cast<float*>(reinterpret_cast<char*>(split_area) + split_bytes - ws_round(per_split * splits) - info_bytes);
   }
   if (splits > 1) {
     p.part_o = split_area;
     p.part_ml = split_area + (size_t)splits * token_bucket * kHq * kD;
-    p.split_counters = split_counters;
+    p.tile_info = reinterpret_cast<int4*>(reinterpret_cast<char*>(split_area) + ws_round(sizeof(float) * (size_t)splits * token_bucket * kHq * (kD + 2)));
     p.pair_slots = slots;
   }
   dim3 grid(2 * pairs, kHkv, splits);
   prefill_umma2_kernel<<<grid, kU2Threads, kSmemBytes, stream>>>(k_map, v_map, p);
+  if (cudaGetLastError() != cudaSuccess) return NVJ_ERR_LAUNCH;
+  if (splits > 1) prefill_umma2_merge_kernel<<<dim3(2 * pairs, kHkv, kU2MergeParts), kU2MergeThreads, 0, stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? NVJ_OK : NVJ_ERR_LAUNCH;
 }
 
