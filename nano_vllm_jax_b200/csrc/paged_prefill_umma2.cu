@@ -527,6 +527,8 @@ prefill_umma2_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_con
   const int rank = (int)cluster_ctarank();  // == blockIdx.x & 1
   NVJ_U2_PHASE(0);
   NVJ_U2_NOTE(7, 0ull);
+  // a merge launch follows a launch with splits: let its CTAs take their places now (they wait for this grid to finish)
+  if (gridDim.z > 1) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (blockIdx.z > 0) {  // the extra splits leave at once when no row's key range is long enough to be split
     int any = 0;
     for (int rr = threadIdx.x; rr < p.rows; rr += kU2Threads) any |= p.kv_lens[rr] > (kU2SplitFrom - 1) * kU2Keys ? 1 : 0;
@@ -640,6 +642,9 @@ __global__ void __launch_bounds__(kU2MergeThreads)
 prefill_umma2_merge_kernel(const Umma2Params p) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kvh = blockIdx.y, part = blockIdx.z;
+  // launched with programmatic stream serialization: the CTAs may be resident before the tile kernel has finished, and
+  // wait here until all of it has completed and its writes are visible
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int4 info = __ldcg(p.tile_info + blockIdx.x * kHkv + kvh);
   const int tok0 = info.x, ntok = info.y, splits = info.z;
   if (splits <= 1) return;
@@ -786,7 +791,18 @@ int launch_prefill_umma2(const void* q, int q_dtype, const char* k_cache, const 
   dim3 grid(2 * pairs, kHkv, splits);
   prefill_umma2_kernel<<<grid, kU2Threads, kSmemBytes, stream>>>(k_map, v_map, p);
   if (cudaGetLastError() != cudaSuccess) return NVJ_ERR_LAUNCH;
-  if (splits > 1) prefill_umma2_merge_kernel<<<dim3(2 * pairs, kHkv, kU2MergeParts), kU2MergeThreads, 0, stream>>>(p);
+  if (splits > 1) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * pairs, kHkv, kU2MergeParts);
+    cfg.blockDim = dim3(kU2MergeThreads, 1, 1);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, prefill_umma2_merge_kernel, p) != cudaSuccess) return NVJ_ERR_LAUNCH;
+  }
   return cudaGetLastError() == cudaSuccess ? NVJ_OK : NVJ_ERR_LAUNCH;
 }
 

@@ -364,3 +364,35 @@ def test_hybrid_state_batch_gather_and_store_match_indexing():
     whole = full.gather_batch([0, 1, 2])
     assert whole.conv_state is full.conv and whole.recurrent_state is full.rec
     full.store_batch([0, 1, 2], whole)
+
+
+def test_split_prefill_with_its_merge_launch_replays_from_a_cuda_graph():
+    """The tile kernel and the merge launch behind it (a programmatic dependent launch) captured into one CUDA graph:
+    the replay gives what the eager call gave, also after the inputs changed."""
+    import numpy as np
+    import torch
+    from helpers import BS, SCALE, to_torch
+    from nano_vllm_jax_b200.engine.resident_decode import CapturedStep
+    from nano_vllm_jax_b200.kernels import paged_kv as K
+    rng = np.random.default_rng(33)
+    pool, prefix, chunk = 256, 1024, 256
+    k = to_torch(rng.standard_normal((pool, BS, 2, 256), dtype=np.float32)).to(torch.bfloat16)
+    v = to_torch(rng.standard_normal((pool, BS, 2, 256), dtype=np.float32)).to(torch.bfloat16)
+    tables = to_torch(rng.permutation(pool)[: (prefix + chunk) // BS].astype(np.int32).reshape(1, -1))
+    lens = torch.tensor([prefix + chunk], dtype=torch.int32, device="cuda")
+    pos = (prefix + torch.arange(chunk, dtype=torch.int32, device="cuda"))[None].contiguous()
+    qsl = torch.tensor([0, chunk], dtype=torch.int32, device="cuda")
+    q = to_torch(rng.standard_normal((1, chunk, 8, 256), dtype=np.float32)).to(torch.bfloat16)
+    fn = lambda: K.packed_paged_prefill_attention(q, k, v, tables, lens, pos, qsl, BS, SCALE, 4, variant=4, num_decode_rows=0)
+    eager = fn().clone()
+    step = CapturedStep(fn)
+    step.capture()
+    out = step.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out, eager)
+    q.copy_(to_torch(rng.standard_normal((1, chunk, 8, 256), dtype=np.float32)).to(torch.bfloat16))
+    eager2 = fn().clone()
+    out2 = step.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(out2, eager2) and not torch.equal(eager2, eager)
+    K.check_device_status(torch.device("cuda"))
