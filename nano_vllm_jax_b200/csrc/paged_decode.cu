@@ -314,7 +314,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_pipelined_kernel(Dec
     const int b = base + threadIdx.x;
     int len = 0;
     if (b < p.batch) len = decode_row_len(p, b);
-    mine += (len + kBlk - 1) / kBlk;
+    mine += blocks_in_sequence((len + kBlk - 1) / kBlk);
     const unsigned idle = __ballot_sync(kFullMask, !p.packed_rows && b < p.batch && len <= 0 && (b % grid) == (int)blockIdx.x);
     for (unsigned m = idle; m; m &= m - 1) {
       const int bb = base + (warp << 5) + (__ffs(m) - 1);
@@ -330,7 +330,6 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_pipelined_kernel(Dec
   const long long g0 = pt.start(blockIdx.x);
   const long long g1 = pt.start(blockIdx.x + 1);
   if (g0 == g1) return;
-  const int n_iters = (int)(g1 - g0);
 
   // ---- pass 2: locate (row, block) of g0
   if (threadIdx.x == 0) { sm.start_b = p.batch; sm.start_j = 0; sm.abort_flag = 0; sm.is_last = 0; }
@@ -338,7 +337,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_pipelined_kernel(Dec
   for (int base = 0; base < p.batch && carry <= g0; base += kDecodeThreads) {
     const int b = base + threadIdx.x;
     int n = 0;
-    if (b < p.batch) n = (decode_row_len(p, b) + kBlk - 1) / kBlk;
+    if (b < p.batch) n = blocks_in_sequence((decode_row_len(p, b) + kBlk - 1) / kBlk);
     int chunk_total = 0;
     const long long excl = carry + cta_inclusive_scan(n, sm.scan, chunk_total) - n;
     if (n > 0 && excl <= g0 && g0 < excl + n) { sm.start_b = b; sm.start_j = (int)(g0 - excl); }
@@ -352,6 +351,8 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_pipelined_kernel(Dec
     mbar_fence_init();
   }
   __syncthreads();
+  const int n_iters = blocks_in_range(p, sm.start_b, sm.start_j, g0, g1);  // the range's real blocks
+  if (n_iters == 0) return;
 
   // ---- block-id look-ahead ring, first fill, first kStages copies
   FillState fs;

@@ -340,7 +340,7 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_const
     const int b = base + threadIdx.x;
     int len = 0;
     if (b < p.batch) len = decode_row_len(p, b);
-    mine += (len + kBlk - 1) / kBlk;
+    mine += blocks_in_sequence((len + kBlk - 1) / kBlk);
     const unsigned idle = __ballot_sync(kFullMask, b < p.batch && len <= 0 && (b % (int)gridDim.x) == (int)blockIdx.x);
     for (unsigned m = idle; m; m &= m - 1) {
       const int bb = base + (warp << 5) + (__ffs(m) - 1);
@@ -362,7 +362,7 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_const
   for (int base = 0; base < p.batch && carry <= g0; base += kDecodeThreads) {
     const int b = base + threadIdx.x;
     int n = 0;
-    if (b < p.batch) n = (decode_row_len(p, b) + kBlk - 1) / kBlk;
+    if (b < p.batch) n = blocks_in_sequence((decode_row_len(p, b) + kBlk - 1) / kBlk);
     int chunk_total = 0;
     const long long excl = carry + cta_inclusive_scan(n, sm.scan, chunk_total) - n;
     if (n > 0 && excl <= g0 && g0 < excl + n) { sm.start_b = b; sm.start_j = (int)(g0 - excl); }
@@ -412,10 +412,10 @@ decode_umma_merge_kernel(DecodeParams p, int ranges) {
   __shared__ float red[384];
   __shared__ long long sums[2][kDecodeThreads / 32];
   const int b = blockIdx.x, tok = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  // blocks in front of row b and in all rows
+  // blocks (real and phantom: the sequence the tile kernel cut into ranges) in front of row b and in all rows
   long long before = 0, all = 0;
   for (int r = tid; r < p.batch; r += kDecodeThreads) {
-    const int n = (decode_row_len(p, r) + kBlk - 1) / kBlk;
+    const int n = blocks_in_sequence((decode_row_len(p, r) + kBlk - 1) / kBlk);
     all += n;
     if (r < b) before += n;
   }

@@ -350,8 +350,8 @@ decode_wide_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_const
     const int b = base + threadIdx.x;
     int len = 0;
     if (b < p.batch) len = decode_row_len(p, b);
-    if (base == 0) first_n = (len + kBlk - 1) / kBlk;
-    mine += (len + kBlk - 1) / kBlk;
+    if (base == 0) first_n = blocks_in_sequence((len + kBlk - 1) / kBlk);
+    mine += blocks_in_sequence((len + kBlk - 1) / kBlk);
     const unsigned idle = __ballot_sync(kFullMask, !p.packed_rows && b < p.batch && len <= 0 && (b % grid) == (int)blockIdx.x);
     for (unsigned m = idle; m; m &= m - 1) {
       const int bb = base + (warp << 5) + (__ffs(m) - 1);
@@ -367,18 +367,7 @@ decode_wide_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_const
   const long long g0 = pt.start(blockIdx.x);
   const long long g1 = pt.start(blockIdx.x + 1);
   if (g0 == g1) return;
-  const int n_iters = (int)(g1 - g0);
   NVJ_PHASE(1);
-#ifdef NVJ_PHASE_TIMING
-  {
-    unsigned smid;
-    asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-    NVJ_PHASE_NOTE(8, (unsigned long long)smid);
-    NVJ_PHASE_NOTE(9, (unsigned long long)n_iters);
-    NVJ_PHASE_NOTE(10, 0ull);
-    NVJ_PHASE_NOTE(11, 0ull);
-  }
-#endif
 
   // ---- pass 2: locate (row, block) of g0
   long long carry = 0;
@@ -390,7 +379,7 @@ decode_wide_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_const
   for (int base = 0; base < p.batch && carry <= g0; base += kDecodeThreads) {
     const int b = base + threadIdx.x;
     int n = 0;
-    if (b < p.batch) n = (decode_row_len(p, b) + kBlk - 1) / kBlk;
+    if (b < p.batch) n = blocks_in_sequence((decode_row_len(p, b) + kBlk - 1) / kBlk);
     int chunk_total = 0;
     const long long excl = carry + cta_inclusive_scan(n, sm.scan, chunk_total) - n;
     if (n > 0 && excl <= g0 && g0 < excl + n) { sm.start_b = b; sm.start_j = (int)(g0 - excl); }
@@ -405,6 +394,18 @@ decode_wide_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_const
   }
   __syncthreads();
   NVJ_PHASE(2);
+  const int n_iters = blocks_in_range(p, sm.start_b, sm.start_j, g0, g1);  // the range's real blocks
+  if (n_iters == 0) return;
+#ifdef NVJ_PHASE_TIMING
+  {
+    unsigned smid;
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+    NVJ_PHASE_NOTE(8, (unsigned long long)smid);
+    NVJ_PHASE_NOTE(9, (unsigned long long)n_iters);
+    NVJ_PHASE_NOTE(10, 0ull);
+    NVJ_PHASE_NOTE(11, 0ull);
+  }
+#endif
 
   FillState fs;
   fs.b = sm.start_b; fs.jn = sm.start_j; fs.g = g0; fs.j = 0; fs.nsegs = 0; fs.has = false;
