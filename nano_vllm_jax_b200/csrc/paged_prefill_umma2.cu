@@ -638,6 +638,8 @@ prefill_umma2_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_con
 // every split's (max, sum) and both 16-byte pieces per lane of its rows, all requested before anything is used.  (A
 // build that found its tile and its splits again from the batch's metadata took 8.8 us: five trips.)
 // Warp w folds token 4 part + w / 2, heads 2 (w & 1) and 2 (w & 1) + 1 of the group.
+static_assert(kU2MaxSplits == 4 && kU2Tokens % kU2MergeParts == 0 && kU2MergeThreads == 64 * (kU2Tokens / kU2MergeParts),
+              "the merge launch maps a warp to (token, two heads) and reduces over four lanes");
 __global__ void __launch_bounds__(kU2MergeThreads)
 prefill_umma2_merge_kernel(const Umma2Params p) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
