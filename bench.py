@@ -51,8 +51,8 @@ MIN_TIMED_STEPS = 100
 # dram__bytes_read.sum + dram__bytes_write.sum of decode_wide_kernel in an ncu capture of `--workload c2small`
 # (one launch) and the algorithmic bytes of that launch.  K/V traffic grows in proportion to the tokens
 # read, so a launch of another workload is scaled by its own algorithmic bytes.
-NCU_C2SMALL_DRAM_BYTES = 314.45e6
-NCU_C2SMALL_ALGORITHMIC_BYTES = 310.5e6
+NCU_C2SMALL_DRAM_BYTES = 354.93e6
+NCU_C2SMALL_ALGORITHMIC_BYTES = 356.35e6
 
 WORKLOADS = {
     # rows: per rank (weak) or overall (strong); pool: blocks per rank, or None = sized from the free memory
