@@ -612,7 +612,7 @@ def run_b200(args, w):
                          "bytes_per_launch": bytes_per_launch, "us_per_launch": ms_kernel / len(timed_events) * 1e3,
                          "launch_us": percentiles([m * 1e3 for m in kernel_ms]),
                          "traffic": NCU_C2SMALL_DRAM_BYTES / NCU_C2SMALL_ALGORITHMIC_BYTES * bytes_per_launch,
-                         "traffic_source": "dram bytes of one ncu-captured launch of --workload c2small (314.45 MB for 310.5 MB "
+                         "traffic_source": "dram bytes of one ncu-captured launch of --workload c2small (354.93 MB for 356.35 MB "
                                            "algorithmic) scaled to this launch by algorithmic bytes"},
             "rank_ms": rank_ms, "rank_kernel_us": rank_kernel_us, "gather_us": gather_us,
             "parity_check": parity,
