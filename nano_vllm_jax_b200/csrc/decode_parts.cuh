@@ -19,8 +19,8 @@ constexpr float kNegBig = -1.0e30f;
 // kRowEndCost phantom blocks that nobody reads: a range with more row ends gets fewer real blocks.  (With ranges of
 // equal real blocks the CTAs of a 256-row batch finished 21 us apart, and the time a CTA finished followed the number
 // of rows in its range with a correlation of 0.85: 205.8 / 210.9 / 214.6 / 220.9 us for 2 / 3 / 4 / 5 rows.)
-constexpr int kRowEndCost = 6;
-__host__ __device__ __forceinline__ int blocks_in_sequence(int nb) { return nb > 0 ? nb + kRowEndCost : 0; }
+constexpr int kRowEndCost = 6;  // the mma.sync and the CUDA-core kernel; the tcgen05 wide kernel has its own figure
+__device__ __forceinline__ int blocks_in_sequence(const DecodeParams& p, int nb) { return nb > 0 ? nb + p.row_end_cost : 0; }
 
 struct Seg {
   int b, j0, j1, nb, len;  // real blocks [j0, j1) of row b, which has nb blocks
@@ -33,7 +33,7 @@ __device__ __forceinline__ bool next_seg(const DecodeParams& p, int& b, int& j, 
   while (g < g1 && b < p.batch) {
     const int len = decode_row_len(p, b);
     const int nb = (len + kBlk - 1) / kBlk;
-    const int nbv = blocks_in_sequence(nb);
+    const int nbv = blocks_in_sequence(p, nb);
     if (j >= nbv) { ++b; j = 0; continue; }
     const long long room = g1 - g;
     const int take = (long long)(nbv - j) < room ? (nbv - j) : (int)room;

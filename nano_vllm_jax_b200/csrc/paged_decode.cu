@@ -314,7 +314,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_pipelined_kernel(Dec
     const int b = base + threadIdx.x;
     int len = 0;
     if (b < p.batch) len = decode_row_len(p, b);
-    mine += blocks_in_sequence((len + kBlk - 1) / kBlk);
+    mine += blocks_in_sequence(p, (len + kBlk - 1) / kBlk);
     const unsigned idle = __ballot_sync(kFullMask, !p.packed_rows && b < p.batch && len <= 0 && (b % grid) == (int)blockIdx.x);
     for (unsigned m = idle; m; m &= m - 1) {
       const int bb = base + (warp << 5) + (__ffs(m) - 1);
@@ -337,7 +337,7 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_pipelined_kernel(Dec
   for (int base = 0; base < p.batch && carry <= g0; base += kDecodeThreads) {
     const int b = base + threadIdx.x;
     int n = 0;
-    if (b < p.batch) n = blocks_in_sequence((decode_row_len(p, b) + kBlk - 1) / kBlk);
+    if (b < p.batch) n = blocks_in_sequence(p, (decode_row_len(p, b) + kBlk - 1) / kBlk);
     int chunk_total = 0;
     const long long excl = carry + cta_inclusive_scan(n, sm.scan, chunk_total) - n;
     if (n > 0 && excl <= g0 && g0 < excl + n) { sm.start_b = b; sm.start_j = (int)(g0 - excl); }
@@ -470,7 +470,9 @@ int launch_decode_pipelined(const DecodeParams& p, int num_ctas, cudaStream_t st
                                     (int)sizeof(DecodeSmem)) == cudaSuccess;
       }))
     return NVJ_ERR_LAUNCH;
-  decode_pipelined_kernel<<<num_ctas, kDecodeThreads, sizeof(DecodeSmem), stream>>>(p);
+  DecodeParams q = p;
+  q.row_end_cost = kRowEndCost;
+  decode_pipelined_kernel<<<num_ctas, kDecodeThreads, sizeof(DecodeSmem), stream>>>(q);
   return cudaGetLastError() == cudaSuccess ? NVJ_OK : NVJ_ERR_LAUNCH;
 }
 

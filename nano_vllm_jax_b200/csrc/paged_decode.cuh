@@ -52,6 +52,8 @@ struct DecodeParams {
   // which wide kernel serves rows of several query tokens: 0 = automatic (mma.sync tiles up to width 4, tcgen05 beyond),
   // 1 = mma.sync tiles, 2 = tcgen05
   int wide_form;
+  // what a row end costs a CTA, in blocks (decode_parts.cuh); set by the launchers, the same for every kernel of a call
+  int row_end_cost;
   float* out;
   // workspace
   int32_t* status;

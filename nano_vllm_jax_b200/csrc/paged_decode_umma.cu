@@ -51,6 +51,7 @@ constexpr int kUdColO = 256;      // output accumulator: columns [256, 512)
 constexpr int kUdHalfBlock = kBlk * kD * 2;  // K (or V) of one KV head of one block: 8 KiB
 constexpr float kUdRescaleGap = 8.f;
 constexpr int kUdMaxWidth = 16;  // 64 query rows per KV head: two softmax warps
+constexpr int kUdRowEndCost = 6;  // what a row end costs a CTA here, in blocks (6 and 12 measured alike, 18 and 24 worse)
 
 struct UdSmem {
   alignas(1024) char k[kUdStages][4][kUdTileBlocks * kBlk * 128];  // [stage][64-d chunk][64 keys][128 B], swizzled
@@ -340,7 +341,7 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_const
     const int b = base + threadIdx.x;
     int len = 0;
     if (b < p.batch) len = decode_row_len(p, b);
-    mine += blocks_in_sequence((len + kBlk - 1) / kBlk);
+    mine += blocks_in_sequence(p, (len + kBlk - 1) / kBlk);
     const unsigned idle = __ballot_sync(kFullMask, b < p.batch && len <= 0 && (b % (int)gridDim.x) == (int)blockIdx.x);
     for (unsigned m = idle; m; m &= m - 1) {
       const int bb = base + (warp << 5) + (__ffs(m) - 1);
@@ -362,7 +363,7 @@ decode_umma_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_const
   for (int base = 0; base < p.batch && carry <= g0; base += kDecodeThreads) {
     const int b = base + threadIdx.x;
     int n = 0;
-    if (b < p.batch) n = blocks_in_sequence((decode_row_len(p, b) + kBlk - 1) / kBlk);
+    if (b < p.batch) n = blocks_in_sequence(p, (decode_row_len(p, b) + kBlk - 1) / kBlk);
     int chunk_total = 0;
     const long long excl = carry + cta_inclusive_scan(n, sm.scan, chunk_total) - n;
     if (n > 0 && excl <= g0 && g0 < excl + n) { sm.start_b = b; sm.start_j = (int)(g0 - excl); }
@@ -415,7 +416,7 @@ decode_umma_merge_kernel(DecodeParams p, int ranges) {
   // blocks (real and phantom: the sequence the tile kernel cut into ranges) in front of row b and in all rows
   long long before = 0, all = 0;
   for (int r = tid; r < p.batch; r += kDecodeThreads) {
-    const int n = blocks_in_sequence((decode_row_len(p, r) + kBlk - 1) / kBlk);
+    const int n = blocks_in_sequence(p, (decode_row_len(p, r) + kBlk - 1) / kBlk);
     all += n;
     if (r < b) before += n;
   }
@@ -530,9 +531,11 @@ int launch_decode_umma(const DecodeParams& p, cudaStream_t stream) {
         return cudaFuncSetAttribute(decode_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) == cudaSuccess;
       }))
     return NVJ_ERR_LAUNCH;
-  decode_umma_kernel<<<2 * ranges, kDecodeThreads, kSmemBytes, stream>>>(k_map, v_map, p);
+  DecodeParams q = p;
+  q.row_end_cost = kUdRowEndCost;
+  decode_umma_kernel<<<2 * ranges, kDecodeThreads, kSmemBytes, stream>>>(k_map, v_map, q);
   if (cudaGetLastError() != cudaSuccess) return NVJ_ERR_LAUNCH;
-  decode_umma_merge_kernel<<<dim3(p.batch, p.width), kDecodeThreads, 0, stream>>>(p, ranges);
+  decode_umma_merge_kernel<<<dim3(p.batch, p.width), kDecodeThreads, 0, stream>>>(q, ranges);
   return cudaGetLastError() == cudaSuccess ? NVJ_OK : NVJ_ERR_LAUNCH;
 }
 

@@ -350,8 +350,8 @@ decode_wide_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_const
     const int b = base + threadIdx.x;
     int len = 0;
     if (b < p.batch) len = decode_row_len(p, b);
-    if (base == 0) first_n = blocks_in_sequence((len + kBlk - 1) / kBlk);
-    mine += blocks_in_sequence((len + kBlk - 1) / kBlk);
+    if (base == 0) first_n = blocks_in_sequence(p, (len + kBlk - 1) / kBlk);
+    mine += blocks_in_sequence(p, (len + kBlk - 1) / kBlk);
     const unsigned idle = __ballot_sync(kFullMask, !p.packed_rows && b < p.batch && len <= 0 && (b % grid) == (int)blockIdx.x);
     for (unsigned m = idle; m; m &= m - 1) {
       const int bb = base + (warp << 5) + (__ffs(m) - 1);
@@ -379,7 +379,7 @@ decode_wide_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_const
   for (int base = 0; base < p.batch && carry <= g0; base += kDecodeThreads) {
     const int b = base + threadIdx.x;
     int n = 0;
-    if (b < p.batch) n = blocks_in_sequence((decode_row_len(p, b) + kBlk - 1) / kBlk);
+    if (b < p.batch) n = blocks_in_sequence(p, (decode_row_len(p, b) + kBlk - 1) / kBlk);
     int chunk_total = 0;
     const long long excl = carry + cta_inclusive_scan(n, sm.scan, chunk_total) - n;
     if (n > 0 && excl <= g0 && g0 < excl + n) { sm.start_b = b; sm.start_j = (int)(g0 - excl); }
@@ -621,6 +621,8 @@ int launch_decode_wide(const DecodeParams& p, cudaStream_t stream) {
   }
   if (p.width > kWMaxWidth) return NVJ_ERR_UNSUPPORTED;
   if (p.cta_limit > 0 && p.cta_limit < n) n = p.cta_limit;
+  DecodeParams q = p;
+  q.row_end_cost = kRowEndCost;
   CUtensorMap k_map, v_map;
   if (!tensor_map_cached(&k_map, 0, p.k_cache, (uint64_t)p.num_blocks * kBlk, w_make_map) ||
       !tensor_map_cached(&v_map, 0, p.v_cache, (uint64_t)p.num_blocks * kBlk, w_make_map))
@@ -632,8 +634,8 @@ int launch_decode_wide(const DecodeParams& p, cudaStream_t stream) {
                cudaFuncSetAttribute(decode_wide_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) == cudaSuccess;
       }))
     return NVJ_ERR_LAUNCH;
-  if (p.width > 4) decode_wide_kernel<true><<<n, kDecodeThreads, smem, stream>>>(k_map, v_map, p);
-  else decode_wide_kernel<false><<<n, kDecodeThreads, smem, stream>>>(k_map, v_map, p);
+  if (p.width > 4) decode_wide_kernel<true><<<n, kDecodeThreads, smem, stream>>>(k_map, v_map, q);
+  else decode_wide_kernel<false><<<n, kDecodeThreads, smem, stream>>>(k_map, v_map, q);
   return cudaGetLastError() == cudaSuccess ? NVJ_OK : NVJ_ERR_LAUNCH;
 }
 
