@@ -88,7 +88,7 @@ def test_rows_split_across_many_ctas(variant):
 @pytest.mark.parametrize("variant", [PIPELINED, TENSOR])
 @pytest.mark.parametrize("lens", [(20000,), (9000, 30, 9000, 700, 5), (3000, 12000, 1, 6000)])
 def test_few_long_rows_are_merged_in_two_levels(lens, variant):
-    # rows cut into more than 32 partials: groups of 16 CTAs fold first, the last group folds the groups;
+    # rows cut into more than 32 partials: groups of 13 CTAs fold first, the last group folds the groups;
     # short rows between them share CTAs and groups with the long ones
     c = decode_case(9, 2600, len(lens), 1, 1)
     rng = np.random.default_rng(9)
