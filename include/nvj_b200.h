@@ -338,12 +338,13 @@ int nvj_paged_prefill_packed(const void* q, int q_dtype,
  * The two halves of nvj_paged_prefill_packed as separate launches, for a caller that runs them side by side on two
  * streams: in a mixed batch (nanovllm_jax/engine/scheduler.py:956-1032) the decode rows and the prefill chunks
  * write different rows of `out`, and neither kernel fills the machine alone.  Same arguments; the model's shape
- * only (NVJ_ERR_UNSUPPORTED otherwise: the generic kernel serves a batch in one piece).  The caller zeroes `out`
- * first and orders both launches behind that.
+ * only (NVJ_ERR_UNSUPPORTED otherwise: the generic kernel serves a batch in one piece).  Neither part wants `out`
+ * zeroed: each zeroes what it owns and does not write (rows without keys, padding tokens).
  *   part 1   rows that hold exactly one query token, on the streaming decode kernel with at most `cta_limit` CTAs
  *            (0 = one per SM; give the SM count minus the CTAs of part 2); `workspace` is required
- *   part 2   every other row, on the tile kernel `variant` selects; `workspace` (nullable, NOT the buffer part 1 is
- *            using at the same time) only gives the key-range splits of a short batch their room
+ *   part 2   every other row, on the CTA-pair tile kernel (variant 0, 4 or 5; NVJ_ERR_UNSUPPORTED for another variant,
+ *            or when that kernel cannot run: call nvj_paged_prefill_packed instead); `workspace` (nullable, NOT the
+ *            buffer part 1 is using at the same time) only gives the key-range splits of a short batch their room
  *   part 3   all rows on the tile kernel, which then zeroes what it does not write itself (no zeroed `out` needed):
  *            a batch without decode rows that still wants the key-range splits
  * The reference runs a mixed batch through one packed attention call; the split has no counterpart there.

@@ -16,6 +16,7 @@ from . import build as _build
 
 NVJ_BF16, NVJ_F16, NVJ_F32 = 0, 1, 2
 NVJ_DEV_TIMEOUT, NVJ_DEV_BAD_BLOCK_ID, NVJ_DEV_BAD_LENGTH = 1, 2, 4
+NVJ_ERR_UNSUPPORTED = -2  # a kernel declined the call (shape, dtype, alignment, a missing driver feature)
 
 # name -> (restype, argtypes); one entry per declaration in include/nvj_b200.h
 SIGNATURES = {

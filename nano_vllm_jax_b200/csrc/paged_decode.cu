@@ -315,10 +315,13 @@ __global__ void __launch_bounds__(kDecodeThreads, 2) decode_pipelined_kernel(Dec
     int len = 0;
     if (b < p.batch) len = decode_row_len(p, b);
     mine += blocks_in_sequence(p, (len + kBlk - 1) / kBlk);
-    const unsigned idle = __ballot_sync(kFullMask, !p.packed_rows && b < p.batch && len <= 0 && (b % grid) == (int)blockIdx.x);
+    // rows without keys get zeros; in a packed batch only the rows this pass owns (one query token) are touched
+    const bool mine_to_zero = b < p.batch && len <= 0 && (b % grid) == (int)blockIdx.x &&
+                              (!p.packed_rows || p.query_start_loc[b + 1] - p.query_start_loc[b] == 1);
+    const unsigned idle = __ballot_sync(kFullMask, mine_to_zero);
     for (unsigned m = idle; m; m &= m - 1) {
       const int bb = base + (warp << 5) + (__ffs(m) - 1);
-      float4* o = reinterpret_cast<float4*>(p.out + (long long)bb * kHq * kD);
+      float4* o = reinterpret_cast<float4*>(p.out + (p.packed_rows ? (long long)p.query_start_loc[bb] : (long long)bb) * kHq * kD);
       for (int i = lane; i < kHq * kD / 4; i += 32) o[i] = make_float4(0.f, 0.f, 0.f, 0.f);
     }
   }

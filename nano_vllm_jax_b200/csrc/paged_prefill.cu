@@ -20,6 +20,7 @@ int launch_prefill_umma2(const void* q, int q_dtype, const char* k_cache, const 
                          const int32_t* kv_lens, const int32_t* positions, const int32_t* query_start_loc,
                          int rows, int token_bucket, float scale, float* out, int32_t* status,
                          int skip_single, int split_p, float* split_area, size_t split_bytes, cudaStream_t stream);
+bool prefill_umma2_usable(float scale, long long num_blocks);
 int launch_prefill_umma(const void* q, int q_dtype, const char* k_cache, const char* v_cache,
                         long long num_blocks, const int32_t* block_tables, int table_width,
                         const int32_t* kv_lens, const int32_t* positions, const int32_t* query_start_loc,
@@ -98,9 +99,15 @@ static int run_single_token_rows(const PackedArgs& a, int cta_limit, cudaStream_
   return rc;
 }
 
+// Whether the CTA-pair kernel will serve this call: it and the decode-row pass zero what they do not write, so that the
+// output needs no memset in front; the other tile kernels want a zeroed output when rows are left to the pass above.
+static bool pair_kernel_serves(const PackedArgs& a) {
+  return (a.variant == 0 || a.variant == 4 || a.variant == 5) && prefill_umma2_usable(a.scale, a.num_blocks);
+}
+
 // The query tiles: tcgen05 tiles first (CTA pairs, then single CTAs); they decline when the driver has no tensor-map
 // encoder or the scale is not positive, and the mma.sync tiles take over.  With skip_single the rows of one query
-// token are left to the pass above and `out` has been zeroed by the caller.
+// token are left to the pass above (and, unless the pair kernel serves the call, `out` has been zeroed by the caller).
 static int run_tiles(const PackedArgs& a, int skip_single, cudaStream_t s) {
   const char* kc = static_cast<const char*>(a.k_cache_layer);
   const char* vc = static_cast<const char*>(a.v_cache_layer);
@@ -193,7 +200,9 @@ extern "C" int nvj_paged_prefill_packed(const void* q, int q_dtype, const void* 
   // workspace; everything else goes to the tile kernel.
   int skip_single = 0;
   if (workspace && rows > 0) {
-    if (cudaMemsetAsync(out, 0, sizeof(float) * (size_t)token_bucket * kHq * kD, s) != cudaSuccess) return NVJ_ERR_LAUNCH;
+    if (!pair_kernel_serves(a) &&
+        cudaMemsetAsync(out, 0, sizeof(float) * (size_t)token_bucket * kHq * kD, s) != cudaSuccess)
+      return NVJ_ERR_LAUNCH;
     const int rc1 = run_single_token_rows(a, 0, s);
     if (rc1 == NVJ_OK) skip_single = 1;
     else if (rc1 != NVJ_ERR_WORKSPACE) return rc1;
@@ -222,5 +231,6 @@ extern "C" int nvj_paged_prefill_packed_part(const void* q, int q_dtype, const v
   if (!tile_ok || variant == 1) return NVJ_ERR_UNSUPPORTED;  // the generic kernel serves a batch in one piece
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (part == 1) return run_single_token_rows(a, cta_limit, s);
+  if (part == 2 && !pair_kernel_serves(a)) return NVJ_ERR_UNSUPPORTED;  // the other tile kernels want a zeroed output
   return run_tiles(a, part == 2 ? 1 : 0, s);
 }

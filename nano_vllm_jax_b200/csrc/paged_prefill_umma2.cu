@@ -75,7 +75,7 @@ struct Umma2Params {
   int32_t* status;
   long long num_blocks;
   int rows, token_bucket, table_width, skip_single, q_dtype;
-  int zero_fill;  // 1: the kernel itself zeroes what no tile writes (padding tokens, rows without keys)
+  int zero_fill;  // 1: the kernel itself zeroes what no tile writes (padding tokens, rows of several tokens without keys)
   int split_p;  // 1: P enters P V as two bf16 terms (hi + lo), 0: as one (the weights are then bf16-rounded)
   float scale;
   // key-range splits (gridDim.z > 1): un-normalised rows [split][token][head][kD], their (max, sum)
@@ -742,6 +742,9 @@ static bool u2_make_map(CUtensorMap* map, const void* base, uint64_t outer) {
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Whether launch_prefill_umma2 will take a batch with these parameters (a caller that knows so need not zero the output).
+bool prefill_umma2_usable(float scale, long long num_blocks) { return scale > 0.f && num_blocks >= 1 && u2_encode_fn() != nullptr; }
+
 // Returns NVJ_ERR_UNSUPPORTED when the driver offers no tensor-map encoder or the scale is not positive.
 int launch_prefill_umma2(const void* q, int q_dtype, const char* k_cache, const char* v_cache,
                          long long num_blocks, const int32_t* block_tables, int table_width,
@@ -760,10 +763,10 @@ int launch_prefill_umma2(const void* q, int q_dtype, const char* k_cache, const 
   if (!tensor_map_cached(&k_map, 2, k_cache, (uint64_t)num_blocks * kBlk, u2_make_map) ||
       !tensor_map_cached(&v_map, 2, v_cache, (uint64_t)num_blocks * kBlk, u2_make_map))
     return NVJ_ERR_UNSUPPORTED;
-  // With skip_single the caller has zeroed `out` before its decode-row pass; otherwise the kernel zeroes what no
-  // tile writes itself, which spares a memset launch in front of every pure prefill batch.
+  // The kernel zeroes what no tile writes itself (padding tokens, rows of several tokens without keys), and the
+  // decode-row pass of a mixed batch does the same for its rows: no memset launch in front of a batch.
   Umma2Params p{};
-  p.zero_fill = skip_single ? 0 : 1;
+  p.zero_fill = 1;
   p.q = q; p.q_dtype = q_dtype;
   p.block_tables = block_tables; p.kv_lens = kv_lens; p.positions = positions; p.query_start_loc = query_start_loc;
   p.out = out; p.status = status; p.num_blocks = num_blocks; p.rows = rows; p.token_bucket = token_bucket;

@@ -563,7 +563,7 @@ def packed_paged_prefill_attention(query, k_cache_layer, v_cache_layer, block_ta
     # (one 6-layer step: 369 -> 272 us); launched eagerly the extra stream bookkeeping costs the host more than the
     # overlap saves, so the fork is taken only while the current stream is being captured (NVJ_MIXED_SIDE_BY_SIDE=1
     # forces it, =0 forbids it).
-    mixed = model_shape and variant != 1 and num_decode_rows is not None and 0 < num_decode_rows < rows
+    mixed = model_shape and variant in (0, 4, 5) and num_decode_rows is not None and 0 < num_decode_rows < rows
     mode = os.environ.get("NVJ_MIXED_SIDE_BY_SIDE", "auto")
     side_by_side = mixed and (mode == "1" or (mode != "0" and torch.cuda.is_current_stream_capturing()))
     if mixed and not side_by_side:
@@ -572,7 +572,6 @@ def packed_paged_prefill_attention(query, k_cache_layer, v_cache_layer, block_ta
     if side_by_side:
         cur = torch.cuda.current_stream(q.device)
         side = _side_stream(q.device)
-        out.zero_()
         sms = torch.cuda.get_device_properties(q.device).multi_processor_count
         tile_ctas = 4 * (-(-(tokens - num_decode_rows) // 64) + (rows - num_decode_rows))  # CTA pairs x 2 KV heads
         cta_limit = max(sms // 2, sms - tile_ctas)
@@ -584,6 +583,9 @@ def packed_paged_prefill_attention(query, k_cache_layer, v_cache_layer, block_ta
         rc2 = call(lib.nvj_paged_prefill_packed_part, None, 2, 0)
         cur.wait_stream(side)
         check(rc1, "nvj_paged_prefill_packed_part (decode rows)")
+        if rc2 == _lib.NVJ_ERR_UNSUPPORTED:  # the CTA-pair kernel cannot run here: the batch in one piece after all
+            ws = _workspace(q.device, rows)
+            rc2 = call(lib.nvj_paged_prefill_packed, ws)
         check(rc2, "nvj_paged_prefill_packed_part (tiles)")
     elif model_shape and variant != 1 and num_decode_rows == 0 and os.environ.get("NVJ_PREFILL_KEY_SPLITS", "1") != "0":
         # no decode rows: the tile kernel alone (it zero-fills what it does not write), with the workspace lent for

@@ -177,6 +177,31 @@ def test_mixed_batch_with_host_counts_serial_and_side_by_side(mode, monkeypatch)
         assert not to_numpy(out)[0, sum(chunk):].any()
 
 
+@pytest.mark.parametrize("mode", ["0", "1"])
+def test_mixed_batch_rows_without_keys_come_back_zero(mode, monkeypatch):
+    # The output arrives uncleared (the test session fills new outputs with NaN): a one-token row whose length is 0 (a slot the scheduler left
+    # idle) is zeroed by the pass over the decode rows, the padding behind the last chunk by the chunk kernel.
+    from nano_vllm_jax_b200 import kv_cache as kv
+    monkeypatch.setenv("NVJ_MIXED_SIDE_BY_SIDE", mode)
+    cached = [900, 40, 333, 7, 2100, 64]
+    chunk = [1, 1, 1, 1, 70, 130]
+    c = _prefill_case(11, 700, [0] * 6, cached=cached, chunk=chunk, bucket=256)
+    idle = [1, 3]
+    lens = c["kv_lens"].copy()
+    lens[idle] = 0
+    ref = R.paged_attention_prefill_packed(c["q"], c["k"], c["v"], c["tables"], c["kv_lens"], c["pos"], c["rid"],
+                                           c["qsl"], BS, SCALE, 4)
+    ref[0, idle] = 0.0
+    got = kv.paged_attention_prefill_packed(to_torch(c["q"]), to_torch(c["k"]), to_torch(c["v"]), to_torch(c["tables"]),
+                                            to_torch(lens), to_torch(c["pos"]), to_torch(c["rid"]),
+                                            to_torch(c["qsl"]), BS, SCALE, 4, out_dtype=torch.float32, num_decode_rows=4)
+    torch.cuda.synchronize()
+    g = to_numpy(got)
+    assert np.isfinite(g).all()
+    assert not g[0, idle].any() and not g[0, sum(chunk):].any()
+    assert np.abs(g - ref).max() <= PREFILL_TC
+
+
 def test_copy_blocks_bit_exact_all_layers():
     from nano_vllm_jax_b200.kernels import paged_kv as K
     rng = np.random.default_rng(3)
