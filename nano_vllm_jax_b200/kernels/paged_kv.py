@@ -560,15 +560,19 @@ def packed_paged_prefill_attention(query, k_cache_layer, v_cache_layer, block_ta
     # A mixed batch (decode rows + prefill chunks, counts known on the host): the two kinds of row are served by two
     # kernels that write different rows of `out` and neither fills the machine, so they can run side by side on two
     # streams, the decode pass leaving the tile kernel's SMs free.  That pays when the launches come from a CUDA graph
-    # (one 6-layer step: 369 -> 272 us); launched eagerly the extra stream bookkeeping costs the host more than the
+    # (one 6-layer step: 369 -> 250 us); launched eagerly the extra stream bookkeeping costs the host more than the
     # overlap saves, so the fork is taken only while the current stream is being captured (NVJ_MIXED_SIDE_BY_SIDE=1
     # forces it, =0 forbids it).
     mixed = model_shape and variant in (0, 4, 5) and num_decode_rows is not None and 0 < num_decode_rows < rows
     mode = os.environ.get("NVJ_MIXED_SIDE_BY_SIDE", "auto")
     side_by_side = mixed and (mode == "1" or (mode != "0" and torch.cuda.is_current_stream_capturing()))
     if mixed and not side_by_side:
-        with torch.cuda.stream(_side_stream(q.device)):
-            _workspace(q.device, rows)  # exists before any capture: a capture must not allocate it
+        # the side stream's workspace exists before any capture: a capture must not allocate it
+        side = _side_stream(q.device)
+        have = _workspaces.get((q.device.index if q.device.index is not None else torch.cuda.current_device(), side.cuda_stream))
+        if have is None or have.max_batch < rows:
+            with torch.cuda.stream(side):
+                _workspace(q.device, rows)
     if side_by_side:
         cur = torch.cuda.current_stream(q.device)
         side = _side_stream(q.device)
