@@ -560,19 +560,12 @@ def packed_paged_prefill_attention(query, k_cache_layer, v_cache_layer, block_ta
     # A mixed batch (decode rows + prefill chunks, counts known on the host): the two kinds of row are served by two
     # kernels that write different rows of `out` and neither fills the machine, so they can run side by side on two
     # streams, the decode pass leaving the tile kernel's SMs free.  That pays when the launches come from a CUDA graph
-    # (one 6-layer step: 369 -> 250 us); launched eagerly the extra stream bookkeeping costs the host more than the
+    # (one 6-layer step: 328 -> 233 us); launched eagerly the extra stream bookkeeping costs the host more than the
     # overlap saves, so the fork is taken only while the current stream is being captured (NVJ_MIXED_SIDE_BY_SIDE=1
     # forces it, =0 forbids it).
     mixed = model_shape and variant in (0, 4, 5) and num_decode_rows is not None and 0 < num_decode_rows < rows
     mode = os.environ.get("NVJ_MIXED_SIDE_BY_SIDE", "auto")
     side_by_side = mixed and (mode == "1" or (mode != "0" and torch.cuda.is_current_stream_capturing()))
-    if mixed and not side_by_side:
-        # the side stream's workspace exists before any capture: a capture must not allocate it
-        side = _side_stream(q.device)
-        have = _workspaces.get((q.device.index if q.device.index is not None else torch.cuda.current_device(), side.cuda_stream))
-        if have is None or have.max_batch < rows:
-            with torch.cuda.stream(side):
-                _workspace(q.device, rows)
     if side_by_side:
         cur = torch.cuda.current_stream(q.device)
         side = _side_stream(q.device)
@@ -580,17 +573,23 @@ def packed_paged_prefill_attention(query, k_cache_layer, v_cache_layer, block_ta
         tile_ctas = 4 * (-(-(tokens - num_decode_rows) // 64) + (rows - num_decode_rows))  # CTA pairs x 2 KV heads
         cta_limit = max(sms // 2, sms - tile_ctas)
         side.wait_stream(cur)
+        # The decode rows are the longer of the two: they stay on the current stream and the tiles go to the side
+        # stream, so that the fork and the join are paid on the shorter branch (the other way round the same step
+        # measured 254 instead of 233 us).  No workspace for the tiles: key-range splits would ask for the SMs the
+        # decode pass is running on.  (Starting the decode pass under the caller's append, as a programmatic dependent
+        # launch that waits in front of its first K/V read, was measured too: 272 us, not kept.)
         with torch.cuda.stream(side):
-            ws = _workspace(q.device, rows)  # the side stream's own workspace
-            rc1 = call(lib.nvj_paged_prefill_packed_part, ws, 1, cta_limit)
-        # no workspace for the tiles: key-range splits would ask for the SMs the decode pass is running on
-        rc2 = call(lib.nvj_paged_prefill_packed_part, None, 2, 0)
-        cur.wait_stream(side)
-        check(rc1, "nvj_paged_prefill_packed_part (decode rows)")
+            rc2 = call(lib.nvj_paged_prefill_packed_part, None, 2, 0)
         if rc2 == _lib.NVJ_ERR_UNSUPPORTED:  # the CTA-pair kernel cannot run here: the batch in one piece after all
+            cur.wait_stream(side)
             ws = _workspace(q.device, rows)
-            rc2 = call(lib.nvj_paged_prefill_packed, ws)
-        check(rc2, "nvj_paged_prefill_packed_part (tiles)")
+            check(call(lib.nvj_paged_prefill_packed, ws), "nvj_paged_prefill_packed")
+        else:
+            ws = _workspace(q.device, rows)
+            rc1 = call(lib.nvj_paged_prefill_packed_part, ws, 1, cta_limit)
+            cur.wait_stream(side)
+            check(rc1, "nvj_paged_prefill_packed_part (decode rows)")
+            check(rc2, "nvj_paged_prefill_packed_part (tiles)")
     elif model_shape and variant != 1 and num_decode_rows == 0 and os.environ.get("NVJ_PREFILL_KEY_SPLITS", "1") != "0":
         # no decode rows: the tile kernel alone (it zero-fills what it does not write), with the workspace lent for
         # the key-range splits of a short batch
