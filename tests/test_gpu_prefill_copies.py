@@ -168,7 +168,7 @@ def test_mixed_batch_with_host_counts_serial_and_side_by_side(mode, monkeypatch)
     c = _prefill_case(7, 4500, [0] * 22, cached=cached, chunk=chunk, bucket=384)
     ref = R.paged_attention_prefill_packed(c["q"], c["k"], c["v"], c["tables"], c["kv_lens"], c["pos"], c["rid"],
                                            c["qsl"], BS, SCALE, 4)
-    for _ in range(2):  # twice: counters and the side stream's workspace are left clean
+    for _ in range(2):  # twice: the decode pass leaves its counters clean
         out = kv.paged_attention_prefill_packed(to_torch(c["q"]), to_torch(c["k"]), to_torch(c["v"]), to_torch(c["tables"]),
                                                 to_torch(c["kv_lens"]), to_torch(c["pos"]), to_torch(c["rid"]),
                                                 to_torch(c["qsl"]), BS, SCALE, 4, out_dtype=torch.float32, num_decode_rows=20)
