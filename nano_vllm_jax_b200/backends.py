@@ -137,7 +137,9 @@ class B200Backend:
             token_row_ids=token_row_ids,
             max_query_len=max_query_len if max_query_len is not None else query_len,
             single_token_rows=(sum(1 for n in query_lens_host if int(n) == 1)
-                               if (query_lens_host is not None and token_row_ids is not None) else None))
+                               if (query_lens_host is not None and token_row_ids is not None) else None),
+            query_tile_pairs=(sum(-(-int(n) // 64) for n in query_lens_host if int(n) > 1)
+                              if (query_lens_host is not None and token_row_ids is not None) else None))
 
     # ---- append (backends.py:980-1067)
     def write_kv(self, layer_id, k, v, cache: KVCacheStorage, metadata: AttentionMetadata) -> KVCacheStorage:
@@ -161,7 +163,7 @@ class B200Backend:
                     query, cache.k_cache, cache.v_cache, metadata.block_tables, metadata.seq_lens,
                     metadata.positions, metadata.token_row_ids, metadata.query_start_loc, block_size, scale,
                     num_key_value_groups, layer_idx=layer_id, max_query_len=metadata.max_query_len, out_dtype=f32,
-                    num_decode_rows=metadata.single_token_rows)
+                    num_decode_rows=metadata.single_token_rows, query_tile_pairs=metadata.query_tile_pairs)
             if metadata.positions is None:
                 return kvc.paged_attention(query, cache.k_cache, cache.v_cache, metadata.slot_mapping,
                                            metadata.seq_lens, scale, num_key_value_groups, layer_idx=layer_id,

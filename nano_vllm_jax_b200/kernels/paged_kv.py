@@ -512,14 +512,15 @@ def paged_decode_attention_with_kv_append(query, new_k, new_v, k_cache, v_cache,
 
 def packed_paged_prefill_attention(query, k_cache_layer, v_cache_layer, block_table, kv_lens, positions,
                                    query_start_loc, block_size, scale, num_key_value_groups,
-                                   max_query_len=None, variant=None, num_decode_rows=None):
+                                   max_query_len=None, variant=None, num_decode_rows=None, query_tile_pairs=None):
     """Ragged packed prefill: query `[1, T, Hq, D]` -> fp32 `[1, T, Hq*D]`, padded tokens 0.
 
     `variant`: 0 automatic, 1 generic, 2 mma.sync tiles, 3 tcgen05 tiles, 4 tcgen05 tiles on CTA pairs, 5 = 4 with
     bf16-rounded softmax weights in P V (default: the
     `NVJ_PREFILL_VARIANT` environment variable, else 0).  `num_decode_rows`: how many rows hold a single query
     token (the scheduler's `num_decode_tokens` of a mixed batch); 0 spares the launch that serves such rows,
-    None (unknown) keeps it.
+    None (unknown) keeps it.  `query_tile_pairs`: how many 64-token tiles the other rows make up (sum of
+    ceil(len / 64) over them), for the split of the SMs between the two kernels of a mixed batch; None = an upper bound.
     """
     lib = _lib.load()
     _check_nhd_cache(k_cache_layer, v_cache_layer)
@@ -560,7 +561,7 @@ def packed_paged_prefill_attention(query, k_cache_layer, v_cache_layer, block_ta
     # A mixed batch (decode rows + prefill chunks, counts known on the host): the two kinds of row are served by two
     # kernels that write different rows of `out` and neither fills the machine, so they can run side by side on two
     # streams, the decode pass leaving the tile kernel's SMs free.  That pays when the launches come from a CUDA graph
-    # (one 6-layer step: 328 -> 233 us); launched eagerly the extra stream bookkeeping costs the host more than the
+    # (one 6-layer step: 328 -> 229 us); launched eagerly the extra stream bookkeeping costs the host more than the
     # overlap saves, so the fork is taken only while the current stream is being captured (NVJ_MIXED_SIDE_BY_SIDE=1
     # forces it, =0 forbids it).
     mixed = model_shape and variant in (0, 4, 5) and num_decode_rows is not None and 0 < num_decode_rows < rows
@@ -570,7 +571,10 @@ def packed_paged_prefill_attention(query, k_cache_layer, v_cache_layer, block_ta
         cur = torch.cuda.current_stream(q.device)
         side = _side_stream(q.device)
         sms = torch.cuda.get_device_properties(q.device).multi_processor_count
-        tile_ctas = 4 * (-(-(tokens - num_decode_rows) // 64) + (rows - num_decode_rows))  # CTA pairs x 2 KV heads
+        pairs = -(-(tokens - num_decode_rows) // 64) + (rows - num_decode_rows)  # at most: every chunk may end a tile early
+        if query_tile_pairs is not None:
+            pairs = max(1, min(pairs, int(query_tile_pairs)))
+        tile_ctas = 4 * pairs  # CTA pairs x 2 KV heads
         cta_limit = max(sms // 2, sms - tile_ctas)
         side.wait_stream(cur)
         # The decode rows are the longer of the two: they stay on the current stream and the tiles go to the side

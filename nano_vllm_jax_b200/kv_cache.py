@@ -67,6 +67,8 @@ class AttentionMetadata:
     max_query_len: Optional[int] = None
     # not in the reference: the caller's own count of 1-token rows in a packed batch (None = not told)
     single_token_rows: Optional[int] = None
+    # not in the reference: 64-token query tiles the other rows of that batch make up (sum of ceil(len / 64); None = not told)
+    query_tile_pairs: Optional[int] = None
 
 
 def _read_slot_mapping(self):
@@ -339,7 +341,7 @@ def paged_attention(query, k_cache, v_cache, slot_mapping, kv_lens, scale, num_k
 def paged_attention_prefill_packed(query, k_cache, v_cache, block_table, kv_lens, positions, token_row_ids,
                                    query_start_loc, block_size, scale, num_key_value_groups,
                                    layer_idx: int = 0, max_query_len=None, use_triton=None, out_dtype=None,
-                                   num_decode_rows=None):
+                                   num_decode_rows=None, query_tile_pairs=None):
     """Ragged packed prefill over the paged cache (kv_cache.py:721-849) -> `[1, T, Hq*D]`.
 
     `use_triton` is accepted for signature compatibility and ignored: there is one
@@ -359,5 +361,6 @@ def paged_attention_prefill_packed(query, k_cache, v_cache, block_table, kv_lens
     out = _k.packed_paged_prefill_attention(query, k_layer, v_layer, block_table.to(torch.int32),
                                             kv_lens.to(torch.int32), positions.to(torch.int32),
                                             query_start_loc.to(torch.int32), block_size, scale,
-                                            num_key_value_groups, max_query_len, num_decode_rows=num_decode_rows)
+                                            num_key_value_groups, max_query_len, num_decode_rows=num_decode_rows,
+                                            query_tile_pairs=query_tile_pairs)
     return out.to(out_dtype if out_dtype is not None else k_cache.dtype)
