@@ -329,7 +329,10 @@ def run_b200(args, w):
     K_steps, W_steps = args.steps, max(args.warmup, 3)
     reps = max(1, -(-MIN_TIMED_STEPS // K_steps))  # timed blocks of K steps each, >= 100 steps in all
     long_pass = W_steps + reps * K_steps
-    total_steps = 3 * long_pass + (W_steps + K_steps) + 4  # eager, graph, pipelined end-to-end; serial end-to-end
+    # Every pass (eager, graph, serial and pipelined end-to-end) starts again from the configured lengths and grows
+    # every row by one token per step, so that all of them are timed on the same contexts: rows appended by an earlier
+    # pass are written again with the same values.
+    total_steps = long_pass + 4
     pool_blocks = None
     if w["pool"] is None:  # c5: the pool takes min(150 GB, 0.9 x free) and the tables are drawn over all of it
         free_b, _ = torch.cuda.mem_get_info(dev)
@@ -486,7 +489,39 @@ def run_b200(args, w):
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
+    steps_done = [0]
+
+    def new_pass():
+        steps_done[0] = max(steps_done[0], step_no[0])
+        step_no[0] = 0
+
     ms_eager, _, _ = timed(device_step, blocks=reps)
+    new_pass()
+    # The kernel without the host's launch latency between the events: the K launches of one timed block (fused append +
+    # decode only, one node per step, each at its own lengths) captured into one CUDA graph; events bracket a replay.
+    block_kernel_ms = []
+    try:
+        from nano_vllm_jax_b200.engine.resident_decode import CapturedStep
+
+        def kernel_block():
+            for s in range(W_steps, W_steps + K_steps):
+                K.paged_decode_attention_with_kv_append(q, nk, nv, k_cache, v_cache, tables, all_len[s], all_pos[s], 0, BS,
+                                                        SCALE, HQ // HKV)
+
+        kernel_graph = CapturedStep(kernel_block, dev)
+        kernel_graph.capture()
+        for i in range(1 + max(2, reps)):
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); kernel_graph.replay(); e1.record()
+            torch.cuda.synchronize()
+            if i > 0:
+                block_kernel_ms.append(e0.elapsed_time(e1))
+        del kernel_graph
+    except Exception as exc:  # the per-launch events of the eager pass remain
+        print(f"[bench] kernel-only graph failed ({exc!r}); kernel time from the eager pass's events", file=sys.stderr, flush=True)
+        torch.cuda.synchronize()
+        block_kernel_ms = []
     timed_events = kernel_events[W_steps:]  # the launches of the timed blocks (warm-up launches come first)
     step_mode = "CUDA graph replay over device-resident metadata (append+decode -> argmax+advance)"
     graph_ok = True
@@ -508,8 +543,11 @@ def run_b200(args, w):
         graph_ok = False
         ms_dev, step_mode = ms_eager, "eager launches (graph capture failed)"
         dev_step_ms, dev_block_ms = [], [ms_eager]
+    new_pass()
     ms_e2e_serial, _, _ = timed(e2e_step)
+    new_pass()
     ms_e2e, _, e2e_block_ms = timed(e2e_pipelined_step, finish=pipe.drain, blocks=reps)
+    new_pass()
     if token_gather is not None:
         token_gather.collect(out=gathered_p2p)
         token_gather.check()
@@ -566,11 +604,21 @@ def run_b200(args, w):
     bytes_per_launch = bytes_total // len(timed_events)
     peak, peak_kind = measured_hbm_peak()
     achieved = bytes_total / (ms_kernel * 1e-3) / 1e9
+    us_per_launch = ms_kernel / len(timed_events) * 1e3
+    kernel_timing = "CUDA events around every launch of the eager pass (the host's launch latency lies inside the events)"
+    if block_kernel_ms:
+        block_bytes = sum(algorithmic_bytes(ctx + s + 1, rows) for s in range(W_steps, W_steps + K_steps))
+        bytes_per_launch = block_bytes // K_steps
+        us_per_launch = statistics.mean(block_kernel_ms) / K_steps * 1e3
+        achieved = bytes_per_launch / (us_per_launch * 1e-6) / 1e9
+        kernel_timing = (f"{K_steps} launches (one per step of a timed block, each at its own lengths) replayed from one CUDA graph, "
+                         f"CUDA events around the replay, mean of {len(block_kernel_ms)} replays / {K_steps}: the gaps between the "
+                         "launches are inside, the host's launch latency is not; launch_us = events around single eager launches")
 
     # parity of what was just timed: the last graph step's output and every appended row (rank 0's own rows)
     parity = None
     if rank == 0 and graph_ok:
-        parity = parity_check(torch, k_cache, v_cache, tables_np, ctx, ctx + step_no[0],
+        parity = parity_check(torch, k_cache, v_cache, tables_np, ctx, ctx + steps_done[0],
                               meta.seq_lens.cpu().numpy().astype(np.int64), q, nk, nv, graph.out.view(rows, HQ * D))
 
     cpu = None
@@ -592,7 +640,9 @@ def run_b200(args, w):
                              if world > 1 else None),
             "timed_blocks": {"blocks": reps, "steps_per_block": K_steps,
                              "note": "value and ms_per_step come from the first block of exactly --steps steps; "
-                                     "step_ms covers every timed step of all blocks"},
+                                     "step_ms covers every timed step of all blocks",
+                             "contexts": "every pass (eager, graph, serial and pipelined end to end) starts from the configured "
+                                         "lengths and adds one token per row and step, so all are timed on the same contexts"},
             "step_ms": percentiles(dev_step_ms),
             "e2e": {"value": total_rows / (ms_e2e / K_steps * 1e-3), "unit": "tok/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e / K_steps,
@@ -609,7 +659,7 @@ def run_b200(args, w):
             "roofline": {"bound": "hbm", "kernel": "decode_wide_kernel at width 1 (fused append + paged GQA decode, TMA-staged, tensor-core tiles)",
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": peak_kind + " HBM copy bandwidth", "frac_of_8TBs_nominal": achieved / 8000.0,
-                         "bytes_per_launch": bytes_per_launch, "us_per_launch": ms_kernel / len(timed_events) * 1e3,
+                         "bytes_per_launch": bytes_per_launch, "us_per_launch": us_per_launch, "kernel_timing": kernel_timing,
                          "launch_us": percentiles([m * 1e3 for m in kernel_ms]),
                          "traffic": NCU_C2SMALL_DRAM_BYTES / NCU_C2SMALL_ALGORITHMIC_BYTES * bytes_per_launch,
                          "traffic_source": "dram bytes of one ncu-captured launch of --workload c2small (354.93 MB for 356.35 MB "
