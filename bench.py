@@ -20,8 +20,10 @@ inputs resident in HBM, from the first timed block of exactly --steps steps; the
 block is repeated until at least 100 steps are timed and `step_ms` gives median and
 p10 / p90 over all of them.  `e2e` = the same through the backend API from pinned host
 buffers, copies inside the timed region; `roofline` = algorithmic bytes of the
-fused append+decode kernel over its CUDA-event duration (events around every
-launch of the timed region) against the measured HBM copy peak; `cpu_baseline` =
+fused append+decode kernel over its CUDA-event duration (the launches of one timed
+block replayed from a CUDA graph, events around the replay; events around every
+single launch of the eager pass are reported beside it as `launch_us`) against the
+measured HBM copy peak; every pass starts from the configured context lengths; `cpu_baseline` =
 the CPU restatement of the reference path on the same rows; `parity_check` = the
 last step's output of sampled rows and every appended cache row against that CPU
 restatement, taken after the timed passes.
