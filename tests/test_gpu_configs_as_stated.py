@@ -230,6 +230,8 @@ class _Config3:
             md = self.backend.build_attention_metadata(batch.positions, batch.block_tables, batch.seq_lens, BS, True,
                                                        query_start_loc=batch.query_start_loc, token_row_ids=batch.token_row_ids,
                                                        query_lens_host=batch.query_lens_host)
+            assert md.single_token_rows == sum(1 for c in chunks if c == 1)
+            assert md.query_tile_pairs == sum(-(-c // 64) for c in chunks if c > 1)
             self.cache, out = self.backend.write_kv_and_attention(0, to_torch(q), to_torch(nk), to_torch(nv), self.cache, md,
                                                                   BS, SCALE, 4, True)
             torch.cuda.synchronize()
