@@ -30,7 +30,7 @@ model they are produced by the projections that run in front of this path).
 from __future__ import annotations
 
 import os
-from typing import Optional, Sequence as Seq
+from typing import Optional
 
 import torch
 

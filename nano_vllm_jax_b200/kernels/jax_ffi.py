@@ -24,7 +24,6 @@ the tests and benchmarks use.
 from __future__ import annotations
 
 import ctypes
-import os
 import subprocess
 import threading
 from pathlib import Path

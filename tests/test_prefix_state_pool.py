@@ -8,7 +8,6 @@ published when a snapshot cannot be stored.
 from types import SimpleNamespace
 
 import pytest
-import torch
 
 from nano_vllm_jax_b200.engine import prefix_state as PS
 
