@@ -494,6 +494,19 @@ void nvj_set_wait_limit_ns(uint64_t ns);
 uint64_t nvj_get_wait_limit_ns(void);
 int nvj_selftest_bounded_wait(int32_t* status, int32_t* returned, nvj_stream_t stream);
 
+/* ------------------------------------------------------------------ host staging */
+
+/*
+ * n asynchronous copies on one stream, one cudaMemcpyAsync each, direction inferred from the pointers: a step's
+ * operands from (pinned) host memory to the device, or its result back, in one call for a host loop that cannot
+ * afford a framework call per operand.  `dst`, `src` and `bytes` are HOST arrays of n entries; an entry of 0 bytes is
+ * skipped.  Nothing is retained: the caller keeps every buffer alive and unchanged until the stream has passed the
+ * copies.  The reference stages a step's host arrays one jax.device_put at a time
+ * (nanovllm_jax/engine/model_runner.py:3295, 3464-3465); no counterpart call.
+ */
+int nvj_copy_many_async(void* const* dst, const void* const* src, const size_t* bytes, int n,
+                        nvj_stream_t stream);
+
 /* ------------------------------------------------------------------ tokens */
 
 /*

@@ -85,6 +85,7 @@ SIGNATURES = {
     "nvj_get_wait_limit_ns": (c_uint64, []),
     "nvj_selftest_bounded_wait": (c_int, [c_void_p, c_void_p, c_void_p]),
     "nvj_paged_prefill_workspace_bytes": (c_size_t, [c_int]),
+    "nvj_copy_many_async": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
     "nvj_row_argmax": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "nvj_row_argmax_advance": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),
 }

@@ -387,6 +387,18 @@ extern "C" int nvj_advance_decode_metadata(int32_t* seq_lens, int32_t* positions
   return cudaGetLastError() == cudaSuccess ? NVJ_OK : NVJ_ERR_LAUNCH;
 }
 
+extern "C" int nvj_copy_many_async(void* const* dst, const void* const* src, const size_t* bytes, int n,
+                                   nvj_stream_t stream) {
+  if (n < 0 || (n > 0 && (!dst || !src || !bytes))) return NVJ_ERR_INVALID_ARGUMENT;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  for (int i = 0; i < n; ++i) {
+    if (bytes[i] == 0) continue;
+    if (!dst[i] || !src[i]) return NVJ_ERR_INVALID_ARGUMENT;
+    if (cudaMemcpyAsync(dst[i], src[i], bytes[i], cudaMemcpyDefault, s) != cudaSuccess) return NVJ_ERR_LAUNCH;
+  }
+  return NVJ_OK;
+}
+
 extern "C" int nvj_row_argmax(const float* x, int rows, int row_len, int32_t* tokens,
                               nvj_stream_t stream) {
   using namespace nvj;

@@ -35,6 +35,7 @@ from typing import Dict, Optional
 import torch
 
 from .backends import B200Backend
+from .kernels import paged_kv as _k
 from .kv_cache import KVCacheStorage
 
 
@@ -53,6 +54,11 @@ class _Slot:
     busy: bool = False
     graphs: Dict[int, torch.cuda.CUDAGraph] = field(default_factory=dict)  # per layer, with capture=True
     graph_out: Dict[int, torch.Tensor] = field(default_factory=dict)
+    inputs: tuple = ()           # (q, k, v, tables, positions, seq_lens): the targets of the step's operand copies
+    h2d_list: object = None      # paged_kv.CopyList over `inputs`; the sources are set per step
+    d2h_lists: Dict[int, object] = field(default_factory=dict)  # per layer: host_out <- that layer's graph output
+    sources: list = field(default_factory=list)
+    last_out: Optional[torch.Tensor] = None
 
 
 class HostDecodePipeline:
@@ -82,6 +88,9 @@ class HostDecodePipeline:
                 seq_lens=torch.empty((rows,), dtype=torch.int32, device=dev),
                 host_out=torch.empty((rows, 1, hq * d), dtype=torch.float32).pin_memory(),
                 in_done=torch.cuda.Event(), compute_done=torch.cuda.Event(), out_done=torch.cuda.Event()))
+        for slot in self.slots:
+            slot.inputs = (slot.q, slot.k, slot.v, slot.tables, slot.positions, slot.seq_lens)
+            slot.h2d_list = _k.CopyList(slot.inputs, slot.inputs)  # sources replaced by every submit
         self.compute.wait_stream(torch.cuda.current_stream(dev))  # whatever prepared the cache comes first
         self.submitted = 0
         self.h2d_bytes_per_step = sum(t.numel() * t.element_size() for t in
@@ -100,14 +109,18 @@ class HostDecodePipeline:
         slot = self.slots[ticket % len(self.slots)]
         if slot.busy:
             slot.out_done.synchronize()  # its operands were consumed and its result has left the device
-        with torch.cuda.stream(self.h2d):
-            slot.q.copy_(query.view(slot.q.shape), non_blocking=True)
-            slot.k.copy_(k.view(slot.k.shape), non_blocking=True)
-            slot.v.copy_(v.view(slot.v.shape), non_blocking=True)
-            slot.tables.copy_(block_tables, non_blocking=True)
-            slot.positions.copy_(positions.view(slot.positions.shape), non_blocking=True)
-            slot.seq_lens.copy_(seq_lens, non_blocking=True)
-            slot.in_done.record(self.h2d)
+        # the step's operands: six copies in one library call (a framework copy per operand costs the host ~8 us each)
+        srcs = []
+        for i, (t, dst) in enumerate(zip((query, k, v, block_tables, positions, seq_lens), slot.inputs)):
+            if t.dtype != dst.dtype or not t.is_contiguous():
+                t = t.to(dst.dtype).contiguous()
+            if t.numel() != dst.numel():
+                raise ValueError(f"operand {i} has {t.numel()} elements, the slot holds {dst.numel()}")
+            slot.h2d_list.set_source(i, t)
+            srcs.append(t)
+        slot.sources = srcs  # alive until the slot comes round again
+        slot.h2d_list.issue(self.h2d)
+        slot.in_done.record(self.h2d)
         with torch.cuda.stream(self.compute):
             self.compute.wait_event(slot.in_done)
             if not self.capture:
@@ -118,12 +131,17 @@ class HostDecodePipeline:
             else:
                 out = self._capture(slot, layer_id, after_compute)
             slot.compute_done.record(self.compute)
-        with torch.cuda.stream(self.d2h):
-            self.d2h.wait_event(slot.compute_done)
-            slot.host_out.copy_(out, non_blocking=True)
-            if out is not slot.graph_out.get(layer_id):  # a graph's output lives in the graph's own pool
+        self.d2h.wait_event(slot.compute_done)
+        back = slot.d2h_lists.get(layer_id) if out is slot.graph_out.get(layer_id) else None
+        if back is None:
+            back = _k.CopyList([slot.host_out], [out.reshape(slot.host_out.shape)])
+            if out is slot.graph_out.get(layer_id):
+                slot.d2h_lists[layer_id] = back  # a graph's output lives in the graph's own pool: same address every step
+            else:
                 out.record_stream(self.d2h)
-            slot.out_done.record(self.d2h)
+                slot.last_out = out
+        back.issue(self.d2h)
+        slot.out_done.record(self.d2h)
         slot.busy = True
         self.submitted += 1
         return ticket

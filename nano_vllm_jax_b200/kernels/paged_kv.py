@@ -21,6 +21,7 @@ word to be read back after each call (tests do).
 
 from __future__ import annotations
 
+import ctypes
 import os
 from typing import Optional
 
@@ -793,6 +794,44 @@ def _advance_args(advance, rows):
         if positions.numel() != rows or not positions.is_contiguous():
             raise ValueError("advance: positions must be a contiguous int32 tensor of one entry per row")
     return seq_lens, positions, int(table_width), int(block_size)
+
+
+class CopyList:
+    """A fixed list of copies `dst[i] <- src[i]` issued by one library call (`nvj_copy_many_async`).
+
+    Built once for tensors whose addresses stay put (a pipeline slot's device buffers and its pinned result);
+    `sources` / `targets` may be replaced per call by tensors of the same sizes.  The caller keeps every tensor alive
+    and unchanged until the stream has passed the copies; pageable host memory makes a copy synchronous.
+    """
+
+    def __init__(self, dsts, srcs):
+        if len(dsts) != len(srcs):
+            raise ValueError("as many sources as targets")
+        self.n = len(dsts)
+        self._dst = (ctypes.c_void_p * self.n)()
+        self._src = (ctypes.c_void_p * self.n)()
+        self._bytes = (ctypes.c_size_t * self.n)()
+        for i, (d, s) in enumerate(zip(dsts, srcs)):
+            self._set(i, d, s)
+
+    def _set(self, i, d, s):
+        if not (d.is_contiguous() and s.is_contiguous()):
+            raise ValueError("copies are between contiguous tensors")
+        nbytes = d.numel() * d.element_size()
+        if nbytes != s.numel() * s.element_size() or d.dtype != s.dtype:
+            raise ValueError("source and target of a copy must have the same dtype and size")
+        self._dst[i], self._src[i], self._bytes[i] = d.data_ptr(), s.data_ptr(), nbytes
+
+    def set_source(self, i, s):
+        """Replace source i by a contiguous tensor of the same byte size (its dtype is the caller's to check)."""
+        if s.numel() * s.element_size() != self._bytes[i] or not s.is_contiguous():
+            raise ValueError("a replaced source must be contiguous and of the size the list was built with")
+        self._src[i] = s.data_ptr()
+
+    def issue(self, stream) -> None:
+        """Enqueue the copies on `stream` (a `torch.cuda.Stream`)."""
+        check(_lib.load().nvj_copy_many_async(self._dst, self._src, self._bytes, self.n, stream.cuda_stream),
+              "nvj_copy_many_async")
 
 
 def row_argmax(x: torch.Tensor, out: torch.Tensor | None = None, advance=None) -> torch.Tensor:
